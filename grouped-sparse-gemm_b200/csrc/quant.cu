@@ -1,0 +1,316 @@
+// Activation quantizers: bf16 -> e2m1 codes + one UE4M3 scale per 32 elements, written straight
+// into the grouped GEMM's B-operand layouts (row-major codes, swizzled scale atoms).
+//
+// quant_act and silu_mul_quant_act walk the *scale buffer*: one warp owns one 16-byte line of a
+// scale atom, i.e. the 4 rows {r, r+32, r+64, r+96} x 4 K-blocks whose scales share that line.
+// The warp quantizes the (up to) 4 x 128 elements behind it with 128-bit loads, reduces each
+// block's amax with one shuffle, and writes the line once -- quantized scales where a row is live,
+// the benign byte 0x38 everywhere else -- so the scale buffer is fully defined without a separate
+// fill pass and without byte-sized stores.  Lines whose rows are all past the expert's token
+// count cost one 16-byte store.
+//
+// scatter_quant_act is driven by a routing list instead (source token -> destination row), so its
+// scale buffer is pre-filled with a memset node and each warp quantizes 256 elements of one routed
+// row.
+#include "common.cuh"
+
+namespace pnv {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarpsPerBlock = kThreads / 32;
+
+__device__ __forceinline__ float amax8(const uint4& v) {
+  float m = fmaxf(fabsf(bf16_lo(v.x)), fabsf(bf16_hi(v.x)));
+  m = fmaxf(m, fmaxf(fabsf(bf16_lo(v.y)), fabsf(bf16_hi(v.y))));
+  m = fmaxf(m, fmaxf(fabsf(bf16_lo(v.z)), fabsf(bf16_hi(v.z))));
+  m = fmaxf(m, fmaxf(fabsf(bf16_lo(v.w)), fabsf(bf16_hi(v.w))));
+  return m;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x); f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
+  f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
+}
+
+__device__ __forceinline__ uint32_t quant8(const float (&f)[8], float inv) {
+  float s[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s[i] = __fmul_rn(f[i], inv);
+  return cvt_e2m1x8(s);
+}
+
+// Gather the 16 scale bytes of a line from the lanes that own them (lane g*8 + 2*kq holds the
+// byte of row group g, K-block kq) and store them as four 32-bit words.
+__device__ __forceinline__ void store_sf_line(uint8_t* line, uint32_t my_byte, int lane) {
+  int g8 = lane & ~7;
+  uint32_t w = __shfl_sync(0xffffffffu, my_byte, g8 + 0) |
+               (__shfl_sync(0xffffffffu, my_byte, g8 + 2) << 8) |
+               (__shfl_sync(0xffffffffu, my_byte, g8 + 4) << 16) |
+               (__shfl_sync(0xffffffffu, my_byte, g8 + 6) << 24);
+  if ((lane & 7) == 0) *reinterpret_cast<uint32_t*>(line + (lane >> 3) * 4) = w;
+}
+
+// kGated == false: x is [E, max_n, K].  kGated == true: x is [E, max_n, 2K] holding gate and up.
+template <bool kGated>
+__global__ void __launch_bounds__(kThreads)
+quant_lines_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gscale,
+                   int gscale_per_expert, const int* __restrict__ counts, int E, int max_n, int K,
+                   int interleaved, GatedAct act, uint8_t* __restrict__ b_act,
+                   uint8_t* __restrict__ sfb) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int KB = K / kSfBlock;
+  const int n_rt = sf_row_atoms(max_n);
+  const int n_kt = sf_k_atoms(K);
+  const long long lines = (long long)E * n_rt * n_kt * 32;
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 3;          // row group inside the atom: rows rr + 32 g
+  const int j = lane & 7;           // 16-element piece of the 128-element segment
+  const long long warp0 = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * kWarpsPerBlock;
+  const uint32_t benign4 = kBenignSf * 0x01010101u;
+
+  for (long long c = warp0; c < lines; c += nwarps) {
+    const int rr = (int)(c & 31);
+    long long a = c >> 5;
+    const int kt = (int)(a % n_kt);
+    a /= n_kt;
+    const int rt = (int)(a % n_rt);
+    const int e = (int)(a / n_rt);
+    const int cnt = min(counts[e], max_n);
+    uint8_t* line = sfb + c * 16;
+    if (rt * 128 + rr >= cnt) {   // no live row behind this line
+      if (lane == 0) *reinterpret_cast<uint4*>(line) = make_uint4(benign4, benign4, benign4, benign4);
+      continue;
+    }
+    const int r = rt * 128 + rr + 32 * g;
+    const int kb = kt * 4 + (j >> 1);
+    const bool live = (r < cnt) && (kb < KB);
+    const int k0 = kb * kSfBlock + (j & 1) * 16;
+    uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
+    float f0[8], f1[8];
+    if (live) {
+      const long long row = (long long)e * max_n + r;
+      if (!kGated) {
+        const uint4* p = reinterpret_cast<const uint4*>(x + row * K + k0);
+        v0 = __ldg(p);
+        v1 = __ldg(p + 1);
+        unpack8(v0, f0);
+        unpack8(v1, f1);
+      } else {
+        const __nv_bfloat16* base = x + row * (2LL * K);
+        const int gate_off = interleaved ? kb * 64 + (j & 1) * 16 : k0;
+        const int up_off = interleaved ? gate_off + 32 : K + k0;
+        const uint4* pg = reinterpret_cast<const uint4*>(base + gate_off);
+        const uint4* pu = reinterpret_cast<const uint4*>(base + up_off);
+        uint4 g0 = __ldg(pg), g1 = __ldg(pg + 1), u0 = __ldg(pu), u1 = __ldg(pu + 1);
+        float ga[8], ua[8];
+        unpack8(g0, ga); unpack8(u0, ua);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f0[i] = gated_act(ga[i], ua[i], act);
+        unpack8(g1, ga); unpack8(u1, ua);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f1[i] = gated_act(ga[i], ua[i], act);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { f0[i] = 0.f; f1[i] = 0.f; }
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fmaxf(fabsf(f0[i]), fabsf(f1[i])));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    uint32_t sf_byte = kBenignSf;
+    if (live) {
+      const float gs = gscale_per_expert ? gscale[e] : gscale[0];
+      float inv;
+      block_scale(amax, gs, sf_byte, inv);
+      uint2 codes = make_uint2(quant8(f0, inv), quant8(f1, inv));
+      const long long row = (long long)e * max_n + r;
+      *reinterpret_cast<uint2*>(b_act + row * (K / 2) + k0 / 2) = codes;
+    }
+    store_sf_line(line, sf_byte, lane);
+  }
+}
+
+// One warp per (routing, 256-element segment); lane l owns 8 elements, a quad owns a block.
+__global__ void __launch_bounds__(kThreads)
+scatter_quant_kernel(const __nv_bfloat16* __restrict__ a1, const long long* __restrict__ flat_tok,
+                     const long long* __restrict__ dest_global, const float* __restrict__ topk_w,
+                     const float* __restrict__ gscale, int gscale_per_expert, long long n_routes,
+                     int K, int E, int cap, uint8_t* __restrict__ b_act, uint8_t* __restrict__ sfb) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int segs = ceil_div_i(K, 256);
+  const int n_rt = sf_row_atoms(cap);
+  const int n_kt = sf_k_atoms(K);
+  const long long items = n_routes * segs;
+  const long long trash = (long long)E * cap;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * kWarpsPerBlock;
+  for (long long it = warp0; it < items; it += nwarps) {
+    const long long i = it / segs;
+    const int seg = (int)(it - i * segs);
+    const long long dest = dest_global[i];
+    if (dest == trash) continue;   // dropped routing: non-local expert or past capacity
+    const int k0 = seg * 256 + lane * 8;
+    const bool live = k0 < K;
+    float f[8];
+    if (live) {
+      uint4 v = __ldg(reinterpret_cast<const uint4*>(a1 + flat_tok[i] * K + k0));
+      unpack8(v, f);
+      if (topk_w != nullptr) {
+        const float w = __bfloat162float(__float2bfloat16_rn(topk_w[i]));
+#pragma unroll
+        for (int q = 0; q < 8; ++q) f[q] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(f[q], w)));
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) f[q] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) amax = fmaxf(amax, fabsf(f[q]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    if (live) {
+      const int e = (int)(dest / cap);
+      const int r = (int)(dest - (long long)e * cap);
+      const float gs = gscale_per_expert ? gscale[e] : gscale[0];
+      uint32_t sf_byte;
+      float inv;
+      block_scale(amax, gs, sf_byte, inv);
+      *reinterpret_cast<uint32_t*>(b_act + dest * (K / 2) + k0 / 2) = quant8(f, inv);
+      if ((lane & 3) == 0) sfb[sf_offset(e, r, k0 / kSfBlock, n_rt, n_kt)] = (uint8_t)sf_byte;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+gated_act_kernel(const __nv_bfloat16* __restrict__ x2, long long rows, int N, int interleaved,
+                 GatedAct act, __nv_bfloat16* __restrict__ y) {
+  const int per_row = N / 8;
+  const long long total = rows * per_row;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long row = idx / per_row;
+    const int k0 = (int)(idx - row * per_row) * 8;
+    const __nv_bfloat16* base = x2 + row * (2LL * N);
+    const int gate_off = interleaved ? (k0 / 32) * 64 + (k0 % 32) : k0;
+    const int up_off = interleaved ? gate_off + 32 : N + k0;
+    uint4 gv = __ldg(reinterpret_cast<const uint4*>(base + gate_off));
+    uint4 uv = __ldg(reinterpret_cast<const uint4*>(base + up_off));
+    float ga[8], ua[8];
+    unpack8(gv, ga);
+    unpack8(uv, ua);
+    __nv_bfloat16 o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = __float2bfloat16_rn(gated_act(ga[i], ua[i], act));
+    *reinterpret_cast<uint4*>(y + row * N + k0) = *reinterpret_cast<const uint4*>(o);
+  }
+}
+
+int grid_for(long long warp_items, int sm_count) {
+  long long blocks = (warp_items + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  long long cap = (long long)(sm_count > 0 ? sm_count : 148) * 8;   // 8 x 256 threads fill an SM
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+int check_common(const void* x, const float* gscale, const int32_t* counts, int E, int rows, int K,
+                 const uint8_t* b_act, const uint8_t* sfb, const char* kname) {
+  PNV_REQUIRE(x && gscale && counts && b_act && sfb, "null pointer argument");
+  PNV_REQUIRE(E >= 1 && rows >= 1, "experts and row capacity must be positive, got %d and %d", E, rows);
+  PNV_REQUIRE(K > 0 && K % kSfBlock == 0, "%s must be a multiple of %d, got %d", kname, kSfBlock, K);
+  PNV_REQUIRE(sf_numel(rows, K, E) / 16 < (1LL << 40), "scale buffer too large");
+  return PNV_OK;
+}
+
+}  // namespace
+
+int make_gated_act(int act_kind, float beta, float linear_beta, GatedAct& out) {
+  if (act_kind == PNV_ACT_SILU) {
+    out = GatedAct{PNV_ACT_SILU, 1.0f, -1.0f};
+  } else if (act_kind == PNV_ACT_SITU) {
+    PNV_REQUIRE(beta > 0, "situ: beta must be positive, got %g", (double)beta);
+    out = GatedAct{PNV_ACT_SITU, beta, linear_beta};
+  } else {
+    return fail(PNV_ERR_INVALID_ARGUMENT, "activation must be 'silu' or 'situ', got kind %d", act_kind);
+  }
+  return PNV_OK;
+}
+
+}  // namespace pnv
+
+using namespace pnv;
+
+extern "C" int pnv_quant_act(const void* x, const float* gscale, int gscale_per_expert,
+                             const int32_t* counts, int experts, int max_n, int k, uint8_t* b_act,
+                             uint8_t* sfb, int sm_count, pnv_stream_t stream) {
+  if (int rc = check_common(x, gscale, counts, experts, max_n, k, b_act, sfb, "K")) return rc;
+  long long lines = sf_numel(max_n, k, experts) / 16;
+  GatedAct act{PNV_ACT_SILU, 1.f, -1.f};
+  PNV_CUDA(launch_pdl(quant_lines_kernel<false>, dim3(grid_for(lines, sm_count)), dim3(kThreads), 0,
+                      (cudaStream_t)stream, pdl_enabled(), (const __nv_bfloat16*)x, gscale,
+                      gscale_per_expert, counts, experts, max_n, k, 0, act, b_act, sfb));
+  return PNV_OK;
+}
+
+extern "C" int pnv_silu_mul_quant_act(const void* x2, const float* gscale, int gscale_per_expert,
+                                      const int32_t* counts, int experts, int max_n, int n,
+                                      int interleaved, int act_kind, float beta, float linear_beta,
+                                      uint8_t* b_act, uint8_t* sfb, int sm_count,
+                                      pnv_stream_t stream) {
+  GatedAct act;
+  if (int rc = make_gated_act(act_kind, beta, linear_beta, act)) return rc;
+  if (int rc = check_common(x2, gscale, counts, experts, max_n, n, b_act, sfb, "intermediate width N"))
+    return rc;
+  long long lines = sf_numel(max_n, n, experts) / 16;
+  PNV_CUDA(launch_pdl(quant_lines_kernel<true>, dim3(grid_for(lines, sm_count)), dim3(kThreads), 0,
+                      (cudaStream_t)stream, pdl_enabled(), (const __nv_bfloat16*)x2, gscale,
+                      gscale_per_expert, counts, experts, max_n, n, interleaved ? 1 : 0, act, b_act,
+                      sfb));
+  return PNV_OK;
+}
+
+extern "C" int pnv_scatter_quant_act(const void* a1, const int64_t* flat_tok,
+                                     const int64_t* dest_global, const float* topk_weights,
+                                     const float* gscale, int gscale_per_expert, int64_t n_routes,
+                                     int k, int experts, int cap, uint8_t* b_act, uint8_t* sfb,
+                                     int sm_count, pnv_stream_t stream) {
+  PNV_REQUIRE(cap > 0, "cap must be positive");
+  PNV_REQUIRE(n_routes >= 0, "n_routes must be non-negative");
+  PNV_REQUIRE(n_routes == 0 || (flat_tok && dest_global), "null routing plan");
+  int dummy = 0;
+  if (int rc = check_common(a1 ? a1 : (const void*)&dummy, gscale, &dummy, experts, cap, k, b_act, sfb, "K"))
+    return rc;
+  PNV_REQUIRE(n_routes == 0 || a1, "null pointer argument");
+  cudaStream_t s = (cudaStream_t)stream;
+  PNV_CUDA(cudaMemsetAsync(sfb, kBenignSf, (size_t)sf_numel(cap, k, experts), s));
+  if (n_routes == 0) return PNV_OK;
+  long long items = (long long)n_routes * ceil_div_i(k, 256);
+  PNV_CUDA(launch_pdl(scatter_quant_kernel, dim3(grid_for(items, sm_count)), dim3(kThreads), 0, s,
+                      false, (const __nv_bfloat16*)a1, (const long long*)flat_tok,
+                      (const long long*)dest_global, topk_weights, gscale, gscale_per_expert,
+                      (long long)n_routes, k, experts, cap, b_act, sfb));
+  return PNV_OK;
+}
+
+extern "C" int pnv_gated_act(const void* x2, int64_t rows, int n, int interleaved, int act_kind,
+                             float beta, float linear_beta, void* y, pnv_stream_t stream) {
+  GatedAct act;
+  if (int rc = make_gated_act(act_kind, beta, linear_beta, act)) return rc;
+  PNV_REQUIRE(x2 && y, "null pointer argument");
+  PNV_REQUIRE(n > 0 && n % kSfBlock == 0, "intermediate width N must be a multiple of %d, got %d", kSfBlock, n);
+  if (rows <= 0) return PNV_OK;
+  long long total = rows * (n / 8);
+  long long blocks = (total + kThreads - 1) / kThreads;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  gated_act_kernel<<<(unsigned)blocks, kThreads, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x2, (long long)rows, n, interleaved ? 1 : 0, act, (__nv_bfloat16*)y);
+  PNV_CUDA(cudaGetLastError());
+  return PNV_OK;
+}

@@ -1,0 +1,143 @@
+"""paired_nvfp4_kernels for B200 (sm_100a): paired-4:8 sparse NVFP4 grouped MoE GEMM ops.
+
+Importing this package loads ``libpaired_nvfp4_b200.so`` (hand-written sm_100a CUDA behind a C ABI)
+and registers ``torch.ops.paired_nvfp4.*`` with the reference project's operator schemas
+(csrc/ops.cu:739-773), so code written against the reference's package runs unchanged.  The helper
+surface of the reference's ``paired_nvfp4_kernels/__init__.py`` (tactic enumeration, the gate/up
+interleave permutation, availability probes) is provided under the same names.
+
+There is no CPU or eager-PyTorch fallback: without the compiled library the import fails.
+"""
+import torch
+
+from . import _cabi, ops
+
+__version__ = "0.1.0"
+
+__all__ = [
+    "DEFAULT_TACTIC",
+    "all_tactics",
+    "fused_swiglu_tactics",
+    "interleave_gate_up_rows",
+    "built_archs",
+    "group_mm_configs",
+    "is_available",
+    "loaded_arch",
+    "suggest_tactic",
+    "valid_clusters",
+]
+
+_LOADED_SM = 100
+
+# (config_id, cluster_m, cluster_n): also the schema defaults of torch.ops.paired_nvfp4.group_mm
+DEFAULT_TACTIC = (0, 2, 1)
+_CLUSTER_DIMS = (1, 2, 4)
+
+
+def _register():
+    lib = torch.library.Library("paired_nvfp4", "DEF")
+    lib.define("compress(Tensor w_packed, Tensor w_blockscale, int k) -> (Tensor, Tensor, Tensor)")
+    lib.define("quant_act(Tensor x, Tensor gscale, Tensor expert_num_tokens, int features) -> (Tensor, Tensor)")
+    lib.define("silu_mul_quant_act(Tensor x2, Tensor gscale, Tensor expert_num_tokens, int features, "
+               "bool interleaved=False, str activation=\"silu\", float beta=1.0, float linear_beta=-1.0) "
+               "-> (Tensor, Tensor)")
+    lib.define("scatter_quant_act(Tensor a1, Tensor flat_tok, Tensor dest_global, Tensor? topk_weights, "
+               "Tensor gscale, Tensor expert_num_tokens, int cap) -> (Tensor, Tensor)")
+    lib.define("group_mm(Tensor(a!) out, Tensor a_comp, Tensor e_meta, Tensor sfa, Tensor b_act, Tensor sfb, "
+               "Tensor alphas, Tensor expert_num_tokens, int features, int k, "
+               f"int config_id={DEFAULT_TACTIC[0]}, int cluster_m={DEFAULT_TACTIC[1]}, "
+               f"int cluster_n={DEFAULT_TACTIC[2]}) -> ()")
+    lib.define("group_mm_configs() -> str[]")
+    lib.define("gated_act(Tensor x2, bool interleaved=False, str activation=\"silu\", float beta=1.0, "
+               "float linear_beta=-1.0) -> Tensor")
+    lib.impl("compress", ops.compress, "CUDA")
+    lib.impl("quant_act", ops.quant_act, "CUDA")
+    lib.impl("silu_mul_quant_act", ops.silu_mul_quant_act, "CUDA")
+    lib.impl("scatter_quant_act", ops.scatter_quant_act, "CUDA")
+    lib.impl("group_mm", ops.group_mm, "CUDA")
+    lib.impl("gated_act", ops.gated_act, "CUDA")
+    lib.impl("group_mm_configs", ops.group_mm_configs, "CompositeExplicitAutograd")
+    return lib
+
+
+_LIB = _register()   # kept alive for the life of the process
+
+
+def _current_sm():
+    if not torch.cuda.is_available():
+        return None
+    major, minor = torch.cuda.get_device_capability()
+    return major * 10 + minor
+
+
+def loaded_arch():
+    """SM number the loaded library was built for (100)."""
+    return _LOADED_SM
+
+
+def built_archs():
+    """SM numbers with compiled kernels in this installation."""
+    return [_LOADED_SM]
+
+
+def is_available():
+    """True iff the current CUDA device is an sm_100 part and the ops are registered."""
+    if _current_sm() != _LOADED_SM:
+        return False
+    ns = getattr(torch.ops, "paired_nvfp4", None)
+    return ns is not None and hasattr(ns, "group_mm") and hasattr(ns, "compress")
+
+
+def group_mm_configs():
+    """Names of the tile variants, indexed by config_id."""
+    return list(torch.ops.paired_nvfp4.group_mm_configs())
+
+
+def _is_2sm(config_name):
+    return config_name.split("_")[1] == "2sm"   # sparse_<sm mode>_<TileM>x<TileN>
+
+
+def valid_clusters(config_name, max_product=16):
+    """Legal (cluster_m, cluster_n) pairs for one tile variant (2SM names need an even cluster_m)."""
+    out = []
+    for cm in _CLUSTER_DIMS:
+        if _is_2sm(config_name) and cm % 2:
+            continue
+        out.extend((cm, cn) for cn in _CLUSTER_DIMS if cm * cn <= max_product)
+    return out
+
+
+def all_tactics(max_cluster_product=16):
+    """Every candidate (config_id, cluster_m, cluster_n); the op re-validates each one."""
+    return [(cid, cm, cn) for cid, name in enumerate(group_mm_configs())
+            for cm, cn in valid_clusters(name, max_cluster_product)]
+
+
+def interleave_gate_up_rows(n, device=None):
+    """Row order of W13 ([gate; up], 2n rows) for a GEMM whose epilogue pairs gate and up values:
+    64-row blocks holding gate rows 32b..32b+31 followed by up rows n+32b..n+32b+31.  Apply to the
+    dense packed weight and its block scales before compress().  n must be a multiple of 64."""
+    if n % 64:
+        raise ValueError(f"intermediate size must be a multiple of 64, got {n}")
+    gate = torch.arange(n, device=device).view(n // 32, 1, 32)
+    return torch.cat([gate, gate + n], dim=1).reshape(-1)
+
+
+def fused_swiglu_tactics(max_cluster_product=16):
+    """Candidate tactics of the fused SwiGLU GEMM (empty while the op is not registered)."""
+    ns = torch.ops.paired_nvfp4
+    if not hasattr(ns, "group_mm_swiglu_configs"):
+        return []
+    return [(cid, cm, cn) for cid, name in enumerate(ns.group_mm_swiglu_configs())
+            for cm, cn in valid_clusters(name, max_cluster_product)]
+
+
+def suggest_tactic(max_n):
+    """A reasonable group_mm tactic for a per-expert token capacity of max_n, without autotuning:
+    the narrowest tile that covers max_n, up to 128 columns."""
+    names = group_mm_configs()
+    if max_n <= 32 and "sparse_1sm_128x32" in names:
+        return (names.index("sparse_1sm_128x32"), 1, 1)
+    if max_n <= 64:
+        return (names.index("sparse_1sm_128x64"), 1, 1)
+    return DEFAULT_TACTIC

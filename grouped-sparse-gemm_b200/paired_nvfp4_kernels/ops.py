@@ -1,0 +1,220 @@
+"""torch.ops.paired_nvfp4.* : argument validation, output allocation, stream lookup, then one call
+into the C ABI.  Mirrors the reference's op layer (csrc/ops.cu) schema for schema: same names,
+argument meaning, output shapes and error substrings.  Every forward op only enqueues work on the
+current CUDA stream of the tensors' device; nothing synchronises or reads device memory.
+"""
+import torch
+
+from . import _cabi
+
+_lib = _cabi.lib
+SF_BLOCK = 32
+_ARCH_SM = 100
+_dev_info = {}
+
+
+def _check(cond, msg):
+    if not cond:
+        raise RuntimeError(msg() if callable(msg) else msg)
+
+
+def _device_info(device):
+    """(sm_version, sm_count) of a CUDA device, queried once (reference: csrc/ops.cu:86-103)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    info = _dev_info.get(idx)
+    if info is None:
+        props = torch.cuda.get_device_properties(idx)
+        info = (props.major * 10 + props.minor, props.multi_processor_count)
+        _dev_info[idx] = info
+    return info
+
+
+def _check_arch(t):
+    v = _device_info(t.device)[0]
+    _check(v == _ARCH_SM, lambda: f"paired_nvfp4 ops in this module are built for SM{_ARCH_SM} but the tensor "
+                                  f"is on a compute capability {v // 10}.{v % 10} device")
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _check_gscale_counts(gscale, counts, E):
+    _check(gscale.dtype == torch.float32, "gscale must be float32")
+    _check(gscale.numel() == E or gscale.numel() == 1, "gscale must be [E] (per expert) or [1] (shared)")
+    _check(counts.dtype == torch.int32 and counts.numel() == E, "expert_num_tokens must be [E] int32")
+    _check(gscale.is_contiguous() and counts.is_contiguous(), "gscale and expert_num_tokens must be contiguous")
+
+
+def _act_kind(activation, beta):
+    if activation == "silu":
+        return 0
+    if activation == "situ":
+        _check(beta > 0, lambda: f"situ: beta must be positive, got {beta}")
+        return 1
+    raise RuntimeError(f"activation must be 'silu' or 'situ', got '{activation}'")
+
+
+def compress(w_packed, w_blockscale, k):
+    """csrc/ops.cu:156-223."""
+    _check(w_packed.is_cuda and w_blockscale.is_cuda, "inputs must be CUDA tensors")
+    _check_arch(w_packed)
+    _check(w_packed.dim() == 3, "w_packed must be [E, out_features, K/2]")
+    _check(w_blockscale.dim() == 3, "w_blockscale must be [E, out_features, ceil(K/SFVecSize)]")
+    _check(w_packed.is_contiguous() and w_blockscale.is_contiguous(), "inputs must be contiguous")
+    _check(w_packed.dtype == torch.uint8, "w_packed must be uint8 (2 e2m1 per byte)")
+    E, M, K = w_packed.size(0), w_packed.size(1), int(k)
+    _check(K % 2 == 0 and w_packed.size(2) == K // 2, "w_packed last dim must equal K/2")
+    _check(w_blockscale.size(0) == E and w_blockscale.size(1) == M,
+           "w_blockscale must match w_packed in [E, out_features]")
+    kb = (K + SF_BLOCK - 1) // SF_BLOCK
+    _check(w_blockscale.size(2) == kb,
+           lambda: f"w_blockscale last dim must be ceil(K/{SF_BLOCK}) = {kb}, got {w_blockscale.size(2)}. The "
+                   f"sparse NVFP4 MMA uses one scale per {SF_BLOCK} dense K elements; checkpoints quantized "
+                   "with 16-element groups are incompatible")
+    _check(w_blockscale.element_size() == 1, "w_blockscale must be a 1-byte (e4m3) dtype")
+    m_ac, k_ac, m_e, k_e = _cabi.physical_dims(M, K)
+    dev = w_packed.device
+    a_comp = torch.empty((E, m_ac, k_ac // 2), dtype=torch.uint8, device=dev)
+    e_meta = torch.empty((E, m_e, k_e), dtype=torch.uint8, device=dev)
+    sfa = torch.empty((_cabi.sf_numel(M, K, E),), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _cabi.check(_lib.pnv_compress(w_packed.data_ptr(), w_blockscale.data_ptr(), E, M, K, a_comp.data_ptr(),
+                                      e_meta.data_ptr(), sfa.data_ptr(), _stream(w_packed)))
+    return a_comp, e_meta, sfa
+
+
+def quant_act(x, gscale, expert_num_tokens, features):
+    """csrc/ops.cu:230-262.  `features` is accepted for API symmetry; the layouts do not use it."""
+    _check(x.is_cuda and gscale.is_cuda and expert_num_tokens.is_cuda, "inputs must be CUDA")
+    _check_arch(x)
+    _check(x.dim() == 3, "x must be [E, max_n, K]")
+    _check(x.dtype == torch.bfloat16 and x.is_contiguous(), "x must be contiguous bf16")
+    E, max_n, K = x.shape
+    _check(K % SF_BLOCK == 0, lambda: f"K must be a multiple of {SF_BLOCK}, got {K}")
+    _check_gscale_counts(gscale, expert_num_tokens, E)
+    gpe = 1 if gscale.numel() == E else 0
+    b_act = torch.empty((E, max_n, K // 2), dtype=torch.uint8, device=x.device)
+    sfb = torch.empty((_cabi.sf_numel(max_n, K, E),), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _cabi.check(_lib.pnv_quant_act(x.data_ptr(), gscale.data_ptr(), gpe, expert_num_tokens.data_ptr(), E, max_n,
+                                       K, b_act.data_ptr(), sfb.data_ptr(), _device_info(x.device)[1], _stream(x)))
+    return b_act, sfb
+
+
+def silu_mul_quant_act(x2, gscale, expert_num_tokens, features, interleaved=False, activation="silu",
+                       beta=1.0, linear_beta=-1.0):
+    """csrc/ops.cu:269-306."""
+    _check(x2.is_cuda and gscale.is_cuda and expert_num_tokens.is_cuda, "inputs must be CUDA")
+    _check_arch(x2)
+    _check(x2.dim() == 3, "x2 must be [E, max_n, 2N] ([gate | up] halves)")
+    _check(x2.dtype == torch.bfloat16 and x2.is_contiguous(), "x2 must be contiguous bf16")
+    E, max_n = x2.size(0), x2.size(1)
+    _check(x2.size(2) % 2 == 0, lambda: f"x2 last dim must be even ([gate | up]), got {x2.size(2)}")
+    N = x2.size(2) // 2
+    _check(N % SF_BLOCK == 0, lambda: f"intermediate width N must be a multiple of {SF_BLOCK}, got {N}")
+    _check_gscale_counts(gscale, expert_num_tokens, E)
+    gpe = 1 if gscale.numel() == E else 0
+    kind = _act_kind(activation, beta)
+    b_act = torch.empty((E, max_n, N // 2), dtype=torch.uint8, device=x2.device)
+    sfb = torch.empty((_cabi.sf_numel(max_n, N, E),), dtype=torch.uint8, device=x2.device)
+    with torch.cuda.device(x2.device):
+        _cabi.check(_lib.pnv_silu_mul_quant_act(
+            x2.data_ptr(), gscale.data_ptr(), gpe, expert_num_tokens.data_ptr(), E, max_n, N, 1 if interleaved else 0,
+            kind, float(beta), float(linear_beta), b_act.data_ptr(), sfb.data_ptr(), _device_info(x2.device)[1],
+            _stream(x2)))
+    return b_act, sfb
+
+
+def scatter_quant_act(a1, flat_tok, dest_global, topk_weights, gscale, expert_num_tokens, cap):
+    """csrc/ops.cu:314-367.  expert_num_tokens only supplies E."""
+    _check(a1.is_cuda and flat_tok.is_cuda and dest_global.is_cuda and gscale.is_cuda and expert_num_tokens.is_cuda,
+           "inputs must be CUDA")
+    _check_arch(a1)
+    _check(a1.dim() == 2, "a1 must be [T, K] (token-order hidden states)")
+    _check(a1.dtype == torch.bfloat16 and a1.is_contiguous(), "a1 must be contiguous bf16")
+    K = a1.size(1)
+    _check(K % SF_BLOCK == 0, lambda: f"K must be a multiple of {SF_BLOCK}, got {K}")
+    _check(flat_tok.dtype == torch.int64 and dest_global.dtype == torch.int64, "flat_tok and dest_global must be int64")
+    _check(flat_tok.dim() == 1 and dest_global.dim() == 1 and flat_tok.numel() == dest_global.numel(),
+           "flat_tok and dest_global must be same-length 1D")
+    _check(flat_tok.is_contiguous() and dest_global.is_contiguous(), "plan tensors must be contiguous")
+    _check(cap > 0, "cap must be positive")
+    n = flat_tok.numel()
+    E = expert_num_tokens.numel()
+    _check_gscale_counts(gscale, expert_num_tokens, E)
+    gpe = 1 if gscale.numel() == E else 0
+    w_ptr = None
+    if topk_weights is not None:
+        _check(topk_weights.is_cuda and topk_weights.dtype == torch.float32 and topk_weights.is_contiguous()
+               and topk_weights.numel() == n, "topk_weights must be contiguous float32 [N]")
+        w_ptr = topk_weights.data_ptr()
+    # one extra trailing row, as in the reference: b_act is a view of an (E*cap + 1)-row buffer
+    b_ext = torch.empty((E * cap + 1, K // 2), dtype=torch.uint8, device=a1.device)
+    b_act = b_ext.narrow(0, 0, E * cap).view(E, cap, K // 2)
+    sfb = torch.empty((_cabi.sf_numel(cap, K, E),), dtype=torch.uint8, device=a1.device)
+    with torch.cuda.device(a1.device):
+        _cabi.check(_lib.pnv_scatter_quant_act(
+            a1.data_ptr(), flat_tok.data_ptr(), dest_global.data_ptr(), w_ptr, gscale.data_ptr(), gpe, n, K, E,
+            int(cap), b_ext.data_ptr(), sfb.data_ptr(), _device_info(a1.device)[1], _stream(a1)))
+    return b_act, sfb
+
+
+def gated_act(x2, interleaved=False, activation="silu", beta=1.0, linear_beta=-1.0):
+    """The unfused gated activation (gated_act, csrc/layout.cuh:204-216): bf16 [..., 2N] -> [..., N]."""
+    _check(x2.is_cuda and x2.dtype == torch.bfloat16 and x2.is_contiguous(), "x2 must be contiguous CUDA bf16")
+    N = x2.size(-1) // 2
+    _check(N % SF_BLOCK == 0, lambda: f"intermediate width N must be a multiple of {SF_BLOCK}, got {N}")
+    kind = _act_kind(activation, beta)
+    y = torch.empty(x2.shape[:-1] + (N,), dtype=torch.bfloat16, device=x2.device)
+    rows = x2.numel() // (2 * N) if N else 0
+    with torch.cuda.device(x2.device):
+        _cabi.check(_lib.pnv_gated_act(x2.data_ptr(), rows, N, 1 if interleaved else 0, kind, float(beta),
+                                       float(linear_beta), y.data_ptr(), _stream(x2)))
+    return y
+
+
+def group_mm_configs():
+    """csrc/ops.cu:665-670."""
+    return _cabi.group_mm_config_names()
+
+
+def group_mm(out, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens, features, k, config_id=0,
+             cluster_m=2, cluster_n=1):
+    """csrc/ops.cu:672-735.  Mutates `out` in place."""
+    ts = (out, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens)
+    _check(all(t.is_cuda for t in ts), "all tensors must be CUDA")
+    _check_arch(out)
+    _check(out.dim() == 3 and b_act.dim() == 3 and a_comp.dim() == 3 and e_meta.dim() == 3,
+           "out, b_act, a_comp and e_meta must be 3D")
+    E, M, K, max_n = a_comp.size(0), int(features), int(k), b_act.size(1)
+    _check(out.size(0) == E and b_act.size(0) == E and e_meta.size(0) == E, "expert dim mismatch")
+    _check(out.size(1) == max_n and out.size(2) == M, "out must be [E, max_n, features]")
+    _check(b_act.size(2) == K // 2, "b_act must be [E, max_n, K/2]")
+    _check(out.dtype == torch.bfloat16, "out must be bf16")
+    _check(a_comp.dtype == torch.uint8 and e_meta.dtype == torch.uint8 and b_act.dtype == torch.uint8
+           and sfa.element_size() == 1 and sfb.element_size() == 1,
+           "a_comp, e_meta and b_act must be uint8; sfa, sfb 1-byte")
+    _check(all(t.is_contiguous() for t in ts), "all group_mm tensors must be contiguous")
+    _check(alphas.dtype == torch.float32 and alphas.numel() == E, "alphas must be [E] float32")
+    _check(expert_num_tokens.dtype == torch.int32 and expert_num_tokens.numel() == E,
+           "expert_num_tokens must be [E] int32 (real per-expert token counts, <= max_n)")
+    m_ac, k_ac, m_e, k_e = _cabi.physical_dims(M, K)
+    _check(a_comp.size(1) == m_ac and a_comp.size(2) == k_ac // 2 and e_meta.size(1) == m_e and e_meta.size(2) == k_e,
+           lambda: f"a_comp / e_meta shapes do not match compress() output for features={M}, k={K} "
+                   "(check the features / k arguments)")
+    _check(sfa.numel() >= _cabi.sf_numel(M, K, E), "sfa is smaller than the SFA layout")
+    _check(sfb.numel() >= _cabi.sf_numel(max_n, K, E), "sfb is smaller than the SFB layout")
+    with torch.cuda.device(out.device):
+        _cabi.check(_lib.pnv_group_mm(
+            out.data_ptr(), a_comp.data_ptr(), e_meta.data_ptr(), sfa.data_ptr(), b_act.data_ptr(), sfb.data_ptr(),
+            alphas.data_ptr(), expert_num_tokens.data_ptr(), E, M, K, max_n, int(config_id), int(cluster_m),
+            int(cluster_n), _device_info(out.device)[1], 1, _stream(out)))
+
+
+def group_mm_device_status():
+    """Status word of the bounded waits inside group_mm (0 = all completed); synchronises."""
+    import ctypes
+    v = ctypes.c_int()
+    _cabi.check(_lib.pnv_group_mm_device_status(ctypes.byref(v)))
+    return v.value

@@ -1,0 +1,124 @@
+/*
+ * paired_nvfp4_b200 -- C ABI of the B200 (sm_100a) paired-4:8 sparse NVFP4 grouped MoE GEMM path.
+ *
+ * Every entry point takes raw device pointers, extents, scalar options and a CUDA stream, only
+ * enqueues work on that stream, never synchronises and never reads device memory on the host, so
+ * every forward call may be captured into a CUDA graph.  Unless a comment says otherwise a call
+ * allocates nothing: the caller owns every buffer, sized with the query functions below.
+ *
+ * Return value: 0 on success, a PNV_ERR_* code otherwise; pnv_last_error() then returns a
+ * NUL-terminated description (thread-local, valid until the next failing call on that thread).
+ *
+ * Each declaration names the interface of the reference project (IST-DASLab/grouped-sparse-GEMM,
+ * paths relative to its root) that it stands in for.
+ */
+#ifndef PAIRED_NVFP4_B200_H_
+#define PAIRED_NVFP4_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PNV_ABI_VERSION 1
+
+#define PNV_OK 0
+#define PNV_ERR_INVALID_ARGUMENT 1 /* a shape / option the reference rejects with TORCH_CHECK */
+#define PNV_ERR_CUDA 2             /* a CUDA runtime or driver call failed at enqueue time */
+#define PNV_ERR_UNSUPPORTED 3      /* valid for the reference, not implemented by this build */
+
+/* Same handle as cudaStream_t / CUstream. */
+typedef struct CUstream_st* pnv_stream_t;
+
+/* Gated activation kinds of silu_mul_quant_act (csrc/layout.cuh:197-202, GatedAct::Kind). */
+#define PNV_ACT_SILU 0
+#define PNV_ACT_SITU 1
+
+int pnv_abi_version(void);
+const char* pnv_last_error(void);
+
+/* Device status word of the most recent group_mm launches on the current device: 0 when every
+ * bounded wait inside the kernel completed, otherwise the code of the wait that gave up.  Reading
+ * it synchronises the device; it is a debugging aid, not part of the forward path.
+ * (No counterpart in the reference, whose kernel waits without bound.) */
+int pnv_group_mm_device_status(int* status_out);
+
+/* ---- size queries ------------------------------------------------------------------------- */
+
+/* physical_dims(features, k, groups) (csrc/layout.cuh:83-91): a_comp is
+ * [E, *m_aligned_ac, *k_aligned_ac / 2] bytes, e_meta is [E, *m_aligned_e, *k_aligned_e] bytes. */
+int pnv_physical_dims(int features, int k, int* m_aligned_ac, int* k_aligned_ac, int* m_aligned_e,
+                      int* k_aligned_e);
+
+/* sfa_numel / sfb_numel (csrc/layout.cuh:95-102): bytes of a swizzled scale buffer holding
+ * `rows` rows (features for SFA, max_n or cap for SFB) of ceil(k / 32) scales for `groups` experts. */
+int64_t pnv_sf_numel(int rows, int k, int groups);
+
+/* ---- load time ---------------------------------------------------------------------------- */
+
+/* paired_nvfp4_compress (csrc/ops.cu:156-223).  w_packed u8[E, M, K/2] (two e2m1 per byte, low
+ * nibble = lower K, paired-4:8 zeros in place), w_blockscale u8[E, M, ceil(K/32)] raw UE4M3 in
+ * natural order.  Writes every byte of a_comp, e_meta and sfa (padding is zero). */
+int pnv_compress(const uint8_t* w_packed, const uint8_t* w_blockscale, int experts, int features,
+                 int k, uint8_t* a_comp, uint8_t* e_meta, uint8_t* sfa, pnv_stream_t stream);
+
+/* ---- activation quantizers ---------------------------------------------------------------- */
+
+/* paired_nvfp4_quant_act (csrc/ops.cu:230-262 -> quant_act_kernel, csrc/quant.cuh:238-268).
+ * x bf16[E, max_n, K]; gscale f32[E] (gscale_per_expert != 0) or f32[1]; counts i32[E].
+ * b_act u8[E, max_n, K/2]: rows t >= counts[e] are not written.  sfb u8[pnv_sf_numel(max_n, K, E)]:
+ * every byte is written (quantized scales, 0x38 elsewhere). */
+int pnv_quant_act(const void* x, const float* gscale, int gscale_per_expert, const int32_t* counts,
+                  int experts, int max_n, int k, uint8_t* b_act, uint8_t* sfb, int sm_count,
+                  pnv_stream_t stream);
+
+/* paired_nvfp4_silu_mul_quant_act (csrc/ops.cu:269-306 -> silu_mul_quant_kernel,
+ * csrc/quant.cuh:290-331; activation: make_gated_act csrc/ops.cu:128-141, gated_act
+ * csrc/layout.cuh:204-216).  x2 bf16[E, max_n, 2n]: [gate | up] halves, or, when interleaved != 0,
+ * 64-column blocks of 32 gate then the 32 matching up columns.  beta / linear_beta are read only
+ * for PNV_ACT_SITU.  Outputs as pnv_quant_act with k = n. */
+int pnv_silu_mul_quant_act(const void* x2, const float* gscale, int gscale_per_expert,
+                           const int32_t* counts, int experts, int max_n, int n, int interleaved,
+                           int act_kind, float beta, float linear_beta, uint8_t* b_act,
+                           uint8_t* sfb, int sm_count, pnv_stream_t stream);
+
+/* paired_nvfp4_scatter_quant_act (csrc/ops.cu:314-367 -> scatter_quant_kernel,
+ * csrc/quant.cuh:360-404).  a1 bf16[T, K]; flat_tok / dest_global i64[n_routes]; topk_weights
+ * f32[n_routes] or NULL; routing i with dest_global[i] == experts * cap is dropped.
+ * b_act u8[E * cap, K/2]; sfb u8[pnv_sf_numel(cap, K, E)], fully written. */
+int pnv_scatter_quant_act(const void* a1, const int64_t* flat_tok, const int64_t* dest_global,
+                          const float* topk_weights, const float* gscale, int gscale_per_expert,
+                          int64_t n_routes, int k, int experts, int cap, uint8_t* b_act,
+                          uint8_t* sfb, int sm_count, pnv_stream_t stream);
+
+/* The unfused gated activation the quantizer above folds in (gated_act, csrc/layout.cuh:204-216;
+ * device replica ref_silu_mul_kernel, csrc/testing/selftest.cu:750-760): y bf16[rows, n] from
+ * x2 bf16[rows, 2n].  pnv_silu_mul_quant_act == pnv_gated_act followed by pnv_quant_act, byte for
+ * byte. */
+int pnv_gated_act(const void* x2, int64_t rows, int n, int interleaved, int act_kind, float beta,
+                  float linear_beta, void* y, pnv_stream_t stream);
+
+/* ---- grouped GEMM ------------------------------------------------------------------------- */
+
+/* paired_nvfp4_group_mm_configs (csrc/ops.cu:665-670; table kGroupMmKinds,
+ * csrc/sm100/tactics.cu:35-44): tile-variant names indexed by config_id. */
+int pnv_group_mm_num_configs(void);
+const char* pnv_group_mm_config_name(int config_id);
+
+/* paired_nvfp4_group_mm (csrc/ops.cu:672-735 -> run_group_mm_variant, csrc/group_mm.cuh:92-179;
+ * cluster rules check_cluster, csrc/sm100/tactics.cu:62-69).
+ * out bf16[E, max_n, features]: out[e, t, m] = bf16(alphas[e] * sum_k dq(w)[e,m,k] dq(b)[e,t,k])
+ * for t < counts[e]; every other row keeps the caller's bytes.  a_comp / e_meta / sfa are
+ * pnv_compress outputs for (features, k); b_act / sfb a quantizer's outputs for (max_n, k).
+ * pdl != 0 launches with programmatic dependent launch (the kernel waits on its stream
+ * predecessor before its first dependent read; csrc/pdl.cuh:42-80). */
+int pnv_group_mm(void* out, const uint8_t* a_comp, const uint8_t* e_meta, const uint8_t* sfa,
+                 const uint8_t* b_act, const uint8_t* sfb, const float* alphas,
+                 const int32_t* counts, int experts, int features, int k, int max_n, int config_id,
+                 int cluster_m, int cluster_n, int sm_count, int pdl, pnv_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PAIRED_NVFP4_B200_H_ */

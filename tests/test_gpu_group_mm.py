@@ -1,0 +1,119 @@
+"""GPU parity: group_mm against the oracle's fp32 dequantised matmul.  Bar: relative Frobenius
+error <= 5e-3 on the valid rows (the only error sources are fp32 accumulation order and the final
+bf16 rounding), and every row at or past counts[e] keeps the caller's bytes."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import paired_nvfp4_oracle as orc
+from helpers import bf16_tensor, u8, dev, make_acts, make_weights
+
+pytestmark = pytest.mark.gpu
+
+REL_FROB_TOL = 5e-3
+SENTINEL = -12345.0
+
+
+@pytest.fixture(scope="module")
+def pnk():
+    import paired_nvfp4_kernels
+    return paired_nvfp4_kernels
+
+
+def run_case(pnk, E, M, K, max_n, counts, config_id, seed, wscale=1.0, gscale=None, alphas=None, cluster=None):
+    ops = torch.ops.paired_nvfp4
+    packed, sf, w_dq = make_weights(E, M, K, seed, wscale)
+    x = make_acts(E, max_n, K, seed + 1)
+    cnt = np.asarray(counts, np.int32)
+    g = np.ones(1, np.float32) if gscale is None else np.asarray(gscale, np.float32)
+    al = np.linspace(0.5, 2.0, E).astype(np.float32) if alphas is None else np.asarray(alphas, np.float32)
+    a_comp, e_meta, sfa = ops.compress(dev(packed), dev(sf), K)
+    b_act, sfb = ops.quant_act(bf16_tensor(x), dev(g), dev(cnt), M)
+    out = torch.full((E, max_n, M), SENTINEL, dtype=torch.bfloat16, device="cuda")
+    name = pnk.group_mm_configs()[config_id]
+    cm, cn = cluster or pnk.valid_clusters(name)[0]
+    ops.group_mm(out, a_comp, e_meta, sfa, b_act, sfb, dev(al), dev(cnt), M, K, config_id, cm, cn)
+    torch.cuda.synchronize()
+    from paired_nvfp4_kernels import ops as pyops
+    assert pyops.group_mm_device_status() == 0
+    got = out.float().cpu().numpy()
+    ob, valid, osfb = orc.quant_act(x, g, cnt)
+    assert np.array_equal(u8(sfb), osfb)
+    want = orc.group_mm(w_dq, ob, osfb, al, cnt, sentinel=SENTINEL)
+    assert (got[~valid] == SENTINEL).all(), "rows at or past counts[e] were written"
+    if valid.any():
+        rel = orc.rel_frobenius(got[valid], want[valid])
+        assert rel <= REL_FROB_TOL, f"relative Frobenius error {rel:.3e}"
+    return got, want, valid
+
+
+def config_ids():
+    return list(range(9))
+
+
+@pytest.mark.parametrize("config_id", config_ids())
+def test_small_single_tile(pnk, config_id):
+    run_case(pnk, E=1, M=128, K=256, max_n=32, counts=[32], config_id=config_id, seed=10)
+
+
+@pytest.mark.parametrize("config_id", config_ids())
+def test_zero_count_experts_and_untouched_padding(pnk, config_id):
+    # the reference's tests/test_ops.py:121-145 case: counts straddling every tile boundary
+    run_case(pnk, E=8, M=512, K=512, max_n=512, counts=[0, 1, 255, 256, 257, 512, 0, 64],
+             config_id=config_id, seed=0)
+
+
+SHAPES = [
+    # E, M, K, max_n, counts
+    (8, 2048, 1024, 256, "rand"),                 # the reference's CPU-plumbing config
+    (2, 130, 320, 70, [70, 3]),                   # M tail, K = 2.5 MMA blocks, K atoms with slop
+    (3, 256, 96, 40, [40, 0, 17]),                # K below one MMA block
+    (2, 384, 4096, 16, [16, 5]),                  # long K, decode-sized counts
+    (4, 1536, 2048, 300, [300, 128, 129, 1]),     # Qwen3 gate_up shape
+    (2, 2048, 768, 200, [200, 64]),               # Qwen3 down shape (K = 3 stages)
+    (1, 128, 14336, 8, [8]),                      # Mixtral down K
+]
+
+
+@pytest.mark.parametrize("E,M,K,max_n,counts", SHAPES)
+@pytest.mark.parametrize("config_id", [0, 1, 5, 8])
+def test_shapes(pnk, E, M, K, max_n, counts, config_id):
+    if counts == "rand":
+        counts = np.random.default_rng(1001).integers(1, max_n + 1, E)
+    run_case(pnk, E, M, K, max_n, counts, config_id, seed=E + M + K)
+
+
+def test_gscale_and_alpha_undo_each_other(pnk):
+    E, M, K, max_n = 4, 256, 512, 48
+    x_amax = 4.5
+    g = np.full(E, 6 * 448 / x_amax, np.float32) * np.array([1, 0.5, 0.25, 2], np.float32)
+    got, want, valid = run_case(pnk, E, M, K, max_n, [48, 7, 0, 33], 0, seed=5, wscale=0.02, gscale=g, alphas=1.0 / g)
+    assert np.abs(want[valid]).max() > 0.01
+
+
+def test_every_tactic_matches_default(pnk):
+    E, M, K, max_n = 3, 384, 512, 150
+    base, _, valid = run_case(pnk, E, M, K, max_n, [150, 31, 97], 0, seed=3)
+    for cid, cm, cn in pnk.all_tactics():
+        got, _, _ = run_case(pnk, E, M, K, max_n, [150, 31, 97], cid, seed=3, cluster=(cm, cn))
+        assert np.allclose(got[valid], base[valid], atol=1e-2, rtol=1e-2)
+
+
+def test_argument_checks(pnk):
+    ops = torch.ops.paired_nvfp4
+    E, M, K, max_n = 1, 128, 256, 16
+    packed, sf, _ = make_weights(E, M, K, 1)
+    a_comp, e_meta, sfa = ops.compress(dev(packed), dev(sf), K)
+    cnt = dev(np.array([16], np.int32))
+    b_act, sfb = ops.quant_act(bf16_tensor(make_acts(E, max_n, K, 2)), dev(np.ones(1, np.float32)), cnt, M)
+    al = dev(np.ones(1, np.float32))
+    out = torch.zeros(E, max_n, 2 * M, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="compress"):
+        ops.group_mm(out, a_comp, e_meta, sfa, b_act, sfb, al, cnt, 2 * M, K)
+    out = torch.zeros(E, max_n, M, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="even cluster_m"):
+        ops.group_mm(out, a_comp, e_meta, sfa, b_act, sfb, al, cnt, M, K, 0, 1, 1)
+    with pytest.raises(RuntimeError, match="config_id"):
+        ops.group_mm(out, a_comp, e_meta, sfa, b_act, sfb, al, cnt, M, K, 99, 2, 1)
+    with pytest.raises(RuntimeError, match="powers of two"):
+        ops.group_mm(out, a_comp, e_meta, sfa, b_act, sfb, al, cnt, M, K, 2, 3, 1)
