@@ -25,6 +25,7 @@
 // leaves its loop and meets at the final barrier, where tensor memory is released.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -55,7 +56,8 @@ struct Cfg {
   static constexpr int kBBytes = TILE_N * 128;
   static constexpr int kSfbBytes = TILE_N > 128 ? 2048 : 1024;
   static constexpr int kStageBytes = kABytes + kBBytes + kEBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kStages = TILE_N == 256 ? 4 : (TILE_N == 128 ? 7 : (TILE_N == 64 ? 10 : 12));
+  static constexpr int kStages = TILE_N == 256 ? 4 : (TILE_N == 128 ? 7 : 10);
+  static_assert(TILE_N == 64 || TILE_N == 128 || TILE_N == 256, "tile widths: 64, 128, 256");
   static constexpr int kAccStages = TILE_N == 256 ? 1 : 2;
   static constexpr int kOffA = 0;
   static constexpr int kOffB = kABytes;
@@ -80,6 +82,7 @@ struct Params {
   int e_k_atoms;     // metadata atoms along K = k_stages
   int e_m_atoms;     // metadata atoms along M = n_mt
   int sfb_rt;        // scale row-atoms per expert in sfb = ceil(max_n / 128)
+  unsigned* trace;   // traced build only: host-mapped breadcrumb words, 16 per CTA (first 8 CTAs)
 };
 
 // The walk over (expert, n tile, m tile) shared by all roles.
@@ -107,7 +110,33 @@ struct TileWalk {
   }
 };
 
-template <int TILE_N>
+// Traced build (kTrace): every asynchronous operation is issued alone and waited for, each step
+// leaves a breadcrumb in host-mapped memory (readable even after a fault killed the context), and
+// every copy's addresses and size are checked first; a failed check is recorded and the copy is
+// skipped.  Breadcrumb slots per CTA: 0 setup, 1 producer, 2 MMA issuer, 3 epilogue (warp 2),
+// 4 first failed check (code), 5..7 its operands.
+template <bool kTrace>
+__device__ __forceinline__ void crumb(const unsigned* /*unused*/, unsigned* trace, int slot, unsigned code) {
+  if (kTrace && trace != nullptr && blockIdx.x < 8) {
+    volatile unsigned* t = trace + blockIdx.x * 16 + slot;
+    *t = code;
+    __threadfence_system();
+  }
+}
+template <bool kTrace>
+__device__ __forceinline__ bool check_copy(unsigned* trace, unsigned code, uint32_t dst, uint64_t src,
+                                           uint32_t bytes, uint32_t dst_align) {
+  if (!kTrace) return true;
+  if ((dst % dst_align) == 0 && (src % 16) == 0 && (bytes % 16) == 0) return true;
+  if (trace != nullptr && blockIdx.x < 8) {
+    volatile unsigned* t = trace + blockIdx.x * 16;
+    if (t[4] == 0) { t[4] = code; t[5] = dst; t[6] = (unsigned)(src & 0xFFFFFFFFu); t[7] = bytes; }
+    __threadfence_system();
+  }
+  return false;
+}
+
+template <int TILE_N, bool kTrace>
 __global__ void __launch_bounds__(kThreads, 1)
 group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const Params p) {
@@ -119,8 +148,10 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   uint64_t* empty_bar = full_bar + C::kStages;
   uint64_t* acc_full = empty_bar + C::kStages;
   uint64_t* acc_empty = acc_full + C::kAccStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + C::kAccStages);
+  uint64_t* dbg_bar = acc_empty + C::kAccStages;     // two extra barriers, used by the traced build
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dbg_bar + 2);
   int* s_counts = reinterpret_cast<int*>(tmem_slot + 4);
+#define CRUMB(slot, code) crumb<kTrace>(nullptr, p.trace, slot, code)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -131,11 +162,15 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     ptx::prefetch_tensormap(&map_b);
     for (int s = 0; s < C::kStages; ++s) { ptx::mbar_init(full_bar + s, 1); ptx::mbar_init(empty_bar + s, 1); }
     for (int a = 0; a < C::kAccStages; ++a) { ptx::mbar_init(acc_full + a, 1); ptx::mbar_init(acc_empty + a, 128); }
+    ptx::mbar_init(dbg_bar, 1);
+    ptx::mbar_init(dbg_bar + 1, 1);
     ptx::fence_mbar_init();
+    CRUMB(0, 1);
   }
   if (warp == 1) {
     ptx::tmem_alloc(tmem_slot, kTmemCols);
     ptx::tmem_relinquish();
+    if (lane == 0) CRUMB(0, 2);
   }
   // counts (and everything else the producer kernels wrote) may only be read after this point
   pdl_wait();
@@ -145,6 +180,7 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) { CRUMB(0, 3); CRUMB(8, tmem_base); CRUMB(9, ptx::smem_u32(smem)); CRUMB(10, ptx::smem_u32(full_bar)); }
 
   TileWalk walk;
   walk.init<TILE_N>(s_counts, p.E, p.n_mt);
@@ -154,6 +190,8 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t dbg_phase = 0;
+      (void)dbg_phase;
       bool ok = true;
       for (long long t = blockIdx.x; ok; t += gridDim.x) {
         int mt, nt;
@@ -174,16 +212,47 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const int k_atoms = min(2, p.n_kt - 2 * ks);         // MMA K-blocks present in this stage
           const uint32_t sf_bytes = 512u * k_atoms;
           const uint32_t tx = kABytes + C::kBBytes + kEBytes + sf_bytes * (1 + sfb_row_atoms);
-          ptx::mbar_arrive_expect_tx(full_bar + stage, tx);
-          ptx::tma_load_3d(st + C::kOffA, &map_a, full_bar + stage, ks * 64, mt * kTileM, e);
-          ptx::tma_load_3d(st + C::kOffB, &map_b, full_bar + stage, ks * 128, n0, e);
-          ptx::bulk_load(st + C::kOffE, p.e_meta + (e_atom0 + (long long)ks * p.e_m_atoms) * 2048,
-                         kEBytes, full_bar + stage);
-          ptx::bulk_load(st + C::kOffSfa, p.sfa + (sfa_atom0 + 2 * ks) * 512, sf_bytes, full_bar + stage);
-          for (int ra = 0; ra < sfb_row_atoms; ++ra)
-            ptx::bulk_load(st + C::kOffSfb + ra * 1024,
-                           p.sfb + (sfb_atom0 + (long long)ra * p.n_kt + 2 * ks) * 512, sf_bytes,
-                           full_bar + stage);
+          const uint8_t* e_src = p.e_meta + (e_atom0 + (long long)ks * p.e_m_atoms) * 2048;
+          const uint8_t* sfa_src = p.sfa + (sfa_atom0 + 2 * ks) * 512;
+          if (!kTrace) {
+            ptx::mbar_arrive_expect_tx(full_bar + stage, tx);
+            ptx::tma_load_3d(st + C::kOffA, &map_a, full_bar + stage, ks * 64, mt * kTileM, e);
+            ptx::tma_load_3d(st + C::kOffB, &map_b, full_bar + stage, ks * 128, n0, e);
+            ptx::bulk_load(st + C::kOffE, e_src, kEBytes, full_bar + stage);
+            ptx::bulk_load(st + C::kOffSfa, sfa_src, sf_bytes, full_bar + stage);
+            for (int ra = 0; ra < sfb_row_atoms; ++ra)
+              ptx::bulk_load(st + C::kOffSfb + ra * 1024,
+                             p.sfb + (sfb_atom0 + (long long)ra * p.n_kt + 2 * ks) * 512, sf_bytes,
+                             full_bar + stage);
+          } else {
+            // one copy at a time on a private barrier, then a plain arrive publishes the stage
+            uint32_t dphase = dbg_phase;
+            auto one = [&](unsigned code, uint32_t bytes, auto issue) {
+              CRUMB(1, code);
+              ptx::mbar_arrive_expect_tx(dbg_bar, bytes);
+              issue();
+              bool done = ptx::mbar_wait(dbg_bar, dphase);
+              dphase ^= 1;
+              CRUMB(1, code + (done ? 1 : 2));
+            };
+            if (check_copy<kTrace>(p.trace, 100, ptx::smem_u32(st + C::kOffA), 0, kABytes, 1024))
+              one(110, kABytes, [&] { ptx::tma_load_3d(st + C::kOffA, &map_a, dbg_bar, ks * 64, mt * kTileM, e); });
+            if (check_copy<kTrace>(p.trace, 101, ptx::smem_u32(st + C::kOffB), 0, C::kBBytes, 1024))
+              one(120, C::kBBytes, [&] { ptx::tma_load_3d(st + C::kOffB, &map_b, dbg_bar, ks * 128, n0, e); });
+            if (check_copy<kTrace>(p.trace, 102, ptx::smem_u32(st + C::kOffE), (uint64_t)e_src, kEBytes, 16))
+              one(130, kEBytes, [&] { ptx::bulk_load(st + C::kOffE, e_src, kEBytes, dbg_bar); });
+            if (check_copy<kTrace>(p.trace, 103, ptx::smem_u32(st + C::kOffSfa), (uint64_t)sfa_src, sf_bytes, 16))
+              one(140, sf_bytes, [&] { ptx::bulk_load(st + C::kOffSfa, sfa_src, sf_bytes, dbg_bar); });
+            for (int ra = 0; ra < sfb_row_atoms; ++ra) {
+              const uint8_t* sfb_src = p.sfb + (sfb_atom0 + (long long)ra * p.n_kt + 2 * ks) * 512;
+              if (check_copy<kTrace>(p.trace, 104, ptx::smem_u32(st + C::kOffSfb + ra * 1024), (uint64_t)sfb_src,
+                                     sf_bytes, 16))
+                one(150, sf_bytes, [&] { ptx::bulk_load(st + C::kOffSfb + ra * 1024, sfb_src, sf_bytes, dbg_bar); });
+            }
+            dbg_phase = dphase;
+            ptx::mbar_arrive(full_bar + stage);
+            CRUMB(1, 160);
+          }
           if (++stage == C::kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -198,7 +267,8 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (lane == 0) {
       constexpr uint32_t idesc = ptx::mma_sp_nvf4_idesc(TILE_N);
       int stage = 0, acc = 0;
-      uint32_t phase = 0, acc_phase = 0;
+      uint32_t phase = 0, acc_phase = 0, mma_dbg_phase = 0;
+      (void)mma_dbg_phase;
       bool ok = true;
       for (long long t = blockIdx.x; ok; t += gridDim.x) {
         int mt, nt;
@@ -209,7 +279,8 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * TILE_N;
-        // scales of this tile's rows sit in column (row offset inside the 128-row atom) / 32
+        // The scales of a 64-wide tile's rows sit 0 or 2 columns into the 128-row atom.  The MMA
+        // faults (misaligned address) on an odd column offset, which is why there is no 32-wide tile.
         const uint32_t sfb_col = tmem_base + kColSfb + (TILE_N < 128 ? ((nt * TILE_N) & 127) >> 5 : 0);
         for (int ks = 0; ks < p.k_stages; ++ks) {
           if (!ptx::mbar_wait(full_bar + stage, phase)) {
@@ -220,7 +291,18 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           ptx::tc_fence_after();
           const uint32_t st = ptx::smem_u32(stage_base + stage * C::kStageBytes);
           const int k_atoms = min(2, p.n_kt - 2 * ks);
+          auto settle = [&](unsigned code) {   // traced build: wait until the operation just issued retires
+            if (kTrace) {
+              CRUMB(2, code);
+              ptx::tc_commit(dbg_bar + 1);
+              bool done = ptx::mbar_wait(dbg_bar + 1, mma_dbg_phase);
+              mma_dbg_phase ^= 1;
+              CRUMB(2, code + (done ? 1 : 2));
+            }
+          };
+          if (kTrace) CRUMB(2, 200);
           ptx::tc_cp_128x128b(tmem_base + kColE, ptx::smem_desc(st + C::kOffE, 128, 0, 0));
+          settle(210);
           for (int ka = 0; ka < k_atoms; ++ka) {
             ptx::tc_cp_32x128b_warpx4(tmem_base + kColSfa + ka * 4,
                                       ptx::smem_desc(st + C::kOffSfa + ka * 512, 128, 0, 0));
@@ -233,6 +315,7 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               ptx::tc_cp_32x128b_warpx4(tmem_base + kColSfb + ka * 4,
                                         ptx::smem_desc(st + C::kOffSfb + ka * 512, 128, 0, 0));
             }
+            settle(220 + 10 * ka);
           }
           for (int ka = 0; ka < k_atoms; ++ka) {
             const uint64_t a_desc = ptx::smem_desc(st + C::kOffA + ka * 32, 512, 16, 4);
@@ -240,12 +323,14 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             ptx::tc_mma_sp_nvf4(d_tmem, a_desc, b_desc, idesc, (ks | ka) != 0 ? 1u : 0u,
                                 tmem_base + kColSfa + ka * 4,
                                 sfb_col + ka * (TILE_N > 128 ? 8 : 4), tmem_base + kColE + ka * 2);
+            settle(240 + 10 * ka);
           }
           ptx::tc_commit(empty_bar + stage);   // stage reusable once these MMAs and copies retire
           if (++stage == C::kStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         ptx::tc_commit(acc_full + acc);        // accumulator complete
+        if (kTrace) CRUMB(2, 290);
         if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
       }
     }
@@ -265,6 +350,7 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         break;
       }
       ptx::tc_fence_after();
+      if (kTrace && threadIdx.x == 64) CRUMB(3, 300);
       const float alpha = p.alphas[e];
       const int m = mt * kTileM + sub * 32 + lane;
       const int n0 = nt * TILE_N;
@@ -275,6 +361,7 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         uint32_t r[32];
         ptx::tc_ld_32x32(tmem_base + ((uint32_t)(sub * 32) << 16) + acc * TILE_N + c0, r);
         ptx::tc_ld_wait();
+        if (kTrace && threadIdx.x == 64) CRUMB(3, 310);
         if (m < p.M) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -284,6 +371,7 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           }
         }
       }
+      if (kTrace && threadIdx.x == 64) CRUMB(3, 320);
       ptx::tc_fence_before();
       ptx::mbar_arrive(acc_empty + acc);
       if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
@@ -296,7 +384,9 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     __syncwarp();
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
+    if (lane == 0) CRUMB(0, 9);
   }
+#undef CRUMB
 }
 
 // ---- host side -----------------------------------------------------------------------------------
@@ -337,11 +427,25 @@ int make_map(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t ro
   return PNV_OK;
 }
 
-template <int TILE_N>
-int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p, int sm_count, bool pdl,
-           cudaStream_t stream) {
+// Traced build: breadcrumb buffer in host-mapped memory, enabled with PNV_GROUP_MM_TRACE=1.
+constexpr int kTraceWords = 8 * 16;
+unsigned* g_trace_host = nullptr;   // host view
+unsigned* g_trace_dev = nullptr;    // device view of the same pages
+
+bool trace_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* env = std::getenv("PNV_GROUP_MM_TRACE");
+    v = (env != nullptr && env[0] == '1') ? 1 : 0;
+  }
+  return v == 1;
+}
+
+template <int TILE_N, bool kTrace>
+int launch_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p, int sm_count, bool pdl,
+                cudaStream_t stream) {
   using C = Cfg<TILE_N>;
-  const size_t smem = 1024 + (size_t)C::kStages * C::kStageBytes + 8 * (2 * C::kStages + 2 * C::kAccStages) +
+  const size_t smem = 1024 + (size_t)C::kStages * C::kStageBytes + 8 * (2 * C::kStages + 2 * C::kAccStages + 2) +
                       16 + 4 * (size_t)p.E;
   PNV_REQUIRE(smem <= 227 * 1024, "group_mm: %d experts need %zu bytes of shared memory (limit 232448)", p.E,
               smem);
@@ -350,15 +454,33 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p, 
   int dev = 0;
   PNV_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64 || !opted_in[dev]) {
-    PNV_CUDA(cudaFuncSetAttribute(group_mm_kernel<TILE_N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    PNV_CUDA(cudaFuncSetAttribute(group_mm_kernel<TILE_N, kTrace>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   227 * 1024));
     if (dev >= 0 && dev < 64) opted_in[dev] = true;
   }
   long long max_tiles = (long long)p.E * p.n_mt * ceil_div_i(p.max_n, TILE_N);
   int grid = (int)(max_tiles < sm_count ? max_tiles : sm_count);
   if (grid < 1) grid = 1;
-  PNV_CUDA(launch_pdl(group_mm_kernel<TILE_N>, dim3(grid), dim3(kThreads), smem, stream, pdl, map_a, map_b, p));
+  PNV_CUDA(launch_pdl(group_mm_kernel<TILE_N, kTrace>, dim3(grid), dim3(kThreads), smem, stream, pdl, map_a,
+                      map_b, p));
   return PNV_OK;
+}
+
+template <int TILE_N>
+int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, Params& p, int sm_count, bool pdl,
+           cudaStream_t stream) {
+  if (!trace_enabled()) {
+    p.trace = nullptr;
+    return launch_impl<TILE_N, false>(map_a, map_b, p, sm_count, pdl, stream);
+  }
+  if (g_trace_host == nullptr) {
+    PNV_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&g_trace_host), kTraceWords * sizeof(unsigned),
+                           cudaHostAllocMapped));
+    PNV_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&g_trace_dev), g_trace_host, 0));
+  }
+  for (int i = 0; i < kTraceWords; ++i) g_trace_host[i] = 0;
+  p.trace = g_trace_dev;
+  return launch_impl<TILE_N, true>(map_a, map_b, p, sm_count, false, stream);
 }
 
 struct Kind { const char* name; bool two_sm; int tile_n; };
@@ -367,7 +489,6 @@ const Kind kKinds[] = {
     {"sparse_1sm_128x128", false, 128},  {"sparse_1sm_128x256", false, 256},
     {"sparse_2sm_256x64", true, 64},     {"sparse_1sm_128x64", false, 64},
     {"sparse_2sm_256x64_k512", true, 64}, {"sparse_1sm_128x64_k512", false, 64},
-    {"sparse_1sm_128x32", false, 32},
 };
 constexpr int kNumKinds = sizeof(kKinds) / sizeof(kKinds[0]);
 
@@ -388,6 +509,13 @@ extern "C" int pnv_group_mm_device_status(int* status_out) {
   PNV_CUDA(cudaMemcpyFromSymbol(status_out, g_status, sizeof(int)));
   int zero = 0;
   PNV_CUDA(cudaMemcpyToSymbol(g_status, &zero, sizeof(int)));
+  return PNV_OK;
+}
+
+extern "C" int pnv_group_mm_debug_trace(unsigned* words_out, int n_words) {
+  PNV_REQUIRE(words_out && n_words >= 0, "bad trace buffer");
+  for (int i = 0; i < n_words; ++i)
+    words_out[i] = (g_trace_host != nullptr && i < kTraceWords) ? ((volatile unsigned*)g_trace_host)[i] : 0u;
   return PNV_OK;
 }
 
@@ -441,7 +569,6 @@ extern "C" int pnv_group_mm(void* out, const uint8_t* a_comp, const uint8_t* e_m
   cudaStream_t s = (cudaStream_t)stream;
   const bool use_pdl = pdl != 0 && pdl_enabled();
   switch (kind.tile_n) {
-    case 32: return launch<32>(map_a, map_b, p, sm_count, use_pdl, s);
     case 64: return launch<64>(map_a, map_b, p, sm_count, use_pdl, s);
     case 128: return launch<128>(map_a, map_b, p, sm_count, use_pdl, s);
     default: return launch<256>(map_a, map_b, p, sm_count, use_pdl, s);

@@ -134,10 +134,8 @@ def fused_swiglu_tactics(max_cluster_product=16):
 
 def suggest_tactic(max_n):
     """A reasonable group_mm tactic for a per-expert token capacity of max_n, without autotuning:
-    the narrowest tile that covers max_n, up to 128 columns."""
+    64-column tiles when max_n fits one, the 128-column default otherwise."""
     names = group_mm_configs()
-    if max_n <= 32 and "sparse_1sm_128x32" in names:
-        return (names.index("sparse_1sm_128x32"), 1, 1)
     if max_n <= 64:
         return (names.index("sparse_1sm_128x64"), 1, 1)
     return DEFAULT_TACTIC

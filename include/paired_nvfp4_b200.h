@@ -44,6 +44,13 @@ const char* pnv_last_error(void);
  * (No counterpart in the reference, whose kernel waits without bound.) */
 int pnv_group_mm_device_status(int* status_out);
 
+/* Debugging aid: with the environment variable PNV_GROUP_MM_TRACE=1 group_mm runs a self-checking
+ * build of its kernel that issues every asynchronous operation alone, checks each copy's addresses
+ * before issuing it and leaves progress words in host-mapped memory; this call copies the first
+ * n_words of them out without touching the CUDA context, so it still works after a device fault.
+ * (No counterpart in the reference.) */
+int pnv_group_mm_debug_trace(unsigned* words_out, int n_words);
+
 /* ---- size queries ------------------------------------------------------------------------- */
 
 /* physical_dims(features, k, groups) (csrc/layout.cuh:83-91): a_comp is
