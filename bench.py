@@ -34,7 +34,7 @@ FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool, used only withou
 WORKLOADS = {
     # Mixtral-8x7B expert FFN, decode: per-expert counts uniform in [1, 16]
     "c2": dict(desc="decode Mixtral-8x7B-shaped expert FFN", E=8, hidden=4096, inter=14336, cap=16,
-               routing="counts", seed=1001, config_id=5, wstd=0.02),
+               routing="counts", seed=1001, config_id=7, wstd=0.02),
     # Qwen3-30B-A3B MoE, prefill: 16384 tokens, top-8 of 128, cap 2048
     "c3": dict(desc="prefill Qwen3-30B-A3B-shaped MoE", E=128, hidden=2048, inter=768, cap=2048,
                routing="topk", tokens=16384, topk=8, seed=1002, config_id=2, wstd=0.02),

@@ -1,18 +1,25 @@
 // group_mm: out[e, t, :] = bf16(alpha[e] * W[e] * x[e, t, :]) for t < counts[e], with W stored
 // paired-4:8 sparse NVFP4 (a_comp + e_meta + sfa) and x stored NVFP4 (b_act + sfb).
 //
-// One persistent kernel, one CTA per SM, three warp roles:
-//   warp 0 (one lane)  producer: per 256-K stage, two TMA tile loads (compressed weights with the
-//                      64-byte swizzle, activations with the 128-byte swizzle; one 3-D tensor map
-//                      each covers every expert) and three plain bulk copies (metadata atom, SFA
-//                      and SFB scale atoms, which are stored in global memory in exactly the shape
-//                      tcgen05.cp consumes, so they need no tensor map);
-//   warp 1 (one lane)  MMA issuer: tcgen05.cp of metadata and scales into tensor memory, then two
-//                      tcgen05.mma.sp block-scaled instructions (128 x TILE_N x 128 each) per
-//                      stage, accumulating in tensor memory; tcgen05.commit releases the stage and,
-//                      after the last stage of a tile, publishes the accumulator;
-//   warps 2-5          epilogue: tcgen05.ld the accumulator, scale by alpha[e], round to bf16 and
-//                      store the rows below the expert's token count.
+// One persistent kernel, one CTA per SM, four warp roles (6 + ISSUERS warps):
+//   warp 0 (one lane)  tile producer: per K stage, the TMA tile loads of the compressed weights and
+//                      of the activations (one 3-D tensor map each covers every expert; 128-byte
+//                      swizzle, or 64-byte swizzle for the weights of a 256-K stage);
+//   warp 1 (one lane)  side producer: plain bulk copies of the metadata atoms and of the SFA / SFB
+//                      scale atoms, which sit in global memory in exactly the shape tcgen05.cp
+//                      consumes and so need no tensor map;
+//   ISSUERS warps      MMA issuers (one lane each): issuer j owns a fixed slice of every stage's
+//   (one lane each)    128-K blocks.  It copies their metadata and scales into tensor memory
+//                      (tcgen05.cp), issues one tcgen05.mma.sp block-scaled instruction
+//                      (128 x TILE_N x 128) per block into its own partial accumulator, and commits:
+//                      to the stage's "empty" barrier, and after the tile's last stage to the
+//                      accumulator's "full" barrier.  One thread can only issue a tcgen05 op every
+//                      50-90 cycles and a commit costs it several hundred, so with narrow tiles a
+//                      single issuer, not memory, bounds the kernel; issuers in different warps
+//                      overlap.
+//   last 4 warps       epilogue: tcgen05.ld the partial accumulators 32 token columns at a time, add
+//                      them, scale by alpha[e], round to bf16, transpose through shared memory and
+//                      store 16 bytes per thread, 256 contiguous bytes per output row.
 // Accumulators are double buffered (single buffered for TILE_N = 256, which fills tensor memory),
 // so the epilogue of one tile overlaps the main loop of the next.
 //
@@ -25,6 +32,7 @@
 // leaves its loop and meets at the final barrier, where tensor memory is released.
 #include <cuda.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <mutex>
 
@@ -37,38 +45,63 @@ namespace {
 __device__ int g_status = 0;
 
 constexpr int kTileM = 128;
-constexpr int kStageK = 256;                 // dense K per pipeline stage (two MMA K-blocks)
-constexpr int kABytes = kTileM * 64;         // compressed weights: 64 bytes per row per stage
-constexpr int kEBytes = 2048;                // one metadata atom
-constexpr int kSfaBytes = 1024;              // two scale atoms
-constexpr int kThreads = 192;
+constexpr int kEpilogueThreads = 128;
 constexpr int kTmemCols = 512;
-constexpr int kColE = 448;                   // tensor-memory columns: metadata (4)
-constexpr int kColSfa = 456;                 //   weight scales (8)
-constexpr int kColSfb = 464;                 //   activation scales (8, or 16 for TILE_N = 256)
+constexpr int kColE = 448;                   // tensor-memory columns: metadata (up to 16)
+constexpr int kColSfa = 464;                 //   weight scales (4 per K-block)
+constexpr int kColSfb = 480;                 //   activation scales (4 or 8 per K-block)
+constexpr int kOutStageBytes = 2 * 32 * kTileM * 2;   // epilogue transpose buffers: 2 x [32][128] bf16
+constexpr int kMaxExperts = 2048;            // bounds the shared-memory copy of counts
+constexpr int kSmemLimit = 227 * 1024;
 
 enum Status : int {
-  kOk = 0, kProducerEmptyTimeout = 1, kMmaFullTimeout = 2, kMmaAccTimeout = 3, kEpilogueTimeout = 4
+  kOk = 0, kProducerEmptyTimeout = 1, kMmaFullTimeout = 2, kMmaAccTimeout = 3, kEpilogueTimeout = 4,
+  kSideProducerTimeout = 5
 };
 
-template <int TILE_N>
+template <int TILE_N, int STAGE_K, int ISSUERS>
 struct Cfg {
-  static constexpr int kBBytes = TILE_N * 128;
-  static constexpr int kSfbBytes = TILE_N > 128 ? 2048 : 1024;
+  static_assert(TILE_N == 16 || TILE_N == 32 || TILE_N == 64 || TILE_N == 128 || TILE_N == 256,
+                "tile widths: 16 and 32 (single token tile only), 64, 128, 256");
+  static_assert(ISSUERS == 1 || ISSUERS == 2 || ISSUERS == 4, "MMA issuer warps: 1, 2 or 4");
+  static constexpr int kThreads = (6 + ISSUERS) * 32;
+  static constexpr int kFirstEpilogueWarp = 2 + ISSUERS;
+  static_assert(STAGE_K == 256 || STAGE_K == 512, "stage depths: 256, 512");
+  static constexpr int kAtoms = STAGE_K / 128;            // MMA K-blocks per stage
+  static constexpr int kARowBytes = STAGE_K / 4;          // compressed weight bytes per row per stage
+  static constexpr int kABytes = kTileM * kARowBytes;
+  static constexpr uint32_t kASwizzle = STAGE_K == 512 ? 2 : 4;   // descriptor code: 128-B / 64-B swizzle
+  static constexpr int kBBoxes = STAGE_K / 256;           // 128-byte-wide activation boxes per stage
+  static constexpr int kBBoxBytes = TILE_N * 128;
+  static constexpr int kBBytes = kBBoxes * kBBoxBytes;
+  static constexpr int kEAtoms = STAGE_K / 256;
+  static constexpr int kEBytes = 2048 * kEAtoms;
+  static constexpr int kSfaBytes = 512 * kAtoms;
+  static constexpr int kSfbRowAtoms = TILE_N > 128 ? 2 : 1;
+  static constexpr int kSfbBytes = kSfaBytes * kSfbRowAtoms;
   static constexpr int kStageBytes = kABytes + kBBytes + kEBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kStages = TILE_N == 256 ? 4 : (TILE_N == 128 ? 7 : 10);
-  static_assert(TILE_N == 64 || TILE_N == 128 || TILE_N == 256, "tile widths: 64, 128, 256");
+  static constexpr int kFixedBytes = 1024 + kOutStageBytes + 256 + 4 * kMaxExperts;
+  static constexpr int kStages = (kSmemLimit - kFixedBytes) / kStageBytes;
   static constexpr int kAccStages = TILE_N == 256 ? 1 : 2;
+  static constexpr int kSfbColsPerAtom = 4 * kSfbRowAtoms;
+  static constexpr int kAtomsPerIssuer = kAtoms / ISSUERS;          // K-blocks of a stage per issuer
+  static constexpr int kEAtomsPerIssuer = kAtomsPerIssuer >= 2 ? kAtomsPerIssuer / 2 : 1;
+  static constexpr int kEColsPerIssuer = 4 * kEAtomsPerIssuer;      // private metadata columns
+  static_assert(kAtomsPerIssuer >= 1, "more issuers than K-blocks per stage");
   static constexpr int kOffA = 0;
   static constexpr int kOffB = kABytes;
   static constexpr int kOffE = kOffB + kBBytes;
   static constexpr int kOffSfa = kOffE + kEBytes;
   static constexpr int kOffSfb = kOffSfa + kSfaBytes;
   static_assert(kStageBytes % 1024 == 0, "stage buffers must keep 1024-byte alignment");
-  static_assert(kAccStages * TILE_N <= kColE, "accumulators overlap the metadata columns");
+  static_assert(kStages >= 2, "not enough shared memory for a pipeline");
+  static_assert(kAccStages * ISSUERS * TILE_N <= kColE, "accumulators overlap the metadata columns");
+  static_assert(kColE + kEColsPerIssuer * ISSUERS <= kColSfa && kColSfa + 4 * kAtoms <= kColSfb &&
+                kColSfb + kSfbColsPerAtom * kAtoms <= kTmemCols, "tensor-memory column map overflows");
 };
 
 struct Params {
+  const uint8_t* a_comp;   // only for L2 prefetch; the tiles themselves come through map_a
   const uint8_t* e_meta;
   const uint8_t* sfa;
   const uint8_t* sfb;
@@ -77,11 +110,18 @@ struct Params {
   __nv_bfloat16* out;
   int E, M, K, max_n;
   int n_mt;          // ceil(M / 128)
-  int k_stages;      // ceil(K / 256)
+  int k_stages;      // ceil(K / STAGE_K)
   int n_kt;          // scale K-atoms per row = MMA K-blocks = ceil(K / 128)
-  int e_k_atoms;     // metadata atoms along K = k_stages
+  int e_k_atoms;     // metadata atoms along K = ceil(K / 256)
   int e_m_atoms;     // metadata atoms along M = n_mt
   int sfb_rt;        // scale row-atoms per expert in sfb = ceil(max_n / 128)
+  int a_row_bytes;   // bytes per a_comp row
+  int prefetch;      // issue L2 prefetches of the next tile's weight rows
+  int stages;        // pipeline depth in use (<= Cfg::kStages)
+  int group;         // stages the tile producer fills concurrently (1 = one at a time)
+  int a_box_rows;    // rows per weight TMA box (128, or 32 when group > 1)
+  int skip;          // experiment knob (timing only, results invalid): 1 no B, 2 no E, 4 no SFA, 8 no SFB, 16 no cp, 32 no MMA
+  long long* prof;   // optional per-CTA cycle counters (8 per CTA): see PNV_GROUP_MM_PROFILE
   unsigned* trace;   // traced build only: host-mapped breadcrumb words, 16 per CTA (first 8 CTAs)
 };
 
@@ -113,10 +153,10 @@ struct TileWalk {
 // Traced build (kTrace): every asynchronous operation is issued alone and waited for, each step
 // leaves a breadcrumb in host-mapped memory (readable even after a fault killed the context), and
 // every copy's addresses and size are checked first; a failed check is recorded and the copy is
-// skipped.  Breadcrumb slots per CTA: 0 setup, 1 producer, 2 MMA issuer, 3 epilogue (warp 2),
-// 4 first failed check (code), 5..7 its operands.
+// skipped.  Breadcrumb slots per CTA: 0 setup, 1 tile producer, 2 MMA issuer, 3 epilogue,
+// 4 first failed check (code) with its operands in 5..7, 11 side producer.
 template <bool kTrace>
-__device__ __forceinline__ void crumb(const unsigned* /*unused*/, unsigned* trace, int slot, unsigned code) {
+__device__ __forceinline__ void crumb(unsigned* trace, int slot, unsigned code) {
   if (kTrace && trace != nullptr && blockIdx.x < 8) {
     volatile unsigned* t = trace + blockIdx.x * 16 + slot;
     *t = code;
@@ -136,22 +176,29 @@ __device__ __forceinline__ bool check_copy(unsigned* trace, unsigned code, uint3
   return false;
 }
 
-template <int TILE_N, bool kTrace>
-__global__ void __launch_bounds__(kThreads, 1)
+__device__ __forceinline__ void epilogue_bar_sync() {
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+template <int TILE_N, int STAGE_K, int ISSUERS, bool kTrace>
+__global__ void __launch_bounds__((6 + ISSUERS) * 32, 1)
 group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const Params p) {
-  using C = Cfg<TILE_N>;
+  using C = Cfg<TILE_N, STAGE_K, ISSUERS>;
+  constexpr int kThreads = C::kThreads;
+  constexpr int kFirstEpilogueWarp = C::kFirstEpilogueWarp;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_base = smem;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  __nv_bfloat16* s_out = reinterpret_cast<__nv_bfloat16*>(smem + C::kStages * C::kStageBytes);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes + kOutStageBytes);
   uint64_t* empty_bar = full_bar + C::kStages;
   uint64_t* acc_full = empty_bar + C::kStages;
   uint64_t* acc_empty = acc_full + C::kAccStages;
-  uint64_t* dbg_bar = acc_empty + C::kAccStages;     // two extra barriers, used by the traced build
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dbg_bar + 2);
-  int* s_counts = reinterpret_cast<int*>(tmem_slot + 4);
-#define CRUMB(slot, code) crumb<kTrace>(nullptr, p.trace, slot, code)
+  uint64_t* dbg_bar = acc_empty + C::kAccStages;     // 2 + ISSUERS extra barriers, used by the traced build
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dbg_bar + 2 + ISSUERS);
+  int* s_counts = reinterpret_cast<int*>(smem + C::kStages * C::kStageBytes + kOutStageBytes + 256);
+#define CRUMB(slot, code) crumb<kTrace>(p.trace, slot, code)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -160,17 +207,18 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&map_a);
     ptx::prefetch_tensormap(&map_b);
-    for (int s = 0; s < C::kStages; ++s) { ptx::mbar_init(full_bar + s, 1); ptx::mbar_init(empty_bar + s, 1); }
-    for (int a = 0; a < C::kAccStages; ++a) { ptx::mbar_init(acc_full + a, 1); ptx::mbar_init(acc_empty + a, 128); }
-    ptx::mbar_init(dbg_bar, 1);
-    ptx::mbar_init(dbg_bar + 1, 1);
+    for (int s = 0; s < C::kStages; ++s) { ptx::mbar_init(full_bar + s, 2); ptx::mbar_init(empty_bar + s, ISSUERS); }
+    for (int a = 0; a < C::kAccStages; ++a) {
+      ptx::mbar_init(acc_full + a, ISSUERS);
+      ptx::mbar_init(acc_empty + a, kEpilogueThreads);
+    }
+    for (int d = 0; d < 2 + ISSUERS; ++d) ptx::mbar_init(dbg_bar + d, 1);
     ptx::fence_mbar_init();
     CRUMB(0, 1);
   }
-  if (warp == 1) {
+  if (warp == 2) {
     ptx::tmem_alloc(tmem_slot, kTmemCols);
     ptx::tmem_relinquish();
-    if (lane == 0) CRUMB(0, 2);
   }
   // counts (and everything else the producer kernels wrote) may only be read after this point
   pdl_wait();
@@ -180,53 +228,100 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) { CRUMB(0, 3); CRUMB(8, tmem_base); CRUMB(9, ptx::smem_u32(smem)); CRUMB(10, ptx::smem_u32(full_bar)); }
+  if (threadIdx.x == 0) { CRUMB(0, 3); CRUMB(8, tmem_base); CRUMB(9, ptx::smem_u32(smem)); }
 
   TileWalk walk;
   walk.init<TILE_N>(s_counts, p.E, p.n_mt);
 
   if (warp == 0) {
-    // =============================== producer ===============================
-    if (lane == 0) {
+    // =============================== tile producer (TMA) ===============================
+    // All 32 lanes walk the tile list.  Before lane 0 issues a tile's loads, every lane asks L2 to
+    // fetch four whole weight rows of the CTA's *next* tile: each row is one contiguous run of
+    // K/4 bytes, so DRAM sees long bursts, and the 128-byte-wide TMA box rows that follow one
+    // tile later hit L2 instead of opening a DRAM page for 128 bytes at a time.
+    TileWalk ahead = walk;
+    auto prefetch_tile = [&](long long t) {
+      int pmt, pnt;
+      if (!p.prefetch || !ahead.seek<TILE_N>(t, pmt, pnt)) return;
+      if (pnt != 0) return;   // the rows of later token tiles were fetched with the first one
+      const uint8_t* rows = p.a_comp + ((long long)ahead.e * p.M + (long long)pmt * kTileM) * p.a_row_bytes;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = lane + 32 * j;
+        if (pmt * kTileM + r < p.M) ptx::prefetch_l2(rows + (long long)r * p.a_row_bytes, p.a_row_bytes);
+      }
+    };
+    prefetch_tile(blockIdx.x);
+    {
       int stage = 0;
-      uint32_t phase = 0;
-      uint32_t dbg_phase = 0;
-      (void)dbg_phase;
+      uint32_t phase = 0, dphase = 0;
+      (void)dphase;
       bool ok = true;
-      for (long long t = blockIdx.x; ok; t += gridDim.x) {
+      for (long long t = blockIdx.x;; t += gridDim.x) {
+        // lane 0 owns the pipeline state; the other lanes follow its verdict and idle at the shuffle
+        if (__shfl_sync(0xffffffffu, ok ? 1 : 0, 0) == 0) break;
         int mt, nt;
         if (!walk.seek<TILE_N>(t, mt, nt)) break;
+        prefetch_tile(t + gridDim.x);
+        if (lane != 0) continue;
         const int e = walk.e;
-        const long long e_atom0 = ((long long)e * p.e_k_atoms) * p.e_m_atoms + mt;
-        const long long sfa_atom0 = ((long long)e * p.n_mt + mt) * p.n_kt;
         const int n0 = nt * TILE_N;
-        const long long sfb_atom0 = ((long long)e * p.sfb_rt + (n0 >> 7)) * p.n_kt;
-        const int sfb_row_atoms = TILE_N > 128 ? min(2, p.sfb_rt - (n0 >> 7)) : 1;
+        if (!kTrace && p.group > 1) {
+          // Group fill: claim up to `group` stages, then issue the weight boxes row-group-major
+          // (32 rows at a time, all claimed stages for those rows back to back), so that the
+          // consecutive 128-byte pieces of a weight row are requested together.
+          for (int ks0 = 0; ks0 < p.k_stages && ok; ks0 += p.group) {
+            const int gn = min(p.group, p.k_stages - ks0);
+            int s = stage;
+            uint32_t ph = phase;
+            for (int g = 0; g < gn; ++g) {
+              if (!ptx::mbar_wait(empty_bar + s, ph ^ 1)) {
+                atomicExch(&g_status, kProducerEmptyTimeout);
+                ok = false;
+                break;
+              }
+              const int k_atoms = min(C::kAtoms, p.n_kt - (ks0 + g) * C::kAtoms);
+              const int b_boxes = (k_atoms + 1) / 2;
+              uint8_t* st = stage_base + s * C::kStageBytes;
+              ptx::mbar_arrive_expect_tx(full_bar + s, C::kABytes + b_boxes * C::kBBoxBytes);
+              for (int b = 0; b < b_boxes; ++b)
+                ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + s,
+                                 (ks0 + g) * (STAGE_K / 2) + b * 128, n0, e);
+              if (++s == p.stages) { s = 0; ph ^= 1; }
+            }
+            if (!ok) break;
+            for (int rg = 0; rg < kTileM / 32; ++rg) {
+              int s2 = stage;
+              for (int g = 0; g < gn; ++g) {
+                ptx::tma_load_3d(stage_base + s2 * C::kStageBytes + C::kOffA + rg * 32 * C::kARowBytes, &map_a,
+                                 full_bar + s2, (ks0 + g) * C::kARowBytes, mt * kTileM + rg * 32, e);
+                if (++s2 == p.stages) s2 = 0;
+              }
+            }
+            stage = s;
+            phase = ph;
+          }
+          continue;
+        }
         for (int ks = 0; ks < p.k_stages; ++ks) {
+          long long tq0 = p.prof ? clock64() : 0;
           if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1)) {
             atomicExch(&g_status, kProducerEmptyTimeout);
             ok = false;
             break;
           }
+          if (p.prof) p.prof[blockIdx.x * 8 + 4] += clock64() - tq0;
           uint8_t* st = stage_base + stage * C::kStageBytes;
-          const int k_atoms = min(2, p.n_kt - 2 * ks);         // MMA K-blocks present in this stage
-          const uint32_t sf_bytes = 512u * k_atoms;
-          const uint32_t tx = kABytes + C::kBBytes + kEBytes + sf_bytes * (1 + sfb_row_atoms);
-          const uint8_t* e_src = p.e_meta + (e_atom0 + (long long)ks * p.e_m_atoms) * 2048;
-          const uint8_t* sfa_src = p.sfa + (sfa_atom0 + 2 * ks) * 512;
+          const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
+          const int b_boxes = (k_atoms + 1) / 2;
           if (!kTrace) {
-            ptx::mbar_arrive_expect_tx(full_bar + stage, tx);
-            ptx::tma_load_3d(st + C::kOffA, &map_a, full_bar + stage, ks * 64, mt * kTileM, e);
-            ptx::tma_load_3d(st + C::kOffB, &map_b, full_bar + stage, ks * 128, n0, e);
-            ptx::bulk_load(st + C::kOffE, e_src, kEBytes, full_bar + stage);
-            ptx::bulk_load(st + C::kOffSfa, sfa_src, sf_bytes, full_bar + stage);
-            for (int ra = 0; ra < sfb_row_atoms; ++ra)
-              ptx::bulk_load(st + C::kOffSfb + ra * 1024,
-                             p.sfb + (sfb_atom0 + (long long)ra * p.n_kt + 2 * ks) * 512, sf_bytes,
-                             full_bar + stage);
+            const int bb = (p.skip & 1) ? 0 : b_boxes;
+            ptx::mbar_arrive_expect_tx(full_bar + stage, C::kABytes + bb * C::kBBoxBytes);
+            ptx::tma_load_3d(st + C::kOffA, &map_a, full_bar + stage, ks * C::kARowBytes, mt * kTileM, e);
+            for (int b = 0; b < bb; ++b)
+              ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + stage,
+                               ks * (STAGE_K / 2) + b * 128, n0, e);
           } else {
-            // one copy at a time on a private barrier, then a plain arrive publishes the stage
-            uint32_t dphase = dbg_phase;
             auto one = [&](unsigned code, uint32_t bytes, auto issue) {
               CRUMB(1, code);
               ptx::mbar_arrive_expect_tx(dbg_bar, bytes);
@@ -235,111 +330,216 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               dphase ^= 1;
               CRUMB(1, code + (done ? 1 : 2));
             };
-            if (check_copy<kTrace>(p.trace, 100, ptx::smem_u32(st + C::kOffA), 0, kABytes, 1024))
-              one(110, kABytes, [&] { ptx::tma_load_3d(st + C::kOffA, &map_a, dbg_bar, ks * 64, mt * kTileM, e); });
-            if (check_copy<kTrace>(p.trace, 101, ptx::smem_u32(st + C::kOffB), 0, C::kBBytes, 1024))
-              one(120, C::kBBytes, [&] { ptx::tma_load_3d(st + C::kOffB, &map_b, dbg_bar, ks * 128, n0, e); });
-            if (check_copy<kTrace>(p.trace, 102, ptx::smem_u32(st + C::kOffE), (uint64_t)e_src, kEBytes, 16))
-              one(130, kEBytes, [&] { ptx::bulk_load(st + C::kOffE, e_src, kEBytes, dbg_bar); });
-            if (check_copy<kTrace>(p.trace, 103, ptx::smem_u32(st + C::kOffSfa), (uint64_t)sfa_src, sf_bytes, 16))
-              one(140, sf_bytes, [&] { ptx::bulk_load(st + C::kOffSfa, sfa_src, sf_bytes, dbg_bar); });
-            for (int ra = 0; ra < sfb_row_atoms; ++ra) {
-              const uint8_t* sfb_src = p.sfb + (sfb_atom0 + (long long)ra * p.n_kt + 2 * ks) * 512;
-              if (check_copy<kTrace>(p.trace, 104, ptx::smem_u32(st + C::kOffSfb + ra * 1024), (uint64_t)sfb_src,
-                                     sf_bytes, 16))
-                one(150, sf_bytes, [&] { ptx::bulk_load(st + C::kOffSfb + ra * 1024, sfb_src, sf_bytes, dbg_bar); });
-            }
-            dbg_phase = dphase;
+            if (check_copy<kTrace>(p.trace, 100, ptx::smem_u32(st + C::kOffA), 0, C::kABytes, 1024))
+              one(110, C::kABytes, [&] {
+                ptx::tma_load_3d(st + C::kOffA, &map_a, dbg_bar, ks * C::kARowBytes, mt * kTileM, e);
+              });
+            for (int b = 0; b < b_boxes; ++b)
+              if (check_copy<kTrace>(p.trace, 101, ptx::smem_u32(st + C::kOffB + b * C::kBBoxBytes), 0,
+                                     C::kBBoxBytes, 1024))
+                one(120, C::kBBoxBytes, [&] {
+                  ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, dbg_bar,
+                                   ks * (STAGE_K / 2) + b * 128, n0, e);
+                });
             ptx::mbar_arrive(full_bar + stage);
             CRUMB(1, 160);
           }
-          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
       }
-      if (!ok) {
+      if (!ok && lane == 0) {
         // give copies already in flight time to land before the CTA's shared memory is released
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    // =============================== MMA issuer ===============================
+    // =============================== side producer (bulk copies) ===============================
     if (lane == 0) {
-      constexpr uint32_t idesc = ptx::mma_sp_nvf4_idesc(TILE_N);
-      int stage = 0, acc = 0;
-      uint32_t phase = 0, acc_phase = 0, mma_dbg_phase = 0;
-      (void)mma_dbg_phase;
+      int stage = 0;
+      uint32_t phase = 0, dphase = 0;
+      (void)dphase;
       bool ok = true;
       for (long long t = blockIdx.x; ok; t += gridDim.x) {
         int mt, nt;
         if (!walk.seek<TILE_N>(t, mt, nt)) break;
+        const int e = walk.e;
+        const int n0 = nt * TILE_N;
+        const uint8_t* e_base = p.e_meta + (((long long)e * p.e_k_atoms) * p.e_m_atoms + mt) * 2048;
+        const uint8_t* sfa_base = p.sfa + (((long long)e * p.n_mt + mt) * p.n_kt) * 512;
+        const uint8_t* sfb_base = p.sfb + (((long long)e * p.sfb_rt + (n0 >> 7)) * p.n_kt) * 512;
+        const int sfb_row_atoms = TILE_N > 128 ? min(2, p.sfb_rt - (n0 >> 7)) : 1;
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1)) {
+            atomicExch(&g_status, kSideProducerTimeout);
+            ok = false;
+            break;
+          }
+          uint8_t* st = stage_base + stage * C::kStageBytes;
+          const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
+          const int e_atoms = (k_atoms + 1) / 2;
+          const uint32_t sf_bytes = 512u * k_atoms;
+          const uint8_t* sfa_src = sfa_base + (long long)ks * C::kAtoms * 512;
+          if (!kTrace) {
+            const int ne = (p.skip & 2) ? 0 : e_atoms;
+            const int nsa = (p.skip & 4) ? 0 : 1;
+            const int nsb = (p.skip & 8) ? 0 : sfb_row_atoms;
+            ptx::mbar_arrive_expect_tx(full_bar + stage, ne * 2048 + sf_bytes * (nsa + nsb));
+            for (int ea = 0; ea < ne; ++ea)
+              ptx::bulk_load(st + C::kOffE + ea * 2048,
+                             e_base + (long long)(ks * C::kEAtoms + ea) * p.e_m_atoms * 2048, 2048,
+                             full_bar + stage);
+            if (nsa) ptx::bulk_load(st + C::kOffSfa, sfa_src, sf_bytes, full_bar + stage);
+            for (int ra = 0; ra < nsb; ++ra)
+              ptx::bulk_load(st + C::kOffSfb + ra * C::kSfaBytes,
+                             sfb_base + ((long long)ra * p.n_kt + ks * C::kAtoms) * 512, sf_bytes,
+                             full_bar + stage);
+          } else {
+            auto one = [&](unsigned code, uint32_t bytes, auto issue) {
+              CRUMB(11, code);
+              ptx::mbar_arrive_expect_tx(dbg_bar + 1, bytes);
+              issue();
+              bool done = ptx::mbar_wait(dbg_bar + 1, dphase);
+              dphase ^= 1;
+              CRUMB(11, code + (done ? 1 : 2));
+            };
+            for (int ea = 0; ea < e_atoms; ++ea) {
+              const uint8_t* src = e_base + (long long)(ks * C::kEAtoms + ea) * p.e_m_atoms * 2048;
+              if (check_copy<kTrace>(p.trace, 102, ptx::smem_u32(st + C::kOffE + ea * 2048), (uint64_t)src, 2048, 16))
+                one(130, 2048, [&] { ptx::bulk_load(st + C::kOffE + ea * 2048, src, 2048, dbg_bar + 1); });
+            }
+            if (check_copy<kTrace>(p.trace, 103, ptx::smem_u32(st + C::kOffSfa), (uint64_t)sfa_src, sf_bytes, 16))
+              one(140, sf_bytes, [&] { ptx::bulk_load(st + C::kOffSfa, sfa_src, sf_bytes, dbg_bar + 1); });
+            for (int ra = 0; ra < sfb_row_atoms; ++ra) {
+              const uint8_t* src = sfb_base + ((long long)ra * p.n_kt + ks * C::kAtoms) * 512;
+              if (check_copy<kTrace>(p.trace, 104, ptx::smem_u32(st + C::kOffSfb + ra * C::kSfaBytes),
+                                     (uint64_t)src, sf_bytes, 16))
+                one(150, sf_bytes, [&] {
+                  ptx::bulk_load(st + C::kOffSfb + ra * C::kSfaBytes, src, sf_bytes, dbg_bar + 1);
+                });
+            }
+            ptx::mbar_arrive(full_bar + stage);
+            CRUMB(11, 160);
+          }
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+      }
+    }
+    __syncwarp();
+  } else if (warp < 2 + ISSUERS) {
+    // =============================== MMA issuers ===============================
+    if (lane == 0) {
+      const int issuer = warp - 2;
+      constexpr int kPer = C::kAtomsPerIssuer;
+      const int ka0 = issuer * kPer;               // this issuer's K-blocks of a stage: [ka0, ka0 + kPer)
+      constexpr uint32_t idesc = ptx::mma_sp_nvf4_idesc(TILE_N);
+      const uint32_t e_cols = tmem_base + kColE + issuer * C::kEColsPerIssuer;
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0, dphase = 0;
+      (void)dphase;
+      bool ok = true;
+      long long c_wait_full = 0, c_issue = 0, c_wait_acc = 0, n_stage = 0;
+      const bool prof = p.prof != nullptr && issuer == 0;
+      for (long long t = blockIdx.x; ok; t += gridDim.x) {
+        int mt, nt;
+        if (!walk.seek<TILE_N>(t, mt, nt)) break;
+        long long tp0 = prof ? clock64() : 0;
         if (!ptx::mbar_wait(acc_empty + acc, acc_phase ^ 1)) {
           atomicExch(&g_status, kMmaAccTimeout);
           break;
         }
         ptx::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * TILE_N;
+        if (prof) c_wait_acc += clock64() - tp0;
+        const uint32_t d_tmem = tmem_base + (acc * ISSUERS + issuer) * TILE_N;
         // The scales of a 64-wide tile's rows sit 0 or 2 columns into the 128-row atom.  The MMA
-        // faults (misaligned address) on an odd column offset, which is why there is no 32-wide tile.
+        // faults (misaligned address) on an odd column offset, which is why 16- and 32-wide tiles
+        // exist only for problems with a single token tile (offset 0).
         const uint32_t sfb_col = tmem_base + kColSfb + (TILE_N < 128 ? ((nt * TILE_N) & 127) >> 5 : 0);
         for (int ks = 0; ks < p.k_stages; ++ks) {
+          long long tp1 = prof ? clock64() : 0;
           if (!ptx::mbar_wait(full_bar + stage, phase)) {
             atomicExch(&g_status, kMmaFullTimeout);
             ok = false;
             break;
           }
           ptx::tc_fence_after();
+          long long tp2 = prof ? clock64() : 0;
+          if (prof) { c_wait_full += tp2 - tp1; ++n_stage; }
           const uint32_t st = ptx::smem_u32(stage_base + stage * C::kStageBytes);
-          const int k_atoms = min(2, p.n_kt - 2 * ks);
+          const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
           auto settle = [&](unsigned code) {   // traced build: wait until the operation just issued retires
             if (kTrace) {
               CRUMB(2, code);
-              ptx::tc_commit(dbg_bar + 1);
-              bool done = ptx::mbar_wait(dbg_bar + 1, mma_dbg_phase);
-              mma_dbg_phase ^= 1;
+              ptx::tc_commit(dbg_bar + 2 + issuer);
+              bool done = ptx::mbar_wait(dbg_bar + 2 + issuer, dphase);
+              dphase ^= 1;
               CRUMB(2, code + (done ? 1 : 2));
             }
           };
-          if (kTrace) CRUMB(2, 200);
-          ptx::tc_cp_128x128b(tmem_base + kColE, ptx::smem_desc(st + C::kOffE, 128, 0, 0));
-          settle(210);
-          for (int ka = 0; ka < k_atoms; ++ka) {
-            ptx::tc_cp_32x128b_warpx4(tmem_base + kColSfa + ka * 4,
-                                      ptx::smem_desc(st + C::kOffSfa + ka * 512, 128, 0, 0));
-            if (TILE_N > 128) {
-              ptx::tc_cp_32x128b_warpx4(tmem_base + kColSfb + ka * 8,
-                                        ptx::smem_desc(st + C::kOffSfb + ka * 512, 128, 0, 0));
-              ptx::tc_cp_32x128b_warpx4(tmem_base + kColSfb + ka * 8 + 4,
-                                        ptx::smem_desc(st + C::kOffSfb + 1024 + ka * 512, 128, 0, 0));
-            } else {
-              ptx::tc_cp_32x128b_warpx4(tmem_base + kColSfb + ka * 4,
-                                        ptx::smem_desc(st + C::kOffSfb + ka * 512, 128, 0, 0));
+          if (ka0 < k_atoms && !(p.skip & 16)) {
+            // metadata atoms covering this issuer's K-blocks, into its private columns
+#pragma unroll
+            for (int i = 0; i < C::kEAtomsPerIssuer; ++i) {
+              const int ea = ka0 / 2 + i;
+              if (2 * ea < k_atoms)
+                ptx::tc_cp_128x128b(e_cols + i * 4, ptx::smem_desc(st + C::kOffE + ea * 2048, 128, 0, 0));
             }
-            settle(220 + 10 * ka);
           }
-          for (int ka = 0; ka < k_atoms; ++ka) {
-            const uint64_t a_desc = ptx::smem_desc(st + C::kOffA + ka * 32, 512, 16, 4);
-            const uint64_t b_desc = ptx::smem_desc(st + C::kOffB + ka * 64, 1024, 16, 2);
-            ptx::tc_mma_sp_nvf4(d_tmem, a_desc, b_desc, idesc, (ks | ka) != 0 ? 1u : 0u,
-                                tmem_base + kColSfa + ka * 4,
-                                sfb_col + ka * (TILE_N > 128 ? 8 : 4), tmem_base + kColE + ka * 2);
-            settle(240 + 10 * ka);
+          settle(210);
+#pragma unroll
+          for (int i = 0; i < kPer; ++i) {
+            const int ka = ka0 + i;
+            if (ka < k_atoms && !(p.skip & 16)) {
+              ptx::tc_cp_32x128b_warpx4(tmem_base + kColSfa + ka * 4,
+                                        ptx::smem_desc(st + C::kOffSfa + ka * 512, 128, 0, 0));
+#pragma unroll
+              for (int ra = 0; ra < C::kSfbRowAtoms; ++ra)
+                ptx::tc_cp_32x128b_warpx4(
+                    tmem_base + kColSfb + ka * C::kSfbColsPerAtom + ra * 4,
+                    ptx::smem_desc(st + C::kOffSfb + ra * C::kSfaBytes + ka * 512, 128, 0, 0));
+            }
           }
-          ptx::tc_commit(empty_bar + stage);   // stage reusable once these MMAs and copies retire
-          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+          settle(220);
+#pragma unroll
+          for (int i = 0; i < kPer; ++i) {
+            const int ka = ka0 + i;
+            if (ka < k_atoms && !(p.skip & 32)) {
+              const uint64_t a_desc = ptx::smem_desc(st + C::kOffA + ka * 32, 8 * C::kARowBytes, 16, C::kASwizzle);
+              const uint64_t b_desc =
+                  ptx::smem_desc(st + C::kOffB + (ka >> 1) * C::kBBoxBytes + (ka & 1) * 64, 1024, 16, 2);
+              // metadata columns: 2 per K-block inside the atom that holds it
+              const uint32_t e_tmem = e_cols + (kPer >= 2 ? i * 2 : (ka & 1) * 2);
+              ptx::tc_mma_sp_nvf4(d_tmem, a_desc, b_desc, idesc, (ks | i) != 0 ? 1u : 0u,
+                                  tmem_base + kColSfa + ka * 4, sfb_col + ka * C::kSfbColsPerAtom, e_tmem);
+              settle(240 + 10 * i);
+            }
+          }
+          ptx::tc_commit(empty_bar + stage);   // stage reusable once every issuer's MMAs and copies retire
+          if (prof) c_issue += clock64() - tp2;
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        ptx::tc_commit(acc_full + acc);        // accumulator complete
+        ptx::tc_commit(acc_full + acc);        // this issuer's partial accumulator is complete
         if (kTrace) CRUMB(2, 290);
         if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
+      }
+      if (prof) {
+        long long* q = p.prof + blockIdx.x * 8;
+        q[0] = c_wait_full; q[1] = c_issue; q[2] = c_wait_acc; q[3] = n_stage;
       }
     }
     __syncwarp();
   } else {
     // =============================== epilogue ===============================
     const int sub = warp & 3;                  // tensor-memory lane quarter this warp may read
+    const int ep_tid = threadIdx.x - kFirstEpilogueWarp * 32;
+    const int m_local = sub * 32 + lane;       // accumulator row (output feature) held by this thread
+    const bool vec_ok = (p.M % 8) == 0;        // 16-byte stores need 16-byte aligned output rows
     int acc = 0;
-    uint32_t acc_phase = 0;
+    uint32_t acc_phase = 0, chunk = 0;
     for (long long t = blockIdx.x;; t += gridDim.x) {
       int mt, nt;
       if (!walk.seek<TILE_N>(t, mt, nt)) break;
@@ -350,28 +550,60 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         break;
       }
       ptx::tc_fence_after();
-      if (kTrace && threadIdx.x == 64) CRUMB(3, 300);
+      if (kTrace && ep_tid == 0) CRUMB(3, 300);
       const float alpha = p.alphas[e];
-      const int m = mt * kTileM + sub * 32 + lane;
       const int n0 = nt * TILE_N;
       __nv_bfloat16* out_e = p.out + (long long)e * p.max_n * p.M;
 #pragma unroll 1
+      // issuers whose K-blocks exist for this K (a short K leaves the later issuers idle)
+      const int live = min(ISSUERS, ceil_div_i(min(C::kAtoms, p.n_kt), C::kAtomsPerIssuer));
       for (int c0 = 0; c0 < TILE_N; c0 += 32) {
-        if (n0 + c0 >= cnt) break;             // warp-uniform
+        if (n0 + c0 >= cnt) break;             // uniform over the four epilogue warps
         uint32_t r[32];
-        ptx::tc_ld_32x32(tmem_base + ((uint32_t)(sub * 32) << 16) + acc * TILE_N + c0, r);
+        const uint32_t lane_base = tmem_base + ((uint32_t)(sub * 32) << 16) + c0;
+        ptx::tc_ld_32x32(lane_base + (acc * ISSUERS) * TILE_N, r);
         ptx::tc_ld_wait();
-        if (kTrace && threadIdx.x == 64) CRUMB(3, 310);
-        if (m < p.M) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int n = n0 + c0 + i;
-            if (n < cnt)
-              out_e[(long long)n * p.M + m] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(r[i])));
+        for (int j = 1; j < ISSUERS; ++j) {
+          if (j < live) {                      // add the other issuers' partial sums
+            uint32_t q[32];
+            ptx::tc_ld_32x32(lane_base + (acc * ISSUERS + j) * TILE_N, q);
+            ptx::tc_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__fadd_rn(__uint_as_float(r[i]), __uint_as_float(q[i])));
+          }
+        }
+        if (vec_ok) {
+          // [token column][feature] tile: 32 rows of 128 bf16; lanes write consecutive features
+          __nv_bfloat16* buf = s_out + (chunk & 1) * (32 * kTileM);
+#pragma unroll
+          for (int i = 0; i < (TILE_N < 32 ? TILE_N : 32); ++i)
+            buf[i * kTileM + m_local] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(r[i])));
+          epilogue_bar_sync();
+          const int col = (ep_tid & 15) * 8;
+          const int m = mt * kTileM + col;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int row = (ep_tid >> 4) + 8 * j;
+            const int n = n0 + c0 + row;
+            if (n < cnt && m < p.M)
+              *reinterpret_cast<uint4*>(out_e + (long long)n * p.M + m) =
+                  *reinterpret_cast<const uint4*>(buf + row * kTileM + col);
+          }
+          ++chunk;
+        } else {
+          const int m = mt * kTileM + m_local;
+          if (m < p.M) {
+#pragma unroll
+            for (int i = 0; i < (TILE_N < 32 ? TILE_N : 32); ++i) {
+              const int n = n0 + c0 + i;
+              if (n < cnt)
+                out_e[(long long)n * p.M + m] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(r[i])));
+            }
           }
         }
       }
-      if (kTrace && threadIdx.x == 64) CRUMB(3, 320);
+      if (kTrace && ep_tid == 0) CRUMB(3, 320);
       ptx::tc_fence_before();
       ptx::mbar_arrive(acc_empty + acc);
       if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
@@ -380,7 +612,7 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   ptx::tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 2) {
     __syncwarp();
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
@@ -432,6 +664,34 @@ constexpr int kTraceWords = 8 * 16;
 unsigned* g_trace_host = nullptr;   // host view
 unsigned* g_trace_dev = nullptr;    // device view of the same pages
 
+// PNV_GROUP_MM_PREFETCH=1 turns the L2 prefetch of weight rows on (off by default: it measured slower).
+bool prefetch_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* env = std::getenv("PNV_GROUP_MM_PREFETCH");
+    v = (env != nullptr && env[0] == '1') ? 1 : 0;
+  }
+  return v == 1;
+}
+
+// PNV_GROUP_MM_PROFILE=1: the MMA issuer and the tile producer of every CTA accumulate cycle
+// counters (waiting for data, issuing, waiting for an accumulator, stages; waiting for a free
+// stage) in a device buffer that pnv_group_mm_profile() reads back.  A measuring aid only.
+long long* g_prof_dev = nullptr;
+long long* profile_buffer() {
+  static int v = -1;
+  if (v < 0) {
+    const char* env = std::getenv("PNV_GROUP_MM_PROFILE");
+    v = (env != nullptr && env[0] == '1') ? 1 : 0;
+  }
+  if (v != 1) return nullptr;
+  if (g_prof_dev == nullptr) {
+    if (cudaMalloc(reinterpret_cast<void**>(&g_prof_dev), 256 * 8 * sizeof(long long)) != cudaSuccess) return nullptr;
+  }
+  cudaMemset(g_prof_dev, 0, 256 * 8 * sizeof(long long));
+  return g_prof_dev;
+}
+
 bool trace_enabled() {
   static int v = -1;
   if (v < 0) {
@@ -441,37 +701,42 @@ bool trace_enabled() {
   return v == 1;
 }
 
-template <int TILE_N, bool kTrace>
-int launch_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p, int sm_count, bool pdl,
+template <int TILE_N, int STAGE_K, int ISSUERS, bool kTrace>
+int launch_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p_in, int sm_count, bool pdl,
                 cudaStream_t stream) {
-  using C = Cfg<TILE_N>;
-  const size_t smem = 1024 + (size_t)C::kStages * C::kStageBytes + 8 * (2 * C::kStages + 2 * C::kAccStages + 2) +
-                      16 + 4 * (size_t)p.E;
-  PNV_REQUIRE(smem <= 227 * 1024, "group_mm: %d experts need %zu bytes of shared memory (limit 232448)", p.E,
-              smem);
+  using C = Cfg<TILE_N, STAGE_K, ISSUERS>;
+  Params p = p_in;
+  p.stages = C::kStages;
+  if (const char* env = std::getenv("PNV_GROUP_MM_STAGES")) {   // experiment knob: shallower pipeline
+    int v = std::atoi(env);
+    if (v >= 1 && v < C::kStages) p.stages = v;
+  }
+  if (p.group > p.stages - 1) p.group = p.stages > 1 ? p.stages - 1 : 1;
+  const size_t smem = 1024 + (size_t)C::kStages * C::kStageBytes + kOutStageBytes + 256 + 4 * (size_t)p.E;
+  static_assert(8 * (2 * C::kStages + 2 * C::kAccStages + 2 + ISSUERS) + 16 <= 256, "barrier block overflows its slot");
   // opt in to the large dynamic shared-memory carve-out once per device
   static bool opted_in[64] = {};
   int dev = 0;
   PNV_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64 || !opted_in[dev]) {
-    PNV_CUDA(cudaFuncSetAttribute(group_mm_kernel<TILE_N, kTrace>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  227 * 1024));
+    PNV_CUDA(cudaFuncSetAttribute(group_mm_kernel<TILE_N, STAGE_K, ISSUERS, kTrace>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     if (dev >= 0 && dev < 64) opted_in[dev] = true;
   }
   long long max_tiles = (long long)p.E * p.n_mt * ceil_div_i(p.max_n, TILE_N);
   int grid = (int)(max_tiles < sm_count ? max_tiles : sm_count);
   if (grid < 1) grid = 1;
-  PNV_CUDA(launch_pdl(group_mm_kernel<TILE_N, kTrace>, dim3(grid), dim3(kThreads), smem, stream, pdl, map_a,
-                      map_b, p));
+  PNV_CUDA(launch_pdl(group_mm_kernel<TILE_N, STAGE_K, ISSUERS, kTrace>, dim3(grid), dim3(C::kThreads), smem,
+                      stream, pdl, map_a, map_b, p));
   return PNV_OK;
 }
 
-template <int TILE_N>
+template <int TILE_N, int STAGE_K, int ISSUERS>
 int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, Params& p, int sm_count, bool pdl,
            cudaStream_t stream) {
   if (!trace_enabled()) {
     p.trace = nullptr;
-    return launch_impl<TILE_N, false>(map_a, map_b, p, sm_count, pdl, stream);
+    return launch_impl<TILE_N, STAGE_K, ISSUERS, false>(map_a, map_b, p, sm_count, pdl, stream);
   }
   if (g_trace_host == nullptr) {
     PNV_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&g_trace_host), kTraceWords * sizeof(unsigned),
@@ -480,15 +745,19 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, Params& p, int sm
   }
   for (int i = 0; i < kTraceWords; ++i) g_trace_host[i] = 0;
   p.trace = g_trace_dev;
-  return launch_impl<TILE_N, true>(map_a, map_b, p, sm_count, false, stream);
+  return launch_impl<TILE_N, STAGE_K, ISSUERS, true>(map_a, map_b, p, sm_count, false, stream);
 }
 
-struct Kind { const char* name; bool two_sm; int tile_n; };
+// Tile variants.  The first eight names and ids are the reference's; a "2sm" name is accepted with
+// its cluster rule and runs the same one-CTA tiles as its "1sm" sibling; "_k512" selects 512-K
+// pipeline stages (128-byte weight rows per TMA box) instead of 256-K stages.
+struct Kind { const char* name; bool two_sm; int tile_n; int stage_k; };
 const Kind kKinds[] = {
-    {"sparse_2sm_256x128", true, 128},   {"sparse_2sm_256x256", true, 256},
-    {"sparse_1sm_128x128", false, 128},  {"sparse_1sm_128x256", false, 256},
-    {"sparse_2sm_256x64", true, 64},     {"sparse_1sm_128x64", false, 64},
-    {"sparse_2sm_256x64_k512", true, 64}, {"sparse_1sm_128x64_k512", false, 64},
+    {"sparse_2sm_256x128", true, 128, 256},     {"sparse_2sm_256x256", true, 256, 256},
+    {"sparse_1sm_128x128", false, 128, 256},    {"sparse_1sm_128x256", false, 256, 256},
+    {"sparse_2sm_256x64", true, 64, 256},       {"sparse_1sm_128x64", false, 64, 256},
+    {"sparse_2sm_256x64_k512", true, 64, 512},  {"sparse_1sm_128x64_k512", false, 64, 512},
+    {"sparse_1sm_128x128_k512", false, 128, 512},
 };
 constexpr int kNumKinds = sizeof(kKinds) / sizeof(kKinds[0]);
 
@@ -512,6 +781,14 @@ extern "C" int pnv_group_mm_device_status(int* status_out) {
   return PNV_OK;
 }
 
+extern "C" int pnv_group_mm_profile(long long* out, int n_values) {
+  PNV_REQUIRE(out && n_values >= 0 && n_values <= 256 * 8, "bad profile buffer");
+  PNV_REQUIRE(g_prof_dev != nullptr, "profiling is off: set PNV_GROUP_MM_PROFILE=1 before the first group_mm");
+  PNV_CUDA(cudaDeviceSynchronize());
+  PNV_CUDA(cudaMemcpy(out, g_prof_dev, n_values * sizeof(long long), cudaMemcpyDeviceToHost));
+  return PNV_OK;
+}
+
 extern "C" int pnv_group_mm_debug_trace(unsigned* words_out, int n_words) {
   PNV_REQUIRE(words_out && n_words >= 0, "bad trace buffer");
   for (int i = 0; i < n_words; ++i)
@@ -526,6 +803,8 @@ extern "C" int pnv_group_mm(void* out, const uint8_t* a_comp, const uint8_t* e_m
                             pnv_stream_t stream) {
   PNV_REQUIRE(out && a_comp && e_meta && sfa && b_act && sfb && alphas && counts, "null pointer argument");
   PNV_REQUIRE(experts >= 1 && features >= 1 && max_n >= 1, "experts, features and max_n must be positive");
+  PNV_REQUIRE(experts <= kMaxExperts, "group_mm supports at most %d experts per call, got %d", kMaxExperts,
+              experts);
   PNV_REQUIRE(k > 0 && k % kSfBlock == 0, "K must be a multiple of %d, got %d", kSfBlock, k);
   PNV_REQUIRE(config_id >= 0 && config_id < kNumKinds, "config_id must be in [0, %d), got %d", kNumKinds,
               config_id);
@@ -538,7 +817,7 @@ extern "C" int pnv_group_mm(void* out, const uint8_t* a_comp, const uint8_t* e_m
               "%s is a 2SM kernel and needs an even cluster_m, got %d", kind.name, cluster_m);
   PNV_REQUIRE((reinterpret_cast<uintptr_t>(a_comp) | reinterpret_cast<uintptr_t>(b_act) |
                reinterpret_cast<uintptr_t>(e_meta) | reinterpret_cast<uintptr_t>(sfa) |
-               reinterpret_cast<uintptr_t>(sfb)) % 16 == 0,
+               reinterpret_cast<uintptr_t>(sfb) | reinterpret_cast<uintptr_t>(out)) % 16 == 0,
               "group_mm operands must be 16-byte aligned");
   if (sm_count <= 0) {
     int dev = 0;
@@ -548,29 +827,58 @@ extern "C" int pnv_group_mm(void* out, const uint8_t* a_comp, const uint8_t* e_m
 
   WeightDims wd = weight_dims(features, k);
   Params p;
-  p.e_meta = e_meta; p.sfa = sfa; p.sfb = sfb; p.alphas = alphas; p.counts = counts;
+  p.a_comp = a_comp; p.e_meta = e_meta; p.sfa = sfa; p.sfb = sfb; p.alphas = alphas; p.counts = counts;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.E = experts; p.M = features; p.K = k; p.max_n = max_n;
   p.n_mt = ceil_div_i(features, kTileM);
-  p.k_stages = ceil_div_i(k, kStageK);
+  p.k_stages = ceil_div_i(k, kind.stage_k);
   p.n_kt = sf_k_atoms(k);
   p.e_k_atoms = wd.k_e / 16;
   p.e_m_atoms = wd.m_e / 128;
   p.sfb_rt = sf_row_atoms(max_n);
+  p.a_row_bytes = wd.k_ac / 2;
+  p.prefetch = prefetch_enabled() ? 1 : 0;
+  p.group = 1;
+  if (const char* env = std::getenv("PNV_GROUP_MM_GROUP")) p.group = std::max(1, std::atoi(env));
+  p.a_box_rows = p.group > 1 ? 32 : kTileM;
+  p.skip = 0;
+  p.prof = profile_buffer();
+  if (const char* env = std::getenv("PNV_GROUP_MM_SKIP")) p.skip = std::atoi(env);
+  p.stages = 0;
+  p.trace = nullptr;
+
+  // Tile geometry.  The variant names fix the widest token tile; when every expert's tokens fit one
+  // narrow tile (max_n <= 32) the kernel runs 16- or 32-wide MMAs over 512-K stages with four issuer
+  // warps instead: same results, far less padding and a deeper pipeline.
+  int tile_n = kind.tile_n, stage_k = kind.stage_k;
+  static const bool narrow_ok = [] {
+    const char* env = std::getenv("PNV_GROUP_MM_NARROW");
+    return !(env != nullptr && env[0] == '0');
+  }();
+  if (narrow_ok && max_n <= 32) {
+    tile_n = max_n <= 16 ? 16 : 32;
+    stage_k = 512;
+  }
+  p.k_stages = ceil_div_i(k, stage_k);
 
   CUtensorMap map_a, map_b;
-  if (int rc = make_map(&map_a, a_comp, (uint64_t)wd.k_ac / 2, (uint64_t)wd.m_ac, (uint64_t)experts, 64,
-                        kTileM, CU_TENSOR_MAP_SWIZZLE_64B))
+  if (int rc = make_map(&map_a, a_comp, (uint64_t)wd.k_ac / 2, (uint64_t)wd.m_ac, (uint64_t)experts,
+                        (uint32_t)stage_k / 4, (uint32_t)p.a_box_rows,
+                        stage_k == 512 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B))
     return rc;
   if (int rc = make_map(&map_b, b_act, (uint64_t)k / 2, (uint64_t)max_n, (uint64_t)experts, 128,
-                        (uint32_t)kind.tile_n, CU_TENSOR_MAP_SWIZZLE_128B))
+                        (uint32_t)tile_n, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
 
   cudaStream_t s = (cudaStream_t)stream;
   const bool use_pdl = pdl != 0 && pdl_enabled();
-  switch (kind.tile_n) {
-    case 64: return launch<64>(map_a, map_b, p, sm_count, use_pdl, s);
-    case 128: return launch<128>(map_a, map_b, p, sm_count, use_pdl, s);
-    default: return launch<256>(map_a, map_b, p, sm_count, use_pdl, s);
+  switch (tile_n * 1000 + stage_k) {
+    case 16512: return launch<16, 512, 4>(map_a, map_b, p, sm_count, use_pdl, s);
+    case 32512: return launch<32, 512, 4>(map_a, map_b, p, sm_count, use_pdl, s);
+    case 64256: return launch<64, 256, 2>(map_a, map_b, p, sm_count, use_pdl, s);
+    case 64512: return launch<64, 512, 2>(map_a, map_b, p, sm_count, use_pdl, s);
+    case 128256: return launch<128, 256, 1>(map_a, map_b, p, sm_count, use_pdl, s);
+    case 128512: return launch<128, 512, 1>(map_a, map_b, p, sm_count, use_pdl, s);
+    default: return launch<256, 256, 1>(map_a, map_b, p, sm_count, use_pdl, s);
   }
 }

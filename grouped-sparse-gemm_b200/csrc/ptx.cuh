@@ -97,6 +97,12 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
       : "memory");
 }
 
+// Fire-and-forget prefetch of a contiguous global range into L2 (address and size multiples of 16).
+__device__ __forceinline__ void prefetch_l2(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(src)), "r"(bytes)
+               : "memory");
+}
+
 // ---- tensor memory -------------------------------------------------------------------------------
 
 // Warp-wide: allocate `cols` (power of two >= 32) columns, base address written to *slot.

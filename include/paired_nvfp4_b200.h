@@ -51,6 +51,12 @@ int pnv_group_mm_device_status(int* status_out);
  * (No counterpart in the reference.) */
 int pnv_group_mm_debug_trace(unsigned* words_out, int n_words);
 
+/* Measuring aid: with PNV_GROUP_MM_PROFILE=1 every CTA of the last group_mm launch leaves 8 cycle
+ * counters (MMA issuer: waiting for data, issuing, waiting for an accumulator, stages seen; tile
+ * producer: waiting for a free stage; 3 unused); this call synchronises and copies n_values of them
+ * out.  (No counterpart in the reference.) */
+int pnv_group_mm_profile(long long* values_out, int n_values);
+
 /* ---- size queries ------------------------------------------------------------------------- */
 
 /* physical_dims(features, k, groups) (csrc/layout.cuh:83-91): a_comp is

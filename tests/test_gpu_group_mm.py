@@ -48,7 +48,7 @@ def run_case(pnk, E, M, K, max_n, counts, config_id, seed, wscale=1.0, gscale=No
 
 
 def config_ids():
-    return list(range(8))
+    return list(range(9))
 
 
 @pytest.mark.parametrize("config_id", config_ids())
@@ -76,7 +76,7 @@ SHAPES = [
 
 
 @pytest.mark.parametrize("E,M,K,max_n,counts", SHAPES)
-@pytest.mark.parametrize("config_id", [0, 1, 5])
+@pytest.mark.parametrize("config_id", [0, 1, 5, 7, 8])
 def test_shapes(pnk, E, M, K, max_n, counts, config_id):
     if counts == "rand":
         counts = np.random.default_rng(1001).integers(1, max_n + 1, E)
