@@ -30,6 +30,10 @@ for _p in (ROOT, os.path.join(ROOT, "grouped-sparse-gemm_b200")):
 
 FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool, used only without MEASURED_PEAKS.json
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate_up group_mm launch, from the ncu captures
+# summarised under profiles/ (same workload, so no scaling)
+NCU_TRAFFIC_BYTES = {"c2": 329.86e6}
+
 # name -> dict(E, hidden, inter, max_n/cap, routing)
 WORKLOADS = {
     # Mixtral-8x7B expert FFN, decode: per-expert counts uniform in [1, 16]
@@ -413,7 +417,7 @@ def main():
         peak, src = FALLBACK_HBM_GBS, "fallback"
     achieved = acct["bytes_w13"] / k13 / 1e9
     roofline = dict(bound="hbm", kernel="group_mm gate_up", achieved=achieved, peak=peak, unit="GB/s",
-                    frac=achieved / peak, peak_source=src, traffic=None,
+                    frac=achieved / peak, peak_source=src, traffic=NCU_TRAFFIC_BYTES.get(wl_name),
                     algorithmic_bytes=acct["bytes_w13"], launch_us=k13 * 1e6)
 
     if rank == 0:
