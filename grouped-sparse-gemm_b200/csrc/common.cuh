@@ -147,6 +147,19 @@ __device__ __forceinline__ void block_scale(float amax, float g, uint32_t& sf_by
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
 
+// Eight bf16 (one 128-bit word) -> floats, and eight floats -> one word of e2m1 codes after scaling.
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x); f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
+  f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
+}
+
+__device__ __forceinline__ uint32_t quant8(const float (&f)[8], float inv) {
+  float s[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s[i] = __fmul_rn(f[i], inv);
+  return cvt_e2m1x8(s);
+}
+
 // The gated activation applied between the two expert GEMMs, with the rounding chain of the
 // unfused path: silu  -> bf16(float(bf16(g / (1 + expf(-g)))) * u)
 //               situ  -> bf16((0.5 b) tanhf(g / b) (1 + tanhf(g / 2)) * (l > 0 ? l tanhf(u / l) : u))
@@ -170,5 +183,8 @@ __device__ __forceinline__ float gated_act(float g, float u, const GatedAct& a) 
   float s_bf = __bfloat162float(__float2bfloat16_rn(s));
   return __bfloat162float(__float2bfloat16_rn(__fmul_rn(s_bf, u)));
 }
+
+// (activation kind, beta, linear_beta) -> GatedAct with the reference's argument checks (quant.cu)
+int make_gated_act(int act_kind, float beta, float linear_beta, GatedAct& out);
 
 }  // namespace pnv

@@ -50,7 +50,8 @@ constexpr int kTmemCols = 512;
 constexpr int kColE = 448;                   // tensor-memory columns: metadata (up to 16)
 constexpr int kColSfa = 464;                 //   weight scales (4 per K-block)
 constexpr int kColSfb = 480;                 //   activation scales (4 or 8 per K-block)
-constexpr int kOutStageBytes = 2 * 32 * kTileM * 2;   // epilogue transpose buffers: 2 x [32][128] bf16
+constexpr int kOutRow = kTileM + 8;          // padded row of the epilogue transpose buffer (bank spread)
+constexpr int kOutStageBytes = 2 * 32 * kOutRow * 2;   // 2 x [32 token columns][136] bf16
 constexpr int kMaxExperts = 2048;            // bounds the shared-memory copy of counts
 constexpr int kSmemLimit = 227 * 1024;
 
@@ -121,6 +122,14 @@ struct Params {
   int group;         // stages the tile producer fills concurrently (1 = one at a time)
   int a_box_rows;    // rows per weight TMA box (128, or 32 when group > 1)
   int skip;          // experiment knob (timing only, results invalid): 1 no B, 2 no E, 4 no SFA, 8 no SFB, 16 no cp, 32 no MMA
+  // fused SwiGLU + requantise epilogue (kFused kernels): GEMM2's operands instead of a bf16 output
+  uint8_t* f_b_out;        // [E, max_n, N/2] e2m1 codes, N = M / 2
+  uint8_t* f_sfb_out;      // swizzled scales for (max_n, N), pre-filled with 0x38
+  const float* f_gscale;   // GEMM2 activation global scale, [E] or [1]
+  int f_gpe;
+  int f_n;                 // N
+  int f_n_kt;              // scale K-atoms of the N-wide output
+  GatedAct f_act;
   long long* prof;   // optional per-CTA cycle counters (8 per CTA): see PNV_GROUP_MM_PROFILE
   unsigned* trace;   // traced build only: host-mapped breadcrumb words, 16 per CTA (first 8 CTAs)
 };
@@ -180,7 +189,7 @@ __device__ __forceinline__ void epilogue_bar_sync() {
   asm volatile("bar.sync 1, 128;" ::: "memory");
 }
 
-template <int TILE_N, int STAGE_K, int ISSUERS, bool kTrace>
+template <int TILE_N, int STAGE_K, int ISSUERS, bool kTrace, bool kFused>
 __global__ void __launch_bounds__((6 + ISSUERS) * 32, 1)
 group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const Params p) {
@@ -573,12 +582,59 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__fadd_rn(__uint_as_float(r[i]), __uint_as_float(q[i])));
           }
         }
-        if (vec_ok) {
+        if (kFused) {
+          // The weight rows are interleaved in 64-row blocks (32 gate rows, then the 32 matching up
+          // rows), so lanes of the even 32-lane quarters hold gates and the odd quarters the ups of
+          // the same 32 output features: exactly one quantization block per token.
+          __nv_bfloat16* buf = s_out + (chunk & 1) * (32 * kOutRow);
+          constexpr int kCols = TILE_N < 32 ? TILE_N : 32;
+          __nv_bfloat16 h[kCols];
+#pragma unroll
+          for (int i = 0; i < kCols; ++i) h[i] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(r[i])));
+          const bool is_up = (sub & 1) != 0;
+          if (is_up) {
+#pragma unroll
+            for (int i = 0; i < kCols; ++i) buf[i * kOutRow + m_local] = h[i];
+          }
+          epilogue_bar_sync();
+          if (!is_up) {
+#pragma unroll
+            for (int i = 0; i < kCols; ++i) {
+              const float u = __bfloat162float(buf[i * kOutRow + m_local + 32]);
+              buf[i * kOutRow + m_local] = __float2bfloat16_rn(gated_act(__bfloat162float(h[i]), u, p.f_act));
+            }
+          }
+          epilogue_bar_sync();
+          if (ep_tid < 64) {
+            const int i = ep_tid & 31, blk = ep_tid >> 5;
+            const int n = n0 + c0 + i;
+            if (i < kCols && n < cnt) {
+              const uint4* src = reinterpret_cast<const uint4*>(buf + i * kOutRow + blk * 64);
+              float f[4][8];
+              float amax = 0.f;
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                unpack8(src[q], f[q]);
+#pragma unroll
+                for (int z = 0; z < 8; ++z) amax = fmaxf(amax, fabsf(f[q][z]));
+              }
+              uint32_t sf_byte;
+              float inv;
+              block_scale(amax, p.f_gpe ? p.f_gscale[e] : p.f_gscale[0], sf_byte, inv);
+              const int kb = mt * 2 + blk;     // 32-feature block of the N-wide output
+              const long long row = (long long)e * p.max_n + n;
+              *reinterpret_cast<uint4*>(p.f_b_out + row * (p.f_n / 2) + kb * 16) =
+                  make_uint4(quant8(f[0], inv), quant8(f[1], inv), quant8(f[2], inv), quant8(f[3], inv));
+              p.f_sfb_out[sf_offset(e, n, kb, p.sfb_rt, p.f_n_kt)] = (uint8_t)sf_byte;
+            }
+          }
+          ++chunk;
+        } else if (vec_ok) {
           // [token column][feature] tile: 32 rows of 128 bf16; lanes write consecutive features
-          __nv_bfloat16* buf = s_out + (chunk & 1) * (32 * kTileM);
+          __nv_bfloat16* buf = s_out + (chunk & 1) * (32 * kOutRow);
 #pragma unroll
           for (int i = 0; i < (TILE_N < 32 ? TILE_N : 32); ++i)
-            buf[i * kTileM + m_local] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(r[i])));
+            buf[i * kOutRow + m_local] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(r[i])));
           epilogue_bar_sync();
           const int col = (ep_tid & 15) * 8;
           const int m = mt * kTileM + col;
@@ -588,7 +644,7 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int n = n0 + c0 + row;
             if (n < cnt && m < p.M)
               *reinterpret_cast<uint4*>(out_e + (long long)n * p.M + m) =
-                  *reinterpret_cast<const uint4*>(buf + row * kTileM + col);
+                  *reinterpret_cast<const uint4*>(buf + row * kOutRow + col);
           }
           ++chunk;
         } else {
@@ -701,7 +757,7 @@ bool trace_enabled() {
   return v == 1;
 }
 
-template <int TILE_N, int STAGE_K, int ISSUERS, bool kTrace>
+template <int TILE_N, int STAGE_K, int ISSUERS, bool kTrace, bool kFused>
 int launch_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p_in, int sm_count, bool pdl,
                 cudaStream_t stream) {
   using C = Cfg<TILE_N, STAGE_K, ISSUERS>;
@@ -713,20 +769,21 @@ int launch_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params
   }
   if (p.group > p.stages - 1) p.group = p.stages > 1 ? p.stages - 1 : 1;
   const size_t smem = 1024 + (size_t)C::kStages * C::kStageBytes + kOutStageBytes + 256 + 4 * (size_t)p.E;
+  static_assert(kOutStageBytes % 16 == 0, "barrier block must stay aligned");
   static_assert(8 * (2 * C::kStages + 2 * C::kAccStages + 2 + ISSUERS) + 16 <= 256, "barrier block overflows its slot");
   // opt in to the large dynamic shared-memory carve-out once per device
   static bool opted_in[64] = {};
   int dev = 0;
   PNV_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64 || !opted_in[dev]) {
-    PNV_CUDA(cudaFuncSetAttribute(group_mm_kernel<TILE_N, STAGE_K, ISSUERS, kTrace>,
+    PNV_CUDA(cudaFuncSetAttribute(group_mm_kernel<TILE_N, STAGE_K, ISSUERS, kTrace, kFused>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     if (dev >= 0 && dev < 64) opted_in[dev] = true;
   }
   long long max_tiles = (long long)p.E * p.n_mt * ceil_div_i(p.max_n, TILE_N);
   int grid = (int)(max_tiles < sm_count ? max_tiles : sm_count);
   if (grid < 1) grid = 1;
-  PNV_CUDA(launch_pdl(group_mm_kernel<TILE_N, STAGE_K, ISSUERS, kTrace>, dim3(grid), dim3(C::kThreads), smem,
+  PNV_CUDA(launch_pdl(group_mm_kernel<TILE_N, STAGE_K, ISSUERS, kTrace, kFused>, dim3(grid), dim3(C::kThreads), smem,
                       stream, pdl, map_a, map_b, p));
   return PNV_OK;
 }
@@ -734,9 +791,13 @@ int launch_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params
 template <int TILE_N, int STAGE_K, int ISSUERS>
 int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, Params& p, int sm_count, bool pdl,
            cudaStream_t stream) {
+  if (p.f_b_out != nullptr) {
+    p.trace = nullptr;
+    return launch_impl<TILE_N, STAGE_K, ISSUERS, false, true>(map_a, map_b, p, sm_count, pdl, stream);
+  }
   if (!trace_enabled()) {
     p.trace = nullptr;
-    return launch_impl<TILE_N, STAGE_K, ISSUERS, false>(map_a, map_b, p, sm_count, pdl, stream);
+    return launch_impl<TILE_N, STAGE_K, ISSUERS, false, false>(map_a, map_b, p, sm_count, pdl, stream);
   }
   if (g_trace_host == nullptr) {
     PNV_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&g_trace_host), kTraceWords * sizeof(unsigned),
@@ -745,7 +806,7 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, Params& p, int sm
   }
   for (int i = 0; i < kTraceWords; ++i) g_trace_host[i] = 0;
   p.trace = g_trace_dev;
-  return launch_impl<TILE_N, STAGE_K, ISSUERS, true>(map_a, map_b, p, sm_count, false, stream);
+  return launch_impl<TILE_N, STAGE_K, ISSUERS, true, false>(map_a, map_b, p, sm_count, false, stream);
 }
 
 // Tile variants.  The first eight names and ids are the reference's; a "2sm" name is accepted with
@@ -796,11 +857,30 @@ extern "C" int pnv_group_mm_debug_trace(unsigned* words_out, int n_words) {
   return PNV_OK;
 }
 
-extern "C" int pnv_group_mm(void* out, const uint8_t* a_comp, const uint8_t* e_meta, const uint8_t* sfa,
-                            const uint8_t* b_act, const uint8_t* sfb, const float* alphas,
-                            const int32_t* counts, int experts, int features, int k, int max_n,
-                            int config_id, int cluster_m, int cluster_n, int sm_count, int pdl,
-                            pnv_stream_t stream) {
+namespace pnv {
+namespace {
+
+struct FusedArgs {
+  uint8_t* b_out = nullptr;
+  uint8_t* sfb_out = nullptr;
+  const float* gscale = nullptr;
+  int gpe = 0;
+  GatedAct act{PNV_ACT_SILU, 1.f, -1.f};
+};
+
+// The tile variants of the fused op, by the reference's names (csrc/sm100/tactics.cu:52-57).
+struct FusedKind { const char* name; bool two_sm; int base_config; };
+const FusedKind kFusedKinds[] = {
+    {"fused_2sm_256x64_k512", true, 6}, {"fused_2sm_256x64", true, 4},
+    {"fused_1sm_128x64", false, 5},     {"fused_2sm_256x128", true, 0},
+};
+constexpr int kNumFusedKinds = sizeof(kFusedKinds) / sizeof(kFusedKinds[0]);
+
+int group_mm_common(void* out, const FusedArgs* fused, const uint8_t* a_comp, const uint8_t* e_meta,
+                    const uint8_t* sfa, const uint8_t* b_act, const uint8_t* sfb, const float* alphas,
+                    const int32_t* counts, int experts, int features, int k, int max_n, int config_id,
+                    int cluster_m, int cluster_n, int sm_count, int pdl, pnv_stream_t stream,
+                    const char* display_name) {
   PNV_REQUIRE(out && a_comp && e_meta && sfa && b_act && sfb && alphas && counts, "null pointer argument");
   PNV_REQUIRE(experts >= 1 && features >= 1 && max_n >= 1, "experts, features and max_n must be positive");
   PNV_REQUIRE(experts <= kMaxExperts, "group_mm supports at most %d experts per call, got %d", kMaxExperts,
@@ -809,12 +889,13 @@ extern "C" int pnv_group_mm(void* out, const uint8_t* a_comp, const uint8_t* e_m
   PNV_REQUIRE(config_id >= 0 && config_id < kNumKinds, "config_id must be in [0, %d), got %d", kNumKinds,
               config_id);
   const Kind& kind = kKinds[config_id];
+  const char* name = display_name ? display_name : kind.name;
   auto pow2_le4 = [](int x) { return x == 1 || x == 2 || x == 4; };
   PNV_REQUIRE(pow2_le4(cluster_m) && pow2_le4(cluster_n) && cluster_m * cluster_n <= 16,
-              "%s: cluster dims must be powers of two <= 4 with product <= 16, got %dx%d", kind.name,
+              "%s: cluster dims must be powers of two <= 4 with product <= 16, got %dx%d", name,
               cluster_m, cluster_n);
   PNV_REQUIRE(!kind.two_sm || cluster_m % 2 == 0,
-              "%s is a 2SM kernel and needs an even cluster_m, got %d", kind.name, cluster_m);
+              "%s is a 2SM kernel and needs an even cluster_m, got %d", name, cluster_m);
   PNV_REQUIRE((reinterpret_cast<uintptr_t>(a_comp) | reinterpret_cast<uintptr_t>(b_act) |
                reinterpret_cast<uintptr_t>(e_meta) | reinterpret_cast<uintptr_t>(sfa) |
                reinterpret_cast<uintptr_t>(sfb) | reinterpret_cast<uintptr_t>(out)) % 16 == 0,
@@ -829,6 +910,12 @@ extern "C" int pnv_group_mm(void* out, const uint8_t* a_comp, const uint8_t* e_m
   Params p;
   p.a_comp = a_comp; p.e_meta = e_meta; p.sfa = sfa; p.sfb = sfb; p.alphas = alphas; p.counts = counts;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.f_b_out = nullptr; p.f_sfb_out = nullptr; p.f_gscale = nullptr; p.f_gpe = 0; p.f_n = 0; p.f_n_kt = 0;
+  p.f_act = GatedAct{PNV_ACT_SILU, 1.f, -1.f};
+  if (fused != nullptr) {
+    p.f_b_out = fused->b_out; p.f_sfb_out = fused->sfb_out; p.f_gscale = fused->gscale; p.f_gpe = fused->gpe;
+    p.f_n = features / 2; p.f_n_kt = sf_k_atoms(features / 2); p.f_act = fused->act;
+  }
   p.E = experts; p.M = features; p.K = k; p.max_n = max_n;
   p.n_mt = ceil_div_i(features, kTileM);
   p.k_stages = ceil_div_i(k, kind.stage_k);
@@ -881,4 +968,47 @@ extern "C" int pnv_group_mm(void* out, const uint8_t* a_comp, const uint8_t* e_m
     case 128512: return launch<128, 512, 1>(map_a, map_b, p, sm_count, use_pdl, s);
     default: return launch<256, 256, 1>(map_a, map_b, p, sm_count, use_pdl, s);
   }
+}
+
+}  // namespace
+}  // namespace pnv
+
+extern "C" int pnv_group_mm(void* out, const uint8_t* a_comp, const uint8_t* e_meta, const uint8_t* sfa,
+                            const uint8_t* b_act, const uint8_t* sfb, const float* alphas,
+                            const int32_t* counts, int experts, int features, int k, int max_n,
+                            int config_id, int cluster_m, int cluster_n, int sm_count, int pdl,
+                            pnv_stream_t stream) {
+  return group_mm_common(out, nullptr, a_comp, e_meta, sfa, b_act, sfb, alphas, counts, experts, features, k,
+                         max_n, config_id, cluster_m, cluster_n, sm_count, pdl, stream, nullptr);
+}
+
+extern "C" int pnv_group_mm_swiglu_num_configs(void) { return kNumFusedKinds; }
+
+extern "C" const char* pnv_group_mm_swiglu_config_name(int config_id) {
+  return (config_id >= 0 && config_id < kNumFusedKinds) ? kFusedKinds[config_id].name : nullptr;
+}
+
+extern "C" int pnv_group_mm_swiglu_quant(uint8_t* b_out, uint8_t* sfb_out, const uint8_t* a_comp,
+                                         const uint8_t* e_meta, const uint8_t* sfa, const uint8_t* b_act,
+                                         const uint8_t* sfb, const float* alphas, const int32_t* counts,
+                                         const float* gscale, int gscale_per_expert, int experts,
+                                         int features, int k, int max_n, int config_id, int cluster_m,
+                                         int cluster_n, int act_kind, float beta, float linear_beta,
+                                         int sm_count, int pdl, pnv_stream_t stream) {
+  PNV_REQUIRE(b_out && sfb_out && gscale, "null pointer argument");
+  PNV_REQUIRE(features % 128 == 0,
+              "features (2N) must be a multiple of 128 (whole 64-row gate/up blocks per CTA), got %d", features);
+  PNV_REQUIRE(config_id >= 0 && config_id < kNumFusedKinds, "config_id must be in [0, %d), got %d",
+              kNumFusedKinds, config_id);
+  PNV_REQUIRE((reinterpret_cast<uintptr_t>(b_out) | reinterpret_cast<uintptr_t>(sfb_out)) % 16 == 0,
+              "group_mm operands must be 16-byte aligned");
+  FusedArgs f;
+  if (int rc = make_gated_act(act_kind, beta, linear_beta, f.act)) return rc;
+  f.b_out = b_out; f.sfb_out = sfb_out; f.gscale = gscale; f.gpe = gscale_per_expert ? 1 : 0;
+  PNV_REQUIRE(experts >= 1 && max_n >= 1, "experts and max_n must be positive");
+  // every scale slot the epilogue does not write must read 1.0
+  PNV_CUDA(cudaMemsetAsync(sfb_out, kBenignSf, (size_t)sf_numel(max_n, features / 2, experts), (cudaStream_t)stream));
+  const FusedKind& fk = kFusedKinds[config_id];
+  return group_mm_common(b_out, &f, a_comp, e_meta, sfa, b_act, sfb, alphas, counts, experts, features, k, max_n,
+                         fk.base_config, cluster_m, cluster_n, sm_count, pdl, stream, fk.name);
 }

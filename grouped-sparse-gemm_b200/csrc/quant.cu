@@ -20,26 +20,6 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarpsPerBlock = kThreads / 32;
 
-__device__ __forceinline__ float amax8(const uint4& v) {
-  float m = fmaxf(fabsf(bf16_lo(v.x)), fabsf(bf16_hi(v.x)));
-  m = fmaxf(m, fmaxf(fabsf(bf16_lo(v.y)), fabsf(bf16_hi(v.y))));
-  m = fmaxf(m, fmaxf(fabsf(bf16_lo(v.z)), fabsf(bf16_hi(v.z))));
-  m = fmaxf(m, fmaxf(fabsf(bf16_lo(v.w)), fabsf(bf16_hi(v.w))));
-  return m;
-}
-
-__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
-  f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x); f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
-  f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
-}
-
-__device__ __forceinline__ uint32_t quant8(const float (&f)[8], float inv) {
-  float s[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) s[i] = __fmul_rn(f[i], inv);
-  return cvt_e2m1x8(s);
-}
-
 // Gather the 16 scale bytes of a line from the lanes that own them (lane g*8 + 2*kq holds the
 // byte of row group g, K-block kq) and store them as four 32-bit words.
 __device__ __forceinline__ void store_sf_line(uint8_t* line, uint32_t my_byte, int lane) {

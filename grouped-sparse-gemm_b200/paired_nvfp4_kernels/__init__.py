@@ -48,6 +48,11 @@ def _register():
                f"int config_id={DEFAULT_TACTIC[0]}, int cluster_m={DEFAULT_TACTIC[1]}, "
                f"int cluster_n={DEFAULT_TACTIC[2]}) -> ()")
     lib.define("group_mm_configs() -> str[]")
+    lib.define("group_mm_swiglu_quant(Tensor a_comp, Tensor e_meta, Tensor sfa, Tensor b_act, Tensor sfb, "
+               "Tensor alphas, Tensor expert_num_tokens, Tensor gscale, int features, int k, int config_id=0, "
+               f"int cluster_m={DEFAULT_TACTIC[1]}, int cluster_n={DEFAULT_TACTIC[2]}, "
+               "str activation=\"silu\", float beta=1.0, float linear_beta=-1.0) -> (Tensor, Tensor)")
+    lib.define("group_mm_swiglu_configs() -> str[]")
     lib.define("gated_act(Tensor x2, bool interleaved=False, str activation=\"silu\", float beta=1.0, "
                "float linear_beta=-1.0) -> Tensor")
     lib.impl("compress", ops.compress, "CUDA")
@@ -56,7 +61,9 @@ def _register():
     lib.impl("scatter_quant_act", ops.scatter_quant_act, "CUDA")
     lib.impl("group_mm", ops.group_mm, "CUDA")
     lib.impl("gated_act", ops.gated_act, "CUDA")
+    lib.impl("group_mm_swiglu_quant", ops.group_mm_swiglu_quant, "CUDA")
     lib.impl("group_mm_configs", ops.group_mm_configs, "CompositeExplicitAutograd")
+    lib.impl("group_mm_swiglu_configs", ops.group_mm_swiglu_configs, "CompositeExplicitAutograd")
     return lib
 
 
@@ -124,7 +131,7 @@ def interleave_gate_up_rows(n, device=None):
 
 
 def fused_swiglu_tactics(max_cluster_product=16):
-    """Candidate tactics of the fused SwiGLU GEMM (empty while the op is not registered)."""
+    """Candidate (config_id, cluster_m, cluster_n) for group_mm_swiglu_quant."""
     ns = torch.ops.paired_nvfp4
     if not hasattr(ns, "group_mm_swiglu_configs"):
         return []

@@ -33,6 +33,9 @@ SIGNATURES = {
     "pnv_group_mm_num_configs": (_i, []),
     "pnv_group_mm_config_name": (ctypes.c_char_p, [_i]),
     "pnv_group_mm": (_i, [_p] * 8 + [_i] * 9 + [_p]),
+    "pnv_group_mm_swiglu_num_configs": (_i, []),
+    "pnv_group_mm_swiglu_config_name": (ctypes.c_char_p, [_i]),
+    "pnv_group_mm_swiglu_quant": (_i, [_p] * 10 + [_i] * 9 + [_f, _f, _i, _i, _p]),
 }
 
 
@@ -71,6 +74,10 @@ def physical_dims(features, k):
 
 def sf_numel(rows, k, groups):
     return int(lib.pnv_sf_numel(rows, k, groups))
+
+
+def group_mm_swiglu_config_names():
+    return [lib.pnv_group_mm_swiglu_config_name(i).decode() for i in range(lib.pnv_group_mm_swiglu_num_configs())]
 
 
 def group_mm_config_names():

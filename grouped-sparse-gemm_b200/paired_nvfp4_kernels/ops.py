@@ -212,6 +212,43 @@ def group_mm(out, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens, fe
             int(cluster_n), _device_info(out.device)[1], 1, _stream(out)))
 
 
+def group_mm_swiglu_configs():
+    """csrc/ops.cu:585-589."""
+    return _cabi.group_mm_swiglu_config_names()
+
+
+def group_mm_swiglu_quant(a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens, gscale, features, k,
+                          config_id=0, cluster_m=2, cluster_n=1, activation="silu", beta=1.0, linear_beta=-1.0):
+    """csrc/ops.cu:591-658.  GEMM1 + gated activation + GEMM2's input quantization in one kernel;
+    returns GEMM2's operands (b_act [E, max_n, N/2], sfb)."""
+    ts = (a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens, gscale)
+    _check(all(t.is_cuda for t in ts), "all tensors must be CUDA")
+    _check_arch(b_act)
+    E, M, K, max_n = a_comp.size(0), int(features), int(k), b_act.size(1)
+    N = M // 2
+    _check(M % 128 == 0, lambda: "features (2N) must be a multiple of 128 (whole 64-row gate/up blocks per CTA), "
+                                 f"got {M}")
+    _check(b_act.dim() == 3 and b_act.size(0) == E and b_act.size(2) == K // 2, "b_act must be [E, max_n, K/2]")
+    _check(all(t.is_contiguous() for t in (a_comp, e_meta, sfa, b_act, sfb, alphas)), "inputs must be contiguous")
+    _check(alphas.dtype == torch.float32 and alphas.numel() == E, "alphas must be [E] float32")
+    _check_gscale_counts(gscale, expert_num_tokens, E)
+    m_ac, k_ac, m_e, k_e = _cabi.physical_dims(M, K)
+    _check(a_comp.size(1) == m_ac and a_comp.size(2) == k_ac // 2 and e_meta.size(1) == m_e and e_meta.size(2) == k_e,
+           lambda: f"a_comp / e_meta shapes do not match compress() output for features={M}, k={K}")
+    _check(sfa.numel() >= _cabi.sf_numel(M, K, E), "sfa is smaller than the SFA layout")
+    _check(sfb.numel() >= _cabi.sf_numel(max_n, K, E), "sfb is smaller than the SFB layout")
+    kind = _act_kind(activation, beta)
+    b_out = torch.empty((E, max_n, N // 2), dtype=torch.uint8, device=b_act.device)
+    sfb_out = torch.empty((_cabi.sf_numel(max_n, N, E),), dtype=torch.uint8, device=b_act.device)
+    with torch.cuda.device(b_act.device):
+        _cabi.check(_lib.pnv_group_mm_swiglu_quant(
+            b_out.data_ptr(), sfb_out.data_ptr(), a_comp.data_ptr(), e_meta.data_ptr(), sfa.data_ptr(),
+            b_act.data_ptr(), sfb.data_ptr(), alphas.data_ptr(), expert_num_tokens.data_ptr(), gscale.data_ptr(),
+            1 if gscale.numel() == E else 0, E, M, K, max_n, int(config_id), int(cluster_m), int(cluster_n), kind,
+            float(beta), float(linear_beta), _device_info(b_act.device)[1], 1, _stream(b_act)))
+    return b_out, sfb_out
+
+
 def group_mm_device_status():
     """Status word of the bounded waits inside group_mm (0 = all completed); synchronises."""
     import ctypes

@@ -131,6 +131,23 @@ int pnv_group_mm(void* out, const uint8_t* a_comp, const uint8_t* e_meta, const 
                  const int32_t* counts, int experts, int features, int k, int max_n, int config_id,
                  int cluster_m, int cluster_n, int sm_count, int pdl, pnv_stream_t stream);
 
+/* paired_nvfp4_group_mm_swiglu_configs / paired_nvfp4_group_mm_swiglu_quant (csrc/ops.cu:585-658 ->
+ * SwigluFp4Epilogue, csrc/sm100/swiglu_epilogue.cuh:52-236; variant table kSwigluMmKinds,
+ * csrc/sm100/tactics.cu:52-57).  GEMM1 on a W13 whose rows are interleaved in 64-row blocks (32 gate
+ * rows, then the 32 matching up rows; features = 2N, a multiple of 128), with the gated activation
+ * and GEMM2's input quantization fused into the epilogue: writes b_out u8[E, max_n, N/2] (rows
+ * t >= counts[e] untouched) and sfb_out u8[pnv_sf_numel(max_n, N, E)] (every byte), byte-identical
+ * to pnv_group_mm followed by pnv_silu_mul_quant_act(interleaved = 1) with the same gscale. */
+int pnv_group_mm_swiglu_num_configs(void);
+const char* pnv_group_mm_swiglu_config_name(int config_id);
+int pnv_group_mm_swiglu_quant(uint8_t* b_out, uint8_t* sfb_out, const uint8_t* a_comp,
+                              const uint8_t* e_meta, const uint8_t* sfa, const uint8_t* b_act,
+                              const uint8_t* sfb, const float* alphas, const int32_t* counts,
+                              const float* gscale, int gscale_per_expert, int experts, int features,
+                              int k, int max_n, int config_id, int cluster_m, int cluster_n,
+                              int act_kind, float beta, float linear_beta, int sm_count, int pdl,
+                              pnv_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
