@@ -61,6 +61,7 @@ def parse_args():
     ap.add_argument("--config-id", type=int, default=None, help="group_mm tile variant override")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--unfused", action="store_true", help="separate silu_mul_quant_act launch instead of the fused GEMM1 epilogue")
     return ap.parse_args()
 
 
@@ -80,7 +81,7 @@ def gemm_bytes(active, M, K, rows):
     return w + rows * (K // 2 + K // 32) + rows * 2 * M
 
 
-def layer_accounting(wl, counts):
+def layer_accounting(wl, counts, fused=True):
     rows = int(counts.sum())
     active = int((counts > 0).sum())
     H, I = wl["hidden"], wl["inter"]
@@ -89,6 +90,9 @@ def layer_accounting(wl, counts):
     b2 = gemm_bytes(active, H, I, rows)
     quant1 = rows * (2 * H + H // 2 + H // 32)
     quant2 = rows * (4 * I + I // 2 + I // 32)
+    if fused:   # GEMM1 writes GEMM2's codes + scales instead of bf16; no separate activation pass
+        b13 += rows * (I // 2 + I // 32) - rows * 2 * (2 * I)
+        quant2 = 0
     return dict(rows=rows, active=active, flops=flops, bytes_w13=b13, bytes_w2=b2,
                 bytes_total=b13 + b2 + quant1 + quant2)
 
@@ -134,7 +138,7 @@ def plan_from_ids(ids, first_expert, num_local, cap):
 class Layer:
     """Device state of one expert-FFN layer and the four launches of a step, through the C ABI."""
 
-    def __init__(self, wl, device, config_id=None, copies=2, E_local=None, first_expert=0, seed_shift=0):
+    def __init__(self, wl, device, config_id=None, copies=2, E_local=None, first_expert=0, seed_shift=0, fused=True):
         import torch
         from paired_nvfp4_kernels import _cabi, reference as wref
         self.torch, self.lib, self.cabi = torch, _cabi.lib, _cabi
@@ -142,8 +146,14 @@ class Layer:
         self.E = E_local if E_local is not None else wl["E"]
         self.H, self.I, self.cap = wl["hidden"], wl["inter"], wl["cap"]
         self.cfg = wl["config_id"] if config_id is None else config_id
+        self.fused = fused
         names = _cabi.group_mm_config_names()
         self.cluster_m = 2 if names[self.cfg].split("_")[1] == "2sm" else 1
+        # fused variant with the same tile as the chosen group_mm variant
+        fmap = {6: 0, 7: 0, 4: 1, 5: 2, 0: 3, 2: 3}
+        self.fused_cfg = fmap.get(self.cfg, 3)
+        if fused:
+            self.cluster_m = 2 if _cabi.group_mm_swiglu_config_names()[self.fused_cfg].split("_")[1] == "2sm" else self.cluster_m
         self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
         ops = torch.ops.paired_nvfp4
         E, H, I = self.E, self.H, self.I
@@ -158,6 +168,10 @@ class Layer:
                 w13 = torch.randn((1, 2 * I, H), generator=g, device=device) * wl["wstd"]
                 w2 = torch.randn((1, H, I), generator=g, device=device) * wl["wstd"]
                 p13, s13, _ = wref.quantize_weight(wref.prune_paired_4of8(w13))
+                if fused:   # gate/up rows interleaved in 64-row blocks for the fused epilogue
+                    import paired_nvfp4_kernels as pnk
+                    perm = pnk.interleave_gate_up_rows(I, device=device)
+                    p13, s13 = p13[:, perm].contiguous(), s13[:, perm].contiguous()
                 p2, s2, _ = wref.quantize_weight(wref.prune_paired_4of8(w2))
                 if c == 0 and e < 2:
                     self.host_sample[e] = tuple(t.cpu().numpy() for t in (p13, s13, p2, s2))
@@ -196,15 +210,25 @@ class Layer:
                                          self.b1.data_ptr(), self.sfb1.data_ptr(), sm, stream))
         if events:
             events[0].record()
-        ck(lib.pnv_group_mm(self.out1.data_ptr(), w["a13"].data_ptr(), w["e13"].data_ptr(), w["s13"].data_ptr(),
-                            self.b1.data_ptr(), self.sfb1.data_ptr(), self.al1.data_ptr(), self.counts.data_ptr(),
-                            E, 2 * I, H, cap, self.cfg, self.cluster_m, 1, sm, 1, stream))
-        if events:
-            events[1].record()
-        ck(lib.pnv_silu_mul_quant_act(self.out1.data_ptr(), self.g2.data_ptr(), 1, self.counts.data_ptr(), E, cap, I,
-                                      0, 0, 1.0, -1.0, self.b2.data_ptr(), self.sfb2.data_ptr(), sm, stream))
-        if events:
-            events[2].record()
+        if self.fused:
+            ck(lib.pnv_group_mm_swiglu_quant(self.b2.data_ptr(), self.sfb2.data_ptr(), w["a13"].data_ptr(),
+                                             w["e13"].data_ptr(), w["s13"].data_ptr(), self.b1.data_ptr(),
+                                             self.sfb1.data_ptr(), self.al1.data_ptr(), self.counts.data_ptr(),
+                                             self.g2.data_ptr(), 1, E, 2 * I, H, cap, self.fused_cfg, self.cluster_m, 1,
+                                             0, 1.0, -1.0, sm, 1, stream))
+            if events:
+                events[1].record()
+                events[2].record()
+        else:
+            ck(lib.pnv_group_mm(self.out1.data_ptr(), w["a13"].data_ptr(), w["e13"].data_ptr(), w["s13"].data_ptr(),
+                                self.b1.data_ptr(), self.sfb1.data_ptr(), self.al1.data_ptr(), self.counts.data_ptr(),
+                                E, 2 * I, H, cap, self.cfg, self.cluster_m, 1, sm, 1, stream))
+            if events:
+                events[1].record()
+            ck(lib.pnv_silu_mul_quant_act(self.out1.data_ptr(), self.g2.data_ptr(), 1, self.counts.data_ptr(), E, cap,
+                                          I, 0, 0, 1.0, -1.0, self.b2.data_ptr(), self.sfb2.data_ptr(), sm, stream))
+            if events:
+                events[2].record()
         ck(lib.pnv_group_mm(self.out2.data_ptr(), w["a2"].data_ptr(), w["e2"].data_ptr(), w["s2"].data_ptr(),
                             self.b2.data_ptr(), self.sfb2.data_ptr(), self.al2.data_ptr(), self.counts.data_ptr(),
                             E, H, I, cap, self.cfg, self.cluster_m, 1, sm, 1, stream))
@@ -244,9 +268,11 @@ def calibrate_second_scale(layer, inputs, stream):
     E = layer.E
     ones = torch.ones(E, device=layer.dev)
     layer.set_inputs(g2=ones, a2=ones, **inputs)
+    was_fused, layer.fused = layer.fused, False
     layer.step(stream)
     torch.cuda.synchronize()
-    y = torch.ops.paired_nvfp4.gated_act(layer.out1)
+    layer.fused = was_fused
+    y = torch.ops.paired_nvfp4.gated_act(layer.out1, was_fused)
     cnt = inputs["counts"].cpu().numpy()
     amax = torch.stack([y[e, :int(cnt[e])].abs().max() if cnt[e] > 0 else torch.ones((), device=layer.dev) for e in range(E)])
     g2 = (6.0 * 448.0 / amax.float().clamp(min=1e-6)).contiguous()
@@ -365,11 +391,12 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     assert wl["E"] % world == 0
     E_local = wl["E"] // world
-    layer = Layer(wl, device, config_id=args.config_id, E_local=E_local, first_expert=rank * E_local)
+    layer = Layer(wl, device, config_id=args.config_id, E_local=E_local, first_expert=rank * E_local,
+                  fused=not args.unfused)
     inputs, counts = make_activation_inputs(wl, layer, rank, world, device)
     stream = torch.cuda.current_stream().cuda_stream
     calibrate_second_scale(layer, inputs, stream)
-    acct = layer_accounting(wl, counts)
+    acct = layer_accounting(wl, counts, fused=not args.unfused)
 
     def barrier():
         if world > 1:
@@ -432,12 +459,13 @@ def main():
             "config": {"workload": f"{wl_name}: {wl['desc']}", "experts": wl["E"], "experts_per_gpu": E_local,
                        "hidden": wl["hidden"], "intermediate": wl["inter"], "cap": wl["cap"],
                        "routed_rows_rank0": acct["rows"], "tile_config": paired_nvfp4_kernels.group_mm_configs()[layer.cfg],
+                       "fused_swiglu_epilogue": layer.fused,
                        "l2": "two weight copies alternate; each step streams > 3x the 126 MB L2" if wl_name == "c2"
                              else "inputs larger than L2; two weight copies alternate"},
             "layer_us": ms_step * 1e3, "hbm_gbs_layer": acct["bytes_total"] / (ms_step * 1e-3) / 1e9,
             "kernels_us": {"group_mm_gate_up": k13 * 1e6, "silu_mul_quant_act": kq2 * 1e6, "group_mm_down": k2 * 1e6},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
-            "gpu_launches": 4 * args.steps + (1 * args.steps if layer.flat_tok is not None else 0),
+            "gpu_launches": (3 if layer.fused else 4) * args.steps,
             "clocks": clocks.summary(),
         }
         print(json.dumps(line))
@@ -466,9 +494,13 @@ def run_e2e(layer, inputs, wl, args, flops):
             b1, s1 = ops.quant_act(dev_x, layer.g1, layer.counts, 2 * I)
         else:
             b1, s1 = ops.scatter_quant_act(dev_x, layer.flat_tok, layer.dest, layer.topk_w, layer.g1, layer.counts, cap)
-        ops.group_mm(out1, w["a13"], w["e13"], w["s13"], b1, s1, layer.al1, layer.counts, 2 * I, H, layer.cfg,
-                     layer.cluster_m, 1)
-        b2, s2 = ops.silu_mul_quant_act(out1, layer.g2, layer.counts, H)
+        if layer.fused:
+            b2, s2 = ops.group_mm_swiglu_quant(w["a13"], w["e13"], w["s13"], b1, s1, layer.al1, layer.counts, layer.g2,
+                                               2 * I, H, layer.fused_cfg, layer.cluster_m, 1)
+        else:
+            ops.group_mm(out1, w["a13"], w["e13"], w["s13"], b1, s1, layer.al1, layer.counts, 2 * I, H, layer.cfg,
+                         layer.cluster_m, 1)
+            b2, s2 = ops.silu_mul_quant_act(out1, layer.g2, layer.counts, H)
         ops.group_mm(out2, w["a2"], w["e2"], w["s2"], b2, s2, layer.al2, layer.counts, H, I, layer.cfg, layer.cluster_m, 1)
         host_out.copy_(out2, non_blocking=True)
         torch.cuda.synchronize()

@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "paired_nvfp4_kernels", "libpaired_nvfp4_b200.so")
-SOURCES = ["abi.cu", "quant.cu", "compress.cu", "group_mm.cu"]
+SOURCES = ["abi.cu", "quant.cu", "compress.cu", "routing.cu", "group_mm.cu"]
 
 
 def _inputs():

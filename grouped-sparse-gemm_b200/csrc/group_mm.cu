@@ -549,6 +549,37 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const bool vec_ok = (p.M % 8) == 0;        // 16-byte stores need 16-byte aligned output rows
     int acc = 0;
     uint32_t acc_phase = 0, chunk = 0;
+    if (kFused) {
+      // Benign fill of GEMM2's scale buffer: every byte the epilogues will not write (rows at or
+      // past counts[e], K-block slop) becomes 0x38.  The epilogue warps of all CTAs share the lines;
+      // live slots are skipped, so the fill never races with a quantized scale.
+      const int KB = p.f_n / kSfBlock;
+      const long long lines = (long long)p.E * p.sfb_rt * p.f_n_kt * 32;
+      const uint32_t w4 = kBenignSf * 0x01010101u;
+      for (long long c = (long long)blockIdx.x * kEpilogueThreads + ep_tid; c < lines;
+           c += (long long)gridDim.x * kEpilogueThreads) {
+        const int rr = (int)(c & 31);
+        long long a = c >> 5;
+        const int kt = (int)(a % p.f_n_kt);
+        a /= p.f_n_kt;
+        const int r0 = (int)(a % p.sfb_rt) * 128 + rr;
+        const int cnt_e = s_counts[(int)(a / p.sfb_rt)];
+        uint8_t* line = p.f_sfb_out + c * 16;
+        if (r0 >= cnt_e) {
+          *reinterpret_cast<uint4*>(line) = make_uint4(w4, w4, w4, w4);
+        } else {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (r0 + 32 * g >= cnt_e) {
+              *reinterpret_cast<uint32_t*>(line + 4 * g) = w4;
+            } else {
+              for (int j = KB - kt * 4; j < 4; ++j)
+                if (j >= 0) line[4 * g + j] = (uint8_t)kBenignSf;
+            }
+          }
+        }
+      }
+    }
     for (long long t = blockIdx.x;; t += gridDim.x) {
       int mt, nt;
       if (!walk.seek<TILE_N>(t, mt, nt)) break;
@@ -1006,8 +1037,6 @@ extern "C" int pnv_group_mm_swiglu_quant(uint8_t* b_out, uint8_t* sfb_out, const
   if (int rc = make_gated_act(act_kind, beta, linear_beta, f.act)) return rc;
   f.b_out = b_out; f.sfb_out = sfb_out; f.gscale = gscale; f.gpe = gscale_per_expert ? 1 : 0;
   PNV_REQUIRE(experts >= 1 && max_n >= 1, "experts and max_n must be positive");
-  // every scale slot the epilogue does not write must read 1.0
-  PNV_CUDA(cudaMemsetAsync(sfb_out, kBenignSf, (size_t)sf_numel(max_n, features / 2, experts), (cudaStream_t)stream));
   const FusedKind& fk = kFusedKinds[config_id];
   return group_mm_common(b_out, &f, a_comp, e_meta, sfa, b_act, sfb, alphas, counts, experts, features, k, max_n,
                          fk.base_config, cluster_m, cluster_n, sm_count, pdl, stream, fk.name);

@@ -31,12 +31,27 @@ __device__ __forceinline__ void store_sf_line(uint8_t* line, uint32_t my_byte, i
   if ((lane & 7) == 0) *reinterpret_cast<uint32_t*>(line + (lane >> 3) * 4) = w;
 }
 
-// kGated == false: x is [E, max_n, K].  kGated == true: x is [E, max_n, 2K] holding gate and up.
-template <bool kGated>
+// Where a live row's values come from.
+//   kPlain   x is [E, max_n, K]
+//   kGated   x is [E, max_n, 2K] holding gate and up; the gated activation is applied first
+//   kPlanned x is token-order [T, K]; row (e, r) is token src_tok[e*max_n + r], optionally scaled by
+//            the router weight of routing src_route[e*max_n + r] (bf16(float(x) * float(bf16(w))))
+//   kFp4     rows are already quantized: q [T, K/2] codes and q_sf [T, K/32] scales are copied
+enum LineSource : int { kPlain = 0, kGated = 1, kPlanned = 2, kFp4 = 3 };
+
+struct PlanArgs {
+  const int* src_tok;
+  const int* src_route;
+  const float* topk_w;
+  const uint8_t* q;
+  const uint8_t* q_sf;
+};
+
+template <int kSrc>
 __global__ void __launch_bounds__(kThreads)
 quant_lines_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gscale,
                    int gscale_per_expert, const int* __restrict__ counts, int E, int max_n, int K,
-                   int interleaved, GatedAct act, uint8_t* __restrict__ b_act,
+                   int interleaved, GatedAct act, PlanArgs plan, uint8_t* __restrict__ b_act,
                    uint8_t* __restrict__ sfb) {
   pdl_wait();
   pdl_launch_dependents();
@@ -70,14 +85,36 @@ quant_lines_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
     const int k0 = kb * kSfBlock + (j & 1) * 16;
     uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
     float f0[8], f1[8];
+    if (kSrc == kFp4) {
+      // byte copy of an already quantized row: 8 code bytes per lane, the scale as stored
+      uint32_t sf_copy = kBenignSf;
+      if (live) {
+        const long long slot = (long long)e * max_n + r;
+        const long long t = plan.src_tok[slot];
+        *reinterpret_cast<uint2*>(b_act + slot * (K / 2) + k0 / 2) =
+            __ldg(reinterpret_cast<const uint2*>(plan.q + t * (K / 2) + k0 / 2));
+        sf_copy = __ldg(plan.q_sf + t * KB + kb);
+      }
+      store_sf_line(line, sf_copy, lane);
+      continue;
+    }
     if (live) {
       const long long row = (long long)e * max_n + r;
-      if (!kGated) {
-        const uint4* p = reinterpret_cast<const uint4*>(x + row * K + k0);
+      if (kSrc == kPlain || kSrc == kPlanned) {
+        const long long src_row = kSrc == kPlanned ? (long long)plan.src_tok[row] : row;
+        const uint4* p = reinterpret_cast<const uint4*>(x + src_row * K + k0);
         v0 = __ldg(p);
         v1 = __ldg(p + 1);
         unpack8(v0, f0);
         unpack8(v1, f1);
+        if (kSrc == kPlanned && plan.topk_w != nullptr) {
+          const float w = __bfloat162float(__float2bfloat16_rn(plan.topk_w[plan.src_route[row]]));
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            f0[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(f0[i], w)));
+            f1[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(f1[i], w)));
+          }
+        }
       } else {
         const __nv_bfloat16* base = x + row * (2LL * K);
         const int gate_off = interleaved ? kb * 64 + (j & 1) * 16 : k0;
@@ -168,6 +205,46 @@ scatter_quant_kernel(const __nv_bfloat16* __restrict__ a1, const long long* __re
   }
 }
 
+// quant_rows: token-order rows -> row-major codes and natural-order scales, one shared global scale.
+// One warp per (row, 256-element segment); a quad owns a block.
+__global__ void __launch_bounds__(kThreads)
+quant_rows_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gscale, long long T, int K,
+                  uint8_t* __restrict__ q, uint8_t* __restrict__ q_sf) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int segs = ceil_div_i(K, 256);
+  const int KB = K / kSfBlock;
+  const long long items = T * segs;
+  const int lane = threadIdx.x & 31;
+  const float gs = gscale[0];
+  const long long warp0 = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * kWarpsPerBlock;
+  for (long long it = warp0; it < items; it += nwarps) {
+    const long long t = it / segs;
+    const int k0 = (int)(it - t * segs) * 256 + lane * 8;
+    const bool live = k0 < K;
+    float f[8];
+    if (live) {
+      unpack8(__ldg(reinterpret_cast<const uint4*>(x + t * K + k0)), f);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    if (live) {
+      uint32_t sf_byte;
+      float inv;
+      block_scale(amax, gs, sf_byte, inv);
+      *reinterpret_cast<uint32_t*>(q + t * (K / 2) + k0 / 2) = quant8(f, inv);
+      if ((lane & 3) == 0) q_sf[t * KB + k0 / kSfBlock] = (uint8_t)sf_byte;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kThreads)
 gated_act_kernel(const __nv_bfloat16* __restrict__ x2, long long rows, int N, int interleaved,
                  GatedAct act, __nv_bfloat16* __restrict__ y) {
@@ -233,9 +310,9 @@ extern "C" int pnv_quant_act(const void* x, const float* gscale, int gscale_per_
   if (int rc = check_common(x, gscale, counts, experts, max_n, k, b_act, sfb, "K")) return rc;
   long long lines = sf_numel(max_n, k, experts) / 16;
   GatedAct act{PNV_ACT_SILU, 1.f, -1.f};
-  PNV_CUDA(launch_pdl(quant_lines_kernel<false>, dim3(grid_for(lines, sm_count)), dim3(kThreads), 0,
+  PNV_CUDA(launch_pdl(quant_lines_kernel<kPlain>, dim3(grid_for(lines, sm_count)), dim3(kThreads), 0,
                       (cudaStream_t)stream, pdl_enabled(), (const __nv_bfloat16*)x, gscale,
-                      gscale_per_expert, counts, experts, max_n, k, 0, act, b_act, sfb));
+                      gscale_per_expert, counts, experts, max_n, k, 0, act, PlanArgs{}, b_act, sfb));
   return PNV_OK;
 }
 
@@ -249,10 +326,10 @@ extern "C" int pnv_silu_mul_quant_act(const void* x2, const float* gscale, int g
   if (int rc = check_common(x2, gscale, counts, experts, max_n, n, b_act, sfb, "intermediate width N"))
     return rc;
   long long lines = sf_numel(max_n, n, experts) / 16;
-  PNV_CUDA(launch_pdl(quant_lines_kernel<true>, dim3(grid_for(lines, sm_count)), dim3(kThreads), 0,
+  PNV_CUDA(launch_pdl(quant_lines_kernel<kGated>, dim3(grid_for(lines, sm_count)), dim3(kThreads), 0,
                       (cudaStream_t)stream, pdl_enabled(), (const __nv_bfloat16*)x2, gscale,
-                      gscale_per_expert, counts, experts, max_n, n, interleaved ? 1 : 0, act, b_act,
-                      sfb));
+                      gscale_per_expert, counts, experts, max_n, n, interleaved ? 1 : 0, act, PlanArgs{},
+                      b_act, sfb));
   return PNV_OK;
 }
 
@@ -292,5 +369,49 @@ extern "C" int pnv_gated_act(const void* x2, int64_t rows, int n, int interleave
   gated_act_kernel<<<(unsigned)blocks, kThreads, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x2, (long long)rows, n, interleaved ? 1 : 0, act, (__nv_bfloat16*)y);
   PNV_CUDA(cudaGetLastError());
+  return PNV_OK;
+}
+
+extern "C" int pnv_scatter_quant_act_planned(const void* a1, const int32_t* src_tok, const int32_t* src_route,
+                                             const float* topk_weights, const float* gscale, int gscale_per_expert,
+                                             const int32_t* counts, int k, int experts, int cap, uint8_t* b_act,
+                                             uint8_t* sfb, int sm_count, pnv_stream_t stream) {
+  PNV_REQUIRE(cap > 0, "cap must be positive");
+  PNV_REQUIRE(src_tok && src_route, "null pointer argument");
+  if (int rc = check_common(a1, gscale, counts, experts, cap, k, b_act, sfb, "K")) return rc;
+  long long lines = sf_numel(cap, k, experts) / 16;
+  GatedAct act{PNV_ACT_SILU, 1.f, -1.f};
+  PlanArgs plan{src_tok, src_route, topk_weights, nullptr, nullptr};
+  PNV_CUDA(launch_pdl(quant_lines_kernel<kPlanned>, dim3(grid_for(lines, sm_count)), dim3(kThreads), 0,
+                      (cudaStream_t)stream, pdl_enabled(), (const __nv_bfloat16*)a1, gscale, gscale_per_expert,
+                      counts, experts, cap, k, 0, act, plan, b_act, sfb));
+  return PNV_OK;
+}
+
+extern "C" int pnv_quant_rows(const void* x, const float* gscale, int64_t tokens, int k, uint8_t* q, uint8_t* q_sf,
+                              int sm_count, pnv_stream_t stream) {
+  PNV_REQUIRE(k > 0 && k % kSfBlock == 0, "K must be a multiple of %d, got %d", kSfBlock, k);
+  PNV_REQUIRE(tokens >= 0, "bad token count");
+  if (tokens == 0) return PNV_OK;
+  PNV_REQUIRE(x && gscale && q && q_sf, "null pointer argument");
+  long long items = (long long)tokens * ceil_div_i(k, 256);
+  PNV_CUDA(launch_pdl(quant_rows_kernel, dim3(grid_for(items, sm_count)), dim3(kThreads), 0, (cudaStream_t)stream,
+                      pdl_enabled(), (const __nv_bfloat16*)x, gscale, (long long)tokens, k, q, q_sf));
+  return PNV_OK;
+}
+
+extern "C" int pnv_scatter_fp4_planned(const uint8_t* q, const uint8_t* q_sf, const int32_t* src_tok,
+                                       const int32_t* counts, int k, int experts, int cap, uint8_t* b_act,
+                                       uint8_t* sfb, int sm_count, pnv_stream_t stream) {
+  PNV_REQUIRE(cap > 0, "cap must be positive");
+  PNV_REQUIRE(q && q_sf && src_tok, "null pointer argument");
+  float dummy = 0.f;
+  if (int rc = check_common(q, &dummy, counts, experts, cap, k, b_act, sfb, "K")) return rc;
+  long long lines = sf_numel(cap, k, experts) / 16;
+  GatedAct act{PNV_ACT_SILU, 1.f, -1.f};
+  PlanArgs plan{src_tok, nullptr, nullptr, q, q_sf};
+  PNV_CUDA(launch_pdl(quant_lines_kernel<kFp4>, dim3(grid_for(lines, sm_count)), dim3(kThreads), 0,
+                      (cudaStream_t)stream, pdl_enabled(), (const __nv_bfloat16*)nullptr, (const float*)nullptr, 0,
+                      counts, experts, cap, k, 0, act, plan, b_act, sfb));
   return PNV_OK;
 }

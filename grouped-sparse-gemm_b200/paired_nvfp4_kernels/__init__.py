@@ -43,6 +43,14 @@ def _register():
                "-> (Tensor, Tensor)")
     lib.define("scatter_quant_act(Tensor a1, Tensor flat_tok, Tensor dest_global, Tensor? topk_weights, "
                "Tensor gscale, Tensor expert_num_tokens, int cap) -> (Tensor, Tensor)")
+    lib.define("dispatch_plan(Tensor topk_ids, int first_expert, int num_local_experts, int cap) "
+               "-> (Tensor, Tensor, Tensor, Tensor)")
+    lib.define("scatter_quant_act_planned(Tensor a1, Tensor src_tok, Tensor src_route, Tensor? topk_weights, "
+               "Tensor gscale, Tensor expert_num_tokens, int cap) -> (Tensor, Tensor)")
+    lib.define("quant_rows(Tensor x, Tensor gscale) -> (Tensor, Tensor)")
+    lib.define("scatter_fp4_planned(Tensor q, Tensor q_sf, Tensor src_tok, Tensor expert_num_tokens, int cap) "
+               "-> (Tensor, Tensor)")
+    lib.define("moe_finalize(Tensor(a!) out, Tensor fused, Tensor route_dest, Tensor? topk_weights) -> ()")
     lib.define("group_mm(Tensor(a!) out, Tensor a_comp, Tensor e_meta, Tensor sfa, Tensor b_act, Tensor sfb, "
                "Tensor alphas, Tensor expert_num_tokens, int features, int k, "
                f"int config_id={DEFAULT_TACTIC[0]}, int cluster_m={DEFAULT_TACTIC[1]}, "
@@ -59,6 +67,11 @@ def _register():
     lib.impl("quant_act", ops.quant_act, "CUDA")
     lib.impl("silu_mul_quant_act", ops.silu_mul_quant_act, "CUDA")
     lib.impl("scatter_quant_act", ops.scatter_quant_act, "CUDA")
+    lib.impl("dispatch_plan", ops.dispatch_plan, "CUDA")
+    lib.impl("scatter_quant_act_planned", ops.scatter_quant_act_planned, "CUDA")
+    lib.impl("quant_rows", ops.quant_rows, "CUDA")
+    lib.impl("scatter_fp4_planned", ops.scatter_fp4_planned, "CUDA")
+    lib.impl("moe_finalize", ops.moe_finalize, "CUDA")
     lib.impl("group_mm", ops.group_mm, "CUDA")
     lib.impl("gated_act", ops.gated_act, "CUDA")
     lib.impl("group_mm_swiglu_quant", ops.group_mm_swiglu_quant, "CUDA")

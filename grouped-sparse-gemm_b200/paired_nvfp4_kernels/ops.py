@@ -160,6 +160,126 @@ def scatter_quant_act(a1, flat_tok, dest_global, topk_weights, gscale, expert_nu
     return b_act, sfb
 
 
+def dispatch_plan(topk_ids, first_expert, num_local_experts, cap):
+    """csrc/ops.cu:374-411.  Returns (expert_num_tokens, route_dest, src_tok, src_route)."""
+    _check(topk_ids.is_cuda, "topk_ids must be CUDA")
+    _check(topk_ids.dim() == 2 and topk_ids.is_contiguous(), "topk_ids must be contiguous [T, topk]")
+    _check(topk_ids.dtype in (torch.int32, torch.int64), "topk_ids must be int32 or int64")
+    E = int(num_local_experts)
+    _check(1 <= E <= 4096, lambda: f"num_local_experts must be in [1, 4096], got {E}")
+    _check(cap >= 1, "cap must be positive")
+    _check(E * cap < (1 << 31), "E * cap must fit int32")
+    T, topk = topk_ids.shape
+    _check(T * topk < (1 << 31), "T * topk must fit int32")
+    i32 = dict(dtype=torch.int32, device=topk_ids.device)
+    counts = torch.empty((E,), **i32)
+    route_dest = torch.empty((T, topk), **i32)
+    src_tok = torch.empty((E * cap,), **i32)
+    src_route = torch.empty((E * cap,), **i32)
+    n_scratch = int(_lib.pnv_dispatch_plan_scratch_ints(T * topk, E))
+    scratch = torch.empty((max(n_scratch, 1),), **i32)
+    with torch.cuda.device(topk_ids.device):
+        _cabi.check(_lib.pnv_dispatch_plan(topk_ids.data_ptr(), 1 if topk_ids.dtype == torch.int64 else 0, T, topk,
+                                           int(first_expert), E, int(cap), counts.data_ptr(), route_dest.data_ptr(),
+                                           src_tok.data_ptr(), src_route.data_ptr(), scratch.data_ptr(),
+                                           _stream(topk_ids)))
+    return counts, route_dest, src_tok, src_route
+
+
+def scatter_quant_act_planned(a1, src_tok, src_route, topk_weights, gscale, expert_num_tokens, cap):
+    """csrc/ops.cu:418-468."""
+    _check(a1.is_cuda and src_tok.is_cuda and src_route.is_cuda and gscale.is_cuda and expert_num_tokens.is_cuda,
+           "inputs must be CUDA")
+    _check_arch(a1)
+    _check(a1.dim() == 2, "a1 must be [T, K] (token-order hidden states)")
+    _check(a1.dtype == torch.bfloat16 and a1.is_contiguous(), "a1 must be contiguous bf16")
+    K = a1.size(1)
+    _check(K % SF_BLOCK == 0, lambda: f"K must be a multiple of {SF_BLOCK}, got {K}")
+    E = expert_num_tokens.numel()
+    _check_gscale_counts(gscale, expert_num_tokens, E)
+    _check(cap > 0, "cap must be positive")
+    _check(src_tok.dtype == torch.int32 and src_route.dtype == torch.int32 and src_tok.is_contiguous()
+           and src_route.is_contiguous() and src_tok.numel() == E * cap and src_route.numel() == E * cap,
+           "src_tok and src_route must be contiguous int32 [E * cap] (dispatch_plan output)")
+    w_ptr = None
+    if topk_weights is not None:
+        _check(topk_weights.is_cuda and topk_weights.dtype == torch.float32 and topk_weights.is_contiguous(),
+               "topk_weights must be contiguous float32 [T * topk]")
+        w_ptr = topk_weights.data_ptr()
+    b_act = torch.empty((E, cap, K // 2), dtype=torch.uint8, device=a1.device)
+    sfb = torch.empty((_cabi.sf_numel(cap, K, E),), dtype=torch.uint8, device=a1.device)
+    with torch.cuda.device(a1.device):
+        _cabi.check(_lib.pnv_scatter_quant_act_planned(
+            a1.data_ptr(), src_tok.data_ptr(), src_route.data_ptr(), w_ptr, gscale.data_ptr(),
+            1 if gscale.numel() == E else 0, expert_num_tokens.data_ptr(), K, E, int(cap), b_act.data_ptr(),
+            sfb.data_ptr(), _device_info(a1.device)[1], _stream(a1)))
+    return b_act, sfb
+
+
+def quant_rows(x, gscale):
+    """csrc/ops.cu:476-500."""
+    _check(x.is_cuda and gscale.is_cuda, "inputs must be CUDA")
+    _check_arch(x)
+    _check(x.dim() == 2 and x.dtype == torch.bfloat16 and x.is_contiguous(), "x must be contiguous bf16 [T, K]")
+    T, K = x.shape
+    _check(K % SF_BLOCK == 0, lambda: f"K must be a multiple of {SF_BLOCK}, got {K}")
+    _check(gscale.dtype == torch.float32 and gscale.numel() >= 1,
+           "gscale must be float32 with the shared global scale first")
+    q = torch.empty((T, K // 2), dtype=torch.uint8, device=x.device)
+    sf = torch.empty((T, K // SF_BLOCK), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _cabi.check(_lib.pnv_quant_rows(x.data_ptr(), gscale.data_ptr(), T, K, q.data_ptr(), sf.data_ptr(),
+                                        _device_info(x.device)[1], _stream(x)))
+    return q, sf
+
+
+def scatter_fp4_planned(q, q_sf, src_tok, expert_num_tokens, cap):
+    """csrc/ops.cu:502-541."""
+    _check(q.is_cuda and q_sf.is_cuda and src_tok.is_cuda and expert_num_tokens.is_cuda, "inputs must be CUDA")
+    _check_arch(q)
+    _check(q.dim() == 2 and q.dtype == torch.uint8 and q.is_contiguous(),
+           "q must be contiguous uint8 [T, K/2] (quant_rows output)")
+    K = q.size(1) * 2
+    _check(K % SF_BLOCK == 0, lambda: f"K must be a multiple of {SF_BLOCK}, got {K}")
+    _check(q_sf.dim() == 2 and q_sf.size(0) == q.size(0) and q_sf.size(1) == K // SF_BLOCK and q_sf.element_size() == 1
+           and q_sf.is_contiguous(), lambda: f"q_sf must be contiguous 1-byte [T, K/{SF_BLOCK}] (quant_rows output)")
+    E = expert_num_tokens.numel()
+    _check(expert_num_tokens.dtype == torch.int32 and expert_num_tokens.is_contiguous(),
+           "expert_num_tokens must be contiguous int32 [E]")
+    _check(cap > 0, "cap must be positive")
+    _check(src_tok.dtype == torch.int32 and src_tok.is_contiguous() and src_tok.numel() == E * cap,
+           "src_tok must be contiguous int32 [E * cap] (dispatch_plan output)")
+    b_act = torch.empty((E, cap, K // 2), dtype=torch.uint8, device=q.device)
+    sfb = torch.empty((_cabi.sf_numel(cap, K, E),), dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        _cabi.check(_lib.pnv_scatter_fp4_planned(q.data_ptr(), q_sf.data_ptr(), src_tok.data_ptr(),
+                                                 expert_num_tokens.data_ptr(), K, E, int(cap), b_act.data_ptr(),
+                                                 sfb.data_ptr(), _device_info(q.device)[1], _stream(q)))
+    return b_act, sfb
+
+
+def moe_finalize(out, fused, route_dest, topk_weights):
+    """csrc/ops.cu:548-575.  Mutates `out` in place."""
+    _check(out.is_cuda and fused.is_cuda and route_dest.is_cuda, "inputs must be CUDA")
+    _check(out.dim() == 2 and out.dtype == torch.bfloat16 and out.is_contiguous(), "out must be contiguous bf16 [T, K]")
+    _check(fused.dtype == torch.bfloat16 and fused.is_contiguous() and fused.dim() >= 2,
+           "fused must be contiguous bf16 [E, cap, K] (or [E * cap, K])")
+    T, K = out.shape
+    _check(fused.size(-1) == K, "fused and out must share K")
+    _check(K % 8 == 0, "K must be a multiple of 8")
+    _check(route_dest.dtype == torch.int32 and route_dest.is_contiguous() and route_dest.dim() == 2
+           and route_dest.size(0) == T, "route_dest must be contiguous int32 [T, topk] (dispatch_plan output)")
+    topk = route_dest.size(1)
+    w_ptr = None
+    if topk_weights is not None:
+        _check(topk_weights.is_cuda and topk_weights.dtype == torch.float32 and topk_weights.is_contiguous()
+               and topk_weights.numel() == T * topk, "topk_weights must be contiguous float32 [T, topk]")
+        w_ptr = topk_weights.data_ptr()
+    with torch.cuda.device(out.device):
+        _cabi.check(_lib.pnv_moe_finalize(out.data_ptr(), fused.data_ptr(), route_dest.data_ptr(), w_ptr, T, topk, K,
+                                          _stream(out)))
+
+
 def gated_act(x2, interleaved=False, activation="silu", beta=1.0, linear_beta=-1.0):
     """The unfused gated activation (gated_act, csrc/layout.cuh:204-216): bf16 [..., 2N] -> [..., N]."""
     _check(x2.is_cuda and x2.dtype == torch.bfloat16 and x2.is_contiguous(), "x2 must be contiguous CUDA bf16")

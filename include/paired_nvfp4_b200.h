@@ -105,6 +105,45 @@ int pnv_scatter_quant_act(const void* a1, const int64_t* flat_tok, const int64_t
                           int64_t n_routes, int k, int experts, int cap, uint8_t* b_act,
                           uint8_t* sfb, int sm_count, pnv_stream_t stream);
 
+/* ---- routing plan, planned scatter, FP4-on-the-wire helpers, combine ------------------------------ */
+
+/* paired_nvfp4_dispatch_plan (csrc/ops.cu:374-411 -> dispatch_plan, csrc/moe_routing.cuh:93-193).
+ * topk_ids i32 or i64 [tokens, topk] global expert ids; this rank owns experts
+ * [first_expert, first_expert + num_local_experts).  Writes counts i32[E] (clamped to cap),
+ * route_dest i32[tokens * topk] (row e*cap + r, or -1), and src_tok / src_route i32[E * cap] for the
+ * assigned rows (other slots are not written).  Plans of more than 1024 routings need `scratch`:
+ * pnv_dispatch_plan_scratch_ints(tokens * topk, E) ints (the reference allocates the same buffer inside
+ * the op, csrc/ops.cu:397-398); smaller plans accept NULL. */
+int64_t pnv_dispatch_plan_scratch_ints(int64_t n_routes, int num_local_experts);
+int pnv_dispatch_plan(const void* topk_ids, int ids_are_int64, int64_t tokens, int topk, int first_expert,
+                      int num_local_experts, int cap, int32_t* counts, int32_t* route_dest,
+                      int32_t* src_tok, int32_t* src_route, int32_t* scratch, pnv_stream_t stream);
+
+/* paired_nvfp4_scatter_quant_act_planned (csrc/ops.cu:418-468 -> scatter_quant_planned_kernel,
+ * csrc/quant.cuh:431-471).  a1 bf16[T, K]; src_tok / src_route from pnv_dispatch_plan; topk_weights
+ * f32[T * topk] or NULL.  Outputs as pnv_quant_act with max_n = cap. */
+int pnv_scatter_quant_act_planned(const void* a1, const int32_t* src_tok, const int32_t* src_route,
+                                  const float* topk_weights, const float* gscale, int gscale_per_expert,
+                                  const int32_t* counts, int k, int experts, int cap, uint8_t* b_act,
+                                  uint8_t* sfb, int sm_count, pnv_stream_t stream);
+
+/* paired_nvfp4_quant_rows (csrc/ops.cu:476-500 -> quant_rows_kernel, csrc/quant.cuh:492-508).
+ * x bf16[tokens, K] -> q u8[tokens, K/2], q_sf u8[tokens, K/32] (natural order), scale gscale[0]. */
+int pnv_quant_rows(const void* x, const float* gscale, int64_t tokens, int k, uint8_t* q, uint8_t* q_sf,
+                   int sm_count, pnv_stream_t stream);
+
+/* paired_nvfp4_scatter_fp4_planned (csrc/ops.cu:502-541 -> scatter_fp4_planned_kernel,
+ * csrc/quant.cuh:525-552): places pnv_quant_rows output into the batched operands. */
+int pnv_scatter_fp4_planned(const uint8_t* q, const uint8_t* q_sf, const int32_t* src_tok,
+                            const int32_t* counts, int k, int experts, int cap, uint8_t* b_act,
+                            uint8_t* sfb, int sm_count, pnv_stream_t stream);
+
+/* paired_nvfp4_moe_finalize (csrc/ops.cu:548-575 -> finalize_kernel, csrc/moe_routing.cuh:203-244).
+ * out bf16[tokens, K] = sum over kept routings in top-k order of fused bf16[E * cap, K] rows
+ * (route_dest i32[tokens, topk], -1 = dropped), weighted by topk_weights f32[tokens, topk] when given. */
+int pnv_moe_finalize(void* out, const void* fused, const int32_t* route_dest, const float* topk_weights,
+                     int64_t tokens, int topk, int k, pnv_stream_t stream);
+
 /* The unfused gated activation the quantizer above folds in (gated_act, csrc/layout.cuh:204-216;
  * device replica ref_silu_mul_kernel, csrc/testing/selftest.cu:750-760): y bf16[rows, n] from
  * x2 bf16[rows, 2n].  pnv_silu_mul_quant_act == pnv_gated_act followed by pnv_quant_act, byte for

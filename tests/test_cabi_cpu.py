@@ -41,7 +41,9 @@ def test_size_queries_match_oracle(pnk):
 
 def test_ops_registered_with_reference_schemas(pnk):
     ns = torch.ops.paired_nvfp4
-    for op in ("compress", "quant_act", "silu_mul_quant_act", "scatter_quant_act", "group_mm", "group_mm_configs"):
+    for op in ("compress", "quant_act", "silu_mul_quant_act", "scatter_quant_act", "group_mm", "group_mm_configs",
+               "dispatch_plan", "scatter_quant_act_planned", "quant_rows", "scatter_fp4_planned", "moe_finalize",
+               "group_mm_swiglu_quant", "group_mm_swiglu_configs"):
         assert hasattr(ns, op), op
     schema = str(ns.group_mm.default._schema)
     cid, cm, cn = pnk.DEFAULT_TACTIC
