@@ -11,6 +11,8 @@
 //
 // moe_finalize: out[t] = sum over kept routings, in top-k order, of the expert output rows,
 // optionally weighted with torch's rounding chain; one thread per 8 output columns.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace pnv {
@@ -135,6 +137,30 @@ int run_plan(const IdT* ids, long long n, int topk, int first, int E, int cap, i
   return PNV_OK;
 }
 
+// Built-in scratch for pnv_dispatch_plan_noalloc: per-chunk expert totals, chunks * E ints, at most
+// kBuiltinScratchInts (256 KiB).  It lives in every GPU that loads the library until the process
+// exits.  In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+constexpr int kBuiltinScratchInts = 65536;
+static __device__ __align__(256) int g_plan_scratch[kBuiltinScratchInts];
+
+// Device address of g_plan_scratch on the current device, looked up once per device.
+int builtin_scratch(int** out) {
+  static std::mutex mu;
+  static int* ptrs[64] = {};
+  int dev = 0;
+  PNV_CUDA(cudaGetDevice(&dev));
+  PNV_REQUIRE(dev >= 0 && dev < 64, "unexpected CUDA device index %d", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    int* p = nullptr;
+    PNV_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_plan_scratch));
+    PNV_REQUIRE(p != nullptr, "cudaGetSymbolAddress returned a null address for the built-in scratch");
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return PNV_OK;
+}
+
 constexpr int kFinThreads = 128;
 
 __global__ void __launch_bounds__(kFinThreads)
@@ -192,6 +218,26 @@ extern "C" int pnv_dispatch_plan(const void* topk_ids, int ids_are_int64, int64_
                     route_dest, src_tok, src_route, scratch, s);
   return run_plan(static_cast<const int*>(topk_ids), n, topk, first_expert, num_local_experts, cap, counts, route_dest,
                   src_tok, src_route, scratch, s);
+}
+
+extern "C" int64_t pnv_dispatch_plan_noalloc_max_scratch_ints(void) { return kBuiltinScratchInts; }
+
+extern "C" int pnv_dispatch_plan_noalloc(const void* topk_ids, int ids_are_int64, int64_t tokens, int topk,
+                                         int first_expert, int num_local_experts, int cap, int32_t* counts,
+                                         int32_t* route_dest, int32_t* src_tok, int32_t* src_route,
+                                         pnv_stream_t stream) {
+  PNV_REQUIRE(tokens >= 0 && topk >= 1 && num_local_experts >= 1, "bad token count, topk or expert count");
+  const int64_t need = pnv_dispatch_plan_scratch_ints(tokens * topk, num_local_experts);
+  PNV_REQUIRE(need <= kBuiltinScratchInts,
+              "dispatch_plan_noalloc: %lld routings over %d local experts need %lld scratch ints, the built-in "
+              "scratch holds %d; use pnv_dispatch_plan with a caller-provided buffer",
+              (long long)(tokens * topk), num_local_experts, (long long)need, kBuiltinScratchInts);
+  int* scratch = nullptr;
+  if (int rc = builtin_scratch(&scratch)) return rc;
+  // Nothing in the scratch has to start at zero: the tally pass writes every total of every chunk
+  // this plan uses before the scan reads it, so whatever an earlier call left behind is ignored.
+  return pnv_dispatch_plan(topk_ids, ids_are_int64, tokens, topk, first_expert, num_local_experts, cap, counts,
+                           route_dest, src_tok, src_route, scratch, stream);
 }
 
 extern "C" int pnv_moe_finalize(void* out, const void* fused, const int32_t* route_dest, const float* topk_weights,

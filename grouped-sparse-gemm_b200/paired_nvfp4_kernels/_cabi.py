@@ -31,6 +31,8 @@ SIGNATURES = {
     "pnv_scatter_quant_act": (_i, [_p, _p, _p, _p, _p, _i, _i64, _i, _i, _i, _p, _p, _i, _p]),
     "pnv_dispatch_plan_scratch_ints": (_i64, [_i64, _i]),
     "pnv_dispatch_plan": (_i, [_p, _i, _i64, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p]),
+    "pnv_dispatch_plan_noalloc_max_scratch_ints": (_i64, []),
+    "pnv_dispatch_plan_noalloc": (_i, [_p, _i, _i64, _i, _i, _i, _i, _p, _p, _p, _p, _p]),
     "pnv_scatter_quant_act_planned": (_i, [_p, _p, _p, _p, _p, _i, _p, _i, _i, _i, _p, _p, _i, _p]),
     "pnv_quant_rows": (_i, [_p, _p, _i64, _i, _p, _p, _i, _p]),
     "pnv_scatter_fp4_planned": (_i, [_p, _p, _p, _p, _i, _i, _i, _p, _p, _i, _p]),

@@ -119,6 +119,25 @@ int pnv_dispatch_plan(const void* topk_ids, int ids_are_int64, int64_t tokens, i
                       int num_local_experts, int cap, int32_t* counts, int32_t* route_dest,
                       int32_t* src_tok, int32_t* src_route, int32_t* scratch, pnv_stream_t stream);
 
+/* pnv_dispatch_plan without any allocation, by anyone.  It has no counterpart in the reference.
+ * The plan's scratch (per-chunk expert totals) lives in an array built into the library instead of a
+ * caller buffer, for callers that cannot obtain device memory at call time: a serving process that
+ * handed the whole GPU to its own arena at start-up, or a latency-critical loop that must not take
+ * cudaMalloc's device-wide stall.  Inputs and outputs are still the caller's.
+ *   - Limit: ceil(tokens * topk / 1024) * num_local_experts <= pnv_dispatch_plan_noalloc_max_scratch_ints()
+ *     (65536 ints = 256 KiB, resident on every GPU that loads the library); larger plans are rejected
+ *     with PNV_ERR_INVALID_ARGUMENT and a message naming the limit.
+ *   - The first call on each device looks up the array's device address (no allocation); make that call
+ *     before starting any stream capture on the device.
+ *   - All calls on a device share the one array, and it keeps the previous call's contents.  Nothing
+ *     in it needs clearing (every value a plan reads was written by that plan first), but two calls
+ *     whose kernels overlap on the GPU - different streams, no ordering between them - race on it. */
+int64_t pnv_dispatch_plan_noalloc_max_scratch_ints(void);
+int pnv_dispatch_plan_noalloc(const void* topk_ids, int ids_are_int64, int64_t tokens, int topk,
+                              int first_expert, int num_local_experts, int cap, int32_t* counts,
+                              int32_t* route_dest, int32_t* src_tok, int32_t* src_route,
+                              pnv_stream_t stream);
+
 /* paired_nvfp4_scatter_quant_act_planned (csrc/ops.cu:418-468 -> scatter_quant_planned_kernel,
  * csrc/quant.cuh:431-471).  a1 bf16[T, K]; src_tok / src_route from pnv_dispatch_plan; topk_weights
  * f32[T * topk] or NULL.  Outputs as pnv_quant_act with max_n = cap. */
