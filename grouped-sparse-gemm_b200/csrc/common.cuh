@@ -169,16 +169,17 @@ struct GatedAct {
   float linear_beta;
 };
 
+static __device__ __noinline__ float situ_act(float g, float u, float beta, float linear_beta) {
+  float inv_beta = __fdiv_rn(1.0f, beta);
+  float gate_out = __fmul_rn(__fmul_rn(__fmul_rn(0.5f, beta), tanhf(__fmul_rn(g, inv_beta))),
+                             __fadd_rn(1.0f, tanhf(__fmul_rn(g, 0.5f))));
+  float up_out = linear_beta > 0.0f ? __fmul_rn(linear_beta, tanhf(__fmul_rn(u, __fdiv_rn(1.0f, linear_beta)))) : u;
+  return __bfloat162float(__float2bfloat16_rn(__fmul_rn(gate_out, up_out)));
+}
+
+// SiLU is the hot case and stays inline; SiTU is a call, so a caller's unrolled loop stays small.
 __device__ __forceinline__ float gated_act(float g, float u, const GatedAct& a) {
-  if (a.kind == PNV_ACT_SITU) {
-    float inv_beta = __fdiv_rn(1.0f, a.beta);
-    float gate_out = __fmul_rn(__fmul_rn(__fmul_rn(0.5f, a.beta), tanhf(__fmul_rn(g, inv_beta))),
-                               __fadd_rn(1.0f, tanhf(__fmul_rn(g, 0.5f))));
-    float up_out = a.linear_beta > 0.0f
-                       ? __fmul_rn(a.linear_beta, tanhf(__fmul_rn(u, __fdiv_rn(1.0f, a.linear_beta))))
-                       : u;
-    return __bfloat162float(__float2bfloat16_rn(__fmul_rn(gate_out, up_out)));
-  }
+  if (a.kind == PNV_ACT_SITU) return situ_act(g, u, a.beta, a.linear_beta);
   float s = __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
   float s_bf = __bfloat162float(__float2bfloat16_rn(s));
   return __bfloat162float(__float2bfloat16_rn(__fmul_rn(s_bf, u)));

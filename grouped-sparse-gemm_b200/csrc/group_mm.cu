@@ -102,7 +102,6 @@ struct Cfg {
 };
 
 struct Params {
-  const uint8_t* a_comp;   // only for L2 prefetch; the tiles themselves come through map_a
   const uint8_t* e_meta;
   const uint8_t* sfa;
   const uint8_t* sfb;
@@ -116,12 +115,7 @@ struct Params {
   int e_k_atoms;     // metadata atoms along K = ceil(K / 256)
   int e_m_atoms;     // metadata atoms along M = n_mt
   int sfb_rt;        // scale row-atoms per expert in sfb = ceil(max_n / 128)
-  int a_row_bytes;   // bytes per a_comp row
-  int prefetch;      // issue L2 prefetches of the next tile's weight rows
   int stages;        // pipeline depth in use (<= Cfg::kStages)
-  int group;         // stages the tile producer fills concurrently (1 = one at a time)
-  int a_box_rows;    // rows per weight TMA box (128, or 32 when group > 1)
-  int skip;          // experiment knob (timing only, results invalid): 1 no B, 2 no E, 4 no SFA, 8 no SFB, 16 no cp, 32 no MMA
   // fused SwiGLU + requantise epilogue (kFused kernels): GEMM2's operands instead of a bf16 output
   uint8_t* f_b_out;        // [E, max_n, N/2] e2m1 codes, N = M / 2
   uint8_t* f_sfb_out;      // swizzled scales for (max_n, N), pre-filled with 0x38
@@ -152,9 +146,10 @@ struct TileWalk {
       if (++e >= E) return false;
       tiles_e = (long long)n_mt * ceil_div_i(cnt[e], TILE_N);
     }
-    long long local = t - base;
-    mt = (int)(local % n_mt);
-    nt = (int)(local / n_mt);
+    // an expert's own tile count fits 32 bits (its output alone would otherwise exceed the device)
+    const unsigned local = (unsigned)(t - base);
+    nt = (int)(local / (unsigned)n_mt);
+    mt = (int)(local - (unsigned)nt * (unsigned)n_mt);
     return true;
   }
 };
@@ -244,74 +239,17 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   if (warp == 0) {
     // =============================== tile producer (TMA) ===============================
-    // All 32 lanes walk the tile list.  Before lane 0 issues a tile's loads, every lane asks L2 to
-    // fetch four whole weight rows of the CTA's *next* tile: each row is one contiguous run of
-    // K/4 bytes, so DRAM sees long bursts, and the 128-byte-wide TMA box rows that follow one
-    // tile later hit L2 instead of opening a DRAM page for 128 bytes at a time.
-    TileWalk ahead = walk;
-    auto prefetch_tile = [&](long long t) {
-      int pmt, pnt;
-      if (!p.prefetch || !ahead.seek<TILE_N>(t, pmt, pnt)) return;
-      if (pnt != 0) return;   // the rows of later token tiles were fetched with the first one
-      const uint8_t* rows = p.a_comp + ((long long)ahead.e * p.M + (long long)pmt * kTileM) * p.a_row_bytes;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int r = lane + 32 * j;
-        if (pmt * kTileM + r < p.M) ptx::prefetch_l2(rows + (long long)r * p.a_row_bytes, p.a_row_bytes);
-      }
-    };
-    prefetch_tile(blockIdx.x);
-    {
+    if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0, dphase = 0;
       (void)dphase;
       bool ok = true;
-      for (long long t = blockIdx.x;; t += gridDim.x) {
-        // lane 0 owns the pipeline state; the other lanes follow its verdict and idle at the shuffle
-        if (__shfl_sync(0xffffffffu, ok ? 1 : 0, 0) == 0) break;
+      for (long long t = blockIdx.x; ok; t += gridDim.x) {
         int mt, nt;
         if (!walk.seek<TILE_N>(t, mt, nt)) break;
-        prefetch_tile(t + gridDim.x);
-        if (lane != 0) continue;
         const int e = walk.e;
         const int n0 = nt * TILE_N;
-        if (!kTrace && p.group > 1) {
-          // Group fill: claim up to `group` stages, then issue the weight boxes row-group-major
-          // (32 rows at a time, all claimed stages for those rows back to back), so that the
-          // consecutive 128-byte pieces of a weight row are requested together.
-          for (int ks0 = 0; ks0 < p.k_stages && ok; ks0 += p.group) {
-            const int gn = min(p.group, p.k_stages - ks0);
-            int s = stage;
-            uint32_t ph = phase;
-            for (int g = 0; g < gn; ++g) {
-              if (!ptx::mbar_wait(empty_bar + s, ph ^ 1)) {
-                atomicExch(&g_status, kProducerEmptyTimeout);
-                ok = false;
-                break;
-              }
-              const int k_atoms = min(C::kAtoms, p.n_kt - (ks0 + g) * C::kAtoms);
-              const int b_boxes = (k_atoms + 1) / 2;
-              uint8_t* st = stage_base + s * C::kStageBytes;
-              ptx::mbar_arrive_expect_tx(full_bar + s, C::kABytes + b_boxes * C::kBBoxBytes);
-              for (int b = 0; b < b_boxes; ++b)
-                ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + s,
-                                 (ks0 + g) * (STAGE_K / 2) + b * 128, n0, e);
-              if (++s == p.stages) { s = 0; ph ^= 1; }
-            }
-            if (!ok) break;
-            for (int rg = 0; rg < kTileM / 32; ++rg) {
-              int s2 = stage;
-              for (int g = 0; g < gn; ++g) {
-                ptx::tma_load_3d(stage_base + s2 * C::kStageBytes + C::kOffA + rg * 32 * C::kARowBytes, &map_a,
-                                 full_bar + s2, (ks0 + g) * C::kARowBytes, mt * kTileM + rg * 32, e);
-                if (++s2 == p.stages) s2 = 0;
-              }
-            }
-            stage = s;
-            phase = ph;
-          }
-          continue;
-        }
+#pragma unroll 1
         for (int ks = 0; ks < p.k_stages; ++ks) {
           long long tq0 = p.prof ? clock64() : 0;
           if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1)) {
@@ -324,10 +262,9 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
           const int b_boxes = (k_atoms + 1) / 2;
           if (!kTrace) {
-            const int bb = (p.skip & 1) ? 0 : b_boxes;
-            ptx::mbar_arrive_expect_tx(full_bar + stage, C::kABytes + bb * C::kBBoxBytes);
+            ptx::mbar_arrive_expect_tx(full_bar + stage, C::kABytes + b_boxes * C::kBBoxBytes);
             ptx::tma_load_3d(st + C::kOffA, &map_a, full_bar + stage, ks * C::kARowBytes, mt * kTileM, e);
-            for (int b = 0; b < bb; ++b)
+            for (int b = 0; b < b_boxes; ++b)
               ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + stage,
                                ks * (STAGE_K / 2) + b * 128, n0, e);
           } else {
@@ -356,8 +293,9 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
       }
-      if (!ok && lane == 0) {
+      if (!ok) {
         // give copies already in flight time to land before the CTA's shared memory is released
+#pragma unroll 1
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);
       }
     }
@@ -390,16 +328,13 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const uint32_t sf_bytes = 512u * k_atoms;
           const uint8_t* sfa_src = sfa_base + (long long)ks * C::kAtoms * 512;
           if (!kTrace) {
-            const int ne = (p.skip & 2) ? 0 : e_atoms;
-            const int nsa = (p.skip & 4) ? 0 : 1;
-            const int nsb = (p.skip & 8) ? 0 : sfb_row_atoms;
-            ptx::mbar_arrive_expect_tx(full_bar + stage, ne * 2048 + sf_bytes * (nsa + nsb));
-            for (int ea = 0; ea < ne; ++ea)
+            ptx::mbar_arrive_expect_tx(full_bar + stage, e_atoms * 2048 + sf_bytes * (1 + sfb_row_atoms));
+            for (int ea = 0; ea < e_atoms; ++ea)
               ptx::bulk_load(st + C::kOffE + ea * 2048,
                              e_base + (long long)(ks * C::kEAtoms + ea) * p.e_m_atoms * 2048, 2048,
                              full_bar + stage);
-            if (nsa) ptx::bulk_load(st + C::kOffSfa, sfa_src, sf_bytes, full_bar + stage);
-            for (int ra = 0; ra < nsb; ++ra)
+            ptx::bulk_load(st + C::kOffSfa, sfa_src, sf_bytes, full_bar + stage);
+            for (int ra = 0; ra < sfb_row_atoms; ++ra)
               ptx::bulk_load(st + C::kOffSfb + ra * C::kSfaBytes,
                              sfb_base + ((long long)ra * p.n_kt + ks * C::kAtoms) * 512, sf_bytes,
                              full_bar + stage);
@@ -434,6 +369,7 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
       }
       if (!ok) {
+#pragma unroll 1
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);
       }
     }
@@ -488,7 +424,7 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               CRUMB(2, code + (done ? 1 : 2));
             }
           };
-          if (ka0 < k_atoms && !(p.skip & 16)) {
+          if (ka0 < k_atoms) {
             // metadata atoms covering this issuer's K-blocks, into its private columns
 #pragma unroll
             for (int i = 0; i < C::kEAtomsPerIssuer; ++i) {
@@ -501,7 +437,7 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
           for (int i = 0; i < kPer; ++i) {
             const int ka = ka0 + i;
-            if (ka < k_atoms && !(p.skip & 16)) {
+            if (ka < k_atoms) {
               ptx::tc_cp_32x128b_warpx4(tmem_base + kColSfa + ka * 4,
                                         ptx::smem_desc(st + C::kOffSfa + ka * 512, 128, 0, 0));
 #pragma unroll
@@ -515,7 +451,7 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
           for (int i = 0; i < kPer; ++i) {
             const int ka = ka0 + i;
-            if (ka < k_atoms && !(p.skip & 32)) {
+            if (ka < k_atoms) {
               const uint64_t a_desc = ptx::smem_desc(st + C::kOffA + ka * 32, 8 * C::kARowBytes, 16, C::kASwizzle);
               const uint64_t b_desc =
                   ptx::smem_desc(st + C::kOffB + (ka >> 1) * C::kBBoxBytes + (ka & 1) * 64, 1024, 16, 2);
@@ -554,17 +490,18 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       // past counts[e], K-block slop) becomes 0x38.  The epilogue warps of all CTAs share the lines;
       // live slots are skipped, so the fill never races with a quantized scale.
       const int KB = p.f_n / kSfBlock;
-      const long long lines = (long long)p.E * p.sfb_rt * p.f_n_kt * 32;
+      const unsigned lines = (unsigned)p.E * p.sfb_rt * p.f_n_kt * 32u;   // < 2^27, checked by the host
       const uint32_t w4 = kBenignSf * 0x01010101u;
-      for (long long c = (long long)blockIdx.x * kEpilogueThreads + ep_tid; c < lines;
-           c += (long long)gridDim.x * kEpilogueThreads) {
+#pragma unroll 1
+      for (unsigned c = blockIdx.x * kEpilogueThreads + ep_tid; c < lines; c += gridDim.x * kEpilogueThreads) {
         const int rr = (int)(c & 31);
-        long long a = c >> 5;
-        const int kt = (int)(a % p.f_n_kt);
-        a /= p.f_n_kt;
-        const int r0 = (int)(a % p.sfb_rt) * 128 + rr;
-        const int cnt_e = s_counts[(int)(a / p.sfb_rt)];
-        uint8_t* line = p.f_sfb_out + c * 16;
+        unsigned a = c >> 5;
+        const unsigned a_kt = a / (unsigned)p.f_n_kt;
+        const int kt = (int)(a - a_kt * p.f_n_kt);
+        const unsigned a_e = a_kt / (unsigned)p.sfb_rt;
+        const int r0 = (int)(a_kt - a_e * p.sfb_rt) * 128 + rr;
+        const int cnt_e = s_counts[a_e];
+        uint8_t* line = p.f_sfb_out + (long long)c * 16;
         if (r0 >= cnt_e) {
           *reinterpret_cast<uint4*>(line) = make_uint4(w4, w4, w4, w4);
         } else {
@@ -585,22 +522,27 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       if (!walk.seek<TILE_N>(t, mt, nt)) break;
       const int e = walk.e;
       const int cnt = s_counts[e];
+      const bool eprof = p.prof != nullptr && ep_tid == 0;
+      long long te0 = eprof ? clock64() : 0;
       if (!ptx::mbar_wait(acc_full + acc, acc_phase)) {
         atomicExch(&g_status, kEpilogueTimeout);
         break;
       }
       ptx::tc_fence_after();
+      long long te1 = eprof ? clock64() : 0;
+      long long t_ld = 0;
       if (kTrace && ep_tid == 0) CRUMB(3, 300);
       const float alpha = p.alphas[e];
       const int n0 = nt * TILE_N;
       __nv_bfloat16* out_e = p.out + (long long)e * p.max_n * p.M;
-#pragma unroll 1
       // issuers whose K-blocks exist for this K (a short K leaves the later issuers idle)
       const int live = min(ISSUERS, ceil_div_i(min(C::kAtoms, p.n_kt), C::kAtomsPerIssuer));
+#pragma unroll 1
       for (int c0 = 0; c0 < TILE_N; c0 += 32) {
         if (n0 + c0 >= cnt) break;             // uniform over the four epilogue warps
         uint32_t r[32];
         const uint32_t lane_base = tmem_base + ((uint32_t)(sub * 32) << 16) + c0;
+        long long tl0 = eprof ? clock64() : 0;
         ptx::tc_ld_32x32(lane_base + (acc * ISSUERS) * TILE_N, r);
         ptx::tc_ld_wait();
 #pragma unroll
@@ -613,6 +555,7 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__fadd_rn(__uint_as_float(r[i]), __uint_as_float(q[i])));
           }
         }
+        if (eprof) t_ld += clock64() - tl0;
         if (kFused) {
           // The weight rows are interleaved in 64-row blocks (32 gate rows, then the 32 matching up
           // rows), so lanes of the even 32-lane quarters hold gates and the odd quarters the ups of
@@ -622,18 +565,31 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           __nv_bfloat16 h[kCols];
 #pragma unroll
           for (int i = 0; i < kCols; ++i) h[i] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(r[i])));
+          // Every lane parks its values; then the gate lane of a feature finishes the even token
+          // columns and the up lane of the same feature the odd ones, each reading its partner's
+          // value from shared memory and leaving the product in the gate's slot.  Loads, math and
+          // stores are kept in separate passes so the 8 or 16 independent chains overlap.
           const bool is_up = (sub & 1) != 0;
-          if (is_up) {
 #pragma unroll
-            for (int i = 0; i < kCols; ++i) buf[i * kOutRow + m_local] = h[i];
-          }
+          for (int i = 0; i < kCols; ++i) buf[i * kOutRow + m_local] = h[i];
           epilogue_bar_sync();
-          if (!is_up) {
+          constexpr int kHalf = kCols / 2;
+          const int par = is_up ? 1 : 0;
+          const int g_row = is_up ? m_local - 32 : m_local;   // the gate's slot, which receives the product
+          __nv_bfloat16* col0 = buf + par * kOutRow + g_row;
+#pragma unroll 1
+          for (int i0 = 0; i0 < kHalf; i0 += 4) {
+            float g[4], u[4];
 #pragma unroll
-            for (int i = 0; i < kCols; ++i) {
-              const float u = __bfloat162float(buf[i * kOutRow + m_local + 32]);
-              buf[i * kOutRow + m_local] = __float2bfloat16_rn(gated_act(__bfloat162float(h[i]), u, p.f_act));
+            for (int i = 0; i < 4; ++i) {
+              g[i] = __bfloat162float(col0[(i0 + i) * 2 * kOutRow]);
+              u[i] = __bfloat162float(col0[(i0 + i) * 2 * kOutRow + 32]);
             }
+            __nv_bfloat16 y[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) y[i] = __float2bfloat16_rn(gated_act(g[i], u[i], p.f_act));
+#pragma unroll
+            for (int i = 0; i < 4; ++i) col0[(i0 + i) * 2 * kOutRow] = y[i];
           }
           epilogue_bar_sync();
           if (ep_tid < 64) {
@@ -694,6 +650,10 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       ptx::tc_fence_before();
       ptx::mbar_arrive(acc_empty + acc);
       if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
+      if (eprof) {   // waiting for an accumulator, reading it, the rest of the tile's epilogue
+        long long* q = p.prof + blockIdx.x * 8;
+        if (!kFused) { q[5] += te1 - te0; q[6] += t_ld; } q[7] += clock64() - te1 - t_ld;
+      }
     }
   }
 
@@ -751,27 +711,17 @@ constexpr int kTraceWords = 8 * 16;
 unsigned* g_trace_host = nullptr;   // host view
 unsigned* g_trace_dev = nullptr;    // device view of the same pages
 
-// PNV_GROUP_MM_PREFETCH=1 turns the L2 prefetch of weight rows on (off by default: it measured slower).
-bool prefetch_enabled() {
-  static int v = -1;
-  if (v < 0) {
-    const char* env = std::getenv("PNV_GROUP_MM_PREFETCH");
-    v = (env != nullptr && env[0] == '1') ? 1 : 0;
-  }
-  return v == 1;
-}
-
 // PNV_GROUP_MM_PROFILE=1: the MMA issuer and the tile producer of every CTA accumulate cycle
 // counters (waiting for data, issuing, waiting for an accumulator, stages; waiting for a free
 // stage) in a device buffer that pnv_group_mm_profile() reads back.  A measuring aid only.
 long long* g_prof_dev = nullptr;
-long long* profile_buffer() {
+long long* profile_buffer(bool fused) {   // PNV_GROUP_MM_PROFILE=2 records the fused launches only
   static int v = -1;
   if (v < 0) {
     const char* env = std::getenv("PNV_GROUP_MM_PROFILE");
-    v = (env != nullptr && env[0] == '1') ? 1 : 0;
+    v = (env != nullptr && (env[0] == '1' || env[0] == '2')) ? env[0] - '0' : 0;
   }
-  if (v != 1) return nullptr;
+  if (v == 0 || (v == 2 && !fused)) return nullptr;
   if (g_prof_dev == nullptr) {
     if (cudaMalloc(reinterpret_cast<void**>(&g_prof_dev), 256 * 8 * sizeof(long long)) != cudaSuccess) return nullptr;
   }
@@ -798,7 +748,6 @@ int launch_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params
     int v = std::atoi(env);
     if (v >= 1 && v < C::kStages) p.stages = v;
   }
-  if (p.group > p.stages - 1) p.group = p.stages > 1 ? p.stages - 1 : 1;
   const size_t smem = 1024 + (size_t)C::kStages * C::kStageBytes + kOutStageBytes + 256 + 4 * (size_t)p.E;
   static_assert(kOutStageBytes % 16 == 0, "barrier block must stay aligned");
   static_assert(8 * (2 * C::kStages + 2 * C::kAccStages + 2 + ISSUERS) + 16 <= 256, "barrier block overflows its slot");
@@ -939,7 +888,7 @@ int group_mm_common(void* out, const FusedArgs* fused, const uint8_t* a_comp, co
 
   WeightDims wd = weight_dims(features, k);
   Params p;
-  p.a_comp = a_comp; p.e_meta = e_meta; p.sfa = sfa; p.sfb = sfb; p.alphas = alphas; p.counts = counts;
+  p.e_meta = e_meta; p.sfa = sfa; p.sfb = sfb; p.alphas = alphas; p.counts = counts;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.f_b_out = nullptr; p.f_sfb_out = nullptr; p.f_gscale = nullptr; p.f_gpe = 0; p.f_n = 0; p.f_n_kt = 0;
   p.f_act = GatedAct{PNV_ACT_SILU, 1.f, -1.f};
@@ -954,14 +903,7 @@ int group_mm_common(void* out, const FusedArgs* fused, const uint8_t* a_comp, co
   p.e_k_atoms = wd.k_e / 16;
   p.e_m_atoms = wd.m_e / 128;
   p.sfb_rt = sf_row_atoms(max_n);
-  p.a_row_bytes = wd.k_ac / 2;
-  p.prefetch = prefetch_enabled() ? 1 : 0;
-  p.group = 1;
-  if (const char* env = std::getenv("PNV_GROUP_MM_GROUP")) p.group = std::max(1, std::atoi(env));
-  p.a_box_rows = p.group > 1 ? 32 : kTileM;
-  p.skip = 0;
-  p.prof = profile_buffer();
-  if (const char* env = std::getenv("PNV_GROUP_MM_SKIP")) p.skip = std::atoi(env);
+  p.prof = profile_buffer(fused != nullptr);
   p.stages = 0;
   p.trace = nullptr;
 
@@ -981,7 +923,7 @@ int group_mm_common(void* out, const FusedArgs* fused, const uint8_t* a_comp, co
 
   CUtensorMap map_a, map_b;
   if (int rc = make_map(&map_a, a_comp, (uint64_t)wd.k_ac / 2, (uint64_t)wd.m_ac, (uint64_t)experts,
-                        (uint32_t)stage_k / 4, (uint32_t)p.a_box_rows,
+                        (uint32_t)stage_k / 4, (uint32_t)kTileM,
                         stage_k == 512 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B))
     return rc;
   if (int rc = make_map(&map_b, b_act, (uint64_t)k / 2, (uint64_t)max_n, (uint64_t)experts, 128,
@@ -1037,6 +979,7 @@ extern "C" int pnv_group_mm_swiglu_quant(uint8_t* b_out, uint8_t* sfb_out, const
   if (int rc = make_gated_act(act_kind, beta, linear_beta, f.act)) return rc;
   f.b_out = b_out; f.sfb_out = sfb_out; f.gscale = gscale; f.gpe = gscale_per_expert ? 1 : 0;
   PNV_REQUIRE(experts >= 1 && max_n >= 1, "experts and max_n must be positive");
+  PNV_REQUIRE(sf_numel(max_n, features / 2, experts) < (1LL << 31), "sfb_out must be smaller than 2 GiB");
   const FusedKind& fk = kFusedKinds[config_id];
   return group_mm_common(b_out, &f, a_comp, e_meta, sfa, b_act, sfb, alphas, counts, experts, features, k, max_n,
                          fk.base_config, cluster_m, cluster_n, sm_count, pdl, stream, fk.name);

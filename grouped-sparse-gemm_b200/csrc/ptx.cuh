@@ -62,12 +62,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  try_wait itself blocks for a hardware-defined slice, so the poll budget below is
 // on the order of a second of wall time; legitimate waits in this kernel are microseconds.
 constexpr uint32_t kMaxPolls = 1u << 20;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// The polling loop lives out of line: inlined at every wait it was the bulk of the kernel's code.
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity) {
+#pragma unroll 1
   for (uint32_t i = 0; i < kMaxPolls; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 64) __nanosleep(128);
   }
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity);
 }
 
 // ---- TMA -----------------------------------------------------------------------------------------
