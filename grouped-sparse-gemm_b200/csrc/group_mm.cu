@@ -57,7 +57,7 @@ constexpr int kSmemLimit = 227 * 1024;
 
 enum Status : int {
   kOk = 0, kProducerEmptyTimeout = 1, kMmaFullTimeout = 2, kMmaAccTimeout = 3, kEpilogueTimeout = 4,
-  kSideProducerTimeout = 5
+  kSideProducerTimeout = 5, kMmaScaleTimeout = 6, kScaleLoaderTimeout = 7
 };
 
 template <int TILE_N, int STAGE_K, int ISSUERS>
@@ -668,6 +668,470 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #undef CRUMB
 }
 
+// ---- wide tiles (TILE_N >= 64) ---------------------------------------------------------------------
+//
+// With 64- to 256-wide token tiles the narrow kernel's single issuer thread is the bottleneck: per
+// 128-K block it issues one MMA but also two or three tcgen05.cp of scale atoms, and every
+// tcgen05 operation costs the issuing thread 50-100 cycles.  This kernel takes the scales off that
+// thread.  Sixteen warps:
+//   warp 0   tile producer (TMA: compressed weights, activations)        } as in the narrow kernel
+//   warp 1   side producer (bulk copies: metadata, SFA, SFB atoms)       }
+//   warp 2   MMA issuer: per stage the metadata tcgen05.cp and the MMAs, nothing else
+//   warp 3   spare
+//   4 - 7    scale loaders, one per tensor-memory lane quarter: read the stage's scale atoms from
+//            shared memory (one 16-byte line per lane) and write them into a ring of scale slots in
+//            tensor memory with tcgen05.st -- the same image tcgen05.cp.32x128b.warpx4 would leave
+//   8 - 15   epilogue, two groups of four warps; a tile's 32-column chunks alternate between them
+// Barriers on top of the stage full/empty pair: sf_full[slot] (the four loaders -> issuer) and
+// sf_empty[slot] (issuer's tcgen05.commit -> loaders); a stage is released by the issuer's commit
+// plus the four loaders (its scales have left shared memory).
+template <int TILE_N, int STAGE_K>
+struct WideCfg {
+  static_assert(TILE_N == 64 || TILE_N == 128 || TILE_N == 256, "wide tile widths: 64, 128, 256");
+  static_assert(STAGE_K == 256 || STAGE_K == 512, "stage depths: 256, 512");
+  static constexpr int kThreads = 512;
+  static constexpr int kAtoms = STAGE_K / 128;
+  static constexpr int kARowBytes = STAGE_K / 4;
+  static constexpr int kABytes = kTileM * kARowBytes;
+  static constexpr uint32_t kASwizzle = STAGE_K == 512 ? 2 : 4;
+  static constexpr int kBBoxes = STAGE_K / 256;
+  static constexpr int kBBoxBytes = TILE_N * 128;
+  static constexpr int kBBytes = kBBoxes * kBBoxBytes;
+  static constexpr int kEAtoms = STAGE_K / 256;
+  static constexpr int kEBytes = 2048 * kEAtoms;
+  static constexpr int kSfaBytes = 512 * kAtoms;
+  static constexpr int kSfbRowAtoms = TILE_N > 128 ? 2 : 1;
+  static constexpr int kSfbBytes = kSfaBytes * kSfbRowAtoms;
+  static constexpr int kStageBytes = kABytes + kBBytes + kEBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kOutBytes = 2 * kOutStageBytes;     // one double-buffered transpose tile per epilogue group
+  static constexpr int kBarrierBytes = 512;
+  static constexpr int kFixedBytes = 1024 + kOutBytes + kBarrierBytes + 4 * kMaxExperts;
+  static constexpr int kStagesFit = (kSmemLimit - kFixedBytes) / kStageBytes;
+  static constexpr int kStages = kStagesFit > 12 ? 12 : kStagesFit;
+  static constexpr int kAccStages = TILE_N == 256 ? 1 : 2;
+  static constexpr int kColE = 256;                         // tensor-memory columns: accumulators below 256
+  static constexpr int kColSf = 272;                        // ring of scale slots
+  static constexpr int kSfbColsPerAtom = 4 * kSfbRowAtoms;
+  static constexpr int kSfSlotCols = kAtoms * (4 + kSfbColsPerAtom);
+  static constexpr int kSfSlots = 4;
+  static constexpr int kOffA = 0;
+  static constexpr int kOffB = kABytes;
+  static constexpr int kOffE = kOffB + kBBytes;
+  static constexpr int kOffSfa = kOffE + kEBytes;
+  static constexpr int kOffSfb = kOffSfa + kSfaBytes;
+  static_assert(kStageBytes % 1024 == 0, "stage buffers must keep 1024-byte alignment");
+  static_assert(kStages >= 2, "not enough shared memory for a pipeline");
+  static_assert(kAccStages * TILE_N <= kColE && kColE + 4 * kEAtoms <= kColSf &&
+                kColSf + kSfSlots * kSfSlotCols <= kTmemCols, "tensor-memory column map overflows");
+  static_assert(8 * (2 * kStages + 2 * kAccStages + 2 * kSfSlots) + 16 <= kBarrierBytes, "barrier block overflows");
+};
+
+__device__ __forceinline__ void epilogue_group_sync(int group) {
+  asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory");
+}
+
+template <int TILE_N, int STAGE_K, bool kFused>
+__global__ void __launch_bounds__(512, 1)
+group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     const Params p) {
+  using C = WideCfg<TILE_N, STAGE_K>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage_base = smem;
+  __nv_bfloat16* s_out = reinterpret_cast<__nv_bfloat16*>(smem + C::kStages * C::kStageBytes);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes + C::kOutBytes);
+  uint64_t* empty_bar = full_bar + C::kStages;
+  uint64_t* acc_full = empty_bar + C::kStages;
+  uint64_t* acc_empty = acc_full + C::kAccStages;
+  uint64_t* sf_full = acc_empty + C::kAccStages;
+  uint64_t* sf_empty = sf_full + C::kSfSlots;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_empty + C::kSfSlots);
+  int* s_counts = reinterpret_cast<int*>(smem + C::kStages * C::kStageBytes + C::kOutBytes + C::kBarrierBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    ptx::prefetch_tensormap(&map_a);
+    ptx::prefetch_tensormap(&map_b);
+    for (int s = 0; s < C::kStages; ++s) { ptx::mbar_init(full_bar + s, 2); ptx::mbar_init(empty_bar + s, 1 + 4); }
+    for (int a = 0; a < C::kAccStages; ++a) { ptx::mbar_init(acc_full + a, 1); ptx::mbar_init(acc_empty + a, 8); }
+    for (int s = 0; s < C::kSfSlots; ++s) { ptx::mbar_init(sf_full + s, 4); ptx::mbar_init(sf_empty + s, 1); }
+    ptx::fence_mbar_init();
+  }
+  if (warp == 2) {
+    ptx::tmem_alloc(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  // counts (and everything else the producer kernels wrote) may only be read after this point
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int i = threadIdx.x; i < p.E; i += C::kThreads) s_counts[i] = max(0, min(p.counts[i], p.max_n));
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  TileWalk walk;
+  walk.init<TILE_N>(s_counts, p.E, p.n_mt);
+
+  if (warp == 0) {
+    // =============================== tile producer (TMA) ===============================
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; ok; t += gridDim.x) {
+        int mt, nt;
+        if (!walk.seek<TILE_N>(t, mt, nt)) break;
+        const int e = walk.e;
+        const int n0 = nt * TILE_N;
+#pragma unroll 1
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          long long tq0 = p.prof ? clock64() : 0;
+          if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1)) {
+            atomicExch(&g_status, kProducerEmptyTimeout);
+            ok = false;
+            break;
+          }
+          if (p.prof) p.prof[blockIdx.x * 8 + 4] += clock64() - tq0;
+          uint8_t* st = stage_base + stage * C::kStageBytes;
+          const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
+          const int b_boxes = (k_atoms + 1) / 2;
+          ptx::mbar_arrive_expect_tx(full_bar + stage, C::kABytes + b_boxes * C::kBBoxBytes);
+          ptx::tma_load_3d(st + C::kOffA, &map_a, full_bar + stage, ks * C::kARowBytes, mt * kTileM, e);
+          for (int b = 0; b < b_boxes; ++b)
+            ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + stage,
+                             ks * (STAGE_K / 2) + b * 128, n0, e);
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // give copies already in flight time to land before the CTA's shared memory is released
+#pragma unroll 1
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // =============================== side producer (bulk copies) ===============================
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; ok; t += gridDim.x) {
+        int mt, nt;
+        if (!walk.seek<TILE_N>(t, mt, nt)) break;
+        const int e = walk.e;
+        const int n0 = nt * TILE_N;
+        const uint8_t* e_base = p.e_meta + (((long long)e * p.e_k_atoms) * p.e_m_atoms + mt) * 2048;
+        const uint8_t* sfa_base = p.sfa + (((long long)e * p.n_mt + mt) * p.n_kt) * 512;
+        const uint8_t* sfb_base = p.sfb + (((long long)e * p.sfb_rt + (n0 >> 7)) * p.n_kt) * 512;
+        const int sfb_row_atoms = TILE_N > 128 ? min(2, p.sfb_rt - (n0 >> 7)) : 1;
+#pragma unroll 1
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1)) {
+            atomicExch(&g_status, kSideProducerTimeout);
+            ok = false;
+            break;
+          }
+          uint8_t* st = stage_base + stage * C::kStageBytes;
+          const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
+          const int e_atoms = (k_atoms + 1) / 2;
+          const uint32_t sf_bytes = 512u * k_atoms;
+          ptx::mbar_arrive_expect_tx(full_bar + stage, e_atoms * 2048 + sf_bytes * (1 + sfb_row_atoms));
+          for (int ea = 0; ea < e_atoms; ++ea)
+            ptx::bulk_load(st + C::kOffE + ea * 2048,
+                           e_base + (long long)(ks * C::kEAtoms + ea) * p.e_m_atoms * 2048, 2048, full_bar + stage);
+          ptx::bulk_load(st + C::kOffSfa, sfa_base + (long long)ks * C::kAtoms * 512, sf_bytes, full_bar + stage);
+          for (int ra = 0; ra < sfb_row_atoms; ++ra)
+            ptx::bulk_load(st + C::kOffSfb + ra * C::kSfaBytes,
+                           sfb_base + ((long long)ra * p.n_kt + ks * C::kAtoms) * 512, sf_bytes, full_bar + stage);
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+#pragma unroll 1
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 2) {
+    // =============================== MMA issuer ===============================
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::mma_sp_nvf4_idesc(TILE_N);
+      int stage = 0, acc = 0, slot = 0;
+      uint32_t phase = 0, acc_phase = 0, slot_phase = 0;
+      bool ok = true;
+      long long c_wait_full = 0, c_wait_sf = 0, c_issue = 0, c_wait_acc = 0, n_stage = 0;
+      const bool prof = p.prof != nullptr;
+      for (long long t = blockIdx.x; ok; t += gridDim.x) {
+        int mt, nt;
+        if (!walk.seek<TILE_N>(t, mt, nt)) break;
+        long long tp0 = prof ? clock64() : 0;
+        if (!ptx::mbar_wait(acc_empty + acc, acc_phase ^ 1)) {
+          atomicExch(&g_status, kMmaAccTimeout);
+          break;
+        }
+        ptx::tc_fence_after();
+        if (prof) c_wait_acc += clock64() - tp0;
+        const uint32_t d_tmem = tmem_base + acc * TILE_N;
+        // a 64-wide tile's scales sit 0 or 2 columns into the 128-row atom (even offsets only: the MMA
+        // faults on an odd scale column)
+        const uint32_t sfb_off = TILE_N < 128 ? ((nt * TILE_N) & 127) >> 5 : 0;
+#pragma unroll 1
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          long long tp1 = prof ? clock64() : 0;
+          if (!ptx::mbar_wait(full_bar + stage, phase)) {
+            atomicExch(&g_status, kMmaFullTimeout);
+            ok = false;
+            break;
+          }
+          long long tp2 = prof ? clock64() : 0;
+          if (!ptx::mbar_wait(sf_full + slot, slot_phase)) {
+            atomicExch(&g_status, kMmaScaleTimeout);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          long long tp3 = prof ? clock64() : 0;
+          if (prof) { c_wait_full += tp2 - tp1; c_wait_sf += tp3 - tp2; ++n_stage; }
+          const uint32_t st = ptx::smem_u32(stage_base + stage * C::kStageBytes);
+          const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
+#pragma unroll
+          for (int ea = 0; ea < C::kEAtoms; ++ea)
+            if (2 * ea < k_atoms)
+              ptx::tc_cp_128x128b(tmem_base + C::kColE + ea * 4, ptx::smem_desc(st + C::kOffE + ea * 2048, 128, 0, 0));
+          const uint32_t sf_cols = tmem_base + C::kColSf + slot * C::kSfSlotCols;
+#pragma unroll
+          for (int ka = 0; ka < C::kAtoms; ++ka) {
+            if (ka < k_atoms) {
+              const uint64_t a_desc = ptx::smem_desc(st + C::kOffA + ka * 32, 8 * C::kARowBytes, 16, C::kASwizzle);
+              const uint64_t b_desc =
+                  ptx::smem_desc(st + C::kOffB + (ka >> 1) * C::kBBoxBytes + (ka & 1) * 64, 1024, 16, 2);
+              ptx::tc_mma_sp_nvf4(d_tmem, a_desc, b_desc, idesc, (ks | ka) != 0 ? 1u : 0u, sf_cols + ka * 4,
+                                  sf_cols + C::kAtoms * 4 + ka * C::kSfbColsPerAtom + sfb_off,
+                                  tmem_base + C::kColE + ka * 2);
+            }
+          }
+          ptx::tc_commit(empty_bar + stage);   // stage reusable once these MMAs and copies retire
+          ptx::tc_commit(sf_empty + slot);     // and so is the scale slot
+          if (prof) c_issue += clock64() - tp3;
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+          if (++slot == C::kSfSlots) { slot = 0; slot_phase ^= 1; }
+        }
+        if (!ok) break;
+        ptx::tc_commit(acc_full + acc);
+        if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
+      }
+      if (prof) {
+        long long* q = p.prof + blockIdx.x * 8;
+        q[0] = c_wait_full; q[1] = c_issue; q[2] = c_wait_acc; q[3] = n_stage; q[5] = c_wait_sf;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 3) {
+    // spare warp: nothing to do until the final barrier
+  } else if (warp < 8) {
+    // =============================== scale loaders ===============================
+    const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + C::kColSf;
+    int stage = 0, slot = 0;
+    uint32_t phase = 0, slot_phase = 0;
+    bool ok = true;
+    for (long long t = blockIdx.x; ok; t += gridDim.x) {
+      int mt, nt;
+      if (!walk.seek<TILE_N>(t, mt, nt)) break;
+#pragma unroll 1
+      for (int ks = 0; ks < p.k_stages; ++ks) {
+        if (!ptx::mbar_wait(full_bar + stage, phase) || !ptx::mbar_wait(sf_empty + slot, slot_phase ^ 1)) {
+          atomicExch(&g_status, kScaleLoaderTimeout);
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint8_t* st = stage_base + stage * C::kStageBytes + lane * 16;
+        const uint32_t cols = lane_base + slot * C::kSfSlotCols;
+#pragma unroll
+        for (int ka = 0; ka < C::kAtoms; ++ka) {
+          ptx::tc_st_32x32_x4(cols + ka * 4, *reinterpret_cast<const uint4*>(st + C::kOffSfa + ka * 512));
+#pragma unroll
+          for (int ra = 0; ra < C::kSfbRowAtoms; ++ra)
+            ptx::tc_st_32x32_x4(cols + C::kAtoms * 4 + ka * C::kSfbColsPerAtom + ra * 4,
+                                *reinterpret_cast<const uint4*>(st + C::kOffSfb + ra * C::kSfaBytes + ka * 512));
+        }
+        ptx::tc_st_wait();
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          ptx::mbar_arrive(sf_full + slot);
+          ptx::mbar_arrive(empty_bar + stage);   // the scales have left shared memory
+        }
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        if (++slot == C::kSfSlots) { slot = 0; slot_phase ^= 1; }
+      }
+    }
+  } else {
+    // =============================== epilogue ===============================
+    const int group = (warp - 8) >> 2;         // chunks of 32 token columns alternate between the groups
+    const int sub = warp & 3;                  // tensor-memory lane quarter this warp may read
+    const int ep_tid = threadIdx.x - 256 - group * 128;
+    const int m_local = sub * 32 + lane;       // accumulator row (output feature) held by this thread
+    const bool vec_ok = (p.M % 8) == 0;        // 16-byte stores need 16-byte aligned output rows
+    __nv_bfloat16* group_out = s_out + group * (2 * 32 * kOutRow);
+    int acc = 0;
+    uint32_t acc_phase = 0, chunk = 0;
+    if (kFused) {
+      // Benign fill of GEMM2's scale buffer: every byte the epilogues will not write (rows at or
+      // past counts[e], K-block slop) becomes 0x38.  All CTAs share the lines; live slots are
+      // skipped, so the fill never races with a quantized scale.
+      const int KB = p.f_n / kSfBlock;
+      const unsigned lines = (unsigned)p.E * p.sfb_rt * p.f_n_kt * 32u;   // < 2^27, checked by the host
+      const uint32_t w4 = kBenignSf * 0x01010101u;
+#pragma unroll 1
+      for (unsigned c = blockIdx.x * 256 + (threadIdx.x - 256); c < lines; c += gridDim.x * 256) {
+        const int rr = (int)(c & 31);
+        unsigned a = c >> 5;
+        const unsigned a_kt = a / (unsigned)p.f_n_kt;
+        const int kt = (int)(a - a_kt * p.f_n_kt);
+        const unsigned a_e = a_kt / (unsigned)p.sfb_rt;
+        const int r0 = (int)(a_kt - a_e * p.sfb_rt) * 128 + rr;
+        const int cnt_e = s_counts[a_e];
+        uint8_t* line = p.f_sfb_out + (long long)c * 16;
+        if (r0 >= cnt_e) {
+          *reinterpret_cast<uint4*>(line) = make_uint4(w4, w4, w4, w4);
+        } else {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (r0 + 32 * g >= cnt_e) {
+              *reinterpret_cast<uint32_t*>(line + 4 * g) = w4;
+            } else {
+              for (int j = KB - kt * 4; j < 4; ++j)
+                if (j >= 0) line[4 * g + j] = (uint8_t)kBenignSf;
+            }
+          }
+        }
+      }
+    }
+    for (long long t = blockIdx.x;; t += gridDim.x) {
+      int mt, nt;
+      if (!walk.seek<TILE_N>(t, mt, nt)) break;
+      const int e = walk.e;
+      const int cnt = s_counts[e];
+      const bool eprof = p.prof != nullptr && ep_tid == 0 && group == 0;
+      long long te0 = eprof ? clock64() : 0;
+      if (!ptx::mbar_wait(acc_full + acc, acc_phase)) {
+        atomicExch(&g_status, kEpilogueTimeout);
+        break;
+      }
+      ptx::tc_fence_after();
+      long long te1 = eprof ? clock64() : 0;
+      const float alpha = p.alphas[e];
+      float gs = 0.f;
+      if (kFused) gs = p.f_gpe ? p.f_gscale[e] : p.f_gscale[0];
+      const int n0 = nt * TILE_N;
+      __nv_bfloat16* out_e = p.out + (long long)e * p.max_n * p.M;
+#pragma unroll 1
+      for (int c0 = group * 32; c0 < TILE_N; c0 += 64) {
+        if (n0 + c0 >= cnt) break;             // uniform over the group's four warps
+        uint32_t r[32];
+        ptx::tc_ld_32x32(tmem_base + ((uint32_t)(sub * 32) << 16) + acc * TILE_N + c0, r);
+        ptx::tc_ld_wait();
+        __nv_bfloat16* buf = group_out + (chunk & 1) * (32 * kOutRow);
+        ++chunk;
+        if (kFused) {
+          // The weight rows are interleaved in 64-row blocks (32 gate rows, then the 32 matching up
+          // rows), so lanes of the even 32-lane quarters hold gates and the odd quarters the ups of
+          // the same 32 output features: exactly one quantization block per token.  Every lane parks
+          // its values; the gate lane of a feature then finishes the even token columns and the up
+          // lane the odd ones, leaving the product in the gate's slot.
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            buf[i * kOutRow + m_local] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(r[i])));
+          epilogue_group_sync(group);
+          const bool is_up = (sub & 1) != 0;
+          __nv_bfloat16* col0 = buf + (is_up ? kOutRow + m_local - 32 : m_local);
+#pragma unroll 1
+          for (int i0 = 0; i0 < 16; i0 += 8) {
+            float g[8], u[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              g[i] = __bfloat162float(col0[(i0 + i) * 2 * kOutRow]);
+              u[i] = __bfloat162float(col0[(i0 + i) * 2 * kOutRow + 32]);
+            }
+            __nv_bfloat16 y[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) y[i] = __float2bfloat16_rn(gated_act(g[i], u[i], p.f_act));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) col0[(i0 + i) * 2 * kOutRow] = y[i];
+          }
+          epilogue_group_sync(group);
+          // quantize: two adjacent lanes share one (token, 32-feature block); each takes 16 features
+          const int pair = ep_tid >> 1, hb = ep_tid & 1;
+          const int i = pair & 31, blk = pair >> 5;
+          const int n = n0 + c0 + i;
+          const uint4* src = reinterpret_cast<const uint4*>(buf + i * kOutRow + blk * 64 + hb * 16);
+          float f[2][8];
+          float amax = 0.f;
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            unpack8(src[q], f[q]);
+#pragma unroll
+            for (int z = 0; z < 8; ++z) amax = fmaxf(amax, fabsf(f[q][z]));
+          }
+          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+          uint32_t sf_byte;
+          float inv;
+          block_scale(amax, gs, sf_byte, inv);
+          if (n < cnt) {
+            const int kb = mt * 2 + blk;       // 32-feature block of the N-wide output
+            const long long row = (long long)e * p.max_n + n;
+            *reinterpret_cast<uint2*>(p.f_b_out + row * (p.f_n / 2) + kb * 16 + hb * 8) =
+                make_uint2(quant8(f[0], inv), quant8(f[1], inv));
+            if (hb == 0) p.f_sfb_out[sf_offset(e, n, kb, p.sfb_rt, p.f_n_kt)] = (uint8_t)sf_byte;
+          }
+        } else {
+          // [token column][feature] tile: 32 rows of 128 bf16; lanes write consecutive features
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            buf[i * kOutRow + m_local] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(r[i])));
+          epilogue_group_sync(group);
+          const int col = (ep_tid & 15) * 8;
+          const int m = mt * kTileM + col;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int row = (ep_tid >> 4) + 8 * j;
+            const int n = n0 + c0 + row;
+            if (n >= cnt || m >= p.M) continue;
+            if (vec_ok) {
+              *reinterpret_cast<uint4*>(out_e + (long long)n * p.M + m) =
+                  *reinterpret_cast<const uint4*>(buf + row * kOutRow + col);
+            } else {
+#pragma unroll 1
+              for (int z = 0; z < 8 && m + z < p.M; ++z) out_e[(long long)n * p.M + m + z] = buf[row * kOutRow + col + z];
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(acc_empty + acc);
+      if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
+      if (eprof) {   // waiting for an accumulator, and group 0's share of the tile's epilogue
+        long long* q = p.prof + blockIdx.x * 8;
+        q[6] += te1 - te0; q[7] += clock64() - te1;
+      }
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    __syncwarp();
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
 // ---- host side -----------------------------------------------------------------------------------
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -787,6 +1251,37 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, Params& p, int sm
   for (int i = 0; i < kTraceWords; ++i) g_trace_host[i] = 0;
   p.trace = g_trace_dev;
   return launch_impl<TILE_N, STAGE_K, ISSUERS, true, false>(map_a, map_b, p, sm_count, false, stream);
+}
+
+template <int TILE_N, int STAGE_K, bool kFused>
+int launch_wide_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p_in, int sm_count, bool pdl,
+                     cudaStream_t stream) {
+  using C = WideCfg<TILE_N, STAGE_K>;
+  Params p = p_in;
+  p.stages = C::kStages;
+  p.trace = nullptr;
+  const size_t smem = 1024 + (size_t)C::kStages * C::kStageBytes + C::kOutBytes + C::kBarrierBytes + 4 * (size_t)p.E;
+  static bool opted_in[64] = {};
+  int dev = 0;
+  PNV_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !opted_in[dev]) {
+    PNV_CUDA(cudaFuncSetAttribute(group_mm_wide_kernel<TILE_N, STAGE_K, kFused>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    if (dev >= 0 && dev < 64) opted_in[dev] = true;
+  }
+  long long max_tiles = (long long)p.E * p.n_mt * ceil_div_i(p.max_n, TILE_N);
+  int grid = (int)(max_tiles < sm_count ? max_tiles : sm_count);
+  if (grid < 1) grid = 1;
+  PNV_CUDA(launch_pdl(group_mm_wide_kernel<TILE_N, STAGE_K, kFused>, dim3(grid), dim3(C::kThreads), smem, stream,
+                      pdl, map_a, map_b, p));
+  return PNV_OK;
+}
+
+template <int TILE_N, int STAGE_K>
+int launch_wide(const CUtensorMap& map_a, const CUtensorMap& map_b, Params& p, int sm_count, bool pdl,
+                cudaStream_t stream) {
+  if (p.f_b_out != nullptr) return launch_wide_impl<TILE_N, STAGE_K, true>(map_a, map_b, p, sm_count, pdl, stream);
+  return launch_wide_impl<TILE_N, STAGE_K, false>(map_a, map_b, p, sm_count, pdl, stream);
 }
 
 // Tile variants.  The first eight names and ids are the reference's; a "2sm" name is accepted with
@@ -932,6 +1427,19 @@ int group_mm_common(void* out, const FusedArgs* fused, const uint8_t* a_comp, co
 
   cudaStream_t s = (cudaStream_t)stream;
   const bool use_pdl = pdl != 0 && pdl_enabled();
+  static const bool wide_ok = [] {   // PNV_GROUP_MM_WIDE=0: run wide tiles on the narrow kernel (comparison aid)
+    const char* env = std::getenv("PNV_GROUP_MM_WIDE");
+    return !(env != nullptr && env[0] == '0');
+  }();
+  if (wide_ok && tile_n >= 64 && !trace_enabled()) {
+    switch (tile_n * 1000 + stage_k) {
+      case 64256: return launch_wide<64, 256>(map_a, map_b, p, sm_count, use_pdl, s);
+      case 64512: return launch_wide<64, 512>(map_a, map_b, p, sm_count, use_pdl, s);
+      case 128256: return launch_wide<128, 256>(map_a, map_b, p, sm_count, use_pdl, s);
+      case 128512: return launch_wide<128, 512>(map_a, map_b, p, sm_count, use_pdl, s);
+      default: return launch_wide<256, 256>(map_a, map_b, p, sm_count, use_pdl, s);
+    }
+  }
   switch (tile_n * 1000 + stage_k) {
     case 16512: return launch<16, 512, 4>(map_a, map_b, p, sm_count, use_pdl, s);
     case 32512: return launch<32, 512, 4>(map_a, map_b, p, sm_count, use_pdl, s);

@@ -199,5 +199,16 @@ __device__ __forceinline__ void tc_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// registers -> tensor memory: each lane of this warp writes 16 bytes to four consecutive 32-bit
+// columns of its own tensor-memory lane (warp w may only touch lanes 32 * (w % 4) ...).
+__device__ __forceinline__ void tc_st_32x32_x4(uint32_t taddr, const uint4& v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void tc_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 }  // namespace ptx
 }  // namespace pnv
