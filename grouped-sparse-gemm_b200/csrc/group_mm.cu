@@ -116,6 +116,7 @@ struct Params {
   int e_m_atoms;     // metadata atoms along M = n_mt
   int sfb_rt;        // scale row-atoms per expert in sfb = ceil(max_n / 128)
   int stages;        // pipeline depth in use (<= Cfg::kStages)
+  int b_res_bytes;   // wide kernel: bytes of the resident activation tile in front of the stage ring (0 = streamed)
   // fused SwiGLU + requantise epilogue (kFused kernels): GEMM2's operands instead of a bf16 output
   uint8_t* f_b_out;        // [E, max_n, N/2] e2m1 codes, N = M / 2
   uint8_t* f_sfb_out;      // swizzled scales for (max_n, N), pre-filled with 0x38
@@ -685,7 +686,15 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 // Barriers on top of the stage full/empty pair: sf_full[slot] (the four loaders -> issuer) and
 // sf_empty[slot] (issuer's tcgen05.commit -> loaders); a stage is released by the issuer's commit
 // plus the four loaders (its scales have left shared memory).
-template <int TILE_N, int STAGE_K>
+//
+// Resident activations (kBRes).  An SM takes in about 48 bytes per cycle from L2, while one MMA reads
+// 12 KB (N = 128) of operands from shared memory in 96 cycles, so a kernel that streams both
+// operands through the stage ring runs at the fill rate, not the tensor rate.  When a whole
+// activation tile (TILE_N tokens x K) fits beside the ring, the CTA's unit of work becomes
+// (expert, token tile): the activation tile is loaded once, in 256-K chunks with a full/empty
+// barrier pair each, and every weight tile of the expert streams against it.  The next unit's
+// chunks are loaded while the last weight tile of this unit is still being multiplied.
+template <int TILE_N, int STAGE_K, bool kBRes>
 struct WideCfg {
   static_assert(TILE_N == 64 || TILE_N == 128 || TILE_N == 256, "wide tile widths: 64, 128, 256");
   static_assert(STAGE_K == 256 || STAGE_K == 512, "stage depths: 256, 512");
@@ -696,7 +705,7 @@ struct WideCfg {
   static constexpr uint32_t kASwizzle = STAGE_K == 512 ? 2 : 4;
   static constexpr int kBBoxes = STAGE_K / 256;
   static constexpr int kBBoxBytes = TILE_N * 128;
-  static constexpr int kBBytes = kBBoxes * kBBoxBytes;
+  static constexpr int kBBytes = kBRes ? 0 : kBBoxes * kBBoxBytes;   // activation bytes inside a stage
   static constexpr int kEAtoms = STAGE_K / 256;
   static constexpr int kEBytes = 2048 * kEAtoms;
   static constexpr int kSfaBytes = 512 * kAtoms;
@@ -704,10 +713,9 @@ struct WideCfg {
   static constexpr int kSfbBytes = kSfaBytes * kSfbRowAtoms;
   static constexpr int kStageBytes = kABytes + kBBytes + kEBytes + kSfaBytes + kSfbBytes;
   static constexpr int kOutBytes = 2 * kOutStageBytes;     // one double-buffered transpose tile per epilogue group
-  static constexpr int kBarrierBytes = 512;
-  static constexpr int kFixedBytes = 1024 + kOutBytes + kBarrierBytes + 4 * kMaxExperts;
-  static constexpr int kStagesFit = (kSmemLimit - kFixedBytes) / kStageBytes;
-  static constexpr int kStages = kStagesFit > 12 ? 12 : kStagesFit;
+  static constexpr int kBarrierBytes = 1024;
+  static constexpr int kMaxStages = 12;
+  static constexpr int kMaxChunks = 16;                     // resident activation tile: at most 16 x 256 K
   static constexpr int kAccStages = TILE_N == 256 ? 1 : 2;
   static constexpr int kColE = 256;                         // tensor-memory columns: accumulators below 256
   static constexpr int kColSf = 272;                        // ring of scale slots
@@ -720,33 +728,53 @@ struct WideCfg {
   static constexpr int kOffSfa = kOffE + kEBytes;
   static constexpr int kOffSfb = kOffSfa + kSfaBytes;
   static_assert(kStageBytes % 1024 == 0, "stage buffers must keep 1024-byte alignment");
-  static_assert(kStages >= 2, "not enough shared memory for a pipeline");
   static_assert(kAccStages * TILE_N <= kColE && kColE + 4 * kEAtoms <= kColSf &&
                 kColSf + kSfSlots * kSfSlotCols <= kTmemCols, "tensor-memory column map overflows");
-  static_assert(8 * (2 * kStages + 2 * kAccStages + 2 * kSfSlots) + 16 <= kBarrierBytes, "barrier block overflows");
+  static_assert(8 * (2 * kMaxStages + 2 * kAccStages + 2 * kSfSlots + 2 * kMaxChunks) + 16 <= kBarrierBytes,
+                "barrier block overflows");
 };
 
 __device__ __forceinline__ void epilogue_group_sync(int group) {
   asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory");
 }
 
-template <int TILE_N, int STAGE_K, bool kFused>
+__device__ __forceinline__ uint64_t pack_desc(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
+// One work item of a CTA: a single tile, or with resident activations every weight tile of one
+// (expert, token tile).  Returns false when the list is exhausted.
+template <int TILE_N, bool kBRes>
+__device__ __forceinline__ bool next_work(TileWalk& walk, long long w, int n_mt, int& mt_lo, int& mt_hi, int& nt) {
+  int mt;
+  if (!walk.seek<TILE_N>(w, mt, nt)) return false;
+  if (kBRes) { mt_lo = 0; mt_hi = n_mt; } else { mt_lo = mt; mt_hi = mt + 1; }
+  return true;
+}
+
+template <int TILE_N, int STAGE_K, bool kFused, bool kBRes>
 __global__ void __launch_bounds__(512, 1)
 group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const Params p) {
-  using C = WideCfg<TILE_N, STAGE_K>;
+  using C = WideCfg<TILE_N, STAGE_K, kBRes>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* stage_base = smem;
-  __nv_bfloat16* s_out = reinterpret_cast<__nv_bfloat16*>(smem + C::kStages * C::kStageBytes);
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes + C::kOutBytes);
-  uint64_t* empty_bar = full_bar + C::kStages;
-  uint64_t* acc_full = empty_bar + C::kStages;
+  uint8_t* b_res = smem;                                   // resident activation tile (kBRes), p.b_res_bytes
+  uint8_t* stage_base = smem + p.b_res_bytes;
+  uint8_t* after_stages = stage_base + p.stages * C::kStageBytes;
+  __nv_bfloat16* s_out = reinterpret_cast<__nv_bfloat16*>(after_stages);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(after_stages + C::kOutBytes);
+  uint64_t* empty_bar = full_bar + C::kMaxStages;
+  uint64_t* acc_full = empty_bar + C::kMaxStages;
   uint64_t* acc_empty = acc_full + C::kAccStages;
   uint64_t* sf_full = acc_empty + C::kAccStages;
   uint64_t* sf_empty = sf_full + C::kSfSlots;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_empty + C::kSfSlots);
-  int* s_counts = reinterpret_cast<int*>(smem + C::kStages * C::kStageBytes + C::kOutBytes + C::kBarrierBytes);
+  uint64_t* b_full = sf_empty + C::kSfSlots;
+  uint64_t* b_empty = b_full + C::kMaxChunks;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_empty + C::kMaxChunks);
+  int* s_counts = reinterpret_cast<int*>(after_stages + C::kOutBytes + C::kBarrierBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -754,7 +782,9 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&map_a);
     ptx::prefetch_tensormap(&map_b);
-    for (int s = 0; s < C::kStages; ++s) { ptx::mbar_init(full_bar + s, 2); ptx::mbar_init(empty_bar + s, 1 + 4); }
+    for (int s = 0; s < p.stages; ++s) { ptx::mbar_init(full_bar + s, 2); ptx::mbar_init(empty_bar + s, 1 + 4); }
+    if (kBRes)
+      for (int c = 0; c < C::kMaxChunks; ++c) { ptx::mbar_init(b_full + c, 1); ptx::mbar_init(b_empty + c, 1); }
     for (int a = 0; a < C::kAccStages; ++a) { ptx::mbar_init(acc_full + a, 1); ptx::mbar_init(acc_empty + a, 8); }
     for (int s = 0; s < C::kSfSlots; ++s) { ptx::mbar_init(sf_full + s, 4); ptx::mbar_init(sf_empty + s, 1); }
     ptx::fence_mbar_init();
@@ -773,38 +803,56 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const uint32_t tmem_base = *tmem_slot;
 
   TileWalk walk;
-  walk.init<TILE_N>(s_counts, p.E, p.n_mt);
+  walk.init<TILE_N>(s_counts, p.E, kBRes ? 1 : p.n_mt);
 
   if (warp == 0) {
     // =============================== tile producer (TMA) ===============================
     if (lane == 0) {
       int stage = 0;
-      uint32_t phase = 0;
+      uint32_t phase = 0, uphase = 0;
       bool ok = true;
-      for (long long t = blockIdx.x; ok; t += gridDim.x) {
-        int mt, nt;
-        if (!walk.seek<TILE_N>(t, mt, nt)) break;
+      for (long long w = blockIdx.x; ok; w += gridDim.x) {
+        int mt_lo, mt_hi, nt;
+        if (!next_work<TILE_N, kBRes>(walk, w, p.n_mt, mt_lo, mt_hi, nt)) break;
         const int e = walk.e;
         const int n0 = nt * TILE_N;
+        for (int mt = mt_lo; mt < mt_hi && ok; ++mt) {
 #pragma unroll 1
-        for (int ks = 0; ks < p.k_stages; ++ks) {
-          long long tq0 = p.prof ? clock64() : 0;
-          if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1)) {
-            atomicExch(&g_status, kProducerEmptyTimeout);
-            ok = false;
-            break;
+          for (int ks = 0; ks < p.k_stages; ++ks) {
+            const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
+            const int b_boxes = (k_atoms + 1) / 2;
+            if (kBRes && mt == mt_lo) {
+              // this unit's activation chunks, each as soon as the previous unit has finished with it
+              for (int b = 0; b < b_boxes && ok; ++b) {
+                const int kc = ks * C::kBBoxes + b;
+                if (!ptx::mbar_wait(b_empty + kc, uphase ^ 1)) {
+                  atomicExch(&g_status, kProducerEmptyTimeout);
+                  ok = false;
+                  break;
+                }
+                ptx::mbar_arrive_expect_tx(b_full + kc, C::kBBoxBytes);
+                ptx::tma_load_3d(b_res + kc * C::kBBoxBytes, &map_b, b_full + kc, kc * 128, n0, e);
+              }
+              if (!ok) break;
+            }
+            long long tq0 = p.prof ? clock64() : 0;
+            if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1)) {
+              atomicExch(&g_status, kProducerEmptyTimeout);
+              ok = false;
+              break;
+            }
+            if (p.prof) p.prof[blockIdx.x * 8 + 4] += clock64() - tq0;
+            uint8_t* st = stage_base + stage * C::kStageBytes;
+            ptx::mbar_arrive_expect_tx(full_bar + stage, C::kABytes + (kBRes ? 0 : b_boxes * C::kBBoxBytes));
+            ptx::tma_load_3d(st + C::kOffA, &map_a, full_bar + stage, ks * C::kARowBytes, mt * kTileM, e);
+            if (!kBRes)
+              for (int b = 0; b < b_boxes; ++b)
+                ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + stage,
+                                 ks * (STAGE_K / 2) + b * 128, n0, e);
+            if (++stage == p.stages) { stage = 0; phase ^= 1; }
           }
-          if (p.prof) p.prof[blockIdx.x * 8 + 4] += clock64() - tq0;
-          uint8_t* st = stage_base + stage * C::kStageBytes;
-          const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
-          const int b_boxes = (k_atoms + 1) / 2;
-          ptx::mbar_arrive_expect_tx(full_bar + stage, C::kABytes + b_boxes * C::kBBoxBytes);
-          ptx::tma_load_3d(st + C::kOffA, &map_a, full_bar + stage, ks * C::kARowBytes, mt * kTileM, e);
-          for (int b = 0; b < b_boxes; ++b)
-            ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + stage,
-                             ks * (STAGE_K / 2) + b * 128, n0, e);
-          if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
+        uphase ^= 1;
       }
       if (!ok) {
         // give copies already in flight time to land before the CTA's shared memory is released
@@ -819,35 +867,37 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (long long t = blockIdx.x; ok; t += gridDim.x) {
-        int mt, nt;
-        if (!walk.seek<TILE_N>(t, mt, nt)) break;
+      for (long long w = blockIdx.x; ok; w += gridDim.x) {
+        int mt_lo, mt_hi, nt;
+        if (!next_work<TILE_N, kBRes>(walk, w, p.n_mt, mt_lo, mt_hi, nt)) break;
         const int e = walk.e;
         const int n0 = nt * TILE_N;
-        const uint8_t* e_base = p.e_meta + (((long long)e * p.e_k_atoms) * p.e_m_atoms + mt) * 2048;
-        const uint8_t* sfa_base = p.sfa + (((long long)e * p.n_mt + mt) * p.n_kt) * 512;
         const uint8_t* sfb_base = p.sfb + (((long long)e * p.sfb_rt + (n0 >> 7)) * p.n_kt) * 512;
         const int sfb_row_atoms = TILE_N > 128 ? min(2, p.sfb_rt - (n0 >> 7)) : 1;
+        for (int mt = mt_lo; mt < mt_hi && ok; ++mt) {
+          const uint8_t* e_base = p.e_meta + (((long long)e * p.e_k_atoms) * p.e_m_atoms + mt) * 2048;
+          const uint8_t* sfa_base = p.sfa + (((long long)e * p.n_mt + mt) * p.n_kt) * 512;
 #pragma unroll 1
-        for (int ks = 0; ks < p.k_stages; ++ks) {
-          if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1)) {
-            atomicExch(&g_status, kSideProducerTimeout);
-            ok = false;
-            break;
+          for (int ks = 0; ks < p.k_stages; ++ks) {
+            if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1)) {
+              atomicExch(&g_status, kSideProducerTimeout);
+              ok = false;
+              break;
+            }
+            uint8_t* st = stage_base + stage * C::kStageBytes;
+            const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
+            const int e_atoms = (k_atoms + 1) / 2;
+            const uint32_t sf_bytes = 512u * k_atoms;
+            ptx::mbar_arrive_expect_tx(full_bar + stage, e_atoms * 2048 + sf_bytes * (1 + sfb_row_atoms));
+            for (int ea = 0; ea < e_atoms; ++ea)
+              ptx::bulk_load(st + C::kOffE + ea * 2048,
+                             e_base + (long long)(ks * C::kEAtoms + ea) * p.e_m_atoms * 2048, 2048, full_bar + stage);
+            ptx::bulk_load(st + C::kOffSfa, sfa_base + (long long)ks * C::kAtoms * 512, sf_bytes, full_bar + stage);
+            for (int ra = 0; ra < sfb_row_atoms; ++ra)
+              ptx::bulk_load(st + C::kOffSfb + ra * C::kSfaBytes,
+                             sfb_base + ((long long)ra * p.n_kt + ks * C::kAtoms) * 512, sf_bytes, full_bar + stage);
+            if (++stage == p.stages) { stage = 0; phase ^= 1; }
           }
-          uint8_t* st = stage_base + stage * C::kStageBytes;
-          const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
-          const int e_atoms = (k_atoms + 1) / 2;
-          const uint32_t sf_bytes = 512u * k_atoms;
-          ptx::mbar_arrive_expect_tx(full_bar + stage, e_atoms * 2048 + sf_bytes * (1 + sfb_row_atoms));
-          for (int ea = 0; ea < e_atoms; ++ea)
-            ptx::bulk_load(st + C::kOffE + ea * 2048,
-                           e_base + (long long)(ks * C::kEAtoms + ea) * p.e_m_atoms * 2048, 2048, full_bar + stage);
-          ptx::bulk_load(st + C::kOffSfa, sfa_base + (long long)ks * C::kAtoms * 512, sf_bytes, full_bar + stage);
-          for (int ra = 0; ra < sfb_row_atoms; ++ra)
-            ptx::bulk_load(st + C::kOffSfb + ra * C::kSfaBytes,
-                           sfb_base + ((long long)ra * p.n_kt + ks * C::kAtoms) * 512, sf_bytes, full_bar + stage);
-          if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
       }
       if (!ok) {
@@ -865,64 +915,98 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       bool ok = true;
       long long c_wait_full = 0, c_wait_sf = 0, c_issue = 0, c_wait_acc = 0, n_stage = 0;
       const bool prof = p.prof != nullptr;
-      for (long long t = blockIdx.x; ok; t += gridDim.x) {
-        int mt, nt;
-        if (!walk.seek<TILE_N>(t, mt, nt)) break;
-        long long tp0 = prof ? clock64() : 0;
-        if (!ptx::mbar_wait(acc_empty + acc, acc_phase ^ 1)) {
-          atomicExch(&g_status, kMmaAccTimeout);
-          break;
-        }
-        ptx::tc_fence_after();
-        if (prof) c_wait_acc += clock64() - tp0;
-        const uint32_t d_tmem = tmem_base + acc * TILE_N;
+      uint32_t uphase = 0, soff = 0;
+      // stage-0 descriptors, split into the 32-bit halves: only the low half changes with the address
+      const uint64_t d_a0 = ptx::smem_desc(ptx::smem_u32(stage_base) + C::kOffA, 8 * C::kARowBytes, 16, C::kASwizzle);
+      const uint64_t d_b0 = ptx::smem_desc(kBRes ? ptx::smem_u32(b_res) : ptx::smem_u32(stage_base) + C::kOffB, 1024, 16, 2);
+      const uint64_t d_e0 = ptx::smem_desc(ptx::smem_u32(stage_base) + C::kOffE, 128, 0, 0);
+      const uint32_t lo_a0 = (uint32_t)d_a0, hi_a = (uint32_t)(d_a0 >> 32);
+      const uint32_t lo_b0 = (uint32_t)d_b0, hi_b = (uint32_t)(d_b0 >> 32);
+      const uint32_t lo_e0 = (uint32_t)d_e0, hi_e = (uint32_t)(d_e0 >> 32);
+      const uint32_t e_cols = tmem_base + C::kColE, sf_cols0 = tmem_base + C::kColSf;
+      for (long long w = blockIdx.x; ok; w += gridDim.x) {
+        int mt_lo, mt_hi, nt;
+        if (!next_work<TILE_N, kBRes>(walk, w, p.n_mt, mt_lo, mt_hi, nt)) break;
         // a 64-wide tile's scales sit 0 or 2 columns into the 128-row atom (even offsets only: the MMA
         // faults on an odd scale column)
         const uint32_t sfb_off = TILE_N < 128 ? ((nt * TILE_N) & 127) >> 5 : 0;
-#pragma unroll 1
-        for (int ks = 0; ks < p.k_stages; ++ks) {
-          long long tp1 = prof ? clock64() : 0;
-          if (!ptx::mbar_wait(full_bar + stage, phase)) {
-            atomicExch(&g_status, kMmaFullTimeout);
-            ok = false;
-            break;
-          }
-          long long tp2 = prof ? clock64() : 0;
-          if (!ptx::mbar_wait(sf_full + slot, slot_phase)) {
-            atomicExch(&g_status, kMmaScaleTimeout);
+        for (int mt = mt_lo; mt < mt_hi && ok; ++mt) {
+          long long tp0 = prof ? clock64() : 0;
+          if (!ptx::mbar_wait(acc_empty + acc, acc_phase ^ 1)) {
+            atomicExch(&g_status, kMmaAccTimeout);
             ok = false;
             break;
           }
           ptx::tc_fence_after();
-          long long tp3 = prof ? clock64() : 0;
-          if (prof) { c_wait_full += tp2 - tp1; c_wait_sf += tp3 - tp2; ++n_stage; }
-          const uint32_t st = ptx::smem_u32(stage_base + stage * C::kStageBytes);
-          const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
-#pragma unroll
-          for (int ea = 0; ea < C::kEAtoms; ++ea)
-            if (2 * ea < k_atoms)
-              ptx::tc_cp_128x128b(tmem_base + C::kColE + ea * 4, ptx::smem_desc(st + C::kOffE + ea * 2048, 128, 0, 0));
-          const uint32_t sf_cols = tmem_base + C::kColSf + slot * C::kSfSlotCols;
-#pragma unroll
-          for (int ka = 0; ka < C::kAtoms; ++ka) {
-            if (ka < k_atoms) {
-              const uint64_t a_desc = ptx::smem_desc(st + C::kOffA + ka * 32, 8 * C::kARowBytes, 16, C::kASwizzle);
-              const uint64_t b_desc =
-                  ptx::smem_desc(st + C::kOffB + (ka >> 1) * C::kBBoxBytes + (ka & 1) * 64, 1024, 16, 2);
-              ptx::tc_mma_sp_nvf4(d_tmem, a_desc, b_desc, idesc, (ks | ka) != 0 ? 1u : 0u, sf_cols + ka * 4,
-                                  sf_cols + C::kAtoms * 4 + ka * C::kSfbColsPerAtom + sfb_off,
-                                  tmem_base + C::kColE + ka * 2);
+          if (prof) c_wait_acc += clock64() - tp0;
+          const uint32_t d_tmem = tmem_base + acc * TILE_N;
+#pragma unroll 1
+          for (int ks = 0; ks < p.k_stages; ++ks) {
+            long long tp1 = prof ? clock64() : 0;
+            const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
+            if (kBRes && mt == mt_lo) {
+              for (int b = 0; b < (k_atoms + 1) / 2 && ok; ++b)
+                if (!ptx::mbar_wait(b_full + ks * C::kBBoxes + b, uphase)) {
+                  atomicExch(&g_status, kMmaFullTimeout);
+                  ok = false;
+                }
+              if (!ok) break;
             }
+            if (!ptx::mbar_wait(full_bar + stage, phase)) {
+              atomicExch(&g_status, kMmaFullTimeout);
+              ok = false;
+              break;
+            }
+            long long tp2 = prof ? clock64() : 0;
+            if (!ptx::mbar_wait(sf_full + slot, slot_phase)) {
+              atomicExch(&g_status, kMmaScaleTimeout);
+              ok = false;
+              break;
+            }
+            ptx::tc_fence_after();
+            long long tp3 = prof ? clock64() : 0;
+            if (prof) { c_wait_full += tp2 - tp1; c_wait_sf += tp3 - tp2; ++n_stage; }
+            // descriptors of this stage: the precomputed ones of stage 0 plus the stage's offset in
+            // 16-byte units (the address field is the low 14 bits, so a 32-bit add cannot carry out)
+            const uint32_t la = lo_a0 + soff, le = lo_e0 + soff;
+            const uint32_t lb = kBRes ? lo_b0 + ks * ((C::kBBoxes * C::kBBoxBytes) >> 4) : lo_b0 + soff;
+            const uint32_t sf_cols = sf_cols0 + slot * C::kSfSlotCols;
+            const uint32_t sfb_cols = sf_cols + C::kAtoms * 4 + sfb_off;
+            if (k_atoms == C::kAtoms) {
+#pragma unroll
+              for (int ea = 0; ea < C::kEAtoms; ++ea) ptx::tc_cp_128x128b(e_cols + ea * 4, pack_desc(le + ea * 128, hi_e));
+#pragma unroll
+              for (int ka = 0; ka < C::kAtoms; ++ka)
+                ptx::tc_mma_sp_nvf4(d_tmem, pack_desc(la + ka * 2, hi_a),
+                                    pack_desc(lb + (ka >> 1) * (C::kBBoxBytes >> 4) + (ka & 1) * 4, hi_b), idesc,
+                                    (ks | ka) != 0 ? 1u : 0u, sf_cols + ka * 4, sfb_cols + ka * C::kSfbColsPerAtom,
+                                    e_cols + ka * 2);
+            } else {
+#pragma unroll
+              for (int ea = 0; ea < C::kEAtoms; ++ea)
+                if (2 * ea < k_atoms) ptx::tc_cp_128x128b(e_cols + ea * 4, pack_desc(le + ea * 128, hi_e));
+#pragma unroll
+              for (int ka = 0; ka < C::kAtoms; ++ka)
+                if (ka < k_atoms)
+                  ptx::tc_mma_sp_nvf4(d_tmem, pack_desc(la + ka * 2, hi_a),
+                                      pack_desc(lb + (ka >> 1) * (C::kBBoxBytes >> 4) + (ka & 1) * 4, hi_b), idesc,
+                                      (ks | ka) != 0 ? 1u : 0u, sf_cols + ka * 4, sfb_cols + ka * C::kSfbColsPerAtom,
+                                      e_cols + ka * 2);
+            }
+            ptx::tc_commit(empty_bar + stage);   // stage reusable once these MMAs and copies retire
+            ptx::tc_commit(sf_empty + slot);     // and so is the scale slot
+            if (kBRes && mt + 1 == mt_hi)        // last weight tile: the activation chunks may be replaced
+              for (int b = 0; b < (k_atoms + 1) / 2; ++b) ptx::tc_commit(b_empty + ks * C::kBBoxes + b);
+            if (prof) c_issue += clock64() - tp3;
+            soff += C::kStageBytes >> 4;
+            if (++stage == p.stages) { stage = 0; soff = 0; phase ^= 1; }
+            if (++slot == C::kSfSlots) { slot = 0; slot_phase ^= 1; }
           }
-          ptx::tc_commit(empty_bar + stage);   // stage reusable once these MMAs and copies retire
-          ptx::tc_commit(sf_empty + slot);     // and so is the scale slot
-          if (prof) c_issue += clock64() - tp3;
-          if (++stage == p.stages) { stage = 0; phase ^= 1; }
-          if (++slot == C::kSfSlots) { slot = 0; slot_phase ^= 1; }
+          if (!ok) break;
+          ptx::tc_commit(acc_full + acc);
+          if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
         }
-        if (!ok) break;
-        ptx::tc_commit(acc_full + acc);
-        if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
+        uphase ^= 1;
       }
       if (prof) {
         long long* q = p.prof + blockIdx.x * 8;
@@ -938,11 +1022,11 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     int stage = 0, slot = 0;
     uint32_t phase = 0, slot_phase = 0;
     bool ok = true;
-    for (long long t = blockIdx.x; ok; t += gridDim.x) {
-      int mt, nt;
-      if (!walk.seek<TILE_N>(t, mt, nt)) break;
+    for (long long w = blockIdx.x; ok; w += gridDim.x) {
+      int mt_lo, mt_hi, nt;
+      if (!next_work<TILE_N, kBRes>(walk, w, p.n_mt, mt_lo, mt_hi, nt)) break;
 #pragma unroll 1
-      for (int ks = 0; ks < p.k_stages; ++ks) {
+      for (int ks = 0; ks < (mt_hi - mt_lo) * p.k_stages; ++ks) {
         if (!ptx::mbar_wait(full_bar + stage, phase) || !ptx::mbar_wait(sf_empty + slot, slot_phase ^ 1)) {
           atomicExch(&g_status, kScaleLoaderTimeout);
           ok = false;
@@ -1012,24 +1096,27 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         }
       }
     }
-    for (long long t = blockIdx.x;; t += gridDim.x) {
-      int mt, nt;
-      if (!walk.seek<TILE_N>(t, mt, nt)) break;
+    bool ok = true;
+    for (long long w = blockIdx.x; ok; w += gridDim.x) {
+      int mt_lo, mt_hi, nt;
+      if (!next_work<TILE_N, kBRes>(walk, w, p.n_mt, mt_lo, mt_hi, nt)) break;
       const int e = walk.e;
       const int cnt = s_counts[e];
-      const bool eprof = p.prof != nullptr && ep_tid == 0 && group == 0;
-      long long te0 = eprof ? clock64() : 0;
-      if (!ptx::mbar_wait(acc_full + acc, acc_phase)) {
-        atomicExch(&g_status, kEpilogueTimeout);
-        break;
-      }
-      ptx::tc_fence_after();
-      long long te1 = eprof ? clock64() : 0;
       const float alpha = p.alphas[e];
       float gs = 0.f;
       if (kFused) gs = p.f_gpe ? p.f_gscale[e] : p.f_gscale[0];
       const int n0 = nt * TILE_N;
       __nv_bfloat16* out_e = p.out + (long long)e * p.max_n * p.M;
+      for (int mt = mt_lo; mt < mt_hi; ++mt) {
+      const bool eprof = p.prof != nullptr && ep_tid == 0 && group == 0;
+      long long te0 = eprof ? clock64() : 0;
+      if (!ptx::mbar_wait(acc_full + acc, acc_phase)) {
+        atomicExch(&g_status, kEpilogueTimeout);
+        ok = false;
+        break;
+      }
+      ptx::tc_fence_after();
+      long long te1 = eprof ? clock64() : 0;
 #pragma unroll 1
       for (int c0 = group * 32; c0 < TILE_N; c0 += 64) {
         if (n0 + c0 >= cnt) break;             // uniform over the group's four warps
@@ -1119,6 +1206,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       if (eprof) {   // waiting for an accumulator, and group 0's share of the tile's epilogue
         long long* q = p.prof + blockIdx.x * 8;
         q[6] += te1 - te0; q[7] += clock64() - te1;
+      }
       }
     }
   }
@@ -1253,35 +1341,66 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, Params& p, int sm
   return launch_impl<TILE_N, STAGE_K, ISSUERS, true, false>(map_a, map_b, p, sm_count, false, stream);
 }
 
-template <int TILE_N, int STAGE_K, bool kFused>
+// PNV_GROUP_MM_BRES=1 keeps the activation tile resident whenever it fits; otherwise it is streamed.
+int bres_mode() {
+  static int v = -2;
+  if (v == -2) {
+    const char* env = std::getenv("PNV_GROUP_MM_BRES");
+    v = env == nullptr ? -1 : (env[0] == '0' ? 0 : 1);
+  }
+  return v;
+}
+
+template <int TILE_N, int STAGE_K, bool kFused, bool kBRes>
 int launch_wide_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p_in, int sm_count, bool pdl,
-                     cudaStream_t stream) {
-  using C = WideCfg<TILE_N, STAGE_K>;
+                     cudaStream_t stream, int stages, int b_res_bytes) {
+  using C = WideCfg<TILE_N, STAGE_K, kBRes>;
   Params p = p_in;
-  p.stages = C::kStages;
+  p.stages = stages;
+  p.b_res_bytes = b_res_bytes;
   p.trace = nullptr;
-  const size_t smem = 1024 + (size_t)C::kStages * C::kStageBytes + C::kOutBytes + C::kBarrierBytes + 4 * (size_t)p.E;
+  const size_t smem = 1024 + (size_t)b_res_bytes + (size_t)stages * C::kStageBytes + C::kOutBytes + C::kBarrierBytes +
+                      4 * (size_t)p.E;
   static bool opted_in[64] = {};
   int dev = 0;
   PNV_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64 || !opted_in[dev]) {
-    PNV_CUDA(cudaFuncSetAttribute(group_mm_wide_kernel<TILE_N, STAGE_K, kFused>,
+    PNV_CUDA(cudaFuncSetAttribute(group_mm_wide_kernel<TILE_N, STAGE_K, kFused, kBRes>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     if (dev >= 0 && dev < 64) opted_in[dev] = true;
   }
-  long long max_tiles = (long long)p.E * p.n_mt * ceil_div_i(p.max_n, TILE_N);
-  int grid = (int)(max_tiles < sm_count ? max_tiles : sm_count);
+  const long long units = (long long)p.E * ceil_div_i(p.max_n, TILE_N);
+  const long long max_work = kBRes ? units : units * p.n_mt;
+  int grid = (int)(max_work < sm_count ? max_work : sm_count);
   if (grid < 1) grid = 1;
-  PNV_CUDA(launch_pdl(group_mm_wide_kernel<TILE_N, STAGE_K, kFused>, dim3(grid), dim3(C::kThreads), smem, stream,
-                      pdl, map_a, map_b, p));
+  PNV_CUDA(launch_pdl(group_mm_wide_kernel<TILE_N, STAGE_K, kFused, kBRes>, dim3(grid), dim3(C::kThreads), smem,
+                      stream, pdl, map_a, map_b, p));
   return PNV_OK;
 }
 
 template <int TILE_N, int STAGE_K>
 int launch_wide(const CUtensorMap& map_a, const CUtensorMap& map_b, Params& p, int sm_count, bool pdl,
                 cudaStream_t stream) {
-  if (p.f_b_out != nullptr) return launch_wide_impl<TILE_N, STAGE_K, true>(map_a, map_b, p, sm_count, pdl, stream);
-  return launch_wide_impl<TILE_N, STAGE_K, false>(map_a, map_b, p, sm_count, pdl, stream);
+  using CS = WideCfg<TILE_N, STAGE_K, false>;
+  using CR = WideCfg<TILE_N, STAGE_K, true>;
+  const int fixed = 1024 + CS::kOutBytes + CS::kBarrierBytes + 4 * p.E;
+  // resident activation tile: ceil(K / 256) chunks of TILE_N x 128 bytes, and still three stages of weights
+  const int chunks = ceil_div_i(p.K, 256);
+  const int b_res = chunks * CR::kBBoxBytes;
+  const int stages_res = std::min((int)CR::kMaxStages, (kSmemLimit - fixed - b_res) / CR::kStageBytes);
+  const long long units = (long long)p.E * ceil_div_i(p.max_n, TILE_N);
+  const bool fits = chunks <= CR::kMaxChunks && b_res < kSmemLimit - fixed && stages_res >= 3;
+  (void)units;   // resident mode is opt-in (PNV_GROUP_MM_BRES=1) until it measures faster than streaming
+  const bool resident = fits && bres_mode() == 1;
+  const bool fused = p.f_b_out != nullptr;
+  if (resident) {
+    if (fused) return launch_wide_impl<TILE_N, STAGE_K, true, true>(map_a, map_b, p, sm_count, pdl, stream, stages_res, b_res);
+    return launch_wide_impl<TILE_N, STAGE_K, false, true>(map_a, map_b, p, sm_count, pdl, stream, stages_res, b_res);
+  }
+  const int stages = std::min((int)CS::kMaxStages, (kSmemLimit - fixed) / CS::kStageBytes);
+  if (stages < 2) return fail(PNV_ERR_INVALID_ARGUMENT, "group_mm: not enough shared memory for a %dx%d pipeline", TILE_N, STAGE_K);
+  if (fused) return launch_wide_impl<TILE_N, STAGE_K, true, false>(map_a, map_b, p, sm_count, pdl, stream, stages, 0);
+  return launch_wide_impl<TILE_N, STAGE_K, false, false>(map_a, map_b, p, sm_count, pdl, stream, stages, 0);
 }
 
 // Tile variants.  The first eight names and ids are the reference's; a "2sm" name is accepted with
@@ -1400,6 +1519,7 @@ int group_mm_common(void* out, const FusedArgs* fused, const uint8_t* a_comp, co
   p.sfb_rt = sf_row_atoms(max_n);
   p.prof = profile_buffer(fused != nullptr);
   p.stages = 0;
+  p.b_res_bytes = 0;
   p.trace = nullptr;
 
   // Tile geometry.  The variant names fix the widest token tile; when every expert's tokens fit one
