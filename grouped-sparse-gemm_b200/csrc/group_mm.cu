@@ -116,6 +116,7 @@ struct Params {
   int e_m_atoms;     // metadata atoms along M = n_mt
   int sfb_rt;        // scale row-atoms per expert in sfb = ceil(max_n / 128)
   int stages;        // pipeline depth in use (<= Cfg::kStages)
+  int prod_lanes;    // wide kernel: lanes of each producer warp that issue copies side by side
   int b_res_bytes;   // wide kernel: bytes of the resident activation tile in front of the stage ring (0 = streamed)
   // fused SwiGLU + requantise epilogue (kFused kernels): GEMM2's operands instead of a bf16 output
   uint8_t* f_b_out;        // [E, max_n, N/2] e2m1 codes, N = M / 2
@@ -677,15 +678,19 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 // thread.  Sixteen warps:
 //   warp 0   tile producer (TMA: compressed weights, activations)        } as in the narrow kernel
 //   warp 1   side producer (bulk copies: metadata, SFA, SFB atoms)       }
-//   warp 2   MMA issuer: per stage the metadata tcgen05.cp and the MMAs, nothing else
-//   warp 3   spare
+//   2 - 3    MMA issuers, alternate tiles: per stage the metadata tcgen05.cp and the MMAs, nothing else
 //   4 - 7    scale loaders, one per tensor-memory lane quarter: read the stage's scale atoms from
 //            shared memory (one 16-byte line per lane) and write them into a ring of scale slots in
 //            tensor memory with tcgen05.st -- the same image tcgen05.cp.32x128b.warpx4 would leave
 //   8 - 15   epilogue, two groups of four warps; a tile's 32-column chunks alternate between them
-// Barriers on top of the stage full/empty pair: sf_full[slot] (the four loaders -> issuer) and
-// sf_empty[slot] (issuer's tcgen05.commit -> loaders); a stage is released by the issuer's commit
-// plus the four loaders (its scales have left shared memory).
+// Every pipeline stage owns one slot of the scale ring.  Barriers: full[s] (copies landed; the
+// loaders wait on it), sf_full[s] (the four loaders -> issuer: scales are in tensor memory, which
+// also tells the issuer that the stage's copies have landed, since the loaders saw full[s] first),
+// empty[s] (issuer's tcgen05.commit plus the four loaders -> producers).  A refilled stage implies
+// that the MMAs which read the slot's previous scales have retired, so the loaders need no barrier
+// of their own for the slot.  The issuer thread is the kernel's critical resource -- one thread
+// executes a few hundred instructions per microsecond at best -- so it does no tile arithmetic:
+// it counts this CTA's tiles once and then only waits, issues and commits.
 //
 // Resident activations (kBRes).  An SM takes in about 48 bytes per cycle from L2, while one MMA reads
 // 12 KB (N = 128) of operands from shared memory in 96 cycles, so a kernel that streams both
@@ -721,17 +726,16 @@ struct WideCfg {
   static constexpr int kColSf = 272;                        // ring of scale slots
   static constexpr int kSfbColsPerAtom = 4 * kSfbRowAtoms;
   static constexpr int kSfSlotCols = kAtoms * (4 + kSfbColsPerAtom);
-  static constexpr int kSfSlots = 4;
+  static constexpr int kSfSlots = (kTmemCols - kColSf) / kSfSlotCols;   // one per stage: caps the pipeline depth
   static constexpr int kOffA = 0;
   static constexpr int kOffB = kABytes;
   static constexpr int kOffE = kOffB + kBBytes;
   static constexpr int kOffSfa = kOffE + kEBytes;
   static constexpr int kOffSfb = kOffSfa + kSfaBytes;
   static_assert(kStageBytes % 1024 == 0, "stage buffers must keep 1024-byte alignment");
-  static_assert(kAccStages * TILE_N <= kColE && kColE + 4 * kEAtoms <= kColSf &&
-                kColSf + kSfSlots * kSfSlotCols <= kTmemCols, "tensor-memory column map overflows");
-  static_assert(8 * (2 * kMaxStages + 2 * kAccStages + 2 * kSfSlots + 2 * kMaxChunks) + 16 <= kBarrierBytes,
-                "barrier block overflows");
+  static_assert(kAccStages * TILE_N <= kColE && kColE + 2 * 4 * kEAtoms <= kColSf && kSfSlots >= 2,
+                "tensor-memory column map overflows");
+  static_assert(8 * (3 * kMaxStages + 2 * kAccStages + 2 * kMaxChunks) + 16 <= kBarrierBytes, "barrier block overflows");
 };
 
 __device__ __forceinline__ void epilogue_group_sync(int group) {
@@ -742,6 +746,18 @@ __device__ __forceinline__ uint64_t pack_desc(uint32_t lo, uint32_t hi) {
   uint64_t d;
   asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
   return d;
+}
+
+// Work items (tiles, or (expert, token tile) units when per_expert == 1) this CTA will process:
+// items b, b + grid, ... of the list every role walks.  Warp-collective.
+template <int TILE_N>
+__device__ __forceinline__ int my_work_items(const int* cnt, int E, int per_expert, int lane) {
+  long long sum = 0;
+  for (int e = lane; e < E; e += 32) sum += ceil_div_i(cnt[e], TILE_N);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const long long total = sum * per_expert;
+  return (long long)blockIdx.x < total ? (int)((total - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
 }
 
 // One work item of a CTA: a single tile, or with resident activations every weight tile of one
@@ -770,8 +786,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   uint64_t* acc_full = empty_bar + C::kMaxStages;
   uint64_t* acc_empty = acc_full + C::kAccStages;
   uint64_t* sf_full = acc_empty + C::kAccStages;
-  uint64_t* sf_empty = sf_full + C::kSfSlots;
-  uint64_t* b_full = sf_empty + C::kSfSlots;
+  uint64_t* b_full = sf_full + C::kMaxStages;
   uint64_t* b_empty = b_full + C::kMaxChunks;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_empty + C::kMaxChunks);
   int* s_counts = reinterpret_cast<int*>(after_stages + C::kOutBytes + C::kBarrierBytes);
@@ -782,11 +797,14 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&map_a);
     ptx::prefetch_tensormap(&map_b);
-    for (int s = 0; s < p.stages; ++s) { ptx::mbar_init(full_bar + s, 2); ptx::mbar_init(empty_bar + s, 1 + 4); }
+    for (int s = 0; s < p.stages; ++s) {
+      ptx::mbar_init(full_bar + s, 2);
+      ptx::mbar_init(empty_bar + s, 1 + 4);
+      ptx::mbar_init(sf_full + s, 4);
+    }
     if (kBRes)
       for (int c = 0; c < C::kMaxChunks; ++c) { ptx::mbar_init(b_full + c, 1); ptx::mbar_init(b_empty + c, 1); }
     for (int a = 0; a < C::kAccStages; ++a) { ptx::mbar_init(acc_full + a, 1); ptx::mbar_init(acc_empty + a, 8); }
-    for (int s = 0; s < C::kSfSlots; ++s) { ptx::mbar_init(sf_full + s, 4); ptx::mbar_init(sf_empty + s, 1); }
     ptx::fence_mbar_init();
   }
   if (warp == 2) {
@@ -807,52 +825,56 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 
   if (warp == 0) {
     // =============================== tile producer (TMA) ===============================
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0, uphase = 0;
+    // p.prod_lanes lanes work side by side, lane i on pipeline slots i, i + lanes, ...: one thread
+    // needs several hundred cycles per (wait, expect, copy) sequence, while the same sequence
+    // issued by several lanes of a warp in one go costs little more than once.
+    if (lane < p.prod_lanes) {
       bool ok = true;
-      for (long long w = blockIdx.x; ok; w += gridDim.x) {
-        int mt_lo, mt_hi, nt;
-        if (!next_work<TILE_N, kBRes>(walk, w, p.n_mt, mt_lo, mt_hi, nt)) break;
+      for (int G = lane; ok; G += p.prod_lanes) {       // G: this CTA's running stage number
+        const int n = G / p.k_stages, ks = G - n * p.k_stages;          // n: running tile number
+        int mt, nt;
+        if (kBRes) {
+          const int u = n / p.n_mt;
+          mt = n - u * p.n_mt;
+          int dummy;
+          if (!walk.seek<TILE_N>(blockIdx.x + (long long)u * gridDim.x, dummy, nt)) break;
+        } else if (!walk.seek<TILE_N>(blockIdx.x + (long long)n * gridDim.x, mt, nt)) {
+          break;
+        }
         const int e = walk.e;
         const int n0 = nt * TILE_N;
-        for (int mt = mt_lo; mt < mt_hi && ok; ++mt) {
-#pragma unroll 1
-          for (int ks = 0; ks < p.k_stages; ++ks) {
-            const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
-            const int b_boxes = (k_atoms + 1) / 2;
-            if (kBRes && mt == mt_lo) {
-              // this unit's activation chunks, each as soon as the previous unit has finished with it
-              for (int b = 0; b < b_boxes && ok; ++b) {
-                const int kc = ks * C::kBBoxes + b;
-                if (!ptx::mbar_wait(b_empty + kc, uphase ^ 1)) {
-                  atomicExch(&g_status, kProducerEmptyTimeout);
-                  ok = false;
-                  break;
-                }
-                ptx::mbar_arrive_expect_tx(b_full + kc, C::kBBoxBytes);
-                ptx::tma_load_3d(b_res + kc * C::kBBoxBytes, &map_b, b_full + kc, kc * 128, n0, e);
-              }
-              if (!ok) break;
-            }
-            long long tq0 = p.prof ? clock64() : 0;
-            if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1)) {
+        const int turn = G / p.stages, stage = G - turn * p.stages;
+        const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
+        const int b_boxes = (k_atoms + 1) / 2;
+        if (kBRes && mt == 0) {
+          // this unit's activation chunks, each as soon as the previous unit has finished with it
+          const uint32_t uphase = (uint32_t)(n / p.n_mt) & 1u;
+          for (int b = 0; b < b_boxes && ok; ++b) {
+            const int kc = ks * C::kBBoxes + b;
+            if (!ptx::mbar_wait(b_empty + kc, uphase ^ 1)) {
               atomicExch(&g_status, kProducerEmptyTimeout);
               ok = false;
               break;
             }
-            if (p.prof) p.prof[blockIdx.x * 8 + 4] += clock64() - tq0;
-            uint8_t* st = stage_base + stage * C::kStageBytes;
-            ptx::mbar_arrive_expect_tx(full_bar + stage, C::kABytes + (kBRes ? 0 : b_boxes * C::kBBoxBytes));
-            ptx::tma_load_3d(st + C::kOffA, &map_a, full_bar + stage, ks * C::kARowBytes, mt * kTileM, e);
-            if (!kBRes)
-              for (int b = 0; b < b_boxes; ++b)
-                ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + stage,
-                                 ks * (STAGE_K / 2) + b * 128, n0, e);
-            if (++stage == p.stages) { stage = 0; phase ^= 1; }
+            ptx::mbar_arrive_expect_tx(b_full + kc, C::kBBoxBytes);
+            ptx::tma_load_3d(b_res + kc * C::kBBoxBytes, &map_b, b_full + kc, kc * 128, n0, e);
           }
+          if (!ok) break;
         }
-        uphase ^= 1;
+        long long tq0 = p.prof ? clock64() : 0;
+        if (!ptx::mbar_wait(empty_bar + stage, ((uint32_t)turn & 1u) ^ 1u)) {
+          atomicExch(&g_status, kProducerEmptyTimeout);
+          ok = false;
+          break;
+        }
+        if (p.prof && lane == 0) p.prof[blockIdx.x * 8 + 4] += clock64() - tq0;
+        uint8_t* st = stage_base + stage * C::kStageBytes;
+        ptx::mbar_arrive_expect_tx(full_bar + stage, C::kABytes + (kBRes ? 0 : b_boxes * C::kBBoxBytes));
+        ptx::tma_load_3d(st + C::kOffA, &map_a, full_bar + stage, ks * C::kARowBytes, mt * kTileM, e);
+        if (!kBRes)
+          for (int b = 0; b < b_boxes; ++b)
+            ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + stage,
+                             ks * (STAGE_K / 2) + b * 128, n0, e);
       }
       if (!ok) {
         // give copies already in flight time to land before the CTA's shared memory is released
@@ -863,42 +885,43 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     __syncwarp();
   } else if (warp == 1) {
     // =============================== side producer (bulk copies) ===============================
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
+    if (lane < p.prod_lanes) {
       bool ok = true;
-      for (long long w = blockIdx.x; ok; w += gridDim.x) {
-        int mt_lo, mt_hi, nt;
-        if (!next_work<TILE_N, kBRes>(walk, w, p.n_mt, mt_lo, mt_hi, nt)) break;
+      for (int G = lane; ok; G += p.prod_lanes) {
+        const int n = G / p.k_stages, ks = G - n * p.k_stages;
+        int mt, nt;
+        if (kBRes) {
+          const int u = n / p.n_mt;
+          mt = n - u * p.n_mt;
+          int dummy;
+          if (!walk.seek<TILE_N>(blockIdx.x + (long long)u * gridDim.x, dummy, nt)) break;
+        } else if (!walk.seek<TILE_N>(blockIdx.x + (long long)n * gridDim.x, mt, nt)) {
+          break;
+        }
         const int e = walk.e;
         const int n0 = nt * TILE_N;
+        const int turn = G / p.stages, stage = G - turn * p.stages;
         const uint8_t* sfb_base = p.sfb + (((long long)e * p.sfb_rt + (n0 >> 7)) * p.n_kt) * 512;
         const int sfb_row_atoms = TILE_N > 128 ? min(2, p.sfb_rt - (n0 >> 7)) : 1;
-        for (int mt = mt_lo; mt < mt_hi && ok; ++mt) {
-          const uint8_t* e_base = p.e_meta + (((long long)e * p.e_k_atoms) * p.e_m_atoms + mt) * 2048;
-          const uint8_t* sfa_base = p.sfa + (((long long)e * p.n_mt + mt) * p.n_kt) * 512;
-#pragma unroll 1
-          for (int ks = 0; ks < p.k_stages; ++ks) {
-            if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1)) {
-              atomicExch(&g_status, kSideProducerTimeout);
-              ok = false;
-              break;
-            }
-            uint8_t* st = stage_base + stage * C::kStageBytes;
-            const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
-            const int e_atoms = (k_atoms + 1) / 2;
-            const uint32_t sf_bytes = 512u * k_atoms;
-            ptx::mbar_arrive_expect_tx(full_bar + stage, e_atoms * 2048 + sf_bytes * (1 + sfb_row_atoms));
-            for (int ea = 0; ea < e_atoms; ++ea)
-              ptx::bulk_load(st + C::kOffE + ea * 2048,
-                             e_base + (long long)(ks * C::kEAtoms + ea) * p.e_m_atoms * 2048, 2048, full_bar + stage);
-            ptx::bulk_load(st + C::kOffSfa, sfa_base + (long long)ks * C::kAtoms * 512, sf_bytes, full_bar + stage);
-            for (int ra = 0; ra < sfb_row_atoms; ++ra)
-              ptx::bulk_load(st + C::kOffSfb + ra * C::kSfaBytes,
-                             sfb_base + ((long long)ra * p.n_kt + ks * C::kAtoms) * 512, sf_bytes, full_bar + stage);
-            if (++stage == p.stages) { stage = 0; phase ^= 1; }
-          }
+        const uint8_t* e_base = p.e_meta + (((long long)e * p.e_k_atoms) * p.e_m_atoms + mt) * 2048;
+        const uint8_t* sfa_base = p.sfa + (((long long)e * p.n_mt + mt) * p.n_kt) * 512;
+        if (!ptx::mbar_wait(empty_bar + stage, ((uint32_t)turn & 1u) ^ 1u)) {
+          atomicExch(&g_status, kSideProducerTimeout);
+          ok = false;
+          break;
         }
+        uint8_t* st = stage_base + stage * C::kStageBytes;
+        const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
+        const int e_atoms = (k_atoms + 1) / 2;
+        const uint32_t sf_bytes = 512u * k_atoms;
+        ptx::mbar_arrive_expect_tx(full_bar + stage, e_atoms * 2048 + sf_bytes * (1 + sfb_row_atoms));
+        for (int ea = 0; ea < e_atoms; ++ea)
+          ptx::bulk_load(st + C::kOffE + ea * 2048,
+                         e_base + (long long)(ks * C::kEAtoms + ea) * p.e_m_atoms * 2048, 2048, full_bar + stage);
+        ptx::bulk_load(st + C::kOffSfa, sfa_base + (long long)ks * C::kAtoms * 512, sf_bytes, full_bar + stage);
+        for (int ra = 0; ra < sfb_row_atoms; ++ra)
+          ptx::bulk_load(st + C::kOffSfb + ra * C::kSfaBytes,
+                         sfb_base + ((long long)ra * p.n_kt + ks * C::kAtoms) * 512, sf_bytes, full_bar + stage);
       }
       if (!ok) {
 #pragma unroll 1
@@ -906,16 +929,41 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       }
     }
     __syncwarp();
-  } else if (warp == 2) {
-    // =============================== MMA issuer ===============================
-    if (lane == 0) {
+  } else if (warp == 2 || warp == 3) {
+    // =============================== MMA issuers ===============================
+    // A tcgen05.mma holds its issuing thread for about as long as it executes, so whatever else
+    // that thread does between two MMAs (waits, descriptor arithmetic, commits: a few hundred
+    // cycles per stage for a lone thread) is time the tensor pipe idles.  Two issuers in two warps
+    // take alternate tiles, each into its own accumulator stage; while one is between MMAs the
+    // other's are executing.  Every tile's MMAs still come from one thread, in K order.
+    constexpr int kIssuers = (C::kAccStages == 2 && !kBRes) ? 2 : 1;
+    const int issuer = warp - 2;
+    const int n_items = my_work_items<TILE_N>(s_counts, p.E, kBRes ? 1 : p.n_mt, lane);
+    if (lane == 0 && issuer < kIssuers) {
       constexpr uint32_t idesc = ptx::mma_sp_nvf4_idesc(TILE_N);
-      int stage = 0, acc = 0, slot = 0;
-      uint32_t phase = 0, acc_phase = 0, slot_phase = 0;
+      int stage = 0, acc = kIssuers == 2 ? issuer : 0;
+      uint32_t phase = 0, acc_phase = 0, uphase = 0, soff = 0;
       bool ok = true;
-      long long c_wait_full = 0, c_wait_sf = 0, c_issue = 0, c_wait_acc = 0, n_stage = 0;
-      const bool prof = p.prof != nullptr;
-      uint32_t uphase = 0, soff = 0;
+      long long c_wait_sf = 0, c_issue = 0, c_wait_acc = 0, n_stage = 0;
+      const bool prof = p.prof != nullptr && issuer == 0;
+      // Pass over the stages of a tile the other issuer takes.  Each one is waited for, not just
+      // counted: a parity wait only tells two consecutive phases of a barrier apart, so an issuer
+      // must see every turn of every slot, or after a long tile it would take an old phase for its own.
+      auto skip_stages = [&](int n) {
+#pragma unroll 1
+        for (int i = 0; i < n && ok; ++i) {
+          if (!ptx::mbar_wait(sf_full + stage, phase)) {
+            atomicExch(&g_status, kMmaScaleTimeout);
+            ok = false;
+          }
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+        soff = (uint32_t)stage * (C::kStageBytes >> 4);
+      };
+      if (kIssuers == 2 && issuer == 1 && n_items > 1) skip_stages(p.k_stages);
+      const long long t_begin = prof ? clock64() : 0;
+      unsigned long long ns_begin = 0;
+      if (prof) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_begin));
       // stage-0 descriptors, split into the 32-bit halves: only the low half changes with the address
       const uint64_t d_a0 = ptx::smem_desc(ptx::smem_u32(stage_base) + C::kOffA, 8 * C::kARowBytes, 16, C::kASwizzle);
       const uint64_t d_b0 = ptx::smem_desc(kBRes ? ptx::smem_u32(b_res) : ptx::smem_u32(stage_base) + C::kOffB, 1024, 16, 2);
@@ -923,14 +971,20 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       const uint32_t lo_a0 = (uint32_t)d_a0, hi_a = (uint32_t)(d_a0 >> 32);
       const uint32_t lo_b0 = (uint32_t)d_b0, hi_b = (uint32_t)(d_b0 >> 32);
       const uint32_t lo_e0 = (uint32_t)d_e0, hi_e = (uint32_t)(d_e0 >> 32);
-      const uint32_t e_cols = tmem_base + C::kColE, sf_cols0 = tmem_base + C::kColSf;
-      for (long long w = blockIdx.x; ok; w += gridDim.x) {
-        int mt_lo, mt_hi, nt;
-        if (!next_work<TILE_N, kBRes>(walk, w, p.n_mt, mt_lo, mt_hi, nt)) break;
+      const uint32_t e_cols = tmem_base + C::kColE + issuer * (4 * C::kEAtoms);   // private metadata columns
+      const uint32_t sf_cols0 = tmem_base + C::kColSf;
+      const int tiles_per_item = kBRes ? p.n_mt : 1;
+      const int last_atoms = p.n_kt - (p.k_stages - 1) * C::kAtoms;     // K-blocks of a tile's last stage
+      for (int item = kIssuers == 2 ? issuer : 0; item < n_items && ok; item += kIssuers) {
         // a 64-wide tile's scales sit 0 or 2 columns into the 128-row atom (even offsets only: the MMA
-        // faults on an odd scale column)
-        const uint32_t sfb_off = TILE_N < 128 ? ((nt * TILE_N) & 127) >> 5 : 0;
-        for (int mt = mt_lo; mt < mt_hi && ok; ++mt) {
+        // faults on an odd scale column); wider tiles start at column 0 and need no tile coordinates
+        uint32_t sfb_off = 0;
+        if (TILE_N < 128) {
+          int mt_lo, mt_hi, nt;
+          if (!next_work<TILE_N, kBRes>(walk, blockIdx.x + (long long)item * gridDim.x, p.n_mt, mt_lo, mt_hi, nt)) break;
+          sfb_off = ((nt * TILE_N) & 127) >> 5;
+        }
+        for (int mt = 0; mt < tiles_per_item && ok; ++mt) {
           long long tp0 = prof ? clock64() : 0;
           if (!ptx::mbar_wait(acc_empty + acc, acc_phase ^ 1)) {
             atomicExch(&g_status, kMmaAccTimeout);
@@ -943,8 +997,8 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 #pragma unroll 1
           for (int ks = 0; ks < p.k_stages; ++ks) {
             long long tp1 = prof ? clock64() : 0;
-            const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
-            if (kBRes && mt == mt_lo) {
+            const int k_atoms = ks + 1 == p.k_stages ? last_atoms : C::kAtoms;
+            if (kBRes && mt == 0) {
               for (int b = 0; b < (k_atoms + 1) / 2 && ok; ++b)
                 if (!ptx::mbar_wait(b_full + ks * C::kBBoxes + b, uphase)) {
                   atomicExch(&g_status, kMmaFullTimeout);
@@ -952,25 +1006,19 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 }
               if (!ok) break;
             }
-            if (!ptx::mbar_wait(full_bar + stage, phase)) {
-              atomicExch(&g_status, kMmaFullTimeout);
-              ok = false;
-              break;
-            }
-            long long tp2 = prof ? clock64() : 0;
-            if (!ptx::mbar_wait(sf_full + slot, slot_phase)) {
+            if (!ptx::mbar_wait(sf_full + stage, phase)) {
               atomicExch(&g_status, kMmaScaleTimeout);
               ok = false;
               break;
             }
             ptx::tc_fence_after();
             long long tp3 = prof ? clock64() : 0;
-            if (prof) { c_wait_full += tp2 - tp1; c_wait_sf += tp3 - tp2; ++n_stage; }
+            if (prof) { c_wait_sf += tp3 - tp1; ++n_stage; }
             // descriptors of this stage: the precomputed ones of stage 0 plus the stage's offset in
             // 16-byte units (the address field is the low 14 bits, so a 32-bit add cannot carry out)
             const uint32_t la = lo_a0 + soff, le = lo_e0 + soff;
             const uint32_t lb = kBRes ? lo_b0 + ks * ((C::kBBoxes * C::kBBoxBytes) >> 4) : lo_b0 + soff;
-            const uint32_t sf_cols = sf_cols0 + slot * C::kSfSlotCols;
+            const uint32_t sf_cols = sf_cols0 + stage * C::kSfSlotCols;
             const uint32_t sfb_cols = sf_cols + C::kAtoms * 4 + sfb_off;
             if (k_atoms == C::kAtoms) {
 #pragma unroll
@@ -993,66 +1041,66 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                                       (ks | ka) != 0 ? 1u : 0u, sf_cols + ka * 4, sfb_cols + ka * C::kSfbColsPerAtom,
                                       e_cols + ka * 2);
             }
-            ptx::tc_commit(empty_bar + stage);   // stage reusable once these MMAs and copies retire
-            ptx::tc_commit(sf_empty + slot);     // and so is the scale slot
-            if (kBRes && mt + 1 == mt_hi)        // last weight tile: the activation chunks may be replaced
+            ptx::tc_commit(empty_bar + stage);   // stage and scale slot reusable once these MMAs and copies retire
+            if (kBRes && mt + 1 == tiles_per_item)   // last weight tile: the activation chunks may be replaced
               for (int b = 0; b < (k_atoms + 1) / 2; ++b) ptx::tc_commit(b_empty + ks * C::kBBoxes + b);
             if (prof) c_issue += clock64() - tp3;
             soff += C::kStageBytes >> 4;
             if (++stage == p.stages) { stage = 0; soff = 0; phase ^= 1; }
-            if (++slot == C::kSfSlots) { slot = 0; slot_phase ^= 1; }
           }
           if (!ok) break;
           ptx::tc_commit(acc_full + acc);
-          if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
+          if (kIssuers == 2) {
+            acc_phase ^= 1;                 // this issuer's accumulator stage comes round every own tile
+            if (item + kIssuers < n_items) skip_stages(p.k_stages);
+          } else if (++acc == C::kAccStages) {
+            acc = 0;
+            acc_phase ^= 1;
+          }
         }
         uphase ^= 1;
       }
       if (prof) {
         long long* q = p.prof + blockIdx.x * 8;
-        q[0] = c_wait_full; q[1] = c_issue; q[2] = c_wait_acc; q[3] = n_stage; q[5] = c_wait_sf;
+        q[0] = 0; q[1] = c_issue; q[2] = c_wait_acc; q[3] = n_stage; q[5] = c_wait_sf;
+        unsigned long long ns_end;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_end));
+        long long* x = p.prof + 256 * 8 + blockIdx.x * 8;   // issuer loop: cycles and nanoseconds
+        x[0] = clock64() - t_begin; x[1] = (long long)(ns_end - ns_begin);
       }
     }
     __syncwarp();
-  } else if (warp == 3) {
-    // spare warp: nothing to do until the final barrier
   } else if (warp < 8) {
     // =============================== scale loaders ===============================
+    const int n_items = my_work_items<TILE_N>(s_counts, p.E, kBRes ? 1 : p.n_mt, lane);
+    const long long n_stages = (long long)n_items * (kBRes ? p.n_mt : 1) * p.k_stages;
     const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + C::kColSf;
-    int stage = 0, slot = 0;
-    uint32_t phase = 0, slot_phase = 0;
-    bool ok = true;
-    for (long long w = blockIdx.x; ok; w += gridDim.x) {
-      int mt_lo, mt_hi, nt;
-      if (!next_work<TILE_N, kBRes>(walk, w, p.n_mt, mt_lo, mt_hi, nt)) break;
+    int stage = 0;
+    uint32_t phase = 0;
 #pragma unroll 1
-      for (int ks = 0; ks < (mt_hi - mt_lo) * p.k_stages; ++ks) {
-        if (!ptx::mbar_wait(full_bar + stage, phase) || !ptx::mbar_wait(sf_empty + slot, slot_phase ^ 1)) {
-          atomicExch(&g_status, kScaleLoaderTimeout);
-          ok = false;
-          break;
-        }
-        ptx::tc_fence_after();
-        const uint8_t* st = stage_base + stage * C::kStageBytes + lane * 16;
-        const uint32_t cols = lane_base + slot * C::kSfSlotCols;
-#pragma unroll
-        for (int ka = 0; ka < C::kAtoms; ++ka) {
-          ptx::tc_st_32x32_x4(cols + ka * 4, *reinterpret_cast<const uint4*>(st + C::kOffSfa + ka * 512));
-#pragma unroll
-          for (int ra = 0; ra < C::kSfbRowAtoms; ++ra)
-            ptx::tc_st_32x32_x4(cols + C::kAtoms * 4 + ka * C::kSfbColsPerAtom + ra * 4,
-                                *reinterpret_cast<const uint4*>(st + C::kOffSfb + ra * C::kSfaBytes + ka * 512));
-        }
-        ptx::tc_st_wait();
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          ptx::mbar_arrive(sf_full + slot);
-          ptx::mbar_arrive(empty_bar + stage);   // the scales have left shared memory
-        }
-        if (++stage == p.stages) { stage = 0; phase ^= 1; }
-        if (++slot == C::kSfSlots) { slot = 0; slot_phase ^= 1; }
+    for (long long g = 0; g < n_stages; ++g) {
+      if (!ptx::mbar_wait(full_bar + stage, phase)) {
+        atomicExch(&g_status, kScaleLoaderTimeout);
+        break;
       }
+      const uint8_t* st = stage_base + stage * C::kStageBytes + lane * 16;
+      const uint32_t cols = lane_base + stage * C::kSfSlotCols;
+#pragma unroll
+      for (int ka = 0; ka < C::kAtoms; ++ka) {
+        ptx::tc_st_32x32_x4(cols + ka * 4, *reinterpret_cast<const uint4*>(st + C::kOffSfa + ka * 512));
+#pragma unroll
+        for (int ra = 0; ra < C::kSfbRowAtoms; ++ra)
+          ptx::tc_st_32x32_x4(cols + C::kAtoms * 4 + ka * C::kSfbColsPerAtom + ra * 4,
+                              *reinterpret_cast<const uint4*>(st + C::kOffSfb + ra * C::kSfaBytes + ka * 512));
+      }
+      ptx::tc_st_wait();
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        ptx::mbar_arrive(sf_full + stage);
+        ptx::mbar_arrive(empty_bar + stage);   // the scales have left shared memory
+      }
+      if (++stage == p.stages) { stage = 0; phase ^= 1; }
     }
   } else {
     // =============================== epilogue ===============================
@@ -1275,9 +1323,9 @@ long long* profile_buffer(bool fused) {   // PNV_GROUP_MM_PROFILE=2 records the 
   }
   if (v == 0 || (v == 2 && !fused)) return nullptr;
   if (g_prof_dev == nullptr) {
-    if (cudaMalloc(reinterpret_cast<void**>(&g_prof_dev), 256 * 8 * sizeof(long long)) != cudaSuccess) return nullptr;
+    if (cudaMalloc(reinterpret_cast<void**>(&g_prof_dev), 256 * 16 * sizeof(long long)) != cudaSuccess) return nullptr;
   }
-  cudaMemset(g_prof_dev, 0, 256 * 8 * sizeof(long long));
+  cudaMemset(g_prof_dev, 0, 256 * 16 * sizeof(long long));
   return g_prof_dev;
 }
 
@@ -1358,6 +1406,13 @@ int launch_wide_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const P
   Params p = p_in;
   p.stages = stages;
   p.b_res_bytes = b_res_bytes;
+  p.prod_lanes = stages >= 8 ? 4 : stages >= 4 ? 2 : 1;
+  if (const char* env = std::getenv("PNV_GROUP_MM_LANES")) {   // experiment knob
+    const int v = std::atoi(env);
+    if (v >= 1 && v <= 16) p.prod_lanes = std::min(v, stages);
+  }
+  // resident mode: a lane must never wait for a chunk that a later lane of the same batch releases
+  if (kBRes) p.prod_lanes = std::max(1, std::min(p.prod_lanes, p.k_stages));
   p.trace = nullptr;
   const size_t smem = 1024 + (size_t)b_res_bytes + (size_t)stages * C::kStageBytes + C::kOutBytes + C::kBarrierBytes +
                       4 * (size_t)p.E;
@@ -1387,7 +1442,7 @@ int launch_wide(const CUtensorMap& map_a, const CUtensorMap& map_b, Params& p, i
   // resident activation tile: ceil(K / 256) chunks of TILE_N x 128 bytes, and still three stages of weights
   const int chunks = ceil_div_i(p.K, 256);
   const int b_res = chunks * CR::kBBoxBytes;
-  const int stages_res = std::min((int)CR::kMaxStages, (kSmemLimit - fixed - b_res) / CR::kStageBytes);
+  const int stages_res = std::min(std::min((int)CR::kMaxStages, (int)CR::kSfSlots), (kSmemLimit - fixed - b_res) / CR::kStageBytes);
   const long long units = (long long)p.E * ceil_div_i(p.max_n, TILE_N);
   const bool fits = chunks <= CR::kMaxChunks && b_res < kSmemLimit - fixed && stages_res >= 3;
   (void)units;   // resident mode is opt-in (PNV_GROUP_MM_BRES=1) until it measures faster than streaming
@@ -1397,7 +1452,7 @@ int launch_wide(const CUtensorMap& map_a, const CUtensorMap& map_b, Params& p, i
     if (fused) return launch_wide_impl<TILE_N, STAGE_K, true, true>(map_a, map_b, p, sm_count, pdl, stream, stages_res, b_res);
     return launch_wide_impl<TILE_N, STAGE_K, false, true>(map_a, map_b, p, sm_count, pdl, stream, stages_res, b_res);
   }
-  const int stages = std::min((int)CS::kMaxStages, (kSmemLimit - fixed) / CS::kStageBytes);
+  const int stages = std::min(std::min((int)CS::kMaxStages, (int)CS::kSfSlots), (kSmemLimit - fixed) / CS::kStageBytes);
   if (stages < 2) return fail(PNV_ERR_INVALID_ARGUMENT, "group_mm: not enough shared memory for a %dx%d pipeline", TILE_N, STAGE_K);
   if (fused) return launch_wide_impl<TILE_N, STAGE_K, true, false>(map_a, map_b, p, sm_count, pdl, stream, stages, 0);
   return launch_wide_impl<TILE_N, STAGE_K, false, false>(map_a, map_b, p, sm_count, pdl, stream, stages, 0);
@@ -1437,7 +1492,7 @@ extern "C" int pnv_group_mm_device_status(int* status_out) {
 }
 
 extern "C" int pnv_group_mm_profile(long long* out, int n_values) {
-  PNV_REQUIRE(out && n_values >= 0 && n_values <= 256 * 8, "bad profile buffer");
+  PNV_REQUIRE(out && n_values >= 0 && n_values <= 256 * 16, "bad profile buffer");
   PNV_REQUIRE(g_prof_dev != nullptr, "profiling is off: set PNV_GROUP_MM_PROFILE=1 before the first group_mm");
   PNV_CUDA(cudaDeviceSynchronize());
   PNV_CUDA(cudaMemcpy(out, g_prof_dev, n_values * sizeof(long long), cudaMemcpyDeviceToHost));
@@ -1517,9 +1572,11 @@ int group_mm_common(void* out, const FusedArgs* fused, const uint8_t* a_comp, co
   p.e_k_atoms = wd.k_e / 16;
   p.e_m_atoms = wd.m_e / 128;
   p.sfb_rt = sf_row_atoms(max_n);
-  p.prof = profile_buffer(fused != nullptr);
+  const char* only_m = std::getenv("PNV_GROUP_MM_PROFILE_M");   // record only launches with this many features
+  p.prof = (only_m != nullptr && std::atoi(only_m) != features) ? nullptr : profile_buffer(fused != nullptr);
   p.stages = 0;
   p.b_res_bytes = 0;
+  p.prod_lanes = 1;
   p.trace = nullptr;
 
   // Tile geometry.  The variant names fix the widest token tile; when every expert's tokens fit one

@@ -192,6 +192,26 @@ finalize_kernel(const __nv_bfloat16* __restrict__ fused, const int* __restrict__
   *reinterpret_cast<uint4*>(out + t * K + col) = *reinterpret_cast<const uint4*>(o);
 }
 
+// gather_rows: dst[i, :] = idx[i] >= 0 ? src[idx[i], :] : 0, rows of `vecs` 16-byte words; one block
+// per destination row.  The copy step either side of an expert-parallel exchange: token rows into
+// send order, expert output rows into return order (dropped routings come back as zero rows).
+constexpr int kGatherThreads = 128;
+
+__global__ void __launch_bounds__(kGatherThreads)
+gather_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ idx, uint4* __restrict__ dst, int vecs) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long long i = blockIdx.x;
+  const int r = idx[i];
+  uint4* out = dst + i * vecs;
+  if (r < 0) {
+    for (int v = threadIdx.x; v < vecs; v += kGatherThreads) out[v] = make_uint4(0u, 0u, 0u, 0u);
+  } else {
+    const uint4* in = src + (long long)r * vecs;
+    for (int v = threadIdx.x; v < vecs; v += kGatherThreads) out[v] = __ldg(in + v);
+  }
+}
+
 }  // namespace
 }  // namespace pnv
 
@@ -251,5 +271,19 @@ extern "C" int pnv_moe_finalize(void* out, const void* fused, const int32_t* rou
   PNV_CUDA(launch_pdl(finalize_kernel, dim3((unsigned)tokens, (unsigned)slabs), dim3(kFinThreads), 0,
                       (cudaStream_t)stream, pdl_enabled(), (const __nv_bfloat16*)fused, (const int*)route_dest,
                       topk_weights, (__nv_bfloat16*)out, topk, k));
+  return PNV_OK;
+}
+
+extern "C" int pnv_gather_rows(const void* src, const int32_t* idx, int64_t n_idx, int64_t row_bytes, void* dst,
+                               pnv_stream_t stream) {
+  PNV_REQUIRE(n_idx >= 0 && n_idx < (1LL << 31), "bad row count");
+  PNV_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0 && row_bytes / 16 < (1LL << 31),
+              "row_bytes must be a positive multiple of 16, got %lld", (long long)row_bytes);
+  if (n_idx == 0) return PNV_OK;
+  PNV_REQUIRE(src && idx && dst, "null pointer argument");
+  PNV_REQUIRE((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) % 16 == 0,
+              "gather_rows buffers must be 16-byte aligned");
+  PNV_CUDA(launch_pdl(gather_rows_kernel, dim3((unsigned)n_idx), dim3(kGatherThreads), 0, (cudaStream_t)stream,
+                      pdl_enabled(), (const uint4*)src, (const int*)idx, (uint4*)dst, (int)(row_bytes / 16)));
   return PNV_OK;
 }

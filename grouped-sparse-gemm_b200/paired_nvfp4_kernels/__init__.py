@@ -51,6 +51,7 @@ def _register():
     lib.define("scatter_fp4_planned(Tensor q, Tensor q_sf, Tensor src_tok, Tensor expert_num_tokens, int cap) "
                "-> (Tensor, Tensor)")
     lib.define("moe_finalize(Tensor(a!) out, Tensor fused, Tensor route_dest, Tensor? topk_weights) -> ()")
+    lib.define("gather_rows(Tensor src, Tensor idx) -> Tensor")
     lib.define("group_mm(Tensor(a!) out, Tensor a_comp, Tensor e_meta, Tensor sfa, Tensor b_act, Tensor sfb, "
                "Tensor alphas, Tensor expert_num_tokens, int features, int k, "
                f"int config_id={DEFAULT_TACTIC[0]}, int cluster_m={DEFAULT_TACTIC[1]}, "
@@ -72,6 +73,7 @@ def _register():
     lib.impl("quant_rows", ops.quant_rows, "CUDA")
     lib.impl("scatter_fp4_planned", ops.scatter_fp4_planned, "CUDA")
     lib.impl("moe_finalize", ops.moe_finalize, "CUDA")
+    lib.impl("gather_rows", ops.gather_rows, "CUDA")
     lib.impl("group_mm", ops.group_mm, "CUDA")
     lib.impl("gated_act", ops.gated_act, "CUDA")
     lib.impl("group_mm_swiglu_quant", ops.group_mm_swiglu_quant, "CUDA")

@@ -280,6 +280,21 @@ def moe_finalize(out, fused, route_dest, topk_weights):
                                           _stream(out)))
 
 
+def gather_rows(src, idx):
+    """dst[i] = src[idx[i]] for idx[i] >= 0, a zero row otherwise: the permutation step either side of
+    the expert-parallel exchange (token rows into send order, expert outputs into return order)."""
+    _check(src.is_cuda and idx.is_cuda, "inputs must be CUDA")
+    _check(src.dim() == 2 and src.is_contiguous(), "src must be contiguous [rows, width]")
+    _check(idx.dtype == torch.int32 and idx.is_contiguous() and idx.dim() == 1, "idx must be contiguous int32 [n]")
+    row_bytes = src.size(1) * src.element_size()
+    _check(row_bytes % 16 == 0, lambda: f"rows must be a multiple of 16 bytes, got {row_bytes}")
+    dst = torch.empty((idx.numel(), src.size(1)), dtype=src.dtype, device=src.device)
+    with torch.cuda.device(src.device):
+        _cabi.check(_lib.pnv_gather_rows(src.data_ptr(), idx.data_ptr(), idx.numel(), row_bytes, dst.data_ptr(),
+                                         _stream(src)))
+    return dst
+
+
 def gated_act(x2, interleaved=False, activation="silu", beta=1.0, linear_beta=-1.0):
     """The unfused gated activation (gated_act, csrc/layout.cuh:204-216): bf16 [..., 2N] -> [..., N]."""
     _check(x2.is_cuda and x2.dtype == torch.bfloat16 and x2.is_contiguous(), "x2 must be contiguous CUDA bf16")

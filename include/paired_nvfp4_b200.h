@@ -163,6 +163,13 @@ int pnv_scatter_fp4_planned(const uint8_t* q, const uint8_t* q_sf, const int32_t
 int pnv_moe_finalize(void* out, const void* fused, const int32_t* route_dest, const float* topk_weights,
                      int64_t tokens, int topk, int k, pnv_stream_t stream);
 
+/* Row gather for the expert-parallel exchange (no op of its own in the reference, which leaves the
+ * permutation to the caller's framework; python/paired_nvfp4_kernels/__init__.py documents the plan
+ * tensors it consumes): dst[i, :] = idx[i] >= 0 ? src[idx[i], :] : 0 for rows of row_bytes bytes
+ * (a multiple of 16; both buffers 16-byte aligned). */
+int pnv_gather_rows(const void* src, const int32_t* idx, int64_t n_idx, int64_t row_bytes, void* dst,
+                    pnv_stream_t stream);
+
 /* The unfused gated activation the quantizer above folds in (gated_act, csrc/layout.cuh:204-216;
  * device replica ref_silu_mul_kernel, csrc/testing/selftest.cu:750-760): y bf16[rows, n] from
  * x2 bf16[rows, 2n].  pnv_silu_mul_quant_act == pnv_gated_act followed by pnv_quant_act, byte for

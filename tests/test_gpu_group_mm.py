@@ -83,6 +83,14 @@ def test_shapes(pnk, E, M, K, max_n, counts, config_id):
     run_case(pnk, E, M, K, max_n, counts, config_id, seed=E + M + K)
 
 
+@pytest.mark.parametrize("config_id", [0, 1, 5, 8])
+def test_many_long_tiles_per_cta(pnk, config_id):
+    # more tiles than SMs, each tile's K loop longer than the shared-memory stage ring: every CTA
+    # walks several tiles and the pipeline barriers go through many phases
+    run_case(pnk, E=4, M=1024, K=2048, max_n=2048, counts=[2048, 1900, 2047, 1500], config_id=config_id, seed=77,
+             wscale=0.05)
+
+
 def test_gscale_and_alpha_undo_each_other(pnk):
     E, M, K, max_n = 4, 256, 512, 48
     x_amax = 4.5
