@@ -257,6 +257,8 @@ def make_activation_inputs(wl, layer, rank, world, device):
         dest = torch.from_numpy(d).to(device)
         topk_w = None   # router weights are applied at combine time
         amax = x.abs().max().float().expand(E).contiguous()
+        layer.global_ids = torch.from_numpy(ids).to(device)
+        layer.router_w = torch.from_numpy(w).to(device)
     g1 = (6.0 * 448.0 / amax.clamp(min=1e-6)).contiguous()
     return dict(x=x, counts=torch.from_numpy(counts).to(device), g1=g1, a1=(1.0 / g1).contiguous(),
                 flat_tok=flat_tok, dest=dest, topk_w=topk_w), counts
@@ -391,6 +393,11 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     assert wl["E"] % world == 0
     E_local = wl["E"] // world
+    if world > 1:
+        assert wl["routing"] != "counts", "expert parallelism needs a routed workload (c3, c4, c5)"
+        assert not args.unfused, "the expert-parallel step always uses the fused gate_up epilogue"
+        # per-rank tokens are fixed, so the load per expert grows with the number of ranks
+        wl = dict(wl, cap=max(wl["cap"], 2 * wl["tokens"] * wl["topk"] * world // wl["E"]))
     layer = Layer(wl, device, config_id=args.config_id, E_local=E_local, first_expert=rank * E_local,
                   fused=not args.unfused)
     inputs, counts = make_activation_inputs(wl, layer, rank, world, device)
@@ -402,6 +409,9 @@ def main():
         if world > 1:
             torch.distributed.barrier()
         torch.cuda.synchronize()
+
+    if world > 1:
+        return run_expert_parallel(args, wl_name, wl, layer, inputs, rank, world, local_rank, device, barrier)
 
     # ---- device-resident timing ---------------------------------------------------------------
     for i in range(max(args.warmup, 3)):
@@ -471,6 +481,95 @@ def main():
         print(json.dumps(line))
     if world > 1:
         torch.distributed.destroy_process_group()
+
+
+def run_expert_parallel(args, wl_name, wl, layer, inputs, rank, world, local_rank, device, barrier):
+    """N > 1: experts sharded over the ranks; every step is dispatch (NVFP4 rows over NCCL all-to-all) ->
+    dispatch_plan -> scatter -> fused gate_up group_mm -> down group_mm -> combine (all-to-all) ->
+    moe_finalize, through torch.ops.paired_nvfp4.* and paired_nvfp4_kernels.ep."""
+    import torch
+    import torch.distributed as dist
+    import paired_nvfp4_kernels
+    from paired_nvfp4_kernels import ep
+    H, I = layer.H, layer.I
+    plan = ep.build_plan(layer.global_ids, layer.E)
+    g1 = inputs["g1"][:1].contiguous()                       # one shared scale: rows are quantized before they travel
+    al1 = (1.0 / g1).expand(layer.E).contiguous()
+    ffns = []
+    for w in layer.weights:
+        ffns.append(ep.ExpertParallelFFN((w["a13"], w["e13"], w["s13"]), (w["a2"], w["e2"], w["s2"]), H, I, layer.cap,
+                                         al1, layer.al2, g1, layer.g2, fused_config=layer.fused_cfg,
+                                         config_id=layer.cfg, cluster_m=layer.cluster_m))
+    x, rw = inputs["x"], layer.router_w
+    out = torch.empty((plan.tokens, H), dtype=torch.bfloat16, device=device)
+    counts = None
+    for i in range(max(args.warmup, 3)):
+        _, counts = ffns[i % len(ffns)].forward(x, plan, rw, out)
+    kept = int(counts.sum().item())
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        e0.record()
+        for i in range(args.steps):
+            ffns[i % len(ffns)].forward(x, plan, rw, out)
+        e1.record()
+        barrier()
+    ms_total = e0.elapsed_time(e1)
+    t = torch.tensor([ms_total], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    f = torch.tensor([2.0 * kept * (2 * I * H + H * I)], device=device, dtype=torch.float64)
+    dist.all_reduce(f)
+    total_flops = float(f.item())
+    value = total_flops / (ms_step * 1e-3) / 1e12
+
+    # end to end: the tokens start in pinned host memory and the layer output returns there
+    host_x, host_out = x.cpu().pin_memory(), torch.empty((plan.tokens, H), dtype=torch.bfloat16).pin_memory()
+    dev_x = torch.empty_like(x)
+
+    def one(i):
+        dev_x.copy_(host_x, non_blocking=True)
+        ffns[i % len(ffns)].forward(dev_x, plan, rw, out)
+        host_out.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+    for i in range(3):
+        one(i)
+    n = max(5, min(args.steps, 50))
+    barrier()
+    e0.record()
+    for i in range(n):
+        one(i)
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_e2e = float(t.item()) / n
+    if rank == 0:
+        wire = plan.n_send * (H // 2 + H // 32 + 4) + plan.n_recv * 2 * H
+        print(json.dumps({
+            "metric": "moe_expert_ffn_group_mm_dense_equiv_tflops", "value": value, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "e2m1 x e2m1 -> f32",
+            "data": "synthetic",
+            "config": {"workload": f"{wl_name}: {wl['desc']}", "experts": wl["E"], "experts_per_gpu": layer.E,
+                       "hidden": H, "intermediate": I, "cap": layer.cap, "tokens_per_gpu": plan.tokens,
+                       "topk": plan.topk, "routed_rows_kept_rank0": kept,
+                       "tile_config": paired_nvfp4_kernels.group_mm_configs()[layer.cfg],
+                       "fused_swiglu_epilogue": True, "parallelism": f"ep{world}",
+                       "exchange": "NCCL all_to_all_single: NVFP4 rows + scales + expert ids out, bf16 rows back",
+                       "l2": "inputs larger than L2; two weight copies alternate"},
+            "layer_us": ms_step * 1e3, "nvlink_bytes_per_gpu_per_step": wire,
+            "roofline": {"bound": "tensor", "kernel": "whole expert-parallel step", "achieved": value / world,
+                         "peak": 18000.0, "unit": "TFLOP/s", "frac": value / world / 18000.0,
+                         "peak_source": "nominal 2:4-sparse FP4 per GPU in dense-equivalent flops (no measured FP4 peak on this pool)",
+                         "traffic": None},
+            "cpu_baseline": None,
+            "e2e": dict(value=total_flops / (ms_e2e * 1e-3) / 1e12, unit="TFLOP/s", ms_per_step=ms_e2e,
+                        h2d_bytes_per_step=host_x.numel() * 2 * world, d2h_bytes_per_step=host_out.numel() * 2 * world,
+                        steps=n),
+            "gpu_launches": 9 * args.steps, "clocks": clocks.summary(),
+        }))
+    dist.destroy_process_group()
 
 
 def run_e2e(layer, inputs, wl, args, flops):
