@@ -58,23 +58,25 @@ quant_lines_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   const int KB = K / kSfBlock;
   const int n_rt = sf_row_atoms(max_n);
   const int n_kt = sf_k_atoms(K);
-  const long long lines = (long long)E * n_rt * n_kt * 32;
+  // line arithmetic in 32 bits (the host checks the line count): 64-bit divisions per line once
+  // cost more instructions than the quantization itself
+  const unsigned lines = (unsigned)E * n_rt * n_kt * 32u;
   const int lane = threadIdx.x & 31;
   const int g = lane >> 3;          // row group inside the atom: rows rr + 32 g
   const int j = lane & 7;           // 16-element piece of the 128-element segment
-  const long long warp0 = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-  const long long nwarps = (long long)gridDim.x * kWarpsPerBlock;
+  const unsigned warp0 = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const unsigned nwarps = gridDim.x * kWarpsPerBlock;
   const uint32_t benign4 = kBenignSf * 0x01010101u;
 
-  for (long long c = warp0; c < lines; c += nwarps) {
+  for (unsigned c = warp0; c < lines; c += nwarps) {
     const int rr = (int)(c & 31);
-    long long a = c >> 5;
-    const int kt = (int)(a % n_kt);
-    a /= n_kt;
-    const int rt = (int)(a % n_rt);
-    const int e = (int)(a / n_rt);
+    const unsigned a = c >> 5;
+    const unsigned a_kt = a / (unsigned)n_kt;
+    const int kt = (int)(a - a_kt * n_kt);
+    const int e = (int)(a_kt / (unsigned)n_rt);
+    const int rt = (int)(a_kt - (unsigned)e * n_rt);
     const int cnt = min(counts[e], max_n);
-    uint8_t* line = sfb + c * 16;
+    uint8_t* line = sfb + (long long)c * 16;
     if (rt * 128 + rr >= cnt) {   // no live row behind this line
       if (lane == 0) *reinterpret_cast<uint4*>(line) = make_uint4(benign4, benign4, benign4, benign4);
       continue;
@@ -151,96 +153,122 @@ quant_lines_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   }
 }
 
-// One warp per (routing, 256-element segment); lane l owns 8 elements, a quad owns a block.
+// The scale bytes of a 256-element segment: lane 4b holds block b's byte (b = 0..7); lanes 0 and 16
+// return the two 32-bit words that cover blocks 0-3 and 4-7.
+__device__ __forceinline__ uint32_t gather_sf_word(uint32_t my_byte, int lane) {
+  const int base = lane & 16;
+  return __shfl_sync(0xffffffffu, my_byte, base) | (__shfl_sync(0xffffffffu, my_byte, base + 4) << 8) |
+         (__shfl_sync(0xffffffffu, my_byte, base + 8) << 16) | (__shfl_sync(0xffffffffu, my_byte, base + 12) << 24);
+}
+
+// One warp per routing: the whole row, 256 elements at a time; lane l owns 8 of them, a quad owns a
+// block; a row's four scales of one 128-K group are one aligned word of the swizzled layout.
 __global__ void __launch_bounds__(kThreads)
 scatter_quant_kernel(const __nv_bfloat16* __restrict__ a1, const long long* __restrict__ flat_tok,
                      const long long* __restrict__ dest_global, const float* __restrict__ topk_w,
-                     const float* __restrict__ gscale, int gscale_per_expert, long long n_routes,
+                     const float* __restrict__ gscale, int gscale_per_expert, unsigned n_routes,
                      int K, int E, int cap, uint8_t* __restrict__ b_act, uint8_t* __restrict__ sfb) {
   pdl_wait();
   pdl_launch_dependents();
   const int segs = ceil_div_i(K, 256);
+  const int KB = K / kSfBlock;
   const int n_rt = sf_row_atoms(cap);
   const int n_kt = sf_k_atoms(K);
-  const long long items = n_routes * segs;
   const long long trash = (long long)E * cap;
   const int lane = threadIdx.x & 31;
-  const long long warp0 = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-  const long long nwarps = (long long)gridDim.x * kWarpsPerBlock;
-  for (long long it = warp0; it < items; it += nwarps) {
-    const long long i = it / segs;
-    const int seg = (int)(it - i * segs);
+  const unsigned warp0 = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const unsigned nwarps = gridDim.x * kWarpsPerBlock;
+  for (unsigned i = warp0; i < n_routes; i += nwarps) {
     const long long dest = dest_global[i];
     if (dest == trash) continue;   // dropped routing: non-local expert or past capacity
-    const int k0 = seg * 256 + lane * 8;
-    const bool live = k0 < K;
-    float f[8];
-    if (live) {
-      uint4 v = __ldg(reinterpret_cast<const uint4*>(a1 + flat_tok[i] * K + k0));
-      unpack8(v, f);
-      if (topk_w != nullptr) {
-        const float w = __bfloat162float(__float2bfloat16_rn(topk_w[i]));
+    const int e = (int)((unsigned)dest / (unsigned)cap);     // dest < E * cap < 2^31
+    const int r = (int)dest - e * cap;
+    const float gs = gscale_per_expert ? gscale[e] : gscale[0];
+    const bool weighted = topk_w != nullptr;
+    const float w = weighted ? __bfloat162float(__float2bfloat16_rn(topk_w[i])) : 1.f;
+    const uint4* src = reinterpret_cast<const uint4*>(a1 + flat_tok[i] * K);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(b_act + dest * (K / 2));
+    uint8_t* sf_row = sfb + sf_offset(e, r, 0, n_rt, n_kt);   // K-block kb of this row: + (kb >> 2) * 512 + (kb & 3)
+#pragma unroll 2
+    for (int seg = 0; seg < segs; ++seg) {
+      const int k0 = seg * 256 + lane * 8;
+      const bool live = k0 < K;
+      float f[8];
+      if (live) {
+        unpack8(__ldg(src + seg * 32 + lane), f);
+        if (weighted) {
 #pragma unroll
-        for (int q = 0; q < 8; ++q) f[q] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(f[q], w)));
+          for (int q = 0; q < 8; ++q) f[q] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(f[q], w)));
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) f[q] = 0.f;
       }
-    } else {
+      float amax = 0.f;
 #pragma unroll
-      for (int q = 0; q < 8; ++q) f[q] = 0.f;
-    }
-    float amax = 0.f;
-#pragma unroll
-    for (int q = 0; q < 8; ++q) amax = fmaxf(amax, fabsf(f[q]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    if (live) {
-      const int e = (int)(dest / cap);
-      const int r = (int)(dest - (long long)e * cap);
-      const float gs = gscale_per_expert ? gscale[e] : gscale[0];
-      uint32_t sf_byte;
-      float inv;
-      block_scale(amax, gs, sf_byte, inv);
-      *reinterpret_cast<uint32_t*>(b_act + dest * (K / 2) + k0 / 2) = quant8(f, inv);
-      if ((lane & 3) == 0) sfb[sf_offset(e, r, k0 / kSfBlock, n_rt, n_kt)] = (uint8_t)sf_byte;
+      for (int q = 0; q < 8; ++q) amax = fmaxf(amax, fabsf(f[q]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      uint32_t sf_byte = kBenignSf;   // blocks past K keep the benign byte in the layout's slop
+      if (live) {
+        float inv;
+        block_scale(amax, gs, sf_byte, inv);
+        dst[seg * 32 + lane] = quant8(f, inv);
+      }
+      const uint32_t word = gather_sf_word(sf_byte, lane);
+      const int kb = seg * 8 + (lane >> 4) * 4;
+      if ((lane & 15) == 0 && kb < KB) *reinterpret_cast<uint32_t*>(sf_row + (kb >> 2) * 512) = word;
     }
   }
 }
 
 // quant_rows: token-order rows -> row-major codes and natural-order scales, one shared global scale.
-// One warp per (row, 256-element segment); a quad owns a block.
+// One warp per row, 256 elements at a time; a quad owns a block; four scales leave as one word.
 __global__ void __launch_bounds__(kThreads)
-quant_rows_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gscale, long long T, int K,
+quant_rows_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gscale, unsigned T, int K,
                   uint8_t* __restrict__ q, uint8_t* __restrict__ q_sf) {
   pdl_wait();
   pdl_launch_dependents();
   const int segs = ceil_div_i(K, 256);
   const int KB = K / kSfBlock;
-  const long long items = T * segs;
   const int lane = threadIdx.x & 31;
   const float gs = gscale[0];
-  const long long warp0 = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-  const long long nwarps = (long long)gridDim.x * kWarpsPerBlock;
-  for (long long it = warp0; it < items; it += nwarps) {
-    const long long t = it / segs;
-    const int k0 = (int)(it - t * segs) * 256 + lane * 8;
-    const bool live = k0 < K;
-    float f[8];
-    if (live) {
-      unpack8(__ldg(reinterpret_cast<const uint4*>(x + t * K + k0)), f);
-    } else {
+  const unsigned warp0 = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const unsigned nwarps = gridDim.x * kWarpsPerBlock;
+  const bool sf_words = (KB % 4) == 0;     // rows of scales are then 4-byte aligned
+  for (unsigned t = warp0; t < T; t += nwarps) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + (long long)t * K);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(q + (long long)t * (K / 2));
+    uint8_t* sf_row = q_sf + (long long)t * KB;
+#pragma unroll 2
+    for (int seg = 0; seg < segs; ++seg) {
+      const int k0 = seg * 256 + lane * 8;
+      const bool live = k0 < K;
+      float f[8];
+      if (live) {
+        unpack8(__ldg(src + seg * 32 + lane), f);
+      } else {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] = 0.f;
-    }
-    float amax = 0.f;
+        for (int i = 0; i < 8; ++i) f[i] = 0.f;
+      }
+      float amax = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    if (live) {
-      uint32_t sf_byte;
-      float inv;
-      block_scale(amax, gs, sf_byte, inv);
-      *reinterpret_cast<uint32_t*>(q + t * (K / 2) + k0 / 2) = quant8(f, inv);
-      if ((lane & 3) == 0) q_sf[t * KB + k0 / kSfBlock] = (uint8_t)sf_byte;
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      uint32_t sf_byte = 0;
+      if (live) {
+        float inv;
+        block_scale(amax, gs, sf_byte, inv);
+        dst[seg * 32 + lane] = quant8(f, inv);
+      }
+      const uint32_t word = gather_sf_word(sf_byte, lane);
+      const int kb = seg * 8 + (lane >> 4) * 4;
+      if (sf_words) {
+        if ((lane & 15) == 0 && kb < KB) *reinterpret_cast<uint32_t*>(sf_row + kb) = word;
+      } else if (live && (lane & 3) == 0) {
+        sf_row[k0 / kSfBlock] = (uint8_t)sf_byte;
+      }
     }
   }
 }
@@ -282,6 +310,7 @@ int check_common(const void* x, const float* gscale, const int32_t* counts, int 
   PNV_REQUIRE(x && gscale && counts && b_act && sfb, "null pointer argument");
   PNV_REQUIRE(E >= 1 && rows >= 1, "experts and row capacity must be positive, got %d and %d", E, rows);
   PNV_REQUIRE(K > 0 && K % kSfBlock == 0, "%s must be a multiple of %d, got %d", kname, kSfBlock, K);
+  PNV_REQUIRE(sf_numel(rows, K, E) / 16 < (1LL << 31) - (1LL << 24), "the scale layout has too many lines for one launch");
   PNV_REQUIRE(sf_numel(rows, K, E) / 16 < (1LL << 40), "scale buffer too large");
   return PNV_OK;
 }
@@ -348,11 +377,11 @@ extern "C" int pnv_scatter_quant_act(const void* a1, const int64_t* flat_tok,
   cudaStream_t s = (cudaStream_t)stream;
   PNV_CUDA(cudaMemsetAsync(sfb, kBenignSf, (size_t)sf_numel(cap, k, experts), s));
   if (n_routes == 0) return PNV_OK;
-  long long items = (long long)n_routes * ceil_div_i(k, 256);
-  PNV_CUDA(launch_pdl(scatter_quant_kernel, dim3(grid_for(items, sm_count)), dim3(kThreads), 0, s,
+  PNV_REQUIRE(n_routes < (1LL << 31) && (long long)experts * cap < (1LL << 31), "T * topk and E * cap must fit int32");
+  PNV_CUDA(launch_pdl(scatter_quant_kernel, dim3(grid_for(n_routes, sm_count)), dim3(kThreads), 0, s,
                       false, (const __nv_bfloat16*)a1, (const long long*)flat_tok,
                       (const long long*)dest_global, topk_weights, gscale, gscale_per_expert,
-                      (long long)n_routes, k, experts, cap, b_act, sfb));
+                      (unsigned)n_routes, k, experts, cap, b_act, sfb));
   return PNV_OK;
 }
 
@@ -394,9 +423,9 @@ extern "C" int pnv_quant_rows(const void* x, const float* gscale, int64_t tokens
   PNV_REQUIRE(tokens >= 0, "bad token count");
   if (tokens == 0) return PNV_OK;
   PNV_REQUIRE(x && gscale && q && q_sf, "null pointer argument");
-  long long items = (long long)tokens * ceil_div_i(k, 256);
-  PNV_CUDA(launch_pdl(quant_rows_kernel, dim3(grid_for(items, sm_count)), dim3(kThreads), 0, (cudaStream_t)stream,
-                      pdl_enabled(), (const __nv_bfloat16*)x, gscale, (long long)tokens, k, q, q_sf));
+  PNV_REQUIRE(tokens < (1LL << 31), "too many tokens");
+  PNV_CUDA(launch_pdl(quant_rows_kernel, dim3(grid_for(tokens, sm_count)), dim3(kThreads), 0, (cudaStream_t)stream,
+                      pdl_enabled(), (const __nv_bfloat16*)x, gscale, (unsigned)tokens, k, q, q_sf));
   return PNV_OK;
 }
 
