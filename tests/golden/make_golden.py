@@ -26,7 +26,9 @@ def load_reference(root):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <checkout of the reference project>")
+    root = sys.argv[1]
     ref = load_reference(root)
     here = os.path.dirname(os.path.abspath(__file__))
     out = {}
