@@ -62,6 +62,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--unfused", action="store_true", help="separate silu_mul_quant_act launch instead of the fused GEMM1 epilogue")
+    ap.add_argument("--ep-sm-margin", type=int, default=0, help="N > 1: SMs left free for the collectives while slices overlap")
+    ap.add_argument("--ep-chunks", type=int, default=1, help="N > 1: token slices whose exchanges overlap the GEMMs (1 = no overlap)")
     return ap.parse_args()
 
 
@@ -493,6 +495,17 @@ def run_expert_parallel(args, wl_name, wl, layer, inputs, rank, world, local_ran
     from paired_nvfp4_kernels import ep
     H, I = layer.H, layer.I
     plan = ep.build_plan(layer.global_ids, layer.E)
+    chunks = max(1, args.ep_chunks)
+    if chunks > 1 and args.ep_sm_margin:
+        from paired_nvfp4_kernels import ops as pyops
+        pyops.set_sm_margin(args.ep_sm_margin)
+    plans = ep.build_chunk_plans(layer.global_ids, layer.E, chunks) if chunks > 1 else None
+    comm = torch.cuda.Stream(device=device)
+
+    def forward(ffn, xin):
+        if plans is None:
+            return ffn.forward(xin, plan, rw, out)[1]
+        return torch.stack(ep.forward_chunked(ffn, xin, plans, rw, out, comm)).sum(0)
     g1 = inputs["g1"][:1].contiguous()                       # one shared scale: rows are quantized before they travel
     al1 = (1.0 / g1).expand(layer.E).contiguous()
     ffns = []
@@ -504,14 +517,14 @@ def run_expert_parallel(args, wl_name, wl, layer, inputs, rank, world, local_ran
     out = torch.empty((plan.tokens, H), dtype=torch.bfloat16, device=device)
     counts = None
     for i in range(max(args.warmup, 3)):
-        _, counts = ffns[i % len(ffns)].forward(x, plan, rw, out)
+        counts = forward(ffns[i % len(ffns)], x)
     kept = int(counts.sum().item())
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     with ClockSampler(local_rank) as clocks:
         e0.record()
         for i in range(args.steps):
-            ffns[i % len(ffns)].forward(x, plan, rw, out)
+            forward(ffns[i % len(ffns)], x)
         e1.record()
         barrier()
     ms_total = e0.elapsed_time(e1)
@@ -529,7 +542,7 @@ def run_expert_parallel(args, wl_name, wl, layer, inputs, rank, world, local_ran
 
     def one(i):
         dev_x.copy_(host_x, non_blocking=True)
-        ffns[i % len(ffns)].forward(dev_x, plan, rw, out)
+        forward(ffns[i % len(ffns)], dev_x)
         host_out.copy_(out, non_blocking=True)
         torch.cuda.synchronize()
     for i in range(3):
@@ -555,7 +568,7 @@ def run_expert_parallel(args, wl_name, wl, layer, inputs, rank, world, local_ran
                        "hidden": H, "intermediate": I, "cap": layer.cap, "tokens_per_gpu": plan.tokens,
                        "topk": plan.topk, "routed_rows_kept_rank0": kept,
                        "tile_config": paired_nvfp4_kernels.group_mm_configs()[layer.cfg],
-                       "fused_swiglu_epilogue": True, "parallelism": f"ep{world}",
+                       "fused_swiglu_epilogue": True, "parallelism": f"ep{world}", "token_slices": chunks,
                        "exchange": "NCCL all_to_all_single: NVFP4 rows + scales + expert ids out, bf16 rows back",
                        "l2": "inputs larger than L2; two weight copies alternate"},
             "layer_us": ms_step * 1e3, "nvlink_bytes_per_gpu_per_step": wire,
@@ -567,7 +580,7 @@ def run_expert_parallel(args, wl_name, wl, layer, inputs, rank, world, local_ran
             "e2e": dict(value=total_flops / (ms_e2e * 1e-3) / 1e12, unit="TFLOP/s", ms_per_step=ms_e2e,
                         h2d_bytes_per_step=host_x.numel() * 2 * world, d2h_bytes_per_step=host_out.numel() * 2 * world,
                         steps=n),
-            "gpu_launches": 9 * args.steps, "clocks": clocks.summary(),
+            "gpu_launches": 9 * chunks * args.steps, "clocks": clocks.summary(),
         }))
     dist.destroy_process_group()
 

@@ -1165,15 +1165,72 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       }
       ptx::tc_fence_after();
       long long te1 = eprof ? clock64() : 0;
+      if (!kFused) {
+        // Plain epilogue, warp by warp with no barrier between warps: 16 token columns at a time, the
+        // next piece's tcgen05.ld in flight while this one is scaled, rounded, transposed through the
+        // warp's own corner of shared memory ([16 tokens][32 features], rows padded to 80 bytes) and
+        // stored 16 bytes per lane, 64 contiguous bytes per output row.
+        constexpr int kWarpRow = 40;
+        constexpr int kPieces = TILE_N / 32;   // per group: TILE_N / 64 chunks of two pieces
+        __nv_bfloat16* wbuf = s_out + (warp - 8) * (2 * 16 * kWarpRow);
+        const uint32_t t_row = tmem_base + ((uint32_t)(sub * 32) << 16) + acc * TILE_N;
+        auto piece_col = [&](int q) { return group * 32 + (q >> 1) * 64 + (q & 1) * 16; };
+        int n_pieces = 0;
+        while (n_pieces < kPieces && n0 + piece_col(n_pieces) < cnt) ++n_pieces;
+        auto process = [&](const uint32_t (&v)[16], int q) {
+          __nv_bfloat16* buf = wbuf + (q & 1) * (16 * kWarpRow);
+          const int c = piece_col(q);
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            buf[i * kWarpRow + lane] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(v[i])));
+          __syncwarp();
+          const int m = mt * kTileM + sub * 32 + (lane & 3) * 8;
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int tok = (lane >> 2) + 8 * j;
+            const int n = n0 + c + tok;
+            if (n >= cnt || m >= p.M) continue;
+            const __nv_bfloat16* src = buf + tok * kWarpRow + (lane & 3) * 8;
+            if (vec_ok) {
+              *reinterpret_cast<uint4*>(out_e + (long long)n * p.M + m) = *reinterpret_cast<const uint4*>(src);
+            } else {
 #pragma unroll 1
-      for (int c0 = group * 32; c0 < TILE_N; c0 += 64) {
+              for (int z = 0; z < 8 && m + z < p.M; ++z) out_e[(long long)n * p.M + m + z] = src[z];
+            }
+          }
+        };
+        uint32_t va[16], vb[16];
+        long long t_w = 0, tq;
+        if (n_pieces > 0) {
+          tq = eprof ? clock64() : 0;
+          ptx::tc_ld_32x16(t_row + piece_col(0), va);
+          ptx::tc_ld_wait();
+          if (eprof) t_w += clock64() - tq;
+        }
+#pragma unroll 1
+        for (int q = 0; q < n_pieces; q += 2) {
+          if (q + 1 < n_pieces) ptx::tc_ld_32x16(t_row + piece_col(q + 1), vb);
+          process(va, q);
+          tq = eprof ? clock64() : 0;
+          ptx::tc_ld_wait();
+          if (eprof) t_w += clock64() - tq;
+          if (q + 2 < n_pieces) ptx::tc_ld_32x16(t_row + piece_col(q + 2), va);
+          if (q + 1 < n_pieces) process(vb, q + 1);
+          tq = eprof ? clock64() : 0;
+          ptx::tc_ld_wait();
+          if (eprof) t_w += clock64() - tq;
+        }
+        if (eprof) p.prof[256 * 8 + blockIdx.x * 8 + 5] += t_w;   // waiting for tensor-memory loads
+      }
+#pragma unroll 1
+      for (int c0 = group * 32; kFused && c0 < TILE_N; c0 += 64) {
         if (n0 + c0 >= cnt) break;             // uniform over the group's four warps
         uint32_t r[32];
         ptx::tc_ld_32x32(tmem_base + ((uint32_t)(sub * 32) << 16) + acc * TILE_N + c0, r);
         ptx::tc_ld_wait();
         __nv_bfloat16* buf = group_out + (chunk & 1) * (32 * kOutRow);
         ++chunk;
-        if (kFused) {
+        {
           // The weight rows are interleaved in 64-row blocks (32 gate rows, then the 32 matching up
           // rows), so lanes of the even 32-lane quarters hold gates and the odd quarters the ups of
           // the same 32 output features: exactly one quantization block per token.  Every lane parks
@@ -1223,27 +1280,6 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             *reinterpret_cast<uint2*>(p.f_b_out + row * (p.f_n / 2) + kb * 16 + hb * 8) =
                 make_uint2(quant8(f[0], inv), quant8(f[1], inv));
             if (hb == 0) p.f_sfb_out[sf_offset(e, n, kb, p.sfb_rt, p.f_n_kt)] = (uint8_t)sf_byte;
-          }
-        } else {
-          // [token column][feature] tile: 32 rows of 128 bf16; lanes write consecutive features
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            buf[i * kOutRow + m_local] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(r[i])));
-          epilogue_group_sync(group);
-          const int col = (ep_tid & 15) * 8;
-          const int m = mt * kTileM + col;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int row = (ep_tid >> 4) + 8 * j;
-            const int n = n0 + c0 + row;
-            if (n >= cnt || m >= p.M) continue;
-            if (vec_ok) {
-              *reinterpret_cast<uint4*>(out_e + (long long)n * p.M + m) =
-                  *reinterpret_cast<const uint4*>(buf + row * kOutRow + col);
-            } else {
-#pragma unroll 1
-              for (int z = 0; z < 8 && m + z < p.M; ++z) out_e[(long long)n * p.M + m + z] = buf[row * kOutRow + col + z];
-            }
           }
         }
       }

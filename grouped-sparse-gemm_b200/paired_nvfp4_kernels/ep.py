@@ -128,3 +128,84 @@ class ExpertParallelFFN:
             out = torch.empty((plan.tokens, H), dtype=torch.bfloat16, device=x.device)
         ops.moe_finalize(out, ret, plan.inv_pos, topk_weights)
         return out, counts
+
+
+def build_chunk_plans(topk_ids: torch.Tensor, experts_per_rank: int, chunks: int,
+                      group: Optional[dist.ProcessGroup] = None) -> List[ExchangePlan]:
+    """One exchange plan per contiguous slice of the tokens (every rank must use the same `chunks`)."""
+    tokens = topk_ids.size(0)
+    bounds = [tokens * c // chunks for c in range(chunks + 1)]
+    return [build_plan(topk_ids[bounds[c]:bounds[c + 1]].contiguous(), experts_per_rank, group) for c in range(chunks)]
+
+
+def forward_chunked(ffn: "ExpertParallelFFN", x: torch.Tensor, plans: List[ExchangePlan], topk_weights: torch.Tensor,
+                    out: torch.Tensor, comm_stream: torch.cuda.Stream):
+    """The same pass as ExpertParallelFFN.forward with the tokens cut into len(plans) slices: the
+    all-to-all of one slice runs on `comm_stream` while the GEMMs of another run on the current
+    stream.  Returns the per-slice expert counts."""
+    ops = torch.ops.paired_nvfp4
+    E, H, I, cap = ffn.num_local, ffn.hidden, ffn.inter, ffn.cap
+    main = torch.cuda.current_stream()
+    bounds = [0]
+    for pl in plans:
+        bounds.append(bounds[-1] + pl.tokens)
+    keep = []          # every tensor that crosses streams stays referenced until both streams have met again
+
+    def on_comm(after: torch.cuda.Event, fn):
+        with torch.cuda.stream(comm_stream):
+            comm_stream.wait_event(after)
+            res = fn()
+            done = torch.cuda.Event()
+            done.record(comm_stream)
+        return res, done
+
+    def prep(c):
+        pl = plans[c]
+        q, q_sf = ops.quant_rows(x[bounds[c]:bounds[c + 1]], ffn.g1)
+        send = (ops.gather_rows(q, pl.send_tok), ops.gather_rows(q_sf, pl.send_tok), pl.send_expert)
+        ev = torch.cuda.Event()
+        ev.record(main)
+        keep.extend(send)
+        return send, ev
+
+    def exchange_out(c, send, ev):
+        return on_comm(ev, lambda: tuple(dispatch(plans[c], t, ffn.group) for t in send))
+
+    def compute(c, recv, ev):
+        main.wait_event(ev)
+        recv_q, recv_sf, recv_e = recv
+        counts, route_dest, src_tok, _ = ops.dispatch_plan(recv_e.view(-1, 1), 0, E, cap)
+        b1, sfb1 = ops.scatter_fp4_planned(recv_q, recv_sf, src_tok, counts, cap)
+        b2, sfb2 = ops.group_mm_swiglu_quant(ffn.w13[0], ffn.w13[1], ffn.w13[2], b1, sfb1, ffn.al1, counts, ffn.g2,
+                                             2 * I, H, ffn.fused_config, ffn.cluster_m, 1, "silu", 1.0, -1.0)
+        y = torch.empty((E, cap, H), dtype=torch.bfloat16, device=x.device)
+        ops.group_mm(y, ffn.w2[0], ffn.w2[1], ffn.w2[2], b2, sfb2, ffn.al2, counts, H, I, ffn.config_id,
+                     ffn.cluster_m, 1)
+        back = ops.gather_rows(y.view(E * cap, H), route_dest.view(-1))
+        done = torch.cuda.Event()
+        done.record(main)
+        keep.extend((recv_q, recv_sf, recv_e, back))
+        return back, done, counts
+
+    n = len(plans)
+    sends = [prep(c) for c in range(n)]
+    recvs = [None] * n
+    recvs[0] = exchange_out(0, *sends[0])
+    rets, all_counts = [None] * n, []
+    for c in range(n):
+        if c + 1 < n:
+            recvs[c + 1] = exchange_out(c + 1, *sends[c + 1])      # travels while slice c is multiplied
+        back, done, counts = compute(c, *recvs[c])
+        all_counts.append(counts)
+        rets[c] = on_comm(done, lambda b=back, c=c: combine(plans[c], b, ffn.group))
+    for c in range(n):
+        ret, ev = rets[c]
+        main.wait_event(ev)
+        keep.append(ret)
+        ops.moe_finalize(out[bounds[c]:bounds[c + 1]], ret, plans[c].inv_pos, topk_weights[bounds[c]:bounds[c + 1]])
+    # the communication stream may not run ahead into memory this pass is still using
+    comm_stream.wait_stream(main)
+    for t in keep:
+        t.record_stream(comm_stream)
+        t.record_stream(main)
+    return all_counts

@@ -18,6 +18,16 @@ def _check(cond, msg):
         raise RuntimeError(msg() if callable(msg) else msg)
 
 
+_sm_margin = 0
+
+
+def set_sm_margin(n):
+    """Leave `n` SMs out of every persistent launch (the kernels size their grids from the SM count passed
+    in), so that a collective running on another stream finds SMs to run on.  0 restores full-width launches."""
+    global _sm_margin
+    _sm_margin = max(0, int(n))
+
+
 def _device_info(device):
     """(sm_version, sm_count) of a CUDA device, queried once (reference: csrc/ops.cu:86-103)."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
@@ -26,6 +36,8 @@ def _device_info(device):
         props = torch.cuda.get_device_properties(idx)
         info = (props.major * 10 + props.minor, props.multi_processor_count)
         _dev_info[idx] = info
+    if _sm_margin:
+        return info[0], max(1, info[1] - _sm_margin)
     return info
 
 

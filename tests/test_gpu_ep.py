@@ -73,6 +73,13 @@ def _worker(rank, world, port, out_dir):
         torch.cuda.synchronize()
         np.save(os.path.join(out_dir, f"ep{rank}.npy"), out.view(torch.int16).cpu().numpy())
         np.save(os.path.join(out_dir, f"cnt{rank}.npy"), counts.cpu().numpy())
+        # the same pass in three token slices, exchanges on a second stream
+        plans = ep.build_chunk_plans(ids, epr, 3)
+        out3 = torch.zeros_like(out)
+        slice_counts = ep.forward_chunked(ffn, x, plans, w, out3, torch.cuda.Stream())
+        torch.cuda.synchronize()
+        np.save(os.path.join(out_dir, f"ep3_{rank}.npy"), out3.view(torch.int16).cpu().numpy())
+        np.save(os.path.join(out_dir, f"cnt3_{rank}.npy"), torch.stack(slice_counts).sum(0).cpu().numpy())
     finally:
         dist.destroy_process_group()
 
@@ -112,3 +119,7 @@ def test_two_rank_forward_matches_single_gpu(tmp_path):
     got_counts = np.concatenate([np.load(tmp_path / f"cnt{r}.npy") for r in range(world)])
     assert np.array_equal(got_counts, want_counts)
     assert np.array_equal(got, want)
+    got3 = np.concatenate([np.load(tmp_path / f"ep3_{r}.npy") for r in range(world)])
+    cnt3 = np.concatenate([np.load(tmp_path / f"cnt3_{r}.npy") for r in range(world)])
+    assert np.array_equal(cnt3, want_counts) and (want_counts <= CAP).all()
+    assert np.array_equal(got3, want)
