@@ -738,8 +738,10 @@ struct WideCfg {
   static_assert(8 * (3 * kMaxStages + 2 * kAccStages + 2 * kMaxChunks) + 16 <= kBarrierBytes, "barrier block overflows");
 };
 
-__device__ __forceinline__ void epilogue_group_sync(int group) {
-  asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory");
+// Barrier of one gate/up warp pair of the fused epilogue (lane quarters 0-1 or 2-3 of a group): the pair owns
+// one 64-row block of the tile (32 gate rows, the 32 matching up rows) and shares nothing with the other pair.
+__device__ __forceinline__ void epilogue_pair_sync(int group, int sub) {
+  asm volatile("bar.sync %0, 64;" ::"r"(1 + group * 2 + (sub >> 1)) : "memory");
 }
 
 __device__ __forceinline__ uint64_t pack_desc(uint32_t lo, uint32_t hi) {
@@ -1239,7 +1241,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             buf[i * kOutRow + m_local] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(r[i])));
-          epilogue_group_sync(group);
+          epilogue_pair_sync(group, sub);
           const bool is_up = (sub & 1) != 0;
           __nv_bfloat16* col0 = buf + (is_up ? kOutRow + m_local - 32 : m_local);
 #pragma unroll 1
@@ -1256,7 +1258,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 #pragma unroll
             for (int i = 0; i < 8; ++i) col0[(i0 + i) * 2 * kOutRow] = y[i];
           }
-          epilogue_group_sync(group);
+          epilogue_pair_sync(group, sub);
           // quantize: two adjacent lanes share one (token, 32-feature block); each takes 16 features
           const int pair = ep_tid >> 1, hb = ep_tid & 1;
           const int i = pair & 31, blk = pair >> 5;

@@ -129,3 +129,20 @@ def test_finalize_bit_identical_with_poisoned_padding(ops, with_w):
     want = orc.moe_finalize(fb, rdn, w)
     assert np.array_equal(bf16_bits(out), want)
     assert not np.isnan(orc.bf16_bits_to_f32(want)).any()
+
+
+@pytest.mark.parametrize("rows,width,dtype", [(37, 16, torch.uint8), (200, 224, torch.uint8), (65, 512, torch.bfloat16)])
+def test_gather_rows(rows, width, dtype):
+    import paired_nvfp4_kernels  # noqa: F401
+    ops = torch.ops.paired_nvfp4
+    g = torch.Generator(device="cpu").manual_seed(rows + width)
+    src = torch.randint(0, 255, (rows, width), generator=g, dtype=torch.uint8)
+    src = (src.to(torch.float32) - 128).to(dtype).cuda() if dtype != torch.uint8 else src.cuda()
+    idx = torch.randint(-1, rows, (3 * rows + 5,), generator=g, dtype=torch.int32).cuda()
+    got = ops.gather_rows(src, idx)
+    want = src[idx.clamp(min=0).long()]
+    want[idx < 0] = 0
+    assert torch.equal(got, want)
+    assert ops.gather_rows(src, idx[:0]).shape == (0, width)
+    with pytest.raises(RuntimeError, match="multiple of 16"):
+        ops.gather_rows(src[:, :4].contiguous(), idx)
