@@ -596,9 +596,23 @@ def run_e2e(layer, inputs, wl, args, flops):
     E, H, I, cap = layer.E, layer.H, layer.I, layer.cap
     out1 = torch.zeros((E, cap, 2 * I), dtype=torch.bfloat16, device=x.device)
     out2 = torch.zeros((E, cap, H), dtype=torch.bfloat16, device=x.device)
-    host_out = torch.empty((E, cap, H), dtype=torch.bfloat16).pin_memory()
     w = layer.weights[0]
     name = layer.cabi.group_mm_config_names()[layer.cfg]
+    routed = layer.flat_tok is not None
+    if routed:   # the step ends with the combine: out[t] = sum_j w[t, j] * expert row of routing (t, j)
+        T, topk = layer.router_w.shape
+        route_dest = torch.where(layer.dest == E * cap, torch.full_like(layer.dest, -1), layer.dest)
+        route_dest = route_dest.to(torch.int32).view(T, topk).contiguous()
+        final = torch.zeros((T, H), dtype=torch.bfloat16, device=x.device)
+        host_out = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
+    else:
+        final = out2
+        host_out = torch.empty((E, cap, H), dtype=torch.bfloat16).pin_memory()
+
+    def finish():
+        if routed:
+            ops.moe_finalize(final, out2, route_dest, layer.router_w)
+        host_out.copy_(final, non_blocking=True)
 
     def one():
         dev_x.copy_(host_x, non_blocking=True)
@@ -614,7 +628,7 @@ def run_e2e(layer, inputs, wl, args, flops):
                          layer.cluster_m, 1)
             b2, s2 = ops.silu_mul_quant_act(out1, layer.g2, layer.counts, H)
         ops.group_mm(out2, w["a2"], w["e2"], w["s2"], b2, s2, layer.al2, layer.counts, H, I, layer.cfg, layer.cluster_m, 1)
-        host_out.copy_(out2, non_blocking=True)
+        finish()
         torch.cuda.synchronize()
 
     for _ in range(3):
@@ -643,7 +657,7 @@ def run_e2e(layer, inputs, wl, args, flops):
                     b2, s2 = ops.silu_mul_quant_act(out1, layer.g2, layer.counts, H)
                 ops.group_mm(out2, w["a2"], w["e2"], w["s2"], b2, s2, layer.al2, layer.counts, H, I, layer.cfg,
                              layer.cluster_m, 1)
-                host_out.copy_(out2, non_blocking=True)
+                finish()
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
 

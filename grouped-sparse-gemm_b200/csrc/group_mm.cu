@@ -1,7 +1,9 @@
 // group_mm: out[e, t, :] = bf16(alpha[e] * W[e] * x[e, t, :]) for t < counts[e], with W stored
 // paired-4:8 sparse NVFP4 (a_comp + e_meta + sfa) and x stored NVFP4 (b_act + sfb).
 //
-// One persistent kernel, one CTA per SM, four warp roles (6 + ISSUERS warps):
+// Two persistent kernels, one CTA per SM.  group_mm_kernel (this comment) runs the narrow token
+// tiles of decode-sized problems; group_mm_wide_kernel (further down) the 64- to 256-wide tiles.
+// Narrow kernel, four warp roles (6 + ISSUERS warps):
 //   warp 0 (one lane)  tile producer: per K stage, the TMA tile loads of the compressed weights and
 //                      of the activations (one 3-D tensor map each covers every expert; 128-byte
 //                      swizzle, or 64-byte swizzle for the weights of a 256-K stage);
@@ -13,15 +15,16 @@
 //                      (tcgen05.cp), issues one tcgen05.mma.sp block-scaled instruction
 //                      (128 x TILE_N x 128) per block into its own partial accumulator, and commits:
 //                      to the stage's "empty" barrier, and after the tile's last stage to the
-//                      accumulator's "full" barrier.  One thread can only issue a tcgen05 op every
-//                      50-90 cycles and a commit costs it several hundred, so with narrow tiles a
-//                      single issuer, not memory, bounds the kernel; issuers in different warps
-//                      overlap.
+//                      accumulator's "full" barrier.  A tcgen05 operation holds its issuing thread
+//                      for about as long as it executes (MMA 66-160 cycles, copy 35-50) and the
+//                      thread's own instructions in between add to that, so with narrow tiles a
+//                      single issuer, not memory, would bound the kernel; issuers in different
+//                      warps overlap.
 //   last 4 warps       epilogue: tcgen05.ld the partial accumulators 32 token columns at a time, add
 //                      them, scale by alpha[e], round to bf16, transpose through shared memory and
-//                      store 16 bytes per thread, 256 contiguous bytes per output row.
-// Accumulators are double buffered (single buffered for TILE_N = 256, which fills tensor memory),
-// so the epilogue of one tile overlaps the main loop of the next.
+//                      store 16 bytes per thread, 256 contiguous bytes per output row; or, in the
+//                      fused variant, apply the gated activation and write GEMM2's codes and scales.
+// Accumulators are double buffered, so the epilogue of one tile overlaps the main loop of the next.
 //
 // Tile schedule: every role walks the same list on its own, derived on the device from
 // counts[]: experts in order, each contributing ceil(M/128) * ceil(counts[e]/TILE_N) tiles
