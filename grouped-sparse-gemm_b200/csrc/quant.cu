@@ -153,16 +153,36 @@ quant_lines_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   }
 }
 
-// The scale bytes of a 256-element segment: lane 4b holds block b's byte (b = 0..7); lanes 0 and 16
-// return the two 32-bit words that cover blocks 0-3 and 4-7.
-__device__ __forceinline__ uint32_t gather_sf_word(uint32_t my_byte, int lane) {
-  const int base = lane & 16;
-  return __shfl_sync(0xffffffffu, my_byte, base) | (__shfl_sync(0xffffffffu, my_byte, base + 4) << 8) |
-         (__shfl_sync(0xffffffffu, my_byte, base + 8) << 16) | (__shfl_sync(0xffffffffu, my_byte, base + 12) << 24);
+// Four adjacent lanes hold the scale bytes of four consecutive K-blocks; lane 4j returns their word.
+__device__ __forceinline__ uint32_t gather_sf_word(uint32_t my_byte) {
+  return my_byte | (__shfl_down_sync(0xffffffffu, my_byte, 1) << 8) |
+         (__shfl_down_sync(0xffffffffu, my_byte, 2) << 16) | (__shfl_down_sync(0xffffffffu, my_byte, 3) << 24);
 }
 
-// One warp per routing: the whole row, 256 elements at a time; lane l owns 8 of them, a quad owns a
-// block; a row's four scales of one 128-K group are one aligned word of the swizzled layout.
+// One 32-element block in one lane: 64 bytes in, amax, scale, 16 bytes of codes.  Doing the whole
+// block in a lane runs the scale step (two IEEE divisions, two format conversions) once per block
+// instead of once per 8 elements, which is what bounds these kernels on B200.
+struct BlockRegs {
+  float f[4][8];
+};
+__device__ __forceinline__ void load_block(const uint4* src, BlockRegs& b) {
+  uint4 v0 = __ldg(src), v1 = __ldg(src + 1), v2 = __ldg(src + 2), v3 = __ldg(src + 3);
+  unpack8(v0, b.f[0]); unpack8(v1, b.f[1]); unpack8(v2, b.f[2]); unpack8(v3, b.f[3]);
+}
+__device__ __forceinline__ float block_amax(const BlockRegs& b) {
+  float m = 0.f;
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+#pragma unroll
+    for (int z = 0; z < 8; ++z) m = fmaxf(m, fabsf(b.f[q][z]));
+  return m;
+}
+__device__ __forceinline__ uint4 block_codes(const BlockRegs& b, float inv) {
+  return make_uint4(quant8(b.f[0], inv), quant8(b.f[1], inv), quant8(b.f[2], inv), quant8(b.f[3], inv));
+}
+
+// One warp per routing: the whole row, 32 K-blocks (1024 elements) at a time, one block per lane; a
+// row's four scales of one 128-K group are one aligned word of the swizzled layout.
 __global__ void __launch_bounds__(kThreads)
 scatter_quant_kernel(const __nv_bfloat16* __restrict__ a1, const long long* __restrict__ flat_tok,
                      const long long* __restrict__ dest_global, const float* __restrict__ topk_w,
@@ -170,7 +190,6 @@ scatter_quant_kernel(const __nv_bfloat16* __restrict__ a1, const long long* __re
                      int K, int E, int cap, uint8_t* __restrict__ b_act, uint8_t* __restrict__ sfb) {
   pdl_wait();
   pdl_launch_dependents();
-  const int segs = ceil_div_i(K, 256);
   const int KB = K / kSfBlock;
   const int n_rt = sf_row_atoms(cap);
   const int n_kt = sf_k_atoms(K);
@@ -187,49 +206,37 @@ scatter_quant_kernel(const __nv_bfloat16* __restrict__ a1, const long long* __re
     const bool weighted = topk_w != nullptr;
     const float w = weighted ? __bfloat162float(__float2bfloat16_rn(topk_w[i])) : 1.f;
     const uint4* src = reinterpret_cast<const uint4*>(a1 + flat_tok[i] * K);
-    uint32_t* dst = reinterpret_cast<uint32_t*>(b_act + dest * (K / 2));
+    uint4* dst = reinterpret_cast<uint4*>(b_act + dest * (K / 2));
     uint8_t* sf_row = sfb + sf_offset(e, r, 0, n_rt, n_kt);   // K-block kb of this row: + (kb >> 2) * 512 + (kb & 3)
-#pragma unroll 2
-    for (int seg = 0; seg < segs; ++seg) {
-      const int k0 = seg * 256 + lane * 8;
-      const bool live = k0 < K;
-      float f[8];
-      if (live) {
-        unpack8(__ldg(src + seg * 32 + lane), f);
+    for (int kb0 = 0; kb0 < KB; kb0 += 32) {
+      const int kb = kb0 + lane;
+      uint32_t sf_byte = kBenignSf;   // blocks past K keep the benign byte in the layout's slop
+      if (kb < KB) {
+        BlockRegs b;
+        load_block(src + kb * 4, b);
         if (weighted) {
 #pragma unroll
-          for (int q = 0; q < 8; ++q) f[q] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(f[q], w)));
+          for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int z = 0; z < 8; ++z) b.f[q][z] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(b.f[q][z], w)));
         }
-      } else {
-#pragma unroll
-        for (int q = 0; q < 8; ++q) f[q] = 0.f;
-      }
-      float amax = 0.f;
-#pragma unroll
-      for (int q = 0; q < 8; ++q) amax = fmaxf(amax, fabsf(f[q]));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-      uint32_t sf_byte = kBenignSf;   // blocks past K keep the benign byte in the layout's slop
-      if (live) {
         float inv;
-        block_scale(amax, gs, sf_byte, inv);
-        dst[seg * 32 + lane] = quant8(f, inv);
+        block_scale(block_amax(b), gs, sf_byte, inv);
+        dst[kb] = block_codes(b, inv);
       }
-      const uint32_t word = gather_sf_word(sf_byte, lane);
-      const int kb = seg * 8 + (lane >> 4) * 4;
-      if ((lane & 15) == 0 && kb < KB) *reinterpret_cast<uint32_t*>(sf_row + (kb >> 2) * 512) = word;
+      const uint32_t word = gather_sf_word(sf_byte);
+      if ((lane & 3) == 0 && kb < KB) *reinterpret_cast<uint32_t*>(sf_row + (kb >> 2) * 512) = word;
     }
   }
 }
 
 // quant_rows: token-order rows -> row-major codes and natural-order scales, one shared global scale.
-// One warp per row, 256 elements at a time; a quad owns a block; four scales leave as one word.
+// One warp per row, one 32-element block per lane; four scales leave as one word.
 __global__ void __launch_bounds__(kThreads)
 quant_rows_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gscale, unsigned T, int K,
                   uint8_t* __restrict__ q, uint8_t* __restrict__ q_sf) {
   pdl_wait();
   pdl_launch_dependents();
-  const int segs = ceil_div_i(K, 256);
   const int KB = K / kSfBlock;
   const int lane = threadIdx.x & 31;
   const float gs = gscale[0];
@@ -238,37 +245,21 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__
   const bool sf_words = (KB % 4) == 0;     // rows of scales are then 4-byte aligned
   for (unsigned t = warp0; t < T; t += nwarps) {
     const uint4* src = reinterpret_cast<const uint4*>(x + (long long)t * K);
-    uint32_t* dst = reinterpret_cast<uint32_t*>(q + (long long)t * (K / 2));
+    uint4* dst = reinterpret_cast<uint4*>(q + (long long)t * (K / 2));
     uint8_t* sf_row = q_sf + (long long)t * KB;
-#pragma unroll 2
-    for (int seg = 0; seg < segs; ++seg) {
-      const int k0 = seg * 256 + lane * 8;
-      const bool live = k0 < K;
-      float f[8];
-      if (live) {
-        unpack8(__ldg(src + seg * 32 + lane), f);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = 0.f;
-      }
-      float amax = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    for (int kb0 = 0; kb0 < KB; kb0 += 32) {
+      const int kb = kb0 + lane;
       uint32_t sf_byte = 0;
-      if (live) {
+      if (kb < KB) {
+        BlockRegs b;
+        load_block(src + kb * 4, b);
         float inv;
-        block_scale(amax, gs, sf_byte, inv);
-        dst[seg * 32 + lane] = quant8(f, inv);
+        block_scale(block_amax(b), gs, sf_byte, inv);
+        dst[kb] = block_codes(b, inv);
+        if (!sf_words) sf_row[kb] = (uint8_t)sf_byte;
       }
-      const uint32_t word = gather_sf_word(sf_byte, lane);
-      const int kb = seg * 8 + (lane >> 4) * 4;
-      if (sf_words) {
-        if ((lane & 15) == 0 && kb < KB) *reinterpret_cast<uint32_t*>(sf_row + kb) = word;
-      } else if (live && (lane & 3) == 0) {
-        sf_row[k0 / kSfBlock] = (uint8_t)sf_byte;
-      }
+      const uint32_t word = gather_sf_word(sf_byte);
+      if (sf_words && (lane & 3) == 0 && kb < KB) *reinterpret_cast<uint32_t*>(sf_row + kb) = word;
     }
   }
 }
