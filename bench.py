@@ -45,6 +45,9 @@ WORKLOADS = {
     # DeepSeek-V3 MoE, one expert-parallel rank's share: 8192 tokens, top-8 of 256
     "c4": dict(desc="DeepSeek-V3-shaped MoE, expert parallel", E=256, hidden=7168, inter=2048, cap=1024,
                routing="topk", tokens=8192, topk=8, seed=1003, config_id=2, wstd=0.02),
+    # the per-rank shape of c4 at 8 ranks (32 local experts, 65536 routed rows), without the exchange
+    "c4r8": dict(desc="DeepSeek-V3-shaped MoE, one rank's expert shard at 8 ranks", E=32, hidden=7168, inter=2048,
+                 cap=4096, routing="topk", tokens=8192, topk=8, seed=1005, config_id=2, wstd=0.02),
     # skewed routing: Zipf(1.2) expert popularity, top-4 of 128 over 8192 tokens, cap 4096
     "c5": dict(desc="skewed-routing MoE (Zipf 1.2)", E=128, hidden=3072, inter=3072, cap=4096,
                routing="zipf", tokens=8192, topk=4, seed=1004, config_id=2, wstd=0.02),
