@@ -828,32 +828,50 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   TileWalk walk;
   walk.init<TILE_N>(s_counts, p.E, kBRes ? 1 : p.n_mt);
 
-  if (warp == 0) {
-    // =============================== tile producer (TMA) ===============================
-    // p.prod_lanes lanes work side by side, lane i on pipeline slots i, i + lanes, ...: one thread
-    // needs several hundred cycles per (wait, expect, copy) sequence, while the same sequence
-    // issued by several lanes of a warp in one go costs little more than once.
+  if (warp < 2) {
+    // =============================== producers ===============================
+    // warp 0: TMA tile copies (compressed weights, activations); warp 1: bulk copies of the
+    // metadata, SFA and SFB atoms.  In each, p.prod_lanes lanes work side by side, lane i on
+    // pipeline slots i, i + lanes, ...: one thread needs several hundred cycles per (wait, expect,
+    // copy) sequence, while the same sequence issued by several lanes of a warp in one go costs
+    // little more than once.  The loop carries its position (tile, K stage, slot, turn) forward with
+    // additions only, and recomputes addresses only when the tile changes: a lone thread retires an
+    // instruction every 6-20 cycles, so divisions per stage would cost as much as the copies.
     if (lane < p.prod_lanes) {
+      const bool tile_role = warp == 0;
       bool ok = true;
-      for (int G = lane; ok; G += p.prod_lanes) {       // G: this CTA's running stage number
-        const int n = G / p.k_stages, ks = G - n * p.k_stages;          // n: running tile number
-        int mt, nt;
-        if (kBRes) {
-          const int u = n / p.n_mt;
-          mt = n - u * p.n_mt;
-          int dummy;
-          if (!walk.seek<TILE_N>(blockIdx.x + (long long)u * gridDim.x, dummy, nt)) break;
-        } else if (!walk.seek<TILE_N>(blockIdx.x + (long long)n * gridDim.x, mt, nt)) {
-          break;
+      int n = 0, ks = lane, stage = lane, cur_n = -1;     // lanes <= stages (host)
+      uint32_t turn = 0;
+      int e = 0, mt = 0, n0 = 0, sfb_row_atoms = 1;
+      uint32_t uphase = 0;
+      const uint8_t *e_base = nullptr, *sfa_base = nullptr, *sfb_base = nullptr;
+      while (ok) {
+        while (ks >= p.k_stages) { ks -= p.k_stages; ++n; }
+        if (n != cur_n) {                                  // a new tile: where it is, and its operand bases
+          int nt;
+          if (kBRes) {
+            const int u = n / p.n_mt;
+            mt = n - u * p.n_mt;
+            uphase = (uint32_t)u & 1u;
+            int dummy;
+            if (!walk.seek<TILE_N>(blockIdx.x + (long long)u * gridDim.x, dummy, nt)) break;
+          } else if (!walk.seek<TILE_N>(blockIdx.x + (long long)n * gridDim.x, mt, nt)) {
+            break;
+          }
+          cur_n = n;
+          e = walk.e;
+          n0 = nt * TILE_N;
+          if (!tile_role) {
+            sfb_base = p.sfb + (((long long)e * p.sfb_rt + (n0 >> 7)) * p.n_kt) * 512;
+            sfb_row_atoms = TILE_N > 128 ? min(2, p.sfb_rt - (n0 >> 7)) : 1;
+            e_base = p.e_meta + (((long long)e * p.e_k_atoms) * p.e_m_atoms + mt) * 2048;
+            sfa_base = p.sfa + (((long long)e * p.n_mt + mt) * p.n_kt) * 512;
+          }
         }
-        const int e = walk.e;
-        const int n0 = nt * TILE_N;
-        const int turn = G / p.stages, stage = G - turn * p.stages;
         const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
         const int b_boxes = (k_atoms + 1) / 2;
-        if (kBRes && mt == 0) {
+        if (kBRes && tile_role && mt == 0) {
           // this unit's activation chunks, each as soon as the previous unit has finished with it
-          const uint32_t uphase = (uint32_t)(n / p.n_mt) & 1u;
           for (int b = 0; b < b_boxes && ok; ++b) {
             const int kc = ks * C::kBBoxes + b;
             if (!ptx::mbar_wait(b_empty + kc, uphase ^ 1)) {
@@ -867,68 +885,38 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           if (!ok) break;
         }
         long long tq0 = p.prof ? clock64() : 0;
-        if (!ptx::mbar_wait(empty_bar + stage, ((uint32_t)turn & 1u) ^ 1u)) {
-          atomicExch(&g_status, kProducerEmptyTimeout);
+        if (!ptx::mbar_wait(empty_bar + stage, turn ^ 1u)) {
+          atomicExch(&g_status, tile_role ? kProducerEmptyTimeout : kSideProducerTimeout);
           ok = false;
           break;
         }
-        if (p.prof && lane == 0) p.prof[blockIdx.x * 8 + 4] += clock64() - tq0;
+        if (p.prof && threadIdx.x == 0) p.prof[blockIdx.x * 8 + 4] += clock64() - tq0;
         uint8_t* st = stage_base + stage * C::kStageBytes;
-        ptx::mbar_arrive_expect_tx(full_bar + stage, C::kABytes + (kBRes ? 0 : b_boxes * C::kBBoxBytes));
-        ptx::tma_load_3d(st + C::kOffA, &map_a, full_bar + stage, ks * C::kARowBytes, mt * kTileM, e);
-        if (!kBRes)
-          for (int b = 0; b < b_boxes; ++b)
-            ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + stage,
-                             ks * (STAGE_K / 2) + b * 128, n0, e);
+        if (tile_role) {
+          ptx::mbar_arrive_expect_tx(full_bar + stage, C::kABytes + (kBRes ? 0 : b_boxes * C::kBBoxBytes));
+          ptx::tma_load_3d(st + C::kOffA, &map_a, full_bar + stage, ks * C::kARowBytes, mt * kTileM, e);
+          if (!kBRes)
+            for (int b = 0; b < b_boxes; ++b)
+              ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + stage,
+                               ks * (STAGE_K / 2) + b * 128, n0, e);
+        } else {
+          const int e_atoms = (k_atoms + 1) / 2;
+          const uint32_t sf_bytes = 512u * k_atoms;
+          ptx::mbar_arrive_expect_tx(full_bar + stage, e_atoms * 2048 + sf_bytes * (1 + sfb_row_atoms));
+          for (int ea = 0; ea < e_atoms; ++ea)
+            ptx::bulk_load(st + C::kOffE + ea * 2048,
+                           e_base + (long long)(ks * C::kEAtoms + ea) * p.e_m_atoms * 2048, 2048, full_bar + stage);
+          ptx::bulk_load(st + C::kOffSfa, sfa_base + ks * (C::kAtoms * 512), sf_bytes, full_bar + stage);
+          for (int ra = 0; ra < sfb_row_atoms; ++ra)
+            ptx::bulk_load(st + C::kOffSfb + ra * C::kSfaBytes,
+                           sfb_base + ((long long)ra * p.n_kt + ks * C::kAtoms) * 512, sf_bytes, full_bar + stage);
+        }
+        ks += p.prod_lanes;
+        stage += p.prod_lanes;
+        if (stage >= p.stages) { stage -= p.stages; turn ^= 1u; }
       }
       if (!ok) {
         // give copies already in flight time to land before the CTA's shared memory is released
-#pragma unroll 1
-        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
-      }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    // =============================== side producer (bulk copies) ===============================
-    if (lane < p.prod_lanes) {
-      bool ok = true;
-      for (int G = lane; ok; G += p.prod_lanes) {
-        const int n = G / p.k_stages, ks = G - n * p.k_stages;
-        int mt, nt;
-        if (kBRes) {
-          const int u = n / p.n_mt;
-          mt = n - u * p.n_mt;
-          int dummy;
-          if (!walk.seek<TILE_N>(blockIdx.x + (long long)u * gridDim.x, dummy, nt)) break;
-        } else if (!walk.seek<TILE_N>(blockIdx.x + (long long)n * gridDim.x, mt, nt)) {
-          break;
-        }
-        const int e = walk.e;
-        const int n0 = nt * TILE_N;
-        const int turn = G / p.stages, stage = G - turn * p.stages;
-        const uint8_t* sfb_base = p.sfb + (((long long)e * p.sfb_rt + (n0 >> 7)) * p.n_kt) * 512;
-        const int sfb_row_atoms = TILE_N > 128 ? min(2, p.sfb_rt - (n0 >> 7)) : 1;
-        const uint8_t* e_base = p.e_meta + (((long long)e * p.e_k_atoms) * p.e_m_atoms + mt) * 2048;
-        const uint8_t* sfa_base = p.sfa + (((long long)e * p.n_mt + mt) * p.n_kt) * 512;
-        if (!ptx::mbar_wait(empty_bar + stage, ((uint32_t)turn & 1u) ^ 1u)) {
-          atomicExch(&g_status, kSideProducerTimeout);
-          ok = false;
-          break;
-        }
-        uint8_t* st = stage_base + stage * C::kStageBytes;
-        const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
-        const int e_atoms = (k_atoms + 1) / 2;
-        const uint32_t sf_bytes = 512u * k_atoms;
-        ptx::mbar_arrive_expect_tx(full_bar + stage, e_atoms * 2048 + sf_bytes * (1 + sfb_row_atoms));
-        for (int ea = 0; ea < e_atoms; ++ea)
-          ptx::bulk_load(st + C::kOffE + ea * 2048,
-                         e_base + (long long)(ks * C::kEAtoms + ea) * p.e_m_atoms * 2048, 2048, full_bar + stage);
-        ptx::bulk_load(st + C::kOffSfa, sfa_base + (long long)ks * C::kAtoms * 512, sf_bytes, full_bar + stage);
-        for (int ra = 0; ra < sfb_row_atoms; ++ra)
-          ptx::bulk_load(st + C::kOffSfb + ra * C::kSfaBytes,
-                         sfb_base + ((long long)ra * p.n_kt + ks * C::kAtoms) * 512, sf_bytes, full_bar + stage);
-      }
-      if (!ok) {
 #pragma unroll 1
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);
       }
