@@ -41,16 +41,16 @@ WORKLOADS = {
                routing="counts", seed=1001, config_id=7, wstd=0.02),
     # Qwen3-30B-A3B MoE, prefill: 16384 tokens, top-8 of 128, cap 2048
     "c3": dict(desc="prefill Qwen3-30B-A3B-shaped MoE", E=128, hidden=2048, inter=768, cap=2048,
-               routing="topk", tokens=16384, topk=8, seed=1002, config_id=2, wstd=0.02),
+               routing="topk", tokens=16384, topk=8, seed=1002, config_id=8, wstd=0.02),
     # DeepSeek-V3 MoE, one expert-parallel rank's share: 8192 tokens, top-8 of 256
     "c4": dict(desc="DeepSeek-V3-shaped MoE, expert parallel", E=256, hidden=7168, inter=2048, cap=1024,
-               routing="topk", tokens=8192, topk=8, seed=1003, config_id=2, wstd=0.02),
+               routing="topk", tokens=8192, topk=8, seed=1003, config_id=8, wstd=0.02),
     # the per-rank shape of c4 at 8 ranks (32 local experts, 65536 routed rows), without the exchange
     "c4r8": dict(desc="DeepSeek-V3-shaped MoE, one rank's expert shard at 8 ranks", E=32, hidden=7168, inter=2048,
-                 cap=4096, routing="topk", tokens=8192, topk=8, seed=1005, config_id=2, wstd=0.02),
+                 cap=4096, routing="topk", tokens=8192, topk=8, seed=1005, config_id=8, wstd=0.02),
     # skewed routing: Zipf(1.2) expert popularity, top-4 of 128 over 8192 tokens, cap 4096
     "c5": dict(desc="skewed-routing MoE (Zipf 1.2)", E=128, hidden=3072, inter=3072, cap=4096,
-               routing="zipf", tokens=8192, topk=4, seed=1004, config_id=2, wstd=0.02),
+               routing="zipf", tokens=8192, topk=4, seed=1004, config_id=8, wstd=0.02),
 }
 
 

@@ -119,6 +119,7 @@ struct Params {
   int e_m_atoms;     // metadata atoms along M = n_mt
   int sfb_rt;        // scale row-atoms per expert in sfb = ceil(max_n / 128)
   int stages;        // pipeline depth in use (<= Cfg::kStages)
+  int b_4d;          // wide kernel: map_b is the 4-D view [E][K/256][max_n][128 B] and one copy fetches a whole stage
   int prod_lanes;    // wide kernel: lanes of each producer warp that issue copies side by side
   int b_res_bytes;   // wide kernel: bytes of the resident activation tile in front of the stage ring (0 = streamed)
   // fused SwiGLU + requantise epilogue (kFused kernels): GEMM2's operands instead of a bf16 output
@@ -720,7 +721,8 @@ struct WideCfg {
   static constexpr int kSfbRowAtoms = TILE_N > 128 ? 2 : 1;
   static constexpr int kSfbBytes = kSfaBytes * kSfbRowAtoms;
   static constexpr int kStageBytes = kABytes + kBBytes + kEBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kOutBytes = 2 * kOutStageBytes;     // one double-buffered transpose tile per epilogue group
+  static constexpr int kOutBytes = 2 * kOutStageBytes;     // fused epilogue: one double-buffered transpose tile per group
+  static constexpr int kPlainOutBytes = 8 * 2 * 16 * 40 * 2;   // plain epilogue: two [16][40] bf16 pieces per warp
   static constexpr int kBarrierBytes = 1024;
   static constexpr int kMaxStages = 12;
   static constexpr int kMaxChunks = 16;                     // resident activation tile: at most 16 x 256 K
@@ -785,8 +787,9 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   uint8_t* b_res = smem;                                   // resident activation tile (kBRes), p.b_res_bytes
   uint8_t* stage_base = smem + p.b_res_bytes;
   uint8_t* after_stages = stage_base + p.stages * C::kStageBytes;
+  constexpr int kOutBytes = kFused ? C::kOutBytes : C::kPlainOutBytes;
   __nv_bfloat16* s_out = reinterpret_cast<__nv_bfloat16*>(after_stages);
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(after_stages + C::kOutBytes);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(after_stages + kOutBytes);
   uint64_t* empty_bar = full_bar + C::kMaxStages;
   uint64_t* acc_full = empty_bar + C::kMaxStages;
   uint64_t* acc_empty = acc_full + C::kAccStages;
@@ -794,7 +797,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   uint64_t* b_full = sf_full + C::kMaxStages;
   uint64_t* b_empty = b_full + C::kMaxChunks;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_empty + C::kMaxChunks);
-  int* s_counts = reinterpret_cast<int*>(after_stages + C::kOutBytes + C::kBarrierBytes);
+  int* s_counts = reinterpret_cast<int*>(after_stages + kOutBytes + C::kBarrierBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -803,7 +806,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     ptx::prefetch_tensormap(&map_a);
     ptx::prefetch_tensormap(&map_b);
     for (int s = 0; s < p.stages; ++s) {
-      ptx::mbar_init(full_bar + s, 2);
+      ptx::mbar_init(full_bar + s, 3);
       ptx::mbar_init(empty_bar + s, 1 + 4);
       ptx::mbar_init(sf_full + s, 4);
     }
@@ -837,10 +840,14 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     // little more than once.  The loop carries its position (tile, K stage, slot, turn) forward with
     // additions only, and recomputes addresses only when the tile changes: a lone thread retires an
     // instruction every 6-20 cycles, so divisions per stage would cost as much as the copies.
-    if (lane < p.prod_lanes) {
-      const bool tile_role = warp == 0;
+    // The bulk-copy warp splits every stage between two lanes (metadata atoms; scale atoms), each with
+    // its own expect-tx arrival, so a stage's full barrier counts three arrivals.
+    const bool tile_role = warp == 0;
+    const int slot_lane = tile_role ? lane : lane >> 1;     // which of the side-by-side pipeline slots
+    const int part = lane & 1;                              // bulk-copy warp: 0 metadata, 1 scales
+    if (slot_lane < p.prod_lanes) {
       bool ok = true;
-      int n = 0, ks = lane, stage = lane, cur_n = -1;     // lanes <= stages (host)
+      int n = 0, ks = slot_lane, stage = slot_lane, cur_n = -1;     // prod_lanes <= stages (host)
       uint32_t turn = 0;
       int e = 0, mt = 0, n0 = 0, sfb_row_atoms = 1;
       uint32_t uphase = 0;
@@ -871,18 +878,21 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
         const int b_boxes = (k_atoms + 1) / 2;
         if (kBRes && tile_role && mt == 0) {
-          // this unit's activation chunks, each as soon as the previous unit has finished with it
-          for (int b = 0; b < b_boxes && ok; ++b) {
-            const int kc = ks * C::kBBoxes + b;
-            if (!ptx::mbar_wait(b_empty + kc, uphase ^ 1)) {
-              atomicExch(&g_status, kProducerEmptyTimeout);
-              ok = false;
-              break;
-            }
-            ptx::mbar_arrive_expect_tx(b_full + kc, C::kBBoxBytes);
-            ptx::tma_load_3d(b_res + kc * C::kBBoxBytes, &map_b, b_full + kc, kc * 128, n0, e);
+          // this unit's activation chunks of this stage, as soon as the previous unit has finished with them
+          if (!ptx::mbar_wait(b_empty + ks, uphase ^ 1)) {
+            atomicExch(&g_status, kProducerEmptyTimeout);
+            ok = false;
+            break;
           }
-          if (!ok) break;
+          uint8_t* dst = b_res + ks * (C::kBBoxes * C::kBBoxBytes);
+          if (p.b_4d) {
+            ptx::mbar_arrive_expect_tx(b_full + ks, C::kBBoxes * C::kBBoxBytes);
+            ptx::tma_load_4d(dst, &map_b, b_full + ks, 0, n0, ks * C::kBBoxes, e);
+          } else {
+            ptx::mbar_arrive_expect_tx(b_full + ks, b_boxes * C::kBBoxBytes);
+            for (int b = 0; b < b_boxes; ++b)
+              ptx::tma_load_3d(dst + b * C::kBBoxBytes, &map_b, b_full + ks, (ks * C::kBBoxes + b) * 128, n0, e);
+          }
         }
         long long tq0 = p.prof ? clock64() : 0;
         if (!ptx::mbar_wait(empty_bar + stage, turn ^ 1u)) {
@@ -893,23 +903,35 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         if (p.prof && threadIdx.x == 0) p.prof[blockIdx.x * 8 + 4] += clock64() - tq0;
         uint8_t* st = stage_base + stage * C::kStageBytes;
         if (tile_role) {
-          ptx::mbar_arrive_expect_tx(full_bar + stage, C::kABytes + (kBRes ? 0 : b_boxes * C::kBBoxBytes));
+          // with the 4-D activation map one copy fetches all of the stage's 256-K chunks (a box past the
+          // last chunk is zero-filled and still counts its full size)
+          const int b_bytes = kBRes ? 0 : (p.b_4d ? C::kBBoxes : b_boxes) * C::kBBoxBytes;
+          ptx::mbar_arrive_expect_tx(full_bar + stage, C::kABytes + b_bytes);
           ptx::tma_load_3d(st + C::kOffA, &map_a, full_bar + stage, ks * C::kARowBytes, mt * kTileM, e);
-          if (!kBRes)
-            for (int b = 0; b < b_boxes; ++b)
-              ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + stage,
-                               ks * (STAGE_K / 2) + b * 128, n0, e);
+          if (!kBRes) {
+            if (p.b_4d) {
+              ptx::tma_load_4d(st + C::kOffB, &map_b, full_bar + stage, 0, n0, ks * C::kBBoxes, e);
+            } else {
+              for (int b = 0; b < b_boxes; ++b)
+                ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + stage,
+                                 ks * (STAGE_K / 2) + b * 128, n0, e);
+            }
+          }
         } else {
           const int e_atoms = (k_atoms + 1) / 2;
           const uint32_t sf_bytes = 512u * k_atoms;
-          ptx::mbar_arrive_expect_tx(full_bar + stage, e_atoms * 2048 + sf_bytes * (1 + sfb_row_atoms));
-          for (int ea = 0; ea < e_atoms; ++ea)
-            ptx::bulk_load(st + C::kOffE + ea * 2048,
-                           e_base + (long long)(ks * C::kEAtoms + ea) * p.e_m_atoms * 2048, 2048, full_bar + stage);
-          ptx::bulk_load(st + C::kOffSfa, sfa_base + ks * (C::kAtoms * 512), sf_bytes, full_bar + stage);
-          for (int ra = 0; ra < sfb_row_atoms; ++ra)
-            ptx::bulk_load(st + C::kOffSfb + ra * C::kSfaBytes,
-                           sfb_base + ((long long)ra * p.n_kt + ks * C::kAtoms) * 512, sf_bytes, full_bar + stage);
+          if (part == 0) {
+            ptx::mbar_arrive_expect_tx(full_bar + stage, e_atoms * 2048);
+            for (int ea = 0; ea < e_atoms; ++ea)
+              ptx::bulk_load(st + C::kOffE + ea * 2048,
+                             e_base + (long long)(ks * C::kEAtoms + ea) * p.e_m_atoms * 2048, 2048, full_bar + stage);
+          } else {
+            ptx::mbar_arrive_expect_tx(full_bar + stage, sf_bytes * (1 + sfb_row_atoms));
+            ptx::bulk_load(st + C::kOffSfa, sfa_base + ks * (C::kAtoms * 512), sf_bytes, full_bar + stage);
+            for (int ra = 0; ra < sfb_row_atoms; ++ra)
+              ptx::bulk_load(st + C::kOffSfb + ra * C::kSfaBytes,
+                             sfb_base + ((long long)ra * p.n_kt + ks * C::kAtoms) * 512, sf_bytes, full_bar + stage);
+          }
         }
         ks += p.prod_lanes;
         stage += p.prod_lanes;
@@ -991,13 +1013,10 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           for (int ks = 0; ks < p.k_stages; ++ks) {
             long long tp1 = prof ? clock64() : 0;
             const int k_atoms = ks + 1 == p.k_stages ? last_atoms : C::kAtoms;
-            if (kBRes && mt == 0) {
-              for (int b = 0; b < (k_atoms + 1) / 2 && ok; ++b)
-                if (!ptx::mbar_wait(b_full + ks * C::kBBoxes + b, uphase)) {
-                  atomicExch(&g_status, kMmaFullTimeout);
-                  ok = false;
-                }
-              if (!ok) break;
+            if (kBRes && mt == 0 && !ptx::mbar_wait(b_full + ks, uphase)) {
+              atomicExch(&g_status, kMmaFullTimeout);
+              ok = false;
+              break;
             }
             if (!ptx::mbar_wait(sf_full + stage, phase)) {
               atomicExch(&g_status, kMmaScaleTimeout);
@@ -1035,8 +1054,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                                       e_cols + ka * 2);
             }
             ptx::tc_commit(empty_bar + stage);   // stage and scale slot reusable once these MMAs and copies retire
-            if (kBRes && mt + 1 == tiles_per_item)   // last weight tile: the activation chunks may be replaced
-              for (int b = 0; b < (k_atoms + 1) / 2; ++b) ptx::tc_commit(b_empty + ks * C::kBBoxes + b);
+            if (kBRes && mt + 1 == tiles_per_item) ptx::tc_commit(b_empty + ks);   // last weight tile: chunks may be replaced
             if (prof) c_issue += clock64() - tp3;
             soff += C::kStageBytes >> 4;
             if (++stage == p.stages) { stage = 0; soff = 0; phase ^= 1; }
@@ -1071,11 +1089,15 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     int stage = 0;
     uint32_t phase = 0;
 #pragma unroll 1
+    const bool lprof = p.prof != nullptr && warp == 4 && lane == 0;
+    long long l_wait = 0, l_work = 0;
     for (long long g = 0; g < n_stages; ++g) {
+      long long tl0 = lprof ? clock64() : 0;
       if (!ptx::mbar_wait(full_bar + stage, phase)) {
         atomicExch(&g_status, kScaleLoaderTimeout);
         break;
       }
+      long long tl1 = lprof ? clock64() : 0;
       const uint8_t* st = stage_base + stage * C::kStageBytes + lane * 16;
       const uint32_t cols = lane_base + stage * C::kSfSlotCols;
 #pragma unroll
@@ -1093,7 +1115,12 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         ptx::mbar_arrive(sf_full + stage);
         ptx::mbar_arrive(empty_bar + stage);   // the scales have left shared memory
       }
+      if (lprof) { l_wait += tl1 - tl0; l_work += clock64() - tl1; }
       if (++stage == p.stages) { stage = 0; phase ^= 1; }
+    }
+    if (lprof) {   // scale loader: waiting for a stage to land, moving its scales
+      p.prof[256 * 8 + blockIdx.x * 8 + 6] = l_wait;
+      p.prof[256 * 8 + blockIdx.x * 8 + 7] = l_work;
     }
   } else {
     // =============================== epilogue ===============================
@@ -1318,6 +1345,25 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // 3-D byte tensor [experts][rows][row_bytes] with a [1][box_rows][box_bytes] box.
+// 4-D view of the activations [experts][K/256 chunks][rows][128 B] for K a multiple of 256: one box
+// [chunks][box_rows][128 B] is `chunks` consecutive 128-byte-swizzled operand tiles in shared memory.
+int make_map_b4(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint64_t experts,
+                uint32_t box_rows, uint32_t box_chunks) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(PNV_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[4] = {128, rows, row_bytes / 128, experts};
+  cuuint64_t strides[3] = {row_bytes, 128, row_bytes * rows};
+  cuuint32_t box[4] = {128, box_rows, box_chunks, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(PNV_ERR_CUDA, "cuTensorMapEncodeTiled (4-D) failed with CUresult %d (row_bytes=%llu rows=%llu)",
+                (int)r, (unsigned long long)row_bytes, (unsigned long long)rows);
+  return PNV_OK;
+}
+
 int make_map(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint64_t experts,
              uint32_t box_bytes, uint32_t box_rows, CUtensorMapSwizzle swz) {
   EncodeTiledFn fn = encode_tiled_fn();
@@ -1434,6 +1480,10 @@ int launch_wide_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const P
   using C = WideCfg<TILE_N, STAGE_K, kBRes>;
   Params p = p_in;
   p.stages = stages;
+  if (const char* env = std::getenv("PNV_GROUP_MM_STAGES")) {   // experiment knob: shallower pipeline
+    const int v = std::atoi(env);
+    if (v >= 2 && v < stages) p.stages = stages = v;
+  }
   p.b_res_bytes = b_res_bytes;
   p.prod_lanes = stages >= 8 ? 4 : stages >= 4 ? 2 : 1;
   if (const char* env = std::getenv("PNV_GROUP_MM_LANES")) {   // experiment knob
@@ -1443,8 +1493,8 @@ int launch_wide_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const P
   // resident mode: a lane must never wait for a chunk that a later lane of the same batch releases
   if (kBRes) p.prod_lanes = std::max(1, std::min(p.prod_lanes, p.k_stages));
   p.trace = nullptr;
-  const size_t smem = 1024 + (size_t)b_res_bytes + (size_t)stages * C::kStageBytes + C::kOutBytes + C::kBarrierBytes +
-                      4 * (size_t)p.E;
+  const size_t smem = 1024 + (size_t)b_res_bytes + (size_t)stages * C::kStageBytes +
+                      (kFused ? C::kOutBytes : C::kPlainOutBytes) + C::kBarrierBytes + 4 * (size_t)p.E;
   static bool opted_in[64] = {};
   int dev = 0;
   PNV_CUDA(cudaGetDevice(&dev));
@@ -1467,16 +1517,15 @@ int launch_wide(const CUtensorMap& map_a, const CUtensorMap& map_b, Params& p, i
                 cudaStream_t stream) {
   using CS = WideCfg<TILE_N, STAGE_K, false>;
   using CR = WideCfg<TILE_N, STAGE_K, true>;
-  const int fixed = 1024 + CS::kOutBytes + CS::kBarrierBytes + 4 * p.E;
-  // resident activation tile: ceil(K / 256) chunks of TILE_N x 128 bytes, and still three stages of weights
-  const int chunks = ceil_div_i(p.K, 256);
-  const int b_res = chunks * CR::kBBoxBytes;
+  const bool fused = p.f_b_out != nullptr;
+  const int fixed = 1024 + (fused ? CS::kOutBytes : CS::kPlainOutBytes) + CS::kBarrierBytes + 4 * p.E;
+  // resident activation tile: one slab of TILE_N x STAGE_K / 2 bytes per K stage, and still two stages of weights
+  const int b_res = p.k_stages * CR::kBBoxes * CR::kBBoxBytes;
   const int stages_res = std::min(std::min((int)CR::kMaxStages, (int)CR::kSfSlots), (kSmemLimit - fixed - b_res) / CR::kStageBytes);
   const long long units = (long long)p.E * ceil_div_i(p.max_n, TILE_N);
-  const bool fits = chunks <= CR::kMaxChunks && b_res < kSmemLimit - fixed && stages_res >= 3;
+  const bool fits = p.k_stages <= CR::kMaxChunks && b_res < kSmemLimit - fixed && stages_res >= 2;
   (void)units;   // resident mode is opt-in (PNV_GROUP_MM_BRES=1) until it measures faster than streaming
   const bool resident = fits && bres_mode() == 1;
-  const bool fused = p.f_b_out != nullptr;
   if (resident) {
     if (fused) return launch_wide_impl<TILE_N, STAGE_K, true, true>(map_a, map_b, p, sm_count, pdl, stream, stages_res, b_res);
     return launch_wide_impl<TILE_N, STAGE_K, false, true>(map_a, map_b, p, sm_count, pdl, stream, stages_res, b_res);
@@ -1605,6 +1654,7 @@ int group_mm_common(void* out, const FusedArgs* fused, const uint8_t* a_comp, co
   p.prof = (only_m != nullptr && std::atoi(only_m) != features) ? nullptr : profile_buffer(fused != nullptr);
   p.stages = 0;
   p.b_res_bytes = 0;
+  p.b_4d = 0;
   p.prod_lanes = 1;
   p.trace = nullptr;
 
@@ -1627,17 +1677,28 @@ int group_mm_common(void* out, const FusedArgs* fused, const uint8_t* a_comp, co
                         (uint32_t)stage_k / 4, (uint32_t)kTileM,
                         stage_k == 512 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B))
     return rc;
-  if (int rc = make_map(&map_b, b_act, (uint64_t)k / 2, (uint64_t)max_n, (uint64_t)experts, 128,
-                        (uint32_t)tile_n, CU_TENSOR_MAP_SWIZZLE_128B))
-    return rc;
-
-  cudaStream_t s = (cudaStream_t)stream;
-  const bool use_pdl = pdl != 0 && pdl_enabled();
   static const bool wide_ok = [] {   // PNV_GROUP_MM_WIDE=0: run wide tiles on the narrow kernel (comparison aid)
     const char* env = std::getenv("PNV_GROUP_MM_WIDE");
     return !(env != nullptr && env[0] == '0');
   }();
-  if (wide_ok && tile_n >= 64 && !trace_enabled()) {
+  const bool wide = wide_ok && tile_n >= 64 && !trace_enabled();
+  static const bool b4d_ok = [] {    // PNV_GROUP_MM_B4D=0: one activation copy per 256-K chunk (comparison aid)
+    const char* env = std::getenv("PNV_GROUP_MM_B4D");
+    return !(env != nullptr && env[0] == '0');
+  }();
+  p.b_4d = (wide && b4d_ok && k % 256 == 0) ? 1 : 0;
+  if (p.b_4d) {
+    if (int rc = make_map_b4(&map_b, b_act, (uint64_t)k / 2, (uint64_t)max_n, (uint64_t)experts, (uint32_t)tile_n,
+                             (uint32_t)stage_k / 256))
+      return rc;
+  } else if (int rc = make_map(&map_b, b_act, (uint64_t)k / 2, (uint64_t)max_n, (uint64_t)experts, 128,
+                               (uint32_t)tile_n, CU_TENSOR_MAP_SWIZZLE_128B)) {
+    return rc;
+  }
+
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool use_pdl = pdl != 0 && pdl_enabled();
+  if (wide) {
     switch (tile_n * 1000 + stage_k) {
       case 64256: return launch_wide<64, 256>(map_a, map_b, p, sm_count, use_pdl, s);
       case 64512: return launch_wide<64, 512>(map_a, map_b, p, sm_count, use_pdl, s);
