@@ -119,7 +119,7 @@ struct Params {
   int e_m_atoms;     // metadata atoms along M = n_mt
   int sfb_rt;        // scale row-atoms per expert in sfb = ceil(max_n / 128)
   int stages;        // pipeline depth in use (<= Cfg::kStages)
-  int b_4d;          // wide kernel: map_b is the 4-D view [E][K/256][max_n][128 B] and one copy fetches a whole stage
+  int b_4d;          // map_b is the 4-D view [E][K/256][max_n][128 B] and one copy fetches a whole stage
   int prod_lanes;    // wide kernel: lanes of each producer warp that issue copies side by side
   int b_res_bytes;   // wide kernel: bytes of the resident activation tile in front of the stage ring (0 = streamed)
   // fused SwiGLU + requantise epilogue (kFused kernels): GEMM2's operands instead of a bf16 output
@@ -217,7 +217,8 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&map_a);
     ptx::prefetch_tensormap(&map_b);
-    for (int s = 0; s < C::kStages; ++s) { ptx::mbar_init(full_bar + s, 2); ptx::mbar_init(empty_bar + s, ISSUERS); }
+    // arrivals on a stage's full barrier: the tile producer and the two bulk-copy lanes (one in the traced build)
+    for (int s = 0; s < C::kStages; ++s) { ptx::mbar_init(full_bar + s, kTrace ? 2 : 3); ptx::mbar_init(empty_bar + s, ISSUERS); }
     for (int a = 0; a < C::kAccStages; ++a) {
       ptx::mbar_init(acc_full + a, ISSUERS);
       ptx::mbar_init(acc_empty + a, kEpilogueThreads);
@@ -268,11 +269,16 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
           const int b_boxes = (k_atoms + 1) / 2;
           if (!kTrace) {
-            ptx::mbar_arrive_expect_tx(full_bar + stage, C::kABytes + b_boxes * C::kBBoxBytes);
+            // with the 4-D activation map one copy fetches both 256-K chunks of the stage
+            ptx::mbar_arrive_expect_tx(full_bar + stage, C::kABytes + (p.b_4d ? C::kBBoxes : b_boxes) * C::kBBoxBytes);
             ptx::tma_load_3d(st + C::kOffA, &map_a, full_bar + stage, ks * C::kARowBytes, mt * kTileM, e);
-            for (int b = 0; b < b_boxes; ++b)
-              ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + stage,
-                               ks * (STAGE_K / 2) + b * 128, n0, e);
+            if (p.b_4d) {
+              ptx::tma_load_4d(st + C::kOffB, &map_b, full_bar + stage, 0, n0, ks * C::kBBoxes, e);
+            } else {
+              for (int b = 0; b < b_boxes; ++b)
+                ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + stage,
+                                 ks * (STAGE_K / 2) + b * 128, n0, e);
+            }
           } else {
             auto one = [&](unsigned code, uint32_t bytes, auto issue) {
               CRUMB(1, code);
@@ -308,7 +314,9 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     __syncwarp();
   } else if (warp == 1) {
     // =============================== side producer (bulk copies) ===============================
-    if (lane == 0) {
+    // two lanes share every stage (lane 0 the metadata atoms, lane 1 the scale atoms), each with its own
+    // expect-tx arrival; the traced build keeps everything in lane 0
+    if (lane < (kTrace ? 1 : 2)) {
       int stage = 0;
       uint32_t phase = 0, dphase = 0;
       (void)dphase;
@@ -334,16 +342,20 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const uint32_t sf_bytes = 512u * k_atoms;
           const uint8_t* sfa_src = sfa_base + (long long)ks * C::kAtoms * 512;
           if (!kTrace) {
-            ptx::mbar_arrive_expect_tx(full_bar + stage, e_atoms * 2048 + sf_bytes * (1 + sfb_row_atoms));
-            for (int ea = 0; ea < e_atoms; ++ea)
-              ptx::bulk_load(st + C::kOffE + ea * 2048,
-                             e_base + (long long)(ks * C::kEAtoms + ea) * p.e_m_atoms * 2048, 2048,
-                             full_bar + stage);
-            ptx::bulk_load(st + C::kOffSfa, sfa_src, sf_bytes, full_bar + stage);
-            for (int ra = 0; ra < sfb_row_atoms; ++ra)
-              ptx::bulk_load(st + C::kOffSfb + ra * C::kSfaBytes,
-                             sfb_base + ((long long)ra * p.n_kt + ks * C::kAtoms) * 512, sf_bytes,
-                             full_bar + stage);
+            if (lane == 0) {
+              ptx::mbar_arrive_expect_tx(full_bar + stage, e_atoms * 2048);
+              for (int ea = 0; ea < e_atoms; ++ea)
+                ptx::bulk_load(st + C::kOffE + ea * 2048,
+                               e_base + (long long)(ks * C::kEAtoms + ea) * p.e_m_atoms * 2048, 2048,
+                               full_bar + stage);
+            } else {
+              ptx::mbar_arrive_expect_tx(full_bar + stage, sf_bytes * (1 + sfb_row_atoms));
+              ptx::bulk_load(st + C::kOffSfa, sfa_src, sf_bytes, full_bar + stage);
+              for (int ra = 0; ra < sfb_row_atoms; ++ra)
+                ptx::bulk_load(st + C::kOffSfb + ra * C::kSfaBytes,
+                               sfb_base + ((long long)ra * p.n_kt + ks * C::kAtoms) * 512, sf_bytes,
+                               full_bar + stage);
+            }
           } else {
             auto one = [&](unsigned code, uint32_t bytes, auto issue) {
               CRUMB(11, code);
@@ -1686,7 +1698,7 @@ int group_mm_common(void* out, const FusedArgs* fused, const uint8_t* a_comp, co
     const char* env = std::getenv("PNV_GROUP_MM_B4D");
     return !(env != nullptr && env[0] == '0');
   }();
-  p.b_4d = (wide && b4d_ok && k % 256 == 0) ? 1 : 0;
+  p.b_4d = (b4d_ok && k % 256 == 0 && !trace_enabled()) ? 1 : 0;
   if (p.b_4d) {
     if (int rc = make_map_b4(&map_b, b_act, (uint64_t)k / 2, (uint64_t)max_n, (uint64_t)experts, (uint32_t)tile_n,
                              (uint32_t)stage_k / 256))
