@@ -167,6 +167,7 @@ struct GatedAct {
   int kind;
   float beta;
   float linear_beta;
+  const uint16_t* silu_tab;   // optional: bf16 bits of silu(g) for every bf16 g (65536 entries), or nullptr
 };
 
 static __device__ __noinline__ float situ_act(float g, float u, float beta, float linear_beta) {
@@ -177,15 +178,32 @@ static __device__ __noinline__ float situ_act(float g, float u, float beta, floa
   return __bfloat162float(__float2bfloat16_rn(__fmul_rn(gate_out, up_out)));
 }
 
-// SiLU is the hot case and stays inline; SiTU is a call, so a caller's unrolled loop stays small.
+// bf16(g / (1 + expf(-g))) for a gate value that is itself a bf16 number.
+__device__ __forceinline__ float silu_direct(float g) {
+  float s = __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
+  return __bfloat162float(__float2bfloat16_rn(s));
+}
+// The same through the table: the gate has only 65536 possible values, and the table is filled with
+// silu_direct on the device, so both give the same bits.  One cached load replaces expf, an IEEE
+// division (whose slow-path branch also keeps the compiler from interleaving neighbouring
+// elements) and a rounding.
+__device__ __forceinline__ float silu_lookup(float g, const uint16_t* tab) {
+  return __uint_as_float((uint32_t)__ldg(tab + (__float_as_uint(g) >> 16)) << 16);
+}
+__device__ __forceinline__ float silu_mul(float g, float u, const uint16_t* tab) {
+  return __bfloat162float(__float2bfloat16_rn(__fmul_rn(silu_lookup(g, tab), u)));
+}
+
+// General form (any activation kind, with or without the table).  SiLU is the hot case and stays
+// inline; SiTU is a call, so a caller's unrolled loop stays small.
 __device__ __forceinline__ float gated_act(float g, float u, const GatedAct& a) {
   if (a.kind == PNV_ACT_SITU) return situ_act(g, u, a.beta, a.linear_beta);
-  float s = __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
-  float s_bf = __bfloat162float(__float2bfloat16_rn(s));
+  float s_bf = a.silu_tab != nullptr ? silu_lookup(g, a.silu_tab) : silu_direct(g);
   return __bfloat162float(__float2bfloat16_rn(__fmul_rn(s_bf, u)));
 }
 
-// (activation kind, beta, linear_beta) -> GatedAct with the reference's argument checks (quant.cu)
-int make_gated_act(int act_kind, float beta, float linear_beta, GatedAct& out);
+// (activation kind, beta, linear_beta) -> GatedAct with the reference's argument checks; for SiLU it also
+// makes sure the lookup table of the current device is filled before anything later on `stream` runs (quant.cu)
+int make_gated_act(int act_kind, float beta, float linear_beta, cudaStream_t stream, GatedAct& out);
 
 }  // namespace pnv

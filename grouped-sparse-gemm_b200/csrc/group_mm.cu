@@ -592,6 +592,11 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           for (int i = 0; i < kCols; ++i) buf[i * kOutRow + m_local] = h[i];
           epilogue_bar_sync();
           constexpr int kHalf = kCols / 2;
+          // decode-sized tiles have few pairs per lane: evaluate SiLU directly rather than through the
+          // table, whose loads (global memory, mostly L2 with this kernel's shared-memory carve-out) only
+          // add latency here
+          GatedAct act = p.f_act;
+          act.silu_tab = nullptr;
           const int par = is_up ? 1 : 0;
           const int g_row = is_up ? m_local - 32 : m_local;   // the gate's slot, which receives the product
           __nv_bfloat16* col0 = buf + par * kOutRow + g_row;
@@ -605,7 +610,7 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
             __nv_bfloat16 y[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) y[i] = __float2bfloat16_rn(gated_act(g[i], u[i], p.f_act));
+            for (int i = 0; i < 4; ++i) y[i] = __float2bfloat16_rn(gated_act(g[i], u[i], act));
 #pragma unroll
             for (int i = 0; i < 4; ++i) col0[(i0 + i) * 2 * kOutRow] = y[i];
           }
@@ -1089,7 +1094,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         unsigned long long ns_end;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_end));
         long long* x = p.prof + 256 * 8 + blockIdx.x * 8;   // issuer loop: cycles and nanoseconds
-        x[0] = clock64() - t_begin; x[1] = (long long)(ns_end - ns_begin);
+        if (!kFused) { x[0] = clock64() - t_begin; x[1] = (long long)(ns_end - ns_begin); }
       }
     }
     __syncwarp();
@@ -1268,27 +1273,48 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           // the same 32 output features: exactly one quantization block per token.  Every lane parks
           // its values; the gate lane of a feature then finishes the even token columns and the up
           // lane the odd ones, leaving the product in the gate's slot.
+          long long tf0 = eprof ? clock64() : 0;
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             buf[i * kOutRow + m_local] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(r[i])));
+          long long tf1 = eprof ? clock64() : 0;
           epilogue_pair_sync(group, sub);
+          long long tf2 = eprof ? clock64() : 0;
           const bool is_up = (sub & 1) != 0;
           __nv_bfloat16* col0 = buf + (is_up ? kOutRow + m_local - 32 : m_local);
-#pragma unroll 1
-          for (int i0 = 0; i0 < 16; i0 += 8) {
-            float g[8], u[8];
+          if (p.f_act.kind == PNV_ACT_SILU && p.f_act.silu_tab != nullptr) {
+            // SiLU through the table: all 16 columns of this lane in one straight-line pass (16 independent
+            // loads of the table in flight)
+            float g[16], u[16];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              g[i] = __bfloat162float(col0[(i0 + i) * 2 * kOutRow]);
-              u[i] = __bfloat162float(col0[(i0 + i) * 2 * kOutRow + 32]);
+            for (int i = 0; i < 16; ++i) {
+              g[i] = __bfloat162float(col0[i * 2 * kOutRow]);
+              u[i] = __bfloat162float(col0[i * 2 * kOutRow + 32]);
             }
-            __nv_bfloat16 y[8];
+            float sv[16];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) y[i] = __float2bfloat16_rn(gated_act(g[i], u[i], p.f_act));
+            for (int i = 0; i < 16; ++i) sv[i] = silu_lookup(g[i], p.f_act.silu_tab);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) col0[(i0 + i) * 2 * kOutRow] = y[i];
+            for (int i = 0; i < 16; ++i) col0[i * 2 * kOutRow] = __float2bfloat16_rn(__fmul_rn(sv[i], u[i]));
+          } else {
+#pragma unroll 1
+            for (int i0 = 0; i0 < 16; i0 += 8) {
+              float g[8], u[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                g[i] = __bfloat162float(col0[(i0 + i) * 2 * kOutRow]);
+                u[i] = __bfloat162float(col0[(i0 + i) * 2 * kOutRow + 32]);
+              }
+              __nv_bfloat16 y[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) y[i] = __float2bfloat16_rn(gated_act(g[i], u[i], p.f_act));
+#pragma unroll
+              for (int i = 0; i < 8; ++i) col0[(i0 + i) * 2 * kOutRow] = y[i];
+            }
           }
+          long long tf3 = eprof ? clock64() : 0;
           epilogue_pair_sync(group, sub);
+          long long tf4 = eprof ? clock64() : 0;
           // quantize: two adjacent lanes share one (token, 32-feature block); each takes 16 features
           const int pair = ep_tid >> 1, hb = ep_tid & 1;
           const int i = pair & 31, blk = pair >> 5;
@@ -1312,6 +1338,10 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             *reinterpret_cast<uint2*>(p.f_b_out + row * (p.f_n / 2) + kb * 16 + hb * 8) =
                 make_uint2(quant8(f[0], inv), quant8(f[1], inv));
             if (hb == 0) p.f_sfb_out[sf_offset(e, n, kb, p.sfb_rt, p.f_n_kt)] = (uint8_t)sf_byte;
+          }
+          if (eprof) {   // fused epilogue phases: park, first barrier, gate math, second barrier, quantize
+            long long* x = p.prof + 256 * 8 + blockIdx.x * 8;
+            x[0] += tf1 - tf0; x[1] += tf2 - tf1; x[2] += tf3 - tf2; x[3] += tf4 - tf3; x[4] += clock64() - tf4;
           }
         }
       }
@@ -1604,7 +1634,7 @@ struct FusedArgs {
   uint8_t* sfb_out = nullptr;
   const float* gscale = nullptr;
   int gpe = 0;
-  GatedAct act{PNV_ACT_SILU, 1.f, -1.f};
+  GatedAct act{PNV_ACT_SILU, 1.f, -1.f, nullptr};
 };
 
 // The tile variants of the fused op, by the reference's names (csrc/sm100/tactics.cu:52-57).
@@ -1650,7 +1680,7 @@ int group_mm_common(void* out, const FusedArgs* fused, const uint8_t* a_comp, co
   p.e_meta = e_meta; p.sfa = sfa; p.sfb = sfb; p.alphas = alphas; p.counts = counts;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.f_b_out = nullptr; p.f_sfb_out = nullptr; p.f_gscale = nullptr; p.f_gpe = 0; p.f_n = 0; p.f_n_kt = 0;
-  p.f_act = GatedAct{PNV_ACT_SILU, 1.f, -1.f};
+  p.f_act = GatedAct{PNV_ACT_SILU, 1.f, -1.f, nullptr};
   if (fused != nullptr) {
     p.f_b_out = fused->b_out; p.f_sfb_out = fused->sfb_out; p.f_gscale = fused->gscale; p.f_gpe = fused->gpe;
     p.f_n = features / 2; p.f_n_kt = sf_k_atoms(features / 2); p.f_act = fused->act;
@@ -1763,7 +1793,7 @@ extern "C" int pnv_group_mm_swiglu_quant(uint8_t* b_out, uint8_t* sfb_out, const
   PNV_REQUIRE((reinterpret_cast<uintptr_t>(b_out) | reinterpret_cast<uintptr_t>(sfb_out)) % 16 == 0,
               "group_mm operands must be 16-byte aligned");
   FusedArgs f;
-  if (int rc = make_gated_act(act_kind, beta, linear_beta, f.act)) return rc;
+  if (int rc = make_gated_act(act_kind, beta, linear_beta, (cudaStream_t)stream, f.act)) return rc;
   f.b_out = b_out; f.sfb_out = sfb_out; f.gscale = gscale; f.gpe = gscale_per_expert ? 1 : 0;
   PNV_REQUIRE(experts >= 1 && max_n >= 1, "experts and max_n must be positive");
   PNV_REQUIRE(sf_numel(max_n, features / 2, experts) < (1LL << 31), "sfb_out must be smaller than 2 GiB");

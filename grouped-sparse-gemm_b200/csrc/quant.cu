@@ -12,6 +12,8 @@
 // scatter_quant_act is driven by a routing list instead (source token -> destination row), so its
 // scale buffer is pre-filled with a memset node and each warp quantizes 256 elements of one routed
 // row.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace pnv {
@@ -126,11 +128,17 @@ quant_lines_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
         uint4 g0 = __ldg(pg), g1 = __ldg(pg + 1), u0 = __ldg(pu), u1 = __ldg(pu + 1);
         float ga[8], ua[8];
         unpack8(g0, ga); unpack8(u0, ua);
+        float gb[8], ub[8];
+        unpack8(g1, gb); unpack8(u1, ub);
+        if (act.kind == PNV_ACT_SILU && act.silu_tab != nullptr) {   // straight-line: 16 independent lookups
 #pragma unroll
-        for (int i = 0; i < 8; ++i) f0[i] = gated_act(ga[i], ua[i], act);
-        unpack8(g1, ga); unpack8(u1, ua);
+          for (int i = 0; i < 8; ++i) { f0[i] = silu_mul(ga[i], ua[i], act.silu_tab); f1[i] = silu_mul(gb[i], ub[i], act.silu_tab); }
+        } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) f1[i] = gated_act(ga[i], ua[i], act);
+          for (int i = 0; i < 8; ++i) f0[i] = gated_act(ga[i], ua[i], act);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f1[i] = gated_act(gb[i], ub[i], act);
+        }
       }
     } else {
 #pragma unroll
@@ -308,12 +316,64 @@ int check_common(const void* x, const float* gscale, const int32_t* counts, int 
 
 }  // namespace
 
-int make_gated_act(int act_kind, float beta, float linear_beta, GatedAct& out) {
+// ---- SiLU table ---------------------------------------------------------------------------------
+// 128 KiB inside the library, one copy per device, filled on first use by a kernel on the caller's
+// stream; later callers on other streams wait for that kernel through an event (no host wait).  A
+// first use inside a stream capture puts the fill kernel into the capture instead (it is
+// idempotent), so a graph never depends on work outside it.
+static __device__ uint16_t g_silu_tab[65536];
+bool g_silu_table_on = true;
+
+__global__ void silu_table_kernel(uint16_t* tab) {
+  const unsigned bits = blockIdx.x * blockDim.x + threadIdx.x;
+  if (bits < 65536u) tab[bits] = (uint16_t)(__float_as_uint(silu_direct(__uint_as_float(bits << 16))) >> 16);
+}
+
+int silu_table(cudaStream_t stream, const uint16_t** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static int state[kMaxDevices] = {};          // 0 nothing yet, 1 fill launched, 2 fill known complete
+  static uint16_t* ptr[kMaxDevices] = {};
+  static cudaEvent_t filled[kMaxDevices] = {};
+  int dev = 0;
+  PNV_CUDA(cudaGetDevice(&dev));
+  PNV_REQUIRE(dev >= 0 && dev < kMaxDevices, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptr[dev] == nullptr) {
+    void* sym = nullptr;
+    PNV_CUDA(cudaGetSymbolAddress(&sym, g_silu_tab));
+    ptr[dev] = static_cast<uint16_t*>(sym);
+  }
+  *out = ptr[dev];
+  if (state[dev] == 2) return PNV_OK;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  PNV_CUDA(cudaStreamIsCapturing(stream, &cap));
+  const bool capturing = cap != cudaStreamCaptureStatusNone;
+  if (state[dev] == 1 && !capturing) {
+    cudaError_t q = cudaEventQuery(filled[dev]);
+    if (q == cudaSuccess) { state[dev] = 2; return PNV_OK; }
+    if (q != cudaErrorNotReady) return fail(PNV_ERR_CUDA, "cudaEventQuery failed: %s", cudaGetErrorString(q));
+    PNV_CUDA(cudaStreamWaitEvent(stream, filled[dev], 0));
+    return PNV_OK;
+  }
+  silu_table_kernel<<<256, 256, 0, stream>>>(ptr[dev]);
+  PNV_CUDA(cudaGetLastError());
+  if (!capturing && state[dev] == 0) {
+    PNV_CUDA(cudaEventCreateWithFlags(&filled[dev], cudaEventDisableTiming));
+    PNV_CUDA(cudaEventRecord(filled[dev], stream));
+    state[dev] = 1;
+  }
+  return PNV_OK;
+}
+
+int make_gated_act(int act_kind, float beta, float linear_beta, cudaStream_t stream, GatedAct& out) {
   if (act_kind == PNV_ACT_SILU) {
-    out = GatedAct{PNV_ACT_SILU, 1.0f, -1.0f};
+    out = GatedAct{PNV_ACT_SILU, 1.0f, -1.0f, nullptr};
+    if (g_silu_table_on)
+      if (int rc = silu_table(stream, &out.silu_tab)) return rc;
   } else if (act_kind == PNV_ACT_SITU) {
     PNV_REQUIRE(beta > 0, "situ: beta must be positive, got %g", (double)beta);
-    out = GatedAct{PNV_ACT_SITU, beta, linear_beta};
+    out = GatedAct{PNV_ACT_SITU, beta, linear_beta, nullptr};
   } else {
     return fail(PNV_ERR_INVALID_ARGUMENT, "activation must be 'silu' or 'situ', got kind %d", act_kind);
   }
@@ -329,7 +389,7 @@ extern "C" int pnv_quant_act(const void* x, const float* gscale, int gscale_per_
                              uint8_t* sfb, int sm_count, pnv_stream_t stream) {
   if (int rc = check_common(x, gscale, counts, experts, max_n, k, b_act, sfb, "K")) return rc;
   long long lines = sf_numel(max_n, k, experts) / 16;
-  GatedAct act{PNV_ACT_SILU, 1.f, -1.f};
+  GatedAct act{PNV_ACT_SILU, 1.f, -1.f, nullptr};
   PNV_CUDA(launch_pdl(quant_lines_kernel<kPlain>, dim3(grid_for(lines, sm_count)), dim3(kThreads), 0,
                       (cudaStream_t)stream, pdl_enabled(), (const __nv_bfloat16*)x, gscale,
                       gscale_per_expert, counts, experts, max_n, k, 0, act, PlanArgs{}, b_act, sfb));
@@ -342,7 +402,7 @@ extern "C" int pnv_silu_mul_quant_act(const void* x2, const float* gscale, int g
                                       uint8_t* b_act, uint8_t* sfb, int sm_count,
                                       pnv_stream_t stream) {
   GatedAct act;
-  if (int rc = make_gated_act(act_kind, beta, linear_beta, act)) return rc;
+  if (int rc = make_gated_act(act_kind, beta, linear_beta, (cudaStream_t)stream, act)) return rc;
   if (int rc = check_common(x2, gscale, counts, experts, max_n, n, b_act, sfb, "intermediate width N"))
     return rc;
   long long lines = sf_numel(max_n, n, experts) / 16;
@@ -379,7 +439,7 @@ extern "C" int pnv_scatter_quant_act(const void* a1, const int64_t* flat_tok,
 extern "C" int pnv_gated_act(const void* x2, int64_t rows, int n, int interleaved, int act_kind,
                              float beta, float linear_beta, void* y, pnv_stream_t stream) {
   GatedAct act;
-  if (int rc = make_gated_act(act_kind, beta, linear_beta, act)) return rc;
+  if (int rc = make_gated_act(act_kind, beta, linear_beta, (cudaStream_t)stream, act)) return rc;
   PNV_REQUIRE(x2 && y, "null pointer argument");
   PNV_REQUIRE(n > 0 && n % kSfBlock == 0, "intermediate width N must be a multiple of %d, got %d", kSfBlock, n);
   if (rows <= 0) return PNV_OK;
@@ -400,7 +460,7 @@ extern "C" int pnv_scatter_quant_act_planned(const void* a1, const int32_t* src_
   PNV_REQUIRE(src_tok && src_route, "null pointer argument");
   if (int rc = check_common(a1, gscale, counts, experts, cap, k, b_act, sfb, "K")) return rc;
   long long lines = sf_numel(cap, k, experts) / 16;
-  GatedAct act{PNV_ACT_SILU, 1.f, -1.f};
+  GatedAct act{PNV_ACT_SILU, 1.f, -1.f, nullptr};
   PlanArgs plan{src_tok, src_route, topk_weights, nullptr, nullptr};
   PNV_CUDA(launch_pdl(quant_lines_kernel<kPlanned>, dim3(grid_for(lines, sm_count)), dim3(kThreads), 0,
                       (cudaStream_t)stream, pdl_enabled(), (const __nv_bfloat16*)a1, gscale, gscale_per_expert,
@@ -428,10 +488,15 @@ extern "C" int pnv_scatter_fp4_planned(const uint8_t* q, const uint8_t* q_sf, co
   float dummy = 0.f;
   if (int rc = check_common(q, &dummy, counts, experts, cap, k, b_act, sfb, "K")) return rc;
   long long lines = sf_numel(cap, k, experts) / 16;
-  GatedAct act{PNV_ACT_SILU, 1.f, -1.f};
+  GatedAct act{PNV_ACT_SILU, 1.f, -1.f, nullptr};
   PlanArgs plan{src_tok, nullptr, nullptr, q, q_sf};
   PNV_CUDA(launch_pdl(quant_lines_kernel<kFp4>, dim3(grid_for(lines, sm_count)), dim3(kThreads), 0,
                       (cudaStream_t)stream, pdl_enabled(), (const __nv_bfloat16*)nullptr, (const float*)nullptr, 0,
                       counts, experts, cap, k, 0, act, plan, b_act, sfb));
+  return PNV_OK;
+}
+
+extern "C" int pnv_set_silu_table(int enabled) {
+  g_silu_table_on = enabled != 0;
   return PNV_OK;
 }

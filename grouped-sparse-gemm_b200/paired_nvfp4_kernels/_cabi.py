@@ -38,6 +38,7 @@ SIGNATURES = {
     "pnv_scatter_fp4_planned": (_i, [_p, _p, _p, _p, _i, _i, _i, _p, _p, _i, _p]),
     "pnv_moe_finalize": (_i, [_p, _p, _p, _p, _i64, _i, _i, _p]),
     "pnv_gather_rows": (_i, [_p, _p, _i64, _i64, _p, _p]),
+    "pnv_set_silu_table": (_i, [_i]),
     "pnv_gated_act": (_i, [_p, _i64, _i, _i, _i, _f, _f, _p, _p]),
     "pnv_group_mm_num_configs": (_i, []),
     "pnv_group_mm_config_name": (ctypes.c_char_p, [_i]),

@@ -292,6 +292,11 @@ def moe_finalize(out, fused, route_dest, topk_weights):
                                           _stream(out)))
 
 
+def set_silu_table(enabled):
+    """Testing aid: evaluate SiLU through the library's lookup table (default) or directly."""
+    _cabi.check(_lib.pnv_set_silu_table(1 if enabled else 0))
+
+
 def gather_rows(src, idx):
     """dst[i] = src[idx[i]] for idx[i] >= 0, a zero row otherwise: the permutation step either side of
     the expert-parallel exchange (token rows into send order, expert outputs into return order)."""

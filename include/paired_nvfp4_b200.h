@@ -177,6 +177,11 @@ int pnv_gather_rows(const void* src, const int32_t* idx, int64_t n_idx, int64_t 
 int pnv_gated_act(const void* x2, int64_t rows, int n, int interleaved, int act_kind, float beta,
                   float linear_beta, void* y, pnv_stream_t stream);
 
+/* Testing aid (no reference counterpart): SiLU is evaluated through a 65536-entry table of bf16(g / (1 + expf(-g)))
+ * built into the library and filled on the device with that same expression; 0 switches the table off so that a
+ * test can compare both paths bit for bit.  Process-wide; default on. */
+int pnv_set_silu_table(int enabled);
+
 /* ---- grouped GEMM ------------------------------------------------------------------------- */
 
 /* paired_nvfp4_group_mm_configs (csrc/ops.cu:665-670; table kGroupMmKinds,

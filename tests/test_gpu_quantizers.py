@@ -183,3 +183,23 @@ def test_compress_rejects_per16_scales(ops):
     w_sf16 = torch.zeros(E, M, K // 16, dtype=torch.uint8, device="cuda")
     with pytest.raises(RuntimeError, match="ceil"):
         ops.compress(w_packed, w_sf16, K)
+
+
+def test_silu_table_matches_direct_evaluation(ops):
+    """SiLU goes through a 65536-entry table filled on the device; every possible gate value (all bf16 bit
+    patterns, NaNs and infinities included) must give the same bits as evaluating the expression."""
+    from paired_nvfp4_kernels import ops as pyops
+    bits = np.arange(65536, dtype=np.uint16).reshape(2048, 32)
+    rng = np.random.default_rng(7)
+    for up_scale in (1.0, 37.5):
+        up = orc.f32_to_bf16_bits((rng.standard_normal((2048, 32)) * up_scale).astype(np.float32))
+        if up_scale == 1.0:
+            up[:] = 0x3F80          # up = 1: the output is the table entry itself
+        x2 = bf16_tensor(np.concatenate([bits, up], axis=1)[None])
+        try:
+            y_table = bf16_bits(ops.gated_act(x2))
+            pyops.set_silu_table(False)
+            y_direct = bf16_bits(ops.gated_act(x2))
+        finally:
+            pyops.set_silu_table(True)
+        assert np.array_equal(y_table, y_direct)
