@@ -51,10 +51,12 @@ int pnv_group_mm_device_status(int* status_out);
  * (No counterpart in the reference.) */
 int pnv_group_mm_debug_trace(unsigned* words_out, int n_words);
 
-/* Measuring aid: with PNV_GROUP_MM_PROFILE=1 every CTA of the last group_mm launch leaves 8 cycle
- * counters (MMA issuer: waiting for data, issuing, waiting for an accumulator, stages seen; tile
- * producer: waiting for a free stage; 3 unused); this call synchronises and copies n_values of them
- * out.  (No counterpart in the reference.) */
+/* Measuring aid: with PNV_GROUP_MM_PROFILE=1 (2: fused launches only; PNV_GROUP_MM_PROFILE_M=<features>: only
+ * launches with that many features) every CTA of the last recorded group_mm launch leaves cycle counters: 8 per CTA
+ * from value 0 (issuer: waiting for data, issuing, waiting for an accumulator, stages seen; producer: waiting for a
+ * free stage; issuer: waiting for scales; epilogue: waiting for an accumulator, busy) and 8 more per CTA from value
+ * 2048 (wide kernel: issuer loop cycles and nanoseconds or the fused epilogue's phases, scale-loader wait / work).
+ * This call synchronises and copies n_values (<= 4096) of them out.  (No counterpart in the reference.) */
 int pnv_group_mm_profile(long long* values_out, int n_values);
 
 /* ---- size queries ------------------------------------------------------------------------- */
