@@ -32,7 +32,7 @@ FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool, used only withou
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate_up group_mm launch, from the ncu captures
 # summarised under profiles/ (same workload, so no scaling)
-NCU_TRAFFIC_BYTES = {"c2": 328.59e6, "c3": 338.16e6}
+NCU_TRAFFIC_BYTES = {"c2": 328.10e6, "c3": 337.87e6}
 
 # name -> dict(E, hidden, inter, max_n/cap, routing)
 WORKLOADS = {
