@@ -1203,27 +1203,29 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       ptx::tc_fence_after();
       long long te1 = eprof ? clock64() : 0;
       if (!kFused) {
-        // Plain epilogue, warp by warp with no barrier between warps: 16 token columns at a time, the
-        // next piece's tcgen05.ld in flight while this one is scaled, rounded, transposed through the
-        // warp's own corner of shared memory ([16 tokens][32 features], rows padded to 80 bytes) and
-        // stored 16 bytes per lane, 64 contiguous bytes per output row.
+        // Plain epilogue, warp by warp with no barrier between warps: 32 token columns at a time are
+        // scaled, rounded, transposed through the warp's own corner of shared memory ([32 tokens][32
+        // features], rows padded to 80 bytes) and stored 16 bytes per lane, 64 contiguous bytes per
+        // output row.  (Waiting for the tensor-memory load is a negligible part of the time, so the
+        // loads are not double buffered; registers go to the wider piece instead.)
         constexpr int kWarpRow = 40;
-        constexpr int kPieces = TILE_N / 32;   // per group: TILE_N / 64 chunks of two pieces
-        __nv_bfloat16* wbuf = s_out + (warp - 8) * (2 * 16 * kWarpRow);
+        __nv_bfloat16* buf = s_out + (warp - 8) * (32 * kWarpRow);
         const uint32_t t_row = tmem_base + ((uint32_t)(sub * 32) << 16) + acc * TILE_N;
-        auto piece_col = [&](int q) { return group * 32 + (q >> 1) * 64 + (q & 1) * 16; };
-        int n_pieces = 0;
-        while (n_pieces < kPieces && n0 + piece_col(n_pieces) < cnt) ++n_pieces;
-        auto process = [&](const uint32_t (&v)[16], int q) {
-          __nv_bfloat16* buf = wbuf + (q & 1) * (16 * kWarpRow);
-          const int c = piece_col(q);
+        const int m = mt * kTileM + sub * 32 + (lane & 3) * 8;
+        long long t_w = 0;
+#pragma unroll 1
+        for (int c = group * 32; c < TILE_N && n0 + c < cnt; c += 64) {
+          uint32_t v[32];
+          long long tq = eprof ? clock64() : 0;
+          ptx::tc_ld_32x32(t_row + c, v);
+          ptx::tc_ld_wait();
+          if (eprof) t_w += clock64() - tq;
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
+          for (int i = 0; i < 32; ++i)
             buf[i * kWarpRow + lane] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(v[i])));
           __syncwarp();
-          const int m = mt * kTileM + sub * 32 + (lane & 3) * 8;
 #pragma unroll
-          for (int j = 0; j < 2; ++j) {
+          for (int j = 0; j < 4; ++j) {
             const int tok = (lane >> 2) + 8 * j;
             const int n = n0 + c + tok;
             if (n >= cnt || m >= p.M) continue;
@@ -1235,27 +1237,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
               for (int z = 0; z < 8 && m + z < p.M; ++z) out_e[(long long)n * p.M + m + z] = src[z];
             }
           }
-        };
-        uint32_t va[16], vb[16];
-        long long t_w = 0, tq;
-        if (n_pieces > 0) {
-          tq = eprof ? clock64() : 0;
-          ptx::tc_ld_32x16(t_row + piece_col(0), va);
-          ptx::tc_ld_wait();
-          if (eprof) t_w += clock64() - tq;
-        }
-#pragma unroll 1
-        for (int q = 0; q < n_pieces; q += 2) {
-          if (q + 1 < n_pieces) ptx::tc_ld_32x16(t_row + piece_col(q + 1), vb);
-          process(va, q);
-          tq = eprof ? clock64() : 0;
-          ptx::tc_ld_wait();
-          if (eprof) t_w += clock64() - tq;
-          if (q + 2 < n_pieces) ptx::tc_ld_32x16(t_row + piece_col(q + 2), va);
-          if (q + 1 < n_pieces) process(vb, q + 1);
-          tq = eprof ? clock64() : 0;
-          ptx::tc_ld_wait();
-          if (eprof) t_w += clock64() - tq;
+          __syncwarp();   // the next piece overwrites the buffer
         }
         if (eprof) p.prof[256 * 8 + blockIdx.x * 8 + 5] += t_w;   // waiting for tensor-memory loads
       }
