@@ -1,0 +1,596 @@
+// group_mm, wide token tiles (64 to 256 tokens per tile): prefill-sized problems.
+//
+// Included by group_mm.cu inside namespace pnv::{anonymous}, after Params, TileWalk and the status codes.
+//
+// One kernel in two forms.
+//   single CTA (kPair = false)  one CTA per SM multiplies 128 weight rows by TILE_N tokens per tile.
+//   CTA pair   (kPair = true)   a cluster of two CTAs on neighbouring SMs multiplies 256 weight rows by
+//                               TILE_N tokens with one tcgen05.mma.sp.cta_group::2 per 128-K block.  Each
+//                               CTA loads its own 128 weight rows (with their metadata and scales) and HALF
+//                               of the token rows into its own shared memory with ordinary TMA copies (no
+//                               cluster multicast anywhere), and the tensor cores of both SMs read the two
+//                               halves.  Against the single-CTA form that halves the activation bytes an SM
+//                               has to pull from L2 per unit of math, which is what bounds these shapes.
+//
+// 24 warps per CTA:
+//   warp 0   tile producer: TMA copies of the compressed weights and of the activations
+//   warp 1   side producer: bulk copies of the metadata, SFA and SFB atoms (they sit in global memory in
+//            the shape tensor memory wants)
+//   2 - 3    MMA issuers (of a pair: in the first CTA only), alternate tiles, each into its own accumulator
+//            stage: per pipeline stage the metadata tcgen05.cp and the MMAs, nothing else
+//   4 - 7    scale loaders, one per tensor-memory lane quarter: shared memory -> registers -> tcgen05.st into a
+//            ring of scale slots (one slot per pipeline stage): the image tcgen05.cp.32x128b.warpx4 would leave
+//   8 - 23   epilogue, four groups of four warps (one warp per lane quarter); a tile's chunks of token
+//            columns are dealt round-robin to the groups
+//
+// Barriers per pipeline stage s: full[s] (this CTA's copies landed; its scale loaders wait on it),
+// sf_full[s] (scale loaders -> issuer: the scales are in tensor memory, which also says that the
+// stage's copies have landed, since the loaders saw full[s] first; of a pair, the second CTA's loaders
+// arrive on the first CTA's barrier), empty[s] (issuer's tcgen05.commit, delivered to both CTAs of a
+// pair, plus the CTA's four loaders -> producers).  Per accumulator stage: acc_full (commit, both CTAs),
+// acc_empty (all epilogue warps of the CTA or pair -> issuers).  Every wait is bounded.
+
+template <int TILE_N, int STAGE_K, bool kPair>
+struct WideCfg {
+  static_assert(TILE_N == 64 || TILE_N == 128 || TILE_N == 256, "wide tile widths: 64, 128, 256");
+  static_assert(STAGE_K == 256 || STAGE_K == 512, "stage depths: 256, 512");
+  static constexpr int kCtas = kPair ? 2 : 1;
+  static constexpr int kEpilogueWarps = 16;
+  static constexpr int kThreads = (8 + kEpilogueWarps) * 32;
+  static constexpr int kAtoms = STAGE_K / 128;
+  static constexpr int kARowBytes = STAGE_K / 4;
+  static constexpr int kABytes = kTileM * kARowBytes;
+  static constexpr uint32_t kASwizzle = STAGE_K == 512 ? 2 : 4;
+  static constexpr int kBRows = TILE_N / kCtas;              // token rows this CTA loads
+  static constexpr int kBBoxes = STAGE_K / 256;
+  static constexpr int kBBoxBytes = kBRows * 128;
+  static constexpr int kBBytes = kBBoxes * kBBoxBytes;
+  static constexpr int kEAtoms = STAGE_K / 256;
+  static constexpr int kEBytes = 2048 * kEAtoms;
+  static constexpr int kSfaBytes = 512 * kAtoms;
+  static constexpr int kSfbRowAtoms = TILE_N > 128 ? 2 : 1;  // every CTA holds the scales of all TILE_N tokens
+  static constexpr int kSfbBytes = kSfaBytes * kSfbRowAtoms;
+  static constexpr int kStageBytes = kABytes + kBBytes + kEBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kChunk = TILE_N >= 128 ? 32 : 16;     // token columns an epilogue group takes at a time
+  static constexpr int kOutBytes = 4 * 8192;                 // one 8 KiB staging area per epilogue group
+  static constexpr int kBarrierBytes = 1024;
+  static constexpr int kMaxStages = 12;
+  static constexpr int kAccStages = TILE_N == 256 ? 1 : 2;
+  static constexpr int kColE = 256;                          // tensor-memory columns: accumulators below 256
+  static constexpr int kColSf = 272;                         // ring of scale slots
+  static constexpr int kSfbColsPerAtom = 4 * kSfbRowAtoms;
+  static constexpr int kSfSlotCols = kAtoms * (4 + kSfbColsPerAtom);
+  static constexpr int kSfSlots = (kTmemCols - kColSf) / kSfSlotCols;   // one per stage: caps the pipeline depth
+  static constexpr int kOffA = 0;
+  static constexpr int kOffB = kABytes;
+  static constexpr int kOffE = kOffB + kBBytes;
+  static constexpr int kOffSfa = kOffE + kEBytes;
+  static constexpr int kOffSfb = kOffSfa + kSfaBytes;
+  static_assert(kStageBytes % 1024 == 0 && kOffB % 1024 == 0, "operand tiles must keep 1024-byte alignment");
+  static_assert(kAccStages * TILE_N <= kColE && kColE + 2 * 4 * kEAtoms <= kColSf && kSfSlots >= 2,
+                "tensor-memory column map overflows");
+  static_assert(8 * (3 * kMaxStages + 2 * kAccStages) + 16 <= kBarrierBytes, "barrier block overflows");
+};
+
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+__device__ __forceinline__ uint64_t pack_desc(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
+// Work items (tiles) position `unit` of `n_units` will process: items unit, unit + n_units, ... of the
+// list every role walks.  Warp-collective.
+template <int TILE_N>
+__device__ __forceinline__ int my_work_items(const int* cnt, int E, int per_token_tile, int unit, int n_units, int lane) {
+  long long sum = 0;
+  for (int e = lane; e < E; e += 32) sum += ceil_div_i(cnt[e], TILE_N);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const long long total = sum * per_token_tile;
+  return (long long)unit < total ? (int)((total - unit + n_units - 1) / n_units) : 0;
+}
+
+// tensor memory -> registers, kChunk (16 or 32) consecutive columns of this warp's lane quarter
+template <int N>
+__device__ __forceinline__ void tc_ld_cols(uint32_t taddr, uint32_t (&r)[N]);
+template <>
+__device__ __forceinline__ void tc_ld_cols<32>(uint32_t taddr, uint32_t (&r)[32]) { ptx::tc_ld_32x32(taddr, r); }
+template <>
+__device__ __forceinline__ void tc_ld_cols<16>(uint32_t taddr, uint32_t (&r)[16]) { ptx::tc_ld_32x16(taddr, r); }
+
+template <int TILE_N, int STAGE_K, bool kFused, bool kPair>
+__global__ void __launch_bounds__(768, 1)
+group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     const Params p) {
+  using C = WideCfg<TILE_N, STAGE_K, kPair>;
+  constexpr int kCtas = C::kCtas;
+  constexpr int kChunk = C::kChunk;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage_base = smem;
+  uint8_t* after_stages = stage_base + p.stages * C::kStageBytes;
+  uint8_t* s_out = after_stages;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(after_stages + C::kOutBytes);
+  uint64_t* empty_bar = full_bar + C::kMaxStages;
+  uint64_t* sf_full = empty_bar + C::kMaxStages;
+  uint64_t* acc_full = sf_full + C::kMaxStages;
+  uint64_t* acc_empty = acc_full + C::kAccStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + C::kAccStages);
+  int* s_counts = reinterpret_cast<int*>(after_stages + C::kOutBytes + C::kBarrierBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  // position of this CTA (or CTA pair) in the work list, and of this CTA inside its pair
+  const uint32_t rank = kPair ? ptx::cluster_ctarank() : 0u;
+  const int unit = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int n_units = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int n_mu = kPair ? (p.n_mt + 1) / 2 : p.n_mt;      // work items per token tile: M tiles, or pairs of them
+
+  if (threadIdx.x == 0) {
+    ptx::prefetch_tensormap(&map_a);
+    ptx::prefetch_tensormap(&map_b);
+    for (int s = 0; s < p.stages; ++s) {
+      ptx::mbar_init(full_bar + s, 3);
+      ptx::mbar_init(empty_bar + s, 1 + 4);
+      ptx::mbar_init(sf_full + s, 4 * kCtas);
+    }
+    for (int a = 0; a < C::kAccStages; ++a) {
+      ptx::mbar_init(acc_full + a, 1);
+      ptx::mbar_init(acc_empty + a, C::kEpilogueWarps * kCtas);
+    }
+    ptx::fence_mbar_init();
+  }
+  if (warp == 2) {
+    ptx::tmem_alloc<kCtas>(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish<kCtas>();
+  }
+  // counts (and everything else the producer kernels wrote) may only be read after this point
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int i = threadIdx.x; i < p.E; i += C::kThreads) s_counts[i] = max(0, min(p.counts[i], p.max_n));
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (kPair) ptx::cluster_sync();     // the partner's barriers are initialised before anything arrives on them
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  TileWalk walk;
+  walk.init<TILE_N>(s_counts, p.E, n_mu);
+
+  if (warp < 2) {
+    // =============================== producers ===============================
+    // In each producer warp p.prod_lanes lanes work side by side, lane i on pipeline slots i, i + lanes, ...:
+    // one thread needs several hundred cycles per (wait, expect, copy) sequence, while the same sequence
+    // issued by several lanes in one go costs little more than once.  The loop carries its position (tile, K
+    // stage, slot, turn) forward with additions only and recomputes addresses only when the tile changes.
+    // The bulk-copy warp splits every stage between two lanes (metadata atoms; scale atoms), each with its
+    // own expect-tx arrival, so a stage's full barrier counts three arrivals.
+    const bool tile_role = warp == 0;
+    const int slot_lane = tile_role ? lane : lane >> 1;     // which of the side-by-side pipeline slots
+    const int part = lane & 1;                              // bulk-copy warp: 0 metadata, 1 scales
+    if (slot_lane < p.prod_lanes) {
+      bool ok = true;
+      int n = 0, ks = slot_lane, stage = slot_lane, cur_n = -1;     // prod_lanes <= stages (host)
+      uint32_t turn = 0;
+      int e = 0, mt = 0, n0 = 0, sfb_row_atoms = 1;
+      const uint8_t *e_base = nullptr, *sfa_base = nullptr, *sfb_base = nullptr;
+      while (ok) {
+        while (ks >= p.k_stages) { ks -= p.k_stages; ++n; }
+        if (n != cur_n) {                                  // a new tile: where it is, and its operand bases
+          int mu, nt;
+          if (!walk.seek<TILE_N>(unit + (long long)n * n_units, mu, nt)) break;
+          cur_n = n;
+          e = walk.e;
+          n0 = nt * TILE_N;
+          // the second CTA of a pair takes the odd M tile; past the last tile it re-reads the last one (its
+          // results are never stored), so every copy stays inside the expert's operands
+          mt = kPair ? min(2 * mu + (int)rank, p.n_mt - 1) : mu;
+          if (!tile_role) {
+            sfb_base = p.sfb + (((long long)e * p.sfb_rt + (n0 >> 7)) * p.n_kt) * 512;
+            sfb_row_atoms = TILE_N > 128 ? min(2, p.sfb_rt - (n0 >> 7)) : 1;
+            e_base = p.e_meta + (((long long)e * p.e_k_atoms) * p.e_m_atoms + mt) * 2048;
+            sfa_base = p.sfa + (((long long)e * p.n_mt + mt) * p.n_kt) * 512;
+          }
+        }
+        const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
+        const int b_boxes = (k_atoms + 1) / 2;
+        if (!ptx::mbar_wait(empty_bar + stage, turn ^ 1u)) {
+          atomicExch(&g_status, tile_role ? kProducerEmptyTimeout : kSideProducerTimeout);
+          ok = false;
+          break;
+        }
+        uint8_t* st = stage_base + stage * C::kStageBytes;
+        if (tile_role) {
+          // with the 4-D activation map one copy fetches all of the stage's 256-K chunks (a box past the
+          // last chunk is zero-filled and still counts its full size)
+          const int nb = n0 + (int)rank * C::kBRows;      // this CTA's share of the token rows
+          ptx::mbar_arrive_expect_tx(full_bar + stage, C::kABytes + (p.b_4d ? C::kBBoxes : b_boxes) * C::kBBoxBytes);
+          ptx::tma_load_3d(st + C::kOffA, &map_a, full_bar + stage, ks * C::kARowBytes, mt * kTileM, e);
+          if (p.b_4d) {
+            ptx::tma_load_4d(st + C::kOffB, &map_b, full_bar + stage, 0, nb, ks * C::kBBoxes, e);
+          } else {
+            for (int b = 0; b < b_boxes; ++b)
+              ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + stage,
+                               ks * (STAGE_K / 2) + b * 128, nb, e);
+          }
+        } else {
+          const int e_atoms = (k_atoms + 1) / 2;
+          const uint32_t sf_bytes = 512u * k_atoms;
+          if (part == 0) {
+            ptx::mbar_arrive_expect_tx(full_bar + stage, e_atoms * 2048);
+            for (int ea = 0; ea < e_atoms; ++ea)
+              ptx::bulk_load(st + C::kOffE + ea * 2048,
+                             e_base + (long long)(ks * C::kEAtoms + ea) * p.e_m_atoms * 2048, 2048, full_bar + stage);
+          } else {
+            ptx::mbar_arrive_expect_tx(full_bar + stage, sf_bytes * (1 + sfb_row_atoms));
+            ptx::bulk_load(st + C::kOffSfa, sfa_base + ks * (C::kAtoms * 512), sf_bytes, full_bar + stage);
+            for (int ra = 0; ra < sfb_row_atoms; ++ra)
+              ptx::bulk_load(st + C::kOffSfb + ra * C::kSfaBytes,
+                             sfb_base + ((long long)ra * p.n_kt + ks * C::kAtoms) * 512, sf_bytes, full_bar + stage);
+          }
+        }
+        ks += p.prod_lanes;
+        stage += p.prod_lanes;
+        if (stage >= p.stages) { stage -= p.stages; turn ^= 1u; }
+      }
+      if (!ok) {
+        // give copies already in flight time to land before the CTA's shared memory is released
+#pragma unroll 1
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 2 || warp == 3) {
+    // =============================== MMA issuers ===============================
+    // A tcgen05.mma holds its issuing thread for about as long as it executes, so whatever else that
+    // thread does between two MMAs is time the tensor pipe idles.  Two issuers in two warps take alternate
+    // tiles, each into its own accumulator stage; while one is between MMAs the other's are executing.
+    // Every tile's MMAs still come from one thread, in K order.  The issuer does no tile arithmetic: it
+    // counts its tiles once and then only waits, issues and commits.
+    constexpr int kIssuers = C::kAccStages == 2 ? 2 : 1;
+    const int issuer = warp - 2;
+    const int n_items = my_work_items<TILE_N>(s_counts, p.E, n_mu, unit, n_units, lane);
+    if (lane == 0 && issuer < kIssuers && rank == 0) {
+      constexpr uint32_t idesc = ptx::mma_sp_nvf4_idesc(TILE_N, kTileM * kCtas);
+      int stage = 0, acc = kIssuers == 2 ? issuer : 0;
+      uint32_t phase = 0, acc_phase = 0, soff = 0;
+      bool ok = true;
+      // Pass over the stages of a tile the other issuer takes.  Each one is waited for, not just
+      // counted: a parity wait only tells two consecutive phases of a barrier apart, so an issuer
+      // must see every turn of every slot, or after a long tile it would take an old phase for its own.
+      auto skip_stages = [&](int n) {
+#pragma unroll 1
+        for (int i = 0; i < n && ok; ++i) {
+          if (!ptx::mbar_wait_cluster(sf_full + stage, phase)) {
+            atomicExch(&g_status, kMmaScaleTimeout);
+            ok = false;
+          }
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+        soff = (uint32_t)stage * (C::kStageBytes >> 4);
+      };
+      if (kIssuers == 2 && issuer == 1 && n_items > 1) skip_stages(p.k_stages);
+      // stage-0 descriptors, split into the 32-bit halves: only the low half changes with the address
+      const uint64_t d_a0 = ptx::smem_desc(ptx::smem_u32(stage_base) + C::kOffA, 8 * C::kARowBytes, 16, C::kASwizzle);
+      const uint64_t d_b0 = ptx::smem_desc(ptx::smem_u32(stage_base) + C::kOffB, 1024, 16, 2);
+      const uint64_t d_e0 = ptx::smem_desc(ptx::smem_u32(stage_base) + C::kOffE, 128, 0, 0);
+      const uint32_t lo_a0 = (uint32_t)d_a0, hi_a = (uint32_t)(d_a0 >> 32);
+      const uint32_t lo_b0 = (uint32_t)d_b0, hi_b = (uint32_t)(d_b0 >> 32);
+      const uint32_t lo_e0 = (uint32_t)d_e0, hi_e = (uint32_t)(d_e0 >> 32);
+      const uint32_t e_cols = tmem_base + C::kColE + issuer * (4 * C::kEAtoms);   // private metadata columns
+      const uint32_t sf_cols0 = tmem_base + C::kColSf;
+      const int last_atoms = p.n_kt - (p.k_stages - 1) * C::kAtoms;     // K-blocks of a tile's last stage
+      for (int item = kIssuers == 2 ? issuer : 0; item < n_items && ok; item += kIssuers) {
+        // a 64-wide tile's scales sit 0 or 2 columns into the 128-row atom (even offsets only: the MMA
+        // faults on an odd scale column); wider tiles start at column 0 and need no tile coordinates
+        uint32_t sfb_off = 0;
+        if (TILE_N < 128) {
+          int mu, nt;
+          if (!walk.seek<TILE_N>(unit + (long long)item * n_units, mu, nt)) break;
+          sfb_off = ((nt * TILE_N) & 127) >> 5;
+        }
+        if (!ptx::mbar_wait_cluster(acc_empty + acc, acc_phase ^ 1)) {
+          atomicExch(&g_status, kMmaAccTimeout);
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * TILE_N;
+#pragma unroll 1
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          const int k_atoms = ks + 1 == p.k_stages ? last_atoms : C::kAtoms;
+          if (!ptx::mbar_wait_cluster(sf_full + stage, phase)) {
+            atomicExch(&g_status, kMmaScaleTimeout);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          // descriptors of this stage: the precomputed ones of stage 0 plus the stage's offset in
+          // 16-byte units (the address field is the low 14 bits, so a 32-bit add cannot carry out)
+          const uint32_t la = lo_a0 + soff, le = lo_e0 + soff, lb = lo_b0 + soff;
+          const uint32_t sf_cols = sf_cols0 + stage * C::kSfSlotCols;
+          const uint32_t sfb_cols = sf_cols + C::kAtoms * 4 + sfb_off;
+          if (k_atoms == C::kAtoms) {
+#pragma unroll
+            for (int ea = 0; ea < C::kEAtoms; ++ea)
+              ptx::tc_cp_128x128b<kCtas>(e_cols + ea * 4, pack_desc(le + ea * 128, hi_e));
+#pragma unroll
+            for (int ka = 0; ka < C::kAtoms; ++ka)
+              ptx::tc_mma_sp_nvf4<kCtas>(d_tmem, pack_desc(la + ka * 2, hi_a),
+                                         pack_desc(lb + (ka >> 1) * (C::kBBoxBytes >> 4) + (ka & 1) * 4, hi_b), idesc,
+                                         (ks | ka) != 0 ? 1u : 0u, sf_cols + ka * 4,
+                                         sfb_cols + ka * C::kSfbColsPerAtom, e_cols + ka * 2);
+          } else {
+#pragma unroll
+            for (int ea = 0; ea < C::kEAtoms; ++ea)
+              if (2 * ea < k_atoms) ptx::tc_cp_128x128b<kCtas>(e_cols + ea * 4, pack_desc(le + ea * 128, hi_e));
+#pragma unroll
+            for (int ka = 0; ka < C::kAtoms; ++ka)
+              if (ka < k_atoms)
+                ptx::tc_mma_sp_nvf4<kCtas>(d_tmem, pack_desc(la + ka * 2, hi_a),
+                                           pack_desc(lb + (ka >> 1) * (C::kBBoxBytes >> 4) + (ka & 1) * 4, hi_b), idesc,
+                                           (ks | ka) != 0 ? 1u : 0u, sf_cols + ka * 4,
+                                           sfb_cols + ka * C::kSfbColsPerAtom, e_cols + ka * 2);
+          }
+          // stage and scale slot reusable (in both CTAs of a pair) once these MMAs and copies retire
+          ptx::tc_commit_n<kCtas>(empty_bar + stage);
+          soff += C::kStageBytes >> 4;
+          if (++stage == p.stages) { stage = 0; soff = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        ptx::tc_commit_n<kCtas>(acc_full + acc);
+        if (kIssuers == 2) {
+          acc_phase ^= 1;                 // this issuer's accumulator stage comes round every own tile
+          if (item + kIssuers < n_items) skip_stages(p.k_stages);
+        } else if (++acc == C::kAccStages) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp < 8) {
+    // =============================== scale loaders ===============================
+    const int n_items = my_work_items<TILE_N>(s_counts, p.E, n_mu, unit, n_units, lane);
+    const long long n_stages = (long long)n_items * p.k_stages;
+    const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + C::kColSf;
+    int stage = 0;
+    uint32_t phase = 0;
+#pragma unroll 1
+    for (long long g = 0; g < n_stages; ++g) {
+      if (!ptx::mbar_wait(full_bar + stage, phase)) {
+        atomicExch(&g_status, kScaleLoaderTimeout);
+        break;
+      }
+      const uint8_t* st = stage_base + stage * C::kStageBytes + lane * 16;
+      const uint32_t cols = lane_base + stage * C::kSfSlotCols;
+#pragma unroll
+      for (int ka = 0; ka < C::kAtoms; ++ka) {
+        ptx::tc_st_32x32_x4(cols + ka * 4, *reinterpret_cast<const uint4*>(st + C::kOffSfa + ka * 512));
+#pragma unroll
+        for (int ra = 0; ra < C::kSfbRowAtoms; ++ra)
+          ptx::tc_st_32x32_x4(cols + C::kAtoms * 4 + ka * C::kSfbColsPerAtom + ra * 4,
+                              *reinterpret_cast<const uint4*>(st + C::kOffSfb + ra * C::kSfaBytes + ka * 512));
+      }
+      ptx::tc_st_wait();
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (kPair && rank != 0) ptx::mbar_arrive_cluster(sf_full + stage, 0);   // the issuers live in the first CTA
+        else ptx::mbar_arrive(sf_full + stage);
+        ptx::mbar_arrive(empty_bar + stage);   // the scales have left shared memory
+      }
+      if (++stage == p.stages) { stage = 0; phase ^= 1; }
+    }
+  } else {
+    // =============================== epilogue ===============================
+    const int group = (warp - 8) >> 2;         // chunks of kChunk token columns are dealt to the four groups in turn
+    const int sub = warp & 3;                  // tensor-memory lane quarter this warp may read
+    const int m_local = sub * 32 + lane;       // accumulator row (output feature) held by this thread
+    const bool vec_ok = (p.M % 8) == 0;        // 16-byte aligned output rows: needed by the bulk stores
+    uint8_t* gbuf = s_out + group * 8192;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    if (kFused) {
+      // Benign fill of GEMM2's scale buffer: every byte the epilogues will not write (rows at or
+      // past counts[e], K-block slop) becomes 0x38.  All CTAs share the lines; live slots are
+      // skipped, so the fill never races with a quantized scale.
+      const int KB = p.f_n / kSfBlock;
+      const unsigned lines = (unsigned)p.E * p.sfb_rt * p.f_n_kt * 32u;   // < 2^27, checked by the host
+      const uint32_t w4 = kBenignSf * 0x01010101u;
+      constexpr unsigned kFillThreads = C::kEpilogueWarps * 32;
+#pragma unroll 1
+      for (unsigned c = blockIdx.x * kFillThreads + (threadIdx.x - 256); c < lines; c += gridDim.x * kFillThreads) {
+        const int rr = (int)(c & 31);
+        unsigned a = c >> 5;
+        const unsigned a_kt = a / (unsigned)p.f_n_kt;
+        const int kt = (int)(a - a_kt * p.f_n_kt);
+        const unsigned a_e = a_kt / (unsigned)p.sfb_rt;
+        const int r0 = (int)(a_kt - a_e * p.sfb_rt) * 128 + rr;
+        const int cnt_e = s_counts[a_e];
+        uint8_t* line = p.f_sfb_out + (long long)c * 16;
+        if (r0 >= cnt_e) {
+          *reinterpret_cast<uint4*>(line) = make_uint4(w4, w4, w4, w4);
+        } else {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (r0 + 32 * g >= cnt_e) {
+              *reinterpret_cast<uint32_t*>(line + 4 * g) = w4;
+            } else {
+              for (int j = KB - kt * 4; j < 4; ++j)
+                if (j >= 0) line[4 * g + j] = (uint8_t)kBenignSf;
+            }
+          }
+        }
+      }
+    }
+    // A warp hands its accumulator stage back as soon as it has read its last chunk of it (of a pair: to the
+    // first CTA, where the issuers wait).
+    auto release_acc = [&]() {
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (kPair && rank != 0) ptx::mbar_arrive_cluster(acc_empty + acc, 0);
+        else ptx::mbar_arrive(acc_empty + acc);
+      }
+    };
+    for (long long w = unit;; w += n_units) {
+      int mu, nt;
+      if (!walk.seek<TILE_N>(w, mu, nt)) break;
+      const int e = walk.e;
+      const int cnt = s_counts[e];
+      const int mt = kPair ? 2 * mu + (int)rank : mu;
+      const bool mt_valid = mt < p.n_mt;       // the second CTA of the last pair of an odd tile count stores nothing
+      const float alpha = p.alphas[e];
+      const int n0 = nt * TILE_N;
+      if (!ptx::mbar_wait(acc_full + acc, acc_phase)) {
+        atomicExch(&g_status, kEpilogueTimeout);
+        break;
+      }
+      ptx::tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(sub * 32) << 16) + acc * TILE_N;
+      bool released = false;
+      if (!kFused) {
+        // Plain epilogue.  A group (four warps = all 128 features of the tile) takes kChunk token columns:
+        // scale, round to bf16 and transpose into the group's staging area as [token][128 features], rows of
+        // 256 bytes; then a few lanes issue one bulk copy shared -> global per live token row (256
+        // contiguous bytes; rows at or past counts[e] get no copy) and the warps go straight back to the
+        // next tensor-memory load.  The staging area is reused once the earlier copies have read it.
+        __nv_bfloat16* buf = reinterpret_cast<__nv_bfloat16*>(gbuf);
+        constexpr int kRowsPerWarp = kChunk / 4;
+        __nv_bfloat16* out_e = p.out + (long long)e * p.max_n * p.M;
+        const int m0 = mt * kTileM;
+#pragma unroll 1
+        for (int c0 = group * kChunk; c0 < TILE_N && n0 + c0 < cnt; c0 += 4 * kChunk) {
+          uint32_t v[kChunk];
+          tc_ld_cols<kChunk>(t_row + c0, v);
+          ptx::tc_ld_wait();
+          if (c0 + 4 * kChunk >= TILE_N || n0 + c0 + 4 * kChunk >= cnt) { release_acc(); released = true; }
+          if (!mt_valid) continue;
+          if (vec_ok) {
+            if (lane < kRowsPerWarp) ptx::bulk_wait_read_all();
+            named_bar_sync(1 + group, 128);
+#pragma unroll
+            for (int i = 0; i < kChunk; ++i)
+              buf[i * kTileM + m_local] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(v[i])));
+            ptx::fence_proxy_async_smem();
+            named_bar_sync(1 + group, 128);
+            if (lane < kRowsPerWarp) {
+              const int row = sub * kRowsPerWarp + lane;
+              const int n = n0 + c0 + row;
+              if (n < cnt) {
+                const int feats = min(kTileM, p.M - m0);
+                ptx::bulk_store(out_e + (long long)n * p.M + m0, buf + row * kTileM, (uint32_t)feats * 2u);
+              }
+              ptx::bulk_commit();
+            }
+          } else {
+            const int m = m0 + m_local;
+            if (m < p.M) {
+#pragma unroll
+              for (int i = 0; i < kChunk; ++i) {
+                const int n = n0 + c0 + i;
+                if (n < cnt) out_e[(long long)n * p.M + m] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(v[i])));
+              }
+            }
+          }
+        }
+      } else {
+        // Fused epilogue.  The weight rows are interleaved in 64-row blocks (32 gate rows, then the 32
+        // matching up rows), so of a warp pair (lane quarters 0-1 or 2-3) one warp holds the gates and the
+        // other the ups of the same 32 output features: exactly one quantization block per token.  The
+        // pair splits the chunk's tokens: the gate warp finishes the even ones, the up warp the odd ones.
+        // Each parks the values its partner needs ([token pair][feature], 64-byte rows), computes the
+        // activation for its own tokens from its registers and the partner's parked values, transposes the
+        // results through a private corner of shared memory, and then two adjacent lanes quantize one
+        // (token, 32-feature block): 16 features each, the block amax by one shuffle.
+        constexpr int kHalf = kChunk / 2;                    // tokens each warp of a pair finishes
+        const bool is_up = (sub & 1) != 0;
+        const int par = is_up ? 1 : 0;
+        __nv_bfloat16* pbuf = reinterpret_cast<__nv_bfloat16*>(gbuf + (sub >> 1) * 4096);
+        __nv_bfloat16* x_mine = pbuf + par * (kHalf * 32);         // what this warp parks for its partner
+        __nv_bfloat16* x_other = pbuf + (1 - par) * (kHalf * 32);
+        __nv_bfloat16* y_mine = pbuf + 1024 + par * (kHalf * 32);  // this warp's results, [own token][feature]
+        const int pair_bar = 1 + group * 2 + (sub >> 1);
+        float gs = p.f_gpe ? p.f_gscale[e] : p.f_gscale[0];
+#pragma unroll 1
+        for (int c0 = group * kChunk; c0 < TILE_N && n0 + c0 < cnt; c0 += 4 * kChunk) {
+          uint32_t v[kChunk];
+          tc_ld_cols<kChunk>(t_row + c0, v);
+          ptx::tc_ld_wait();
+          if (c0 + 4 * kChunk >= TILE_N || n0 + c0 + 4 * kChunk >= cnt) { release_acc(); released = true; }
+          if (!mt_valid) continue;
+          float h[kChunk];
+#pragma unroll
+          for (int i = 0; i < kChunk; ++i)
+            h[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(v[i]))));
+          named_bar_sync(pair_bar, 64);          // the partner has read what was parked for the previous chunk
+#pragma unroll
+          for (int k = 0; k < kHalf; ++k) x_mine[k * 32 + lane] = __float2bfloat16_rn(is_up ? h[2 * k] : h[2 * k + 1]);
+          named_bar_sync(pair_bar, 64);
+          float o[kHalf];
+#pragma unroll
+          for (int k = 0; k < kHalf; ++k) o[k] = __bfloat162float(x_other[k * 32 + lane]);
+          __nv_bfloat16 y[kHalf];
+          if (p.f_act.kind == PNV_ACT_SILU && p.f_act.silu_tab != nullptr) {
+            float sv[kHalf];
+#pragma unroll
+            for (int k = 0; k < kHalf; ++k) sv[k] = silu_lookup(is_up ? o[k] : h[2 * k], p.f_act.silu_tab);
+#pragma unroll
+            for (int k = 0; k < kHalf; ++k) y[k] = __float2bfloat16_rn(__fmul_rn(sv[k], is_up ? h[2 * k + 1] : o[k]));
+          } else {
+#pragma unroll
+            for (int k = 0; k < kHalf; ++k)
+              y[k] = __float2bfloat16_rn(gated_act(is_up ? o[k] : h[2 * k], is_up ? h[2 * k + 1] : o[k], p.f_act));
+          }
+          __syncwarp();                          // every lane has finished reading the previous chunk's results
+#pragma unroll
+          for (int k = 0; k < kHalf; ++k) y_mine[k * 32 + lane] = y[k];
+          __syncwarp();
+          // quantize: lanes 2k and 2k + 1 share own token k (chunk token 2k + par)
+          const int k = lane >> 1, hb = lane & 1;
+          if (k < kHalf) {
+            const int n = n0 + c0 + 2 * k + par;
+            const uint4* src = reinterpret_cast<const uint4*>(y_mine + k * 32 + hb * 16);
+            float f[2][8];
+            float amax = 0.f;
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              unpack8(src[q], f[q]);
+#pragma unroll
+              for (int z = 0; z < 8; ++z) amax = fmaxf(amax, fabsf(f[q][z]));
+            }
+            amax = fmaxf(amax, __shfl_xor_sync(kHalf == 16 ? 0xffffffffu : 0x0000ffffu, amax, 1));
+            uint32_t sf_byte;
+            float inv;
+            block_scale(amax, gs, sf_byte, inv);
+            if (n < cnt) {
+              const int kb = mt * 2 + (sub >> 1);  // 32-feature block of the N-wide output
+              const long long row = (long long)e * p.max_n + n;
+              *reinterpret_cast<uint2*>(p.f_b_out + row * (p.f_n / 2) + kb * 16 + hb * 8) =
+                  make_uint2(quant8(f[0], inv), quant8(f[1], inv));
+              if (hb == 0) p.f_sfb_out[sf_offset(e, n, kb, p.sfb_rt, p.f_n_kt)] = (uint8_t)sf_byte;
+            }
+          }
+        }
+      }
+      if (!released) release_acc();
+      if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
+    }
+    // shared memory may only be given back once the bulk copies out of it have read it
+    if (!kFused) ptx::bulk_wait_all();
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (kPair) ptx::cluster_sync();     // the partner has stopped reading this CTA's shared and tensor memory
+  if (warp == 2) {
+    __syncwarp();
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc<kCtas>(tmem_base, kTmemCols);
+  }
+}

@@ -76,6 +76,52 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return mbar_wait_slow(bar, parity);
 }
 
+// ---- thread-block clusters (CTA pairs) ---------------------------------------------------------
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Every thread of every CTA of the cluster (release / acquire at cluster scope).
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
+}
+// Arrive on the barrier that sits at the same shared-memory offset in CTA `cta` of this cluster.
+__device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t cta) {
+  asm volatile(
+      "{\n\t.reg .b32 ra;\n\t"
+      "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
+      :
+      : "r"(smem_u32(bar)), "r"(cta)
+      : "memory");
+}
+// Wait whose acquire reaches the whole cluster: for barriers another CTA of the pair arrives on.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+static __device__ __noinline__ bool mbar_wait_cluster_slow(uint64_t* bar, uint32_t parity) {
+#pragma unroll 1
+  for (uint32_t i = 0; i < kMaxPolls; ++i) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (i > 64) __nanosleep(128);
+  }
+  return false;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  return mbar_wait_cluster_slow(bar, parity);
+}
+
 // ---- TMA -----------------------------------------------------------------------------------------
 
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
@@ -115,6 +161,20 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
       : "memory");
 }
 
+// Contiguous bulk copy shared -> global (both addresses 16-byte aligned, size a multiple of 16),
+// tracked by the issuing thread's bulk-copy groups.  Writes made to the source with ordinary
+// stores need fence_proxy_async_smem() before the copy is issued.
+__device__ __forceinline__ void bulk_store(void* dst, const void* src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(reinterpret_cast<uint64_t>(dst)),
+               "r"(smem_u32(src_smem)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// every committed group of this thread has finished READING shared memory (the source may be reused)
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// every committed group of this thread is complete
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // Fire-and-forget prefetch of a contiguous global range into L2 (address and size multiples of 16).
 __device__ __forceinline__ void prefetch_l2(const void* src, uint32_t bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(src)), "r"(bytes)
@@ -123,17 +183,30 @@ __device__ __forceinline__ void prefetch_l2(const void* src, uint32_t bytes) {
 
 // ---- tensor memory -------------------------------------------------------------------------------
 
-// Warp-wide: allocate `cols` (power of two >= 32) columns, base address written to *slot.
+// Warp-wide: allocate `cols` (power of two >= 32) columns, base address written to *slot.  CTAS = 2: the
+// allocation is made in both CTAs of a pair (the same warp of each CTA executes it, same slot offset).
+template <int CTAS = 1>
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)),
-               "r"(cols)
-               : "memory");
+  if (CTAS == 2)
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols)
+                 : "memory");
+  else
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols)
+                 : "memory");
 }
+template <int CTAS = 1>
 __device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if (CTAS == 2)
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  else
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
 }
+template <int CTAS = 1>
 __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+  if (CTAS == 2)
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+  else
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -147,6 +220,19 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                    smem_u32(bar))
                : "memory");
+}
+// The same for operations issued on a CTA pair: the arrival is delivered to the barrier at this
+// shared-memory offset in both CTAs of the pair.
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+  asm volatile(
+      "{\n\t.reg .b16 m;\n\tmov.u16 m, 3;\n\t"
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t}" ::"r"(
+          smem_u32(bar))
+      : "memory");
+}
+template <int CTAS>
+__device__ __forceinline__ void tc_commit_n(uint64_t* bar) {
+  if (CTAS == 2) tc_commit_pair(bar); else tc_commit(bar);
 }
 
 // Shared-memory matrix descriptor.  K-major operand: rows of (swizzle width) bytes, groups of 8
@@ -163,9 +249,14 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t sbo_bytes,
 }
 
 // shared -> tensor memory copies (asynchronous, ordered with later MMAs of the same thread).
-// 128 lanes x 16 bytes: source is 128 lines of 16 bytes.
+// 128 lanes x 16 bytes: source is 128 lines of 16 bytes.  CTAS = 2: each CTA of the pair copies from
+// its own shared memory (same descriptor) into its own tensor memory.
+template <int CTAS = 1>
 __device__ __forceinline__ void tc_cp_128x128b(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::1.128x128b [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+  if (CTAS == 2)
+    asm volatile("tcgen05.cp.cta_group::2.128x128b [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+  else
+    asm volatile("tcgen05.cp.cta_group::1.128x128b [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
 // 32 lines x 16 bytes, replicated into all four 32-lane quarters.
 __device__ __forceinline__ void tc_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
@@ -173,24 +264,37 @@ __device__ __forceinline__ void tc_cp_32x128b_warpx4(uint32_t taddr, uint64_t sd
 }
 
 // D[tmem] (+)= A_sparse[smem] * B[smem]^T with per-32-K UE4M3 scales; e2m1 operands.
-// accumulate == 0 overwrites D.
+// accumulate == 0 overwrites D.  CTAS = 2: one instruction drives both CTAs of a pair: 256 weight
+// rows (128 from each CTA's shared memory, accumulated in that CTA's tensor memory) against N
+// activation rows, the first N/2 read from the issuing CTA's shared memory and the rest from its
+// partner's, at the same offsets; metadata and scales are read from each CTA's own tensor memory.
+template <int CTAS = 1>
 __device__ __forceinline__ void tc_mma_sp_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                                uint32_t idesc, uint32_t accumulate, uint32_t sfa_tmem,
                                                uint32_t sfb_tmem, uint32_t e_tmem) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.sp.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, [%7], %3, [%5], [%6], p;\n\t}"
-      :
-      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem),
-        "r"(sfb_tmem), "r"(e_tmem)
-      : "memory");
+  if (CTAS == 2)
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.sp.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, [%7], %3, [%5], [%6], p;\n\t}"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem),
+          "r"(sfb_tmem), "r"(e_tmem)
+        : "memory");
+  else
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.sp.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, [%7], %3, [%5], [%6], p;\n\t}"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem),
+          "r"(sfb_tmem), "r"(e_tmem)
+        : "memory");
 }
 
-// Instruction descriptor of the sparse block-scaled e2m1 x e2m1 MMA, M = 128, K-major operands,
-// UE4M3 scales, fp32 accumulation: sparse flag bit 2, A/B format (e2m1 = 1) bits 7-9 / 10-12,
-// N/8 bits 17-22, scale format (0 = UE4M3) bit 23, M/16 bits 24-28.
-__host__ __device__ constexpr uint32_t mma_sp_nvf4_idesc(int n) {
-  return (1u << 2) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24);
+// Instruction descriptor of the sparse block-scaled e2m1 x e2m1 MMA, K-major operands, UE4M3 scales,
+// fp32 accumulation: sparse flag bit 2, A/B format (e2m1 = 1) bits 7-9 / 10-12, N/8 bits 17-22,
+// scale format (0 = UE4M3) bit 23, M/16 bits 24-28 (M = 128 for one CTA, 256 for a pair).
+__host__ __device__ constexpr uint32_t mma_sp_nvf4_idesc(int n, int m = 128) {
+  return (1u << 2) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 // tensor memory -> registers: this warp's 32 lanes x 32 consecutive 32-bit columns.

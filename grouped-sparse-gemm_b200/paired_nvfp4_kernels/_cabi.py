@@ -21,8 +21,6 @@ SIGNATURES = {
     "pnv_abi_version": (_i, []),
     "pnv_last_error": (ctypes.c_char_p, []),
     "pnv_group_mm_device_status": (_i, [ctypes.POINTER(_i)]),
-    "pnv_group_mm_debug_trace": (_i, [ctypes.POINTER(ctypes.c_uint), _i]),
-    "pnv_group_mm_profile": (_i, [ctypes.POINTER(ctypes.c_longlong), _i]),
     "pnv_physical_dims": (_i, [_i, _i] + [ctypes.POINTER(_i)] * 4),
     "pnv_sf_numel": (_i64, [_i, _i, _i]),
     "pnv_compress": (_i, [_p, _p, _i, _i, _i, _p, _p, _p, _p]),

@@ -38,26 +38,14 @@ typedef struct CUstream_st* pnv_stream_t;
 int pnv_abi_version(void);
 const char* pnv_last_error(void);
 
-/* Device status word of the most recent group_mm launches on the current device: 0 when every
- * bounded wait inside the kernel completed, otherwise the code of the wait that gave up.  Reading
- * it synchronises the device; it is a debugging aid, not part of the forward path.
+/* Device status word of the group_mm launches on the current device since the last read: 0 when every
+ * bounded wait inside the kernels completed, otherwise the code of a wait that gave up (its launch's
+ * results are then undefined).  Every wait inside the kernels is bounded so that a lost copy or a logic
+ * error ends the launch instead of hanging the GPU; the enqueueing call has long returned PNV_OK by
+ * then, so a caller that wants to know reads this word at one of its own synchronisation points.
+ * Reading synchronises the device and clears the word.
  * (No counterpart in the reference, whose kernel waits without bound.) */
 int pnv_group_mm_device_status(int* status_out);
-
-/* Debugging aid: with the environment variable PNV_GROUP_MM_TRACE=1 group_mm runs a self-checking
- * build of its kernel that issues every asynchronous operation alone, checks each copy's addresses
- * before issuing it and leaves progress words in host-mapped memory; this call copies the first
- * n_words of them out without touching the CUDA context, so it still works after a device fault.
- * (No counterpart in the reference.) */
-int pnv_group_mm_debug_trace(unsigned* words_out, int n_words);
-
-/* Measuring aid: with PNV_GROUP_MM_PROFILE=1 (2: fused launches only; PNV_GROUP_MM_PROFILE_M=<features>: only
- * launches with that many features) every CTA of the last recorded group_mm launch leaves cycle counters: 8 per CTA
- * from value 0 (issuer: waiting for data, issuing, waiting for an accumulator, stages seen; producer: waiting for a
- * free stage; issuer: waiting for scales; epilogue: waiting for an accumulator, busy) and 8 more per CTA from value
- * 2048 (wide kernel: issuer loop cycles and nanoseconds or the fused epilogue's phases, scale-loader wait / work).
- * This call synchronises and copies n_values (<= 4096) of them out.  (No counterpart in the reference.) */
-int pnv_group_mm_profile(long long* values_out, int n_values);
 
 /* ---- size queries ------------------------------------------------------------------------- */
 
