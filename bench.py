@@ -155,7 +155,7 @@ class Layer:
         names = _cabi.group_mm_config_names()
         self.cluster_m = 2 if names[self.cfg].split("_")[1] == "2sm" else 1
         # fused variant with the same tile as the chosen group_mm variant
-        fmap = {6: 0, 7: 0, 4: 1, 5: 2, 0: 3, 2: 3}
+        fmap = {6: 0, 7: 0, 4: 1, 5: 2, 0: 3, 1: 3, 2: 4, 3: 4, 8: 4}
         self.fused_cfg = fmap.get(self.cfg, 3)
         if fused:
             self.cluster_m = 2 if _cabi.group_mm_swiglu_config_names()[self.fused_cfg].split("_")[1] == "2sm" else self.cluster_m

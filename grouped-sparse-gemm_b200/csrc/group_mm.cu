@@ -59,7 +59,7 @@ constexpr int kSmemLimit = 227 * 1024;
 
 enum Status : int {
   kOk = 0, kProducerEmptyTimeout = 1, kMmaFullTimeout = 2, kMmaAccTimeout = 3, kEpilogueTimeout = 4,
-  kSideProducerTimeout = 5, kMmaScaleTimeout = 6, kScaleLoaderTimeout = 7
+  kSideProducerTimeout = 5, kMmaScaleTimeout = 6, kScaleLoaderTimeout = 7, kSelfTestTimeout = 99
 };
 
 template <int TILE_N, int STAGE_K, int ISSUERS>
@@ -823,6 +823,21 @@ extern "C" int pnv_group_mm_device_status(int* status_out) {
 namespace pnv {
 namespace {
 
+// Self-test of the give-up path of the bounded waits: one thread waits, with a short poll budget, on a
+// barrier that nothing ever arrives on.  No copy is in flight and no tensor memory is held, so giving
+// up is all there is to do: record the code, invalidate the barrier, return.
+__global__ void bounded_wait_probe_kernel(int* gave_up) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(&bar, 1);
+    ptx::fence_mbar_init();
+    const bool done = ptx::mbar_wait_limited(&bar, 0, 2048);
+    if (!done) atomicExch(&g_status, kSelfTestTimeout);
+    *gave_up = done ? 0 : 1;
+    ptx::mbar_inval(&bar);
+  }
+}
+
 struct FusedArgs {
   uint8_t* b_out = nullptr;
   uint8_t* sfb_out = nullptr;
@@ -941,6 +956,18 @@ int group_mm_common(void* out, const FusedArgs* fused, const uint8_t* a_comp, co
 
 }  // namespace
 }  // namespace pnv
+
+extern "C" int pnv_selftest_bounded_wait(int* gave_up_out) {
+  PNV_REQUIRE(gave_up_out, "null pointer argument");
+  int* flag = nullptr;
+  PNV_CUDA(cudaMalloc(reinterpret_cast<void**>(&flag), sizeof(int)));
+  bounded_wait_probe_kernel<<<1, 32>>>(flag);
+  cudaError_t err = cudaGetLastError();
+  if (err == cudaSuccess) err = cudaMemcpy(gave_up_out, flag, sizeof(int), cudaMemcpyDeviceToHost);
+  cudaFree(flag);
+  if (err != cudaSuccess) return fail(PNV_ERR_CUDA, "bounded-wait self-test failed: %s", cudaGetErrorString(err));
+  return PNV_OK;
+}
 
 extern "C" int pnv_group_mm(void* out, const uint8_t* a_comp, const uint8_t* e_meta, const uint8_t* sfa,
                             const uint8_t* b_act, const uint8_t* sfb, const float* alphas,

@@ -75,6 +75,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity);
 }
+// The same loop with a caller-chosen poll budget (the self-test of the give-up path uses a short one).
+static __device__ __noinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity, uint32_t max_polls) {
+#pragma unroll 1
+  for (uint32_t i = 0; i < max_polls; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 64) __nanosleep(128);
+  }
+  return false;
+}
 
 // ---- thread-block clusters (CTA pairs) ---------------------------------------------------------
 

@@ -1,16 +1,26 @@
 // Routing plan and combine: the two steps either side of the expert FFN.
 //
-// dispatch_plan: a stable counting sort of the routings by local expert.  Routing i = t*topk + j
-// gets rank r = number of earlier routings to the same local expert; it is kept when r < cap and
-// lands in row e*cap + r.  Chunks of 1024 routings, one per thread:
-//   tally   (plans with more than one chunk) per-chunk totals per expert
-//   offsets (plans with more than one chunk) exclusive scan of the totals over chunks, and counts
-//   place   rank inside the chunk (match_any inside a warp + a per-warp tally in shared memory)
-//           plus the chunk's offset -> route_dest, src_tok, src_route (and counts when 1 chunk)
-// No atomics, so the plan is deterministic; nothing syncs, so it can be captured in a graph.
+// dispatch_plan.  Routing i = t * topk + j goes to local expert e = topk_ids[i] - first_expert (when
+// that is in [0, E)); its rank r is the number of earlier routings (smaller i) to the same expert; it
+// is kept when r < cap and lands in row e * cap + r.  That is a stable sort of the routings by
+// expert, done here in segments of 1024 routings:
+//   sort     one block per segment sorts the keys (expert << 10 | position in segment) with a bitonic
+//            network (strides below 32 by shuffles, the rest through shared memory).  The position in
+//            the low bits makes every key unique, so the unstable network yields the stable order.
+//            In the sorted segment the routings of one expert are one run; a run's start found with
+//            a max-scan gives every routing its rank inside the segment, and the run's length is the
+//            segment's total for that expert.
+//   offsets  (plans of more than one segment) exclusive prefix of the totals over segments, one warp
+//            per expert, and counts[e] = min(total, cap)
+//   place    (plans of more than one segment) rank = rank in segment + offset of (segment, expert)
+//            -> route_dest, src_tok, src_route
+// A plan that fits one segment is finished by the sort kernel alone.  No global atomics and no
+// host reads, so the plan is deterministic and can be captured in a CUDA graph.
 //
-// moe_finalize: out[t] = sum over kept routings, in top-k order, of the expert output rows,
-// optionally weighted with torch's rounding chain; one thread per 8 output columns.
+// moe_finalize.  out[t] = sum over kept routings, in top-k order, of the expert output rows,
+// optionally weighted with torch's rounding chain.  One block per token: destination rows and
+// (pre-rounded) weights of the token go to shared memory once, then every thread issues the loads
+// of all top-k rows of its 8 columns together before it starts adding.
 #include <mutex>
 
 #include "common.cuh"
@@ -18,126 +28,175 @@
 namespace pnv {
 namespace {
 
-constexpr int kChunk = 1024;            // routings per block, one per thread
-constexpr int kWarps = kChunk / 32;
+constexpr int kSeg = 1024;              // routings per segment = threads of the sort block
+constexpr int kSegBits = 10;
+constexpr int kNotLocal = 0x1FFF;       // expert code of routings to other ranks and of padding: sorts last
 
-template <class IdT>
-__device__ __forceinline__ int local_expert_of(const IdT* ids, long long i, long long n, int first, int E) {
-  if (i >= n) return E;                 // padding lanes fall in the "not local" bucket
-  long long e = (long long)ids[i] - first;
-  return (e >= 0 && e < E) ? (int)e : E;
+__device__ __forceinline__ unsigned cmp_swap(unsigned mine, unsigned other, bool keep_small) {
+  return (mine < other) == keep_small ? mine : other;
 }
 
-// Fills tally[warp][e] (uint16) with the number of lanes of each warp routing to e, and returns this
-// thread's expert and its rank among the earlier lanes of its own warp with the same expert.
+// totals: [segments][E] (nullptr for single-segment plans, which write the final outputs themselves)
 template <class IdT>
-__device__ __forceinline__ void warp_tally(const IdT* ids, long long n, int first, int E, uint16_t* tally,
-                                           int& e_out, int& lane_rank) {
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  for (int j = tid; j < kWarps * E; j += kChunk) tally[j] = 0;
-  __syncthreads();
-  const int e = local_expert_of(ids, (long long)blockIdx.x * kChunk + tid, n, first, E);
-  const unsigned same = __match_any_sync(0xffffffffu, e);
-  lane_rank = __popc(same & ((1u << lane) - 1u));
-  if (e < E && lane_rank == 0) tally[warp * E + e] = (uint16_t)__popc(same);
-  __syncthreads();
-  e_out = e;
-}
-
-template <class IdT>
-__global__ void __launch_bounds__(kChunk)
-plan_tally_kernel(const IdT* __restrict__ ids, long long n, int first, int E, int* __restrict__ totals) {
-  extern __shared__ uint16_t tally[];
+__global__ void __launch_bounds__(kSeg)
+plan_sort_kernel(const IdT* __restrict__ ids, int n, int topk, int first, int E, int cap, int* __restrict__ totals,
+                 int* __restrict__ counts, int* __restrict__ route_dest, int* __restrict__ src_tok,
+                 int* __restrict__ src_route) {
+  __shared__ unsigned s_key[kSeg];
+  __shared__ int s_warp_max[kSeg / 32];
+  extern __shared__ int s_total[];      // [E] totals of this segment
   pdl_wait();
   pdl_launch_dependents();
-  int e, lane_rank;
-  warp_tally(ids, n, first, E, tally, e, lane_rank);
-  for (int x = threadIdx.x; x < E; x += kChunk) {
-    int sum = 0;
-    for (int w = 0; w < kWarps; ++w) sum += tally[w * E + x];
-    totals[(long long)blockIdx.x * E + x] = sum;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int seg0 = blockIdx.x * kSeg;
+  for (int x = tid; x < E; x += kSeg) s_total[x] = 0;
+  unsigned code = kNotLocal;
+  if (seg0 + tid < n) {
+    const long long e = (long long)ids[seg0 + tid] - first;
+    if (e >= 0 && e < E) code = (unsigned)e;
   }
-}
-
-// totals[chunk][e] -> exclusive prefix over chunks (in place); counts[e] = min(total, cap).
-__global__ void plan_offsets_kernel(int* __restrict__ totals, int chunks, int E, int cap, int* __restrict__ counts) {
-  pdl_wait();
-  pdl_launch_dependents();
-  for (int x = blockIdx.x * blockDim.x + threadIdx.x; x < E; x += gridDim.x * blockDim.x) {
-    int run = 0;
-    for (int c = 0; c < chunks; ++c) {
-      const int v = totals[(long long)c * E + x];
-      totals[(long long)c * E + x] = run;
-      run += v;
+  unsigned key = (code << kSegBits) | (unsigned)tid;
+  // bitonic sort, ascending, one key per thread
+#pragma unroll 1
+  for (int k = 2; k <= kSeg; k <<= 1) {
+    const bool up = (tid & k) == 0;
+#pragma unroll 1
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      unsigned other;
+      if (j >= 32) {
+        __syncthreads();
+        s_key[tid] = key;
+        __syncthreads();
+        other = s_key[tid ^ j];
+      } else {
+        other = __shfl_xor_sync(0xffffffffu, key, j);
+      }
+      key = cmp_swap(key, other, ((tid & j) == 0) == up);
     }
-    counts[x] = min(run, cap);
+  }
+  // runs of equal expert in the sorted order
+  __syncthreads();
+  s_key[tid] = key;
+  __syncthreads();
+  const unsigned my_code = key >> kSegBits;
+  const bool head = tid == 0 || (s_key[tid - 1] >> kSegBits) != my_code;
+  const bool tail = tid == kSeg - 1 || (s_key[tid + 1] >> kSegBits) != my_code;
+  int start = head ? tid : 0;           // inclusive max-scan of the run starts
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, start, o);
+    if (lane >= o) start = max(start, v);
+  }
+  if (lane == 31) s_warp_max[warp] = start;
+  __syncthreads();
+  if (warp == 0) {
+    int m = s_warp_max[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, m, o);
+      if (lane >= o) m = max(m, v);
+    }
+    s_warp_max[lane] = m;
+  }
+  __syncthreads();
+  if (warp > 0) start = max(start, s_warp_max[warp - 1]);
+  const int rank = tid - start;         // rank of this routing among its expert's routings of the segment
+  const bool local = my_code != (unsigned)kNotLocal;
+  if (local && tail) s_total[my_code] = rank + 1;
+  const int i = seg0 + (int)(key & (kSeg - 1));      // the routing this sorted slot holds
+  if (totals != nullptr) {
+    // several segments: leave the rank in the segment for the place pass
+    if (i < n) route_dest[i] = local ? rank : -1;
+    __syncthreads();
+    for (int x = tid; x < E; x += kSeg) totals[(long long)blockIdx.x * E + x] = s_total[x];
+  } else {
+    if (i < n) {
+      int dest = -1;
+      if (local && rank < cap) {
+        dest = (int)my_code * cap + rank;
+        src_tok[dest] = i / topk;
+        src_route[dest] = i;
+      }
+      route_dest[i] = dest;
+    }
+    __syncthreads();
+    for (int x = tid; x < E; x += kSeg) counts[x] = min(s_total[x], cap);
   }
 }
 
-template <class IdT>
-__global__ void __launch_bounds__(kChunk)
-plan_place_kernel(const IdT* __restrict__ ids, long long n, int topk, int first, int E, int cap,
-                  const int* __restrict__ offsets, int* __restrict__ counts, int* __restrict__ route_dest,
-                  int* __restrict__ src_tok, int* __restrict__ src_route) {
-  extern __shared__ uint16_t tally[];
+// totals[segment][e] -> exclusive prefix over segments, in place; counts[e] = min(total, cap).
+// One warp per expert, 32 segments per step.
+__global__ void __launch_bounds__(256)
+plan_offsets_kernel(int* __restrict__ totals, int segments, int E, int cap, int* __restrict__ counts) {
   pdl_wait();
   pdl_launch_dependents();
-  int e, lane_rank;
-  warp_tally(ids, n, first, E, tally, e, lane_rank);
-  // exclusive prefix over the warps of this chunk, per expert, in place
-  for (int x = threadIdx.x; x < E; x += kChunk) {
-    int run = 0;
-    for (int w = 0; w < kWarps; ++w) {
-      const int v = tally[w * E + x];
-      tally[w * E + x] = (uint16_t)run;
-      run += v;
+  const int lane = threadIdx.x & 31;
+  const int e = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (e >= E) return;
+  int carry = 0;
+  for (int s0 = 0; s0 < segments; s0 += 32) {
+    const int s = s0 + lane;
+    const int v = s < segments ? totals[(long long)s * E + e] : 0;
+    int incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += u;
     }
-    if (offsets == nullptr) counts[x] = min(run, cap);   // single chunk: run is the total
+    if (s < segments) totals[(long long)s * E + e] = carry + incl - v;
+    carry += __shfl_sync(0xffffffffu, incl, 31);
   }
-  __syncthreads();
-  const long long i = (long long)blockIdx.x * kChunk + threadIdx.x;
+  if (lane == 0) counts[e] = min(carry, cap);
+}
+
+template <class IdT>
+__global__ void __launch_bounds__(256)
+plan_place_kernel(const IdT* __restrict__ ids, int n, int topk, int first, int E, int cap,
+                  const int* __restrict__ offsets, int* __restrict__ route_dest, int* __restrict__ src_tok,
+                  int* __restrict__ src_route) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
+  const int in_seg = route_dest[i];
   int dest = -1;
-  if (e < E) {
-    const int r = lane_rank + tally[(threadIdx.x >> 5) * E + e] +
-                  (offsets != nullptr ? offsets[(long long)blockIdx.x * E + e] : 0);
+  if (in_seg >= 0) {
+    const int e = (int)((long long)ids[i] - first);
+    const int r = in_seg + offsets[(long long)(i >> kSegBits) * E + e];
     if (r < cap) {
       dest = e * cap + r;
-      src_tok[dest] = (int)(i / topk);
-      src_route[dest] = (int)i;
+      src_tok[dest] = i / topk;
+      src_route[dest] = i;
     }
   }
   route_dest[i] = dest;
 }
 
 template <class IdT>
-int run_plan(const IdT* ids, long long n, int topk, int first, int E, int cap, int* counts, int* route_dest,
+int run_plan(const IdT* ids, int n, int topk, int first, int E, int cap, int* counts, int* route_dest,
              int* src_tok, int* src_route, int* scratch, cudaStream_t s) {
-  const int chunks = (int)((n + kChunk - 1) / kChunk);
-  if (chunks == 0) {
+  const int segments = (n + kSeg - 1) / kSeg;
+  if (segments == 0) {
     PNV_CUDA(cudaMemsetAsync(counts, 0, sizeof(int) * (size_t)E, s));
     return PNV_OK;
   }
-  const size_t smem = sizeof(uint16_t) * (size_t)kWarps * (size_t)E;
-  if (smem > 48 * 1024) {
-    PNV_CUDA(cudaFuncSetAttribute(plan_place_kernel<IdT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    PNV_CUDA(cudaFuncSetAttribute(plan_tally_kernel<IdT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  }
+  const size_t smem = sizeof(int) * (size_t)E;     // static shared memory takes 4.1 KiB more: always below 48 KiB
   const bool pdl = pdl_enabled();
-  const int* offsets = nullptr;
-  if (chunks > 1) {
-    PNV_REQUIRE(scratch != nullptr, "dispatch_plan: %d chunks need a scratch buffer of chunks * E ints", chunks);
-    PNV_CUDA(launch_pdl(plan_tally_kernel<IdT>, dim3(chunks), dim3(kChunk), smem, s, pdl, ids, n, first, E, scratch));
-    PNV_CUDA(launch_pdl(plan_offsets_kernel, dim3((E + 255) / 256), dim3(256), 0, s, pdl, scratch, chunks, E, cap,
-                        counts));
-    offsets = scratch;
+  if (segments == 1) {
+    PNV_CUDA(launch_pdl(plan_sort_kernel<IdT>, dim3(1), dim3(kSeg), smem, s, pdl, ids, n, topk, first, E, cap,
+                        (int*)nullptr, counts, route_dest, src_tok, src_route));
+    return PNV_OK;
   }
-  PNV_CUDA(launch_pdl(plan_place_kernel<IdT>, dim3(chunks), dim3(kChunk), smem, s, pdl, ids, n, topk, first, E, cap,
-                      offsets, counts, route_dest, src_tok, src_route));
+  PNV_REQUIRE(scratch != nullptr, "dispatch_plan: %d segments need a scratch buffer of segments * E ints", segments);
+  PNV_CUDA(launch_pdl(plan_sort_kernel<IdT>, dim3(segments), dim3(kSeg), smem, s, pdl, ids, n, topk, first, E, cap,
+                      scratch, counts, route_dest, src_tok, src_route));
+  PNV_CUDA(launch_pdl(plan_offsets_kernel, dim3((E + 7) / 8), dim3(256), 0, s, pdl, scratch, segments, E, cap, counts));
+  PNV_CUDA(launch_pdl(plan_place_kernel<IdT>, dim3((n + 255) / 256), dim3(256), 0, s, pdl, ids, n, topk, first, E, cap,
+                      (const int*)scratch, route_dest, src_tok, src_route));
   return PNV_OK;
 }
 
-// Built-in scratch for pnv_dispatch_plan_noalloc: per-chunk expert totals, chunks * E ints, at most
+// Built-in scratch for pnv_dispatch_plan_noalloc: per-segment expert totals, segments * E ints, at most
 // kBuiltinScratchInts (256 KiB).  It lives in every GPU that loads the library until the process
 // exits.  In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
 constexpr int kBuiltinScratchInts = 65536;
@@ -161,35 +220,73 @@ int builtin_scratch(int** out) {
   return PNV_OK;
 }
 
-constexpr int kFinThreads = 128;
+constexpr int kFinThreads = 256;
+constexpr int kFinMaxTopk = 32;         // routings of a token staged in shared memory at a time
 
+// TOPK > 0: the token's top-k row loads of one 16-byte column group are all issued before the first add.
+template <int TOPK>
 __global__ void __launch_bounds__(kFinThreads)
-finalize_kernel(const __nv_bfloat16* __restrict__ fused, const int* __restrict__ route_dest,
-                const float* __restrict__ topk_w, __nv_bfloat16* __restrict__ out, int topk, int K) {
+finalize_kernel(const uint4* __restrict__ fused, const int* __restrict__ route_dest, const float* __restrict__ topk_w,
+                uint4* __restrict__ out, int topk, int vecs) {
+  __shared__ int s_dest[kFinMaxTopk];
+  __shared__ float s_w[kFinMaxTopk];
   pdl_wait();
   pdl_launch_dependents();
   const long long t = blockIdx.x;
-  const int col = (blockIdx.y * kFinThreads + threadIdx.x) * 8;
-  if (col >= K) return;
-  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int k = 0; k < topk; ++k) {
-    const int d = route_dest[t * topk + k];
-    if (d < 0) continue;   // dropped routing: its row is never read
-    float v[8];
-    unpack8(__ldg(reinterpret_cast<const uint4*>(fused + (long long)d * K + col)), v);
-    if (topk_w != nullptr) {
-      const float w = __bfloat162float(__float2bfloat16_rn(topk_w[t * topk + k]));
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], __bfloat162float(__float2bfloat16_rn(__fmul_rn(v[j], w))));
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], v[j]);
+  const int nk = TOPK > 0 ? TOPK : topk;
+  // dropped routings (dest < 0) are never read; the weight is rounded to bf16 once, as torch would
+  if constexpr (TOPK > 0) {
+    if (threadIdx.x < TOPK) {
+      s_dest[threadIdx.x] = route_dest[t * TOPK + threadIdx.x];
+      s_w[threadIdx.x] = topk_w ? __bfloat162float(__float2bfloat16_rn(topk_w[t * TOPK + threadIdx.x])) : 1.f;
     }
+    __syncthreads();
   }
-  __nv_bfloat16 o[8];
+  const bool weighted = topk_w != nullptr;
+  for (int v = threadIdx.x; v < vecs; v += kFinThreads) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if constexpr (TOPK > 0) {
+      uint4 r[TOPK];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(acc[j]);
-  *reinterpret_cast<uint4*>(out + t * K + col) = *reinterpret_cast<const uint4*>(o);
+      for (int k = 0; k < TOPK; ++k) {
+        const int d = s_dest[k];
+        r[k] = d >= 0 ? __ldg(fused + (long long)d * vecs + v) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int k = 0; k < TOPK; ++k) {
+        if (s_dest[k] < 0) continue;
+        float x[8];
+        unpack8(r[k], x);
+        if (weighted) {
+          const float w = s_w[k];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], __bfloat162float(__float2bfloat16_rn(__fmul_rn(x[j], w))));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], x[j]);
+        }
+      }
+    } else {
+      for (int k = 0; k < nk; ++k) {
+        const int d = route_dest[t * nk + k];
+        if (d < 0) continue;
+        float x[8];
+        unpack8(__ldg(fused + (long long)d * vecs + v), x);
+        if (weighted) {
+          const float w = __bfloat162float(__float2bfloat16_rn(topk_w[t * nk + k]));
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], __bfloat162float(__float2bfloat16_rn(__fmul_rn(x[j], w))));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], x[j]);
+        }
+      }
+    }
+    __nv_bfloat16 o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(acc[j]);
+    out[t * vecs + v] = *reinterpret_cast<const uint4*>(o);
+  }
 }
 
 // gather_rows: dst[i, :] = idx[i] >= 0 ? src[idx[i], :] : 0, rows of `vecs` 16-byte words; one block
@@ -218,20 +315,32 @@ gather_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ idx, u
 using namespace pnv;
 
 extern "C" int64_t pnv_dispatch_plan_scratch_ints(int64_t n_routes, int num_local_experts) {
-  const int64_t chunks = (n_routes + kChunk - 1) / kChunk;
-  return chunks > 1 ? chunks * num_local_experts : 0;
+  if (n_routes < 0 || num_local_experts < 1) return 0;
+  const int64_t segments = (n_routes + kSeg - 1) / kSeg;
+  return segments > 1 ? segments * num_local_experts : 0;
 }
 
-extern "C" int pnv_dispatch_plan(const void* topk_ids, int ids_are_int64, int64_t tokens, int topk, int first_expert,
-                                 int num_local_experts, int cap, int32_t* counts, int32_t* route_dest,
-                                 int32_t* src_tok, int32_t* src_route, int32_t* scratch, pnv_stream_t stream) {
+namespace {
+// The argument checks both plan entry points share; everything is validated before any size is derived.
+int check_plan_args(const void* topk_ids, int64_t tokens, int topk, int num_local_experts, int cap,
+                    const int32_t* counts, const int32_t* route_dest, const int32_t* src_tok, const int32_t* src_route) {
   PNV_REQUIRE(num_local_experts >= 1 && num_local_experts <= 4096, "num_local_experts must be in [1, 4096], got %d",
               num_local_experts);
   PNV_REQUIRE(cap >= 1, "cap must be positive");
   PNV_REQUIRE((long long)num_local_experts * cap < (1LL << 31), "E * cap must fit int32");
-  PNV_REQUIRE(tokens >= 0 && topk >= 1 && tokens * topk < (1LL << 31), "T * topk must fit int32");
+  PNV_REQUIRE(tokens >= 0 && topk >= 1 && tokens < (1LL << 31) && tokens * topk < (1LL << 31),
+              "T * topk must fit int32");
   PNV_REQUIRE(counts && (tokens == 0 || (topk_ids && route_dest && src_tok && src_route)), "null pointer argument");
-  const long long n = (long long)tokens * topk;
+  return PNV_OK;
+}
+}  // namespace
+
+extern "C" int pnv_dispatch_plan(const void* topk_ids, int ids_are_int64, int64_t tokens, int topk, int first_expert,
+                                 int num_local_experts, int cap, int32_t* counts, int32_t* route_dest,
+                                 int32_t* src_tok, int32_t* src_route, int32_t* scratch, pnv_stream_t stream) {
+  if (int rc = check_plan_args(topk_ids, tokens, topk, num_local_experts, cap, counts, route_dest, src_tok, src_route))
+    return rc;
+  const int n = (int)(tokens * topk);
   cudaStream_t s = (cudaStream_t)stream;
   if (ids_are_int64)
     return run_plan(static_cast<const long long*>(topk_ids), n, topk, first_expert, num_local_experts, cap, counts,
@@ -246,15 +355,23 @@ extern "C" int pnv_dispatch_plan_noalloc(const void* topk_ids, int ids_are_int64
                                          int first_expert, int num_local_experts, int cap, int32_t* counts,
                                          int32_t* route_dest, int32_t* src_tok, int32_t* src_route,
                                          pnv_stream_t stream) {
-  PNV_REQUIRE(tokens >= 0 && topk >= 1 && num_local_experts >= 1, "bad token count, topk or expert count");
+  if (int rc = check_plan_args(topk_ids, tokens, topk, num_local_experts, cap, counts, route_dest, src_tok, src_route))
+    return rc;
   const int64_t need = pnv_dispatch_plan_scratch_ints(tokens * topk, num_local_experts);
   PNV_REQUIRE(need <= kBuiltinScratchInts,
               "dispatch_plan_noalloc: %lld routings over %d local experts need %lld scratch ints, the built-in "
               "scratch holds %d; use pnv_dispatch_plan with a caller-provided buffer",
               (long long)(tokens * topk), num_local_experts, (long long)need, kBuiltinScratchInts);
+  // The array belongs to the current device; a stream of another device would make the kernels run where
+  // this address means nothing.
+  int dev = 0, stream_dev = 0;
+  PNV_CUDA(cudaGetDevice(&dev));
+  if (stream != nullptr && cudaStreamGetDevice((cudaStream_t)stream, &stream_dev) == cudaSuccess)
+    PNV_REQUIRE(stream_dev == dev, "dispatch_plan_noalloc: the stream belongs to device %d, the current device is %d",
+                stream_dev, dev);
   int* scratch = nullptr;
   if (int rc = builtin_scratch(&scratch)) return rc;
-  // Nothing in the scratch has to start at zero: the tally pass writes every total of every chunk
+  // Nothing in the scratch has to start at zero: the sort pass writes every total of every segment
   // this plan uses before the scan reads it, so whatever an earlier call left behind is ignored.
   return pnv_dispatch_plan(topk_ids, ids_are_int64, tokens, topk, first_expert, num_local_experts, cap, counts,
                            route_dest, src_tok, src_route, scratch, stream);
@@ -267,10 +384,21 @@ extern "C" int pnv_moe_finalize(void* out, const void* fused, const int32_t* rou
   if (tokens == 0) return PNV_OK;
   PNV_REQUIRE(out && fused && route_dest, "null pointer argument");
   PNV_REQUIRE(tokens < (1LL << 31), "too many tokens");
-  const int slabs = (k + kFinThreads * 8 - 1) / (kFinThreads * 8);
-  PNV_CUDA(launch_pdl(finalize_kernel, dim3((unsigned)tokens, (unsigned)slabs), dim3(kFinThreads), 0,
-                      (cudaStream_t)stream, pdl_enabled(), (const __nv_bfloat16*)fused, (const int*)route_dest,
-                      topk_weights, (__nv_bfloat16*)out, topk, k));
+  const int vecs = k / 8;
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool pdl = pdl_enabled();
+  const dim3 grid((unsigned)tokens), block(kFinThreads);
+  const uint4* f = (const uint4*)fused;
+  uint4* o = (uint4*)out;
+  const int* rd = (const int*)route_dest;
+  switch (topk) {
+    case 1: PNV_CUDA(launch_pdl(finalize_kernel<1>, grid, block, 0, s, pdl, f, rd, topk_weights, o, topk, vecs)); break;
+    case 2: PNV_CUDA(launch_pdl(finalize_kernel<2>, grid, block, 0, s, pdl, f, rd, topk_weights, o, topk, vecs)); break;
+    case 4: PNV_CUDA(launch_pdl(finalize_kernel<4>, grid, block, 0, s, pdl, f, rd, topk_weights, o, topk, vecs)); break;
+    case 6: PNV_CUDA(launch_pdl(finalize_kernel<6>, grid, block, 0, s, pdl, f, rd, topk_weights, o, topk, vecs)); break;
+    case 8: PNV_CUDA(launch_pdl(finalize_kernel<8>, grid, block, 0, s, pdl, f, rd, topk_weights, o, topk, vecs)); break;
+    default: PNV_CUDA(launch_pdl(finalize_kernel<0>, grid, block, 0, s, pdl, f, rd, topk_weights, o, topk, vecs)); break;
+  }
   return PNV_OK;
 }
 

@@ -21,6 +21,7 @@ SIGNATURES = {
     "pnv_abi_version": (_i, []),
     "pnv_last_error": (ctypes.c_char_p, []),
     "pnv_group_mm_device_status": (_i, [ctypes.POINTER(_i)]),
+    "pnv_selftest_bounded_wait": (_i, [ctypes.POINTER(_i)]),
     "pnv_physical_dims": (_i, [_i, _i] + [ctypes.POINTER(_i)] * 4),
     "pnv_sf_numel": (_i64, [_i, _i, _i]),
     "pnv_compress": (_i, [_p, _p, _i, _i, _i, _p, _p, _p, _p]),

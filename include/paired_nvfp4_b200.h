@@ -47,6 +47,12 @@ const char* pnv_last_error(void);
  * (No counterpart in the reference, whose kernel waits without bound.) */
 int pnv_group_mm_device_status(int* status_out);
 
+/* Testing aid (allocates 4 bytes, synchronises; no counterpart in the reference): runs a one-thread kernel
+ * that waits, with a short budget, on a barrier nothing arrives on, i.e. the give-up path of the bounded
+ * waits without anything in flight.  *gave_up_out becomes 1 when the wait ran out as it should, and the
+ * device status word then reads 99 until pnv_group_mm_device_status clears it. */
+int pnv_selftest_bounded_wait(int* gave_up_out);
+
 /* ---- size queries ------------------------------------------------------------------------- */
 
 /* physical_dims(features, k, groups) (csrc/layout.cuh:83-91): a_comp is

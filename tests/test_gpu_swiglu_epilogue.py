@@ -50,10 +50,12 @@ def test_fused_equals_unfused_bytes(pnk, N, K, E, max_n, counts, act, beta, lbet
     g2 = dev(np.linspace(3.0, 40.0, E).astype(np.float32))
     valid = np.arange(max_n)[None, :] < o["counts"][:, None]
     names = ops.group_mm_swiglu_configs()
-    assert names == ["fused_2sm_256x64_k512", "fused_2sm_256x64", "fused_1sm_128x64", "fused_2sm_256x128"]
+    # the reference's four names and ids, then this build's addition
+    assert names[:4] == ["fused_2sm_256x64_k512", "fused_2sm_256x64", "fused_1sm_128x64", "fused_2sm_256x128"]
+    assert names[4:] == ["fused_1sm_128x128"]
     # unfused chain on the same interleaved weight; the GEMM tile choice does not change a single bit of its
     # accumulation order per output element, but compare like with like anyway
-    base_cfg = {0: 6, 1: 4, 2: 5, 3: 0}
+    base_cfg = {0: 6, 1: 4, 2: 5, 3: 0, 4: 2}
     for cid, cm, cn in pnk.fused_swiglu_tactics():
         out1 = torch.zeros(E, max_n, 2 * N, dtype=torch.bfloat16, device="cuda")
         ops.group_mm(out1, o["a_comp"], o["e_meta"], o["sfa"], o["b_act"], o["sfb"], o["al"], o["cnt"], 2 * N, K,

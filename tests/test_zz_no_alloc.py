@@ -61,3 +61,35 @@ def test_noalloc_plan_rejects_oversized_plans():
     assert rc == 1
     msg = lib.pnv_last_error().decode()
     assert "65536" in msg and "scratch" in msg
+
+
+def test_noalloc_plan_at_the_limit_and_without_allocating():
+    """64 segments x 1024 local experts use the built-in scratch to its last int.  With every buffer made
+    beforehand and one warm-up call done (the first call on a device looks up the scratch address), neither
+    the driver's free-memory figure nor torch's allocator may move across the call."""
+    from paired_nvfp4_kernels import _cabi
+    lib, check = _cabi.lib, _cabi.check
+    T, topk, E, cap = 8192, 8, 1024, 80
+    assert lib.pnv_dispatch_plan_scratch_ints(T * topk, E) == lib.pnv_dispatch_plan_noalloc_max_scratch_ints()
+    rng = np.random.default_rng(5)
+    ids = torch.from_numpy(rng.integers(0, E + 64, (T, topk)).astype(np.int64)).cuda()   # some ids are not local
+    want = _plan(lib, check, False, ids, 0, E, cap)
+    i32 = dict(dtype=torch.int32, device="cuda")
+    outs = [torch.full((E,), -7, **i32), torch.full((T * topk,), -7, **i32), torch.full((E * cap,), -7, **i32),
+            torch.full((E * cap,), -7, **i32)]
+    stream = torch.cuda.current_stream().cuda_stream
+    args = [ids.data_ptr(), 1, T, topk, 0, E, cap] + [o.data_ptr() for o in outs] + [stream]
+    check(lib.pnv_dispatch_plan_noalloc(*args))          # warm-up
+    torch.cuda.synchronize()
+    free0, allocated0, reserved0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    check(lib.pnv_dispatch_plan_noalloc(*args))
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0
+    assert torch.cuda.memory_allocated() == allocated0 and torch.cuda.memory_reserved() == reserved0
+    for name, g, w in zip(("counts", "route_dest", "src_tok", "src_route"), outs, want):
+        g = g.cpu().numpy()
+        if name.startswith("src"):
+            assigned = w != -7
+            assert np.array_equal(g[assigned], w[assigned]), name
+        else:
+            assert np.array_equal(g, w), name
