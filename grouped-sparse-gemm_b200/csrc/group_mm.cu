@@ -120,6 +120,10 @@ struct Params {
   int stages;        // pipeline depth in use (<= Cfg::kStages)
   int b_4d;          // map_b is the 4-D view [E][K/256][max_n][128 B] and one copy fetches a whole stage
   int prod_lanes;    // wide kernel: lanes of each producer warp that issue copies side by side
+  // narrow kernel, split K (nullptr = every tile on one CTA): per-tile arrival counters (all zero before and
+  // after a launch) followed by two partial-accumulator slots per CTA
+  int* split_counters;
+  float* split_partials;
   // fused SwiGLU + requantise epilogue (kFused kernels): GEMM2's operands instead of a bf16 output
   uint8_t* f_b_out;        // [E, max_n, N/2] e2m1 codes, N = M / 2
   uint8_t* f_sfb_out;      // swizzled scales for (max_n, N), pre-filled with 0x38
@@ -152,6 +156,54 @@ struct TileWalk {
     const unsigned local = (unsigned)(t - base);
     nt = (int)(local / (unsigned)n_mt);
     mt = (int)(local - (unsigned)nt * (unsigned)n_mt);
+    return true;
+  }
+};
+
+// Narrow kernel: the work of one CTA as a list of units (tile, K stages [ks0, ks1)).
+//   unsplit   CTA b takes whole tiles b, b + grid, ...
+//   split K   the K stages of all tiles, laid end to end, are cut into `grid` equal ranges; CTA b takes range b, so
+//             a tile whose stages straddle a cut is multiplied by two or more CTAs.  With few tiles per SM (a
+//             decode step with few active experts) that fills every SM and evens out the tail wave.  A partial
+//             unit leaves its fp32 accumulator in a slot of the workspace (a CTA has at most two: the head of its
+//             range finishing an earlier tile, slot 2b, and the tail starting a later one, slot 2b + 1) and bumps
+//             the tile's arrival counter; whichever CTA arrives last adds the tile's slots in K order, so the sum
+//             does not depend on timing, and runs the ordinary epilogue.  Nobody waits for anybody.
+struct UnitWalk {
+  TileWalk tw;
+  bool split;
+  int ksn, grid;
+  long long total;   // split: K stages of all tiles
+  long long pos, hi; // split: this CTA's range; unsplit: pos is the next tile
+  template <int TILE_N>
+  __device__ void init(const int* s_counts, int E, int n_mt, int k_stages, long long n_tiles, bool split_) {
+    tw.init<TILE_N>(s_counts, E, n_mt);
+    split = split_; ksn = k_stages; grid = (int)gridDim.x;
+    if (split) {
+      total = n_tiles * ksn;
+      pos = range_lo(blockIdx.x);
+      hi = range_lo(blockIdx.x + 1);
+    } else {
+      total = 0; pos = blockIdx.x; hi = 0;
+    }
+  }
+  __device__ long long range_lo(long long b) const { return total * b / grid; }
+  // next unit of this CTA; slot = workspace slot of a partial unit
+  template <int TILE_N>
+  __device__ bool next(long long& tile, int& mt, int& nt, int& ks0, int& ks1, int& slot) {
+    if (!split) {
+      if (!tw.seek<TILE_N>(pos, mt, nt)) return false;
+      tile = pos; ks0 = 0; ks1 = ksn; slot = 0;
+      pos += grid;
+      return true;
+    }
+    if (pos >= hi) return false;
+    tile = pos / ksn;
+    ks0 = (int)(pos - tile * ksn);
+    ks1 = (int)min((long long)ksn, ks0 + (hi - pos));
+    slot = 2 * (int)blockIdx.x + (pos == range_lo(blockIdx.x) ? 0 : 1);
+    tw.seek<TILE_N>(tile, mt, nt);     // inside the list by construction
+    pos += ks1 - ks0;
     return true;
   }
 };
@@ -205,9 +257,18 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // every thread counts the tiles of the launch (the split schedule is cut from their total)
+  long long n_tiles = 0;
+  if (p.split_counters != nullptr) {
+    for (int e = lane; e < p.E; e += 32) n_tiles += (long long)p.n_mt * ceil_div_i(s_counts[e], TILE_N);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) n_tiles += __shfl_xor_sync(0xffffffffu, n_tiles, o);
+  }
 
-  TileWalk walk;
-  walk.init<TILE_N>(s_counts, p.E, p.n_mt);
+  UnitWalk walk;
+  walk.init<TILE_N>(s_counts, p.E, p.n_mt, p.k_stages, n_tiles, p.split_counters != nullptr);
+  long long tile;
+  int mt, nt, ks0, ks1, slot;
 
   if (warp == 0) {
     // =============================== tile producer (TMA) ===============================
@@ -215,13 +276,11 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (long long t = blockIdx.x; ok; t += gridDim.x) {
-        int mt, nt;
-        if (!walk.seek<TILE_N>(t, mt, nt)) break;
-        const int e = walk.e;
+      while (ok && walk.next<TILE_N>(tile, mt, nt, ks0, ks1, slot)) {
+        const int e = walk.tw.e;
         const int n0 = nt * TILE_N;
 #pragma unroll 1
-        for (int ks = 0; ks < p.k_stages; ++ks) {
+        for (int ks = ks0; ks < ks1; ++ks) {
           if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1)) {
             atomicExch(&g_status, kProducerEmptyTimeout);
             ok = false;
@@ -258,16 +317,14 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (long long t = blockIdx.x; ok; t += gridDim.x) {
-        int mt, nt;
-        if (!walk.seek<TILE_N>(t, mt, nt)) break;
-        const int e = walk.e;
+      while (ok && walk.next<TILE_N>(tile, mt, nt, ks0, ks1, slot)) {
+        const int e = walk.tw.e;
         const int n0 = nt * TILE_N;
         const uint8_t* e_base = p.e_meta + (((long long)e * p.e_k_atoms) * p.e_m_atoms + mt) * 2048;
         const uint8_t* sfa_base = p.sfa + (((long long)e * p.n_mt + mt) * p.n_kt) * 512;
         const uint8_t* sfb_base = p.sfb + (((long long)e * p.sfb_rt + (n0 >> 7)) * p.n_kt) * 512;
         const int sfb_row_atoms = TILE_N > 128 ? min(2, p.sfb_rt - (n0 >> 7)) : 1;
-        for (int ks = 0; ks < p.k_stages; ++ks) {
+        for (int ks = ks0; ks < ks1; ++ks) {
           if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1)) {
             atomicExch(&g_status, kSideProducerTimeout);
             ok = false;
@@ -312,9 +369,7 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      for (long long t = blockIdx.x; ok; t += gridDim.x) {
-        int mt, nt;
-        if (!walk.seek<TILE_N>(t, mt, nt)) break;
+      while (ok && walk.next<TILE_N>(tile, mt, nt, ks0, ks1, slot)) {
         if (!ptx::mbar_wait(acc_empty + acc, acc_phase ^ 1)) {
           atomicExch(&g_status, kMmaAccTimeout);
           break;
@@ -325,7 +380,7 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // faults (misaligned address) on an odd column offset, which is why 16- and 32-wide tiles
         // exist only for problems with a single token tile (offset 0).
         const uint32_t sfb_col = tmem_base + kColSfb + (TILE_N < 128 ? ((nt * TILE_N) & 127) >> 5 : 0);
-        for (int ks = 0; ks < p.k_stages; ++ks) {
+        for (int ks = ks0; ks < ks1; ++ks) {
           if (!ptx::mbar_wait(full_bar + stage, phase)) {
             atomicExch(&g_status, kMmaFullTimeout);
             ok = false;
@@ -365,7 +420,8 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                   ptx::smem_desc(st + C::kOffB + (ka >> 1) * C::kBBoxBytes + (ka & 1) * 64, 1024, 16, 2);
               // metadata columns: 2 per K-block inside the atom that holds it
               const uint32_t e_tmem = e_cols + (kPer >= 2 ? i * 2 : (ka & 1) * 2);
-              ptx::tc_mma_sp_nvf4(d_tmem, a_desc, b_desc, idesc, (ks | i) != 0 ? 1u : 0u,
+              // the first MMA of a unit overwrites this issuer's partial accumulator
+              ptx::tc_mma_sp_nvf4(d_tmem, a_desc, b_desc, idesc, ((ks - ks0) | i) != 0 ? 1u : 0u,
                                   tmem_base + kColSfa + ka * 4, sfb_col + ka * C::kSfbColsPerAtom, e_tmem);
             }
           }
@@ -418,10 +474,9 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
       }
     }
-    for (long long t = blockIdx.x;; t += gridDim.x) {
-      int mt, nt;
-      if (!walk.seek<TILE_N>(t, mt, nt)) break;
-      const int e = walk.e;
+    int* s_last = reinterpret_cast<int*>(tmem_slot + 1);     // "this CTA arrived last at the tile", told to all epilogue threads
+    while (walk.next<TILE_N>(tile, mt, nt, ks0, ks1, slot)) {
+      const int e = walk.tw.e;
       const int cnt = s_counts[e];
       if (!ptx::mbar_wait(acc_full + acc, acc_phase)) {
         atomicExch(&g_status, kEpilogueTimeout);
@@ -431,8 +486,12 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const float alpha = p.alphas[e];
       const int n0 = nt * TILE_N;
       __nv_bfloat16* out_e = p.out + (long long)e * p.max_n * p.M;
-      // issuers whose K-blocks exist for this K (a short K leaves the later issuers idle)
-      const int live = min(ISSUERS, ceil_div_i(min(C::kAtoms, p.n_kt), C::kAtomsPerIssuer));
+      // Issuers whose partial accumulators hold something for this unit.  Every issuer has K-blocks in a full
+      // stage; in the (shorter) last stage of a tile the later issuers may have none, and a unit that is just
+      // that stage never touched their accumulators.
+      const int tail_atoms = p.n_kt - (p.k_stages - 1) * C::kAtoms;
+      const int live = ks0 == p.k_stages - 1 ? min(ISSUERS, ceil_div_i(tail_atoms, C::kAtomsPerIssuer)) : ISSUERS;
+      const bool partial = ks0 > 0 || ks1 < p.k_stages;
 #pragma unroll 1
       for (int c0 = 0; c0 < TILE_N; c0 += 32) {
         if (n0 + c0 >= cnt) break;             // uniform over the four epilogue warps
@@ -448,6 +507,43 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             ptx::tc_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__fadd_rn(__uint_as_float(r[i]), __uint_as_float(q[i])));
+          }
+        }
+        if (partial) {
+          // leave this unit's accumulator in its slot ([token column][128 rows] fp32) and count the arrival
+          constexpr int kCols = TILE_N < 32 ? TILE_N : 32;
+          constexpr int kSlotFloats = kTileM * kCols;
+          float* mine = p.split_partials + (long long)slot * kSlotFloats + m_local;
+#pragma unroll
+          for (int i = 0; i < kCols; ++i) __stcg(mine + i * kTileM, __uint_as_float(r[i]));
+          __threadfence();
+          epilogue_bar_sync();
+          // the CTAs that share this tile, first to last in K: cut points are range_lo(c), c = 0 .. grid
+          const long long t_lo = tile * p.k_stages, t_hi = t_lo + p.k_stages;
+          long long c = t_lo * walk.grid / walk.total;
+          while (c > 0 && walk.range_lo(c) > t_lo) --c;
+          while (walk.range_lo(c + 1) <= t_lo) ++c;
+          int parts = 0;
+          for (long long d = c; d < walk.grid && walk.range_lo(d) < t_hi; ++d)
+            if (walk.range_lo(d + 1) > walk.range_lo(d)) ++parts;
+          if (ep_tid == 0) {
+            const int before = atomicAdd(p.split_counters + tile, 1);
+            *s_last = before == parts - 1 ? 1 : 0;
+            if (before == parts - 1) p.split_counters[tile] = 0;     // left zero for the next launch
+          }
+          epilogue_bar_sync();
+          if (*s_last == 0) break;       // another CTA finishes this tile
+          __threadfence();
+#pragma unroll
+          for (int i = 0; i < kCols; ++i) r[i] = 0u;
+          for (long long d = c; d < walk.grid && walk.range_lo(d) < t_hi; ++d) {
+            const long long lo_d = walk.range_lo(d);
+            if (walk.range_lo(d + 1) <= lo_d) continue;
+            const int sl = 2 * (int)d + (max(lo_d, t_lo) == lo_d ? 0 : 1);
+            const float* part = p.split_partials + (long long)sl * kSlotFloats + m_local;
+#pragma unroll
+            for (int i = 0; i < kCols; ++i)
+              r[i] = __float_as_uint(__fadd_rn(__uint_as_float(r[i]), __ldcg(part + i * kTileM)));
           }
         }
         if (kFused) {
@@ -706,8 +802,10 @@ int launch_narrow_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const
   static KernelSetup setup;
   if (int rc = prepare_kernel(group_mm_kernel<TILE_N, STAGE_K, ISSUERS, kFused>, setup, C::kThreads, smem, false, nullptr))
     return rc;
-  long long max_tiles = (long long)p.E * p.n_mt * ceil_div_i(p.max_n, TILE_N);
-  int grid = (int)(max_tiles < sm_count ? max_tiles : sm_count);
+  static_assert(TILE_N <= 32, "the split-K epilogue handles one chunk of token columns per tile");
+  long long max_units = (long long)p.E * p.n_mt * ceil_div_i(p.max_n, TILE_N);
+  if (p.split_counters != nullptr) max_units *= p.k_stages;      // a CTA may get as little as one K stage
+  int grid = (int)(max_units < sm_count ? max_units : sm_count);
   if (grid < 1) grid = 1;
   PNV_CUDA(launch_pdl(group_mm_kernel<TILE_N, STAGE_K, ISSUERS, kFused>, dim3(grid), dim3(C::kThreads), smem,
                       stream, pdl, map_a, map_b, p));
@@ -726,7 +824,8 @@ int launch_narrow(const CUtensorMap& map_a, const CUtensorMap& map_b, Params& p,
 template <class C>
 int wide_stages(int experts) {
   const int fixed = 1024 + C::kOutBytes + C::kBarrierBytes + 4 * experts;
-  return std::min(std::min((int)C::kMaxStages, (int)C::kSfSlots), (kSmemLimit - fixed) / C::kStageBytes);
+  const int n = std::min(std::min((int)C::kMaxStages, (int)C::kSlots), (kSmemLimit - fixed) / C::kStageBytes);
+  return n & ~1;     // even: the two copier threads own alternate ring slots
 }
 
 template <int TILE_N, int STAGE_K, bool kFused, bool kPair>
@@ -805,6 +904,19 @@ constexpr int kNumKinds = sizeof(kKinds) / sizeof(kKinds[0]);
 
 using namespace pnv;
 
+// Split-K workspace of the narrow kernel: one arrival counter per (expert, M tile), padded to 256 bytes, then two
+// partial-accumulator slots of 128 x tile_n floats per CTA.
+static long long split_counter_bytes(int experts, int features) {
+  return ((long long)experts * ceil_div_i(features, kTileM) * 4 + 255) / 256 * 256;
+}
+static int narrow_tile_n(int max_n) { return max_n <= 16 ? 16 : 32; }
+
+extern "C" int64_t pnv_group_mm_workspace_bytes(int experts, int features, int max_n, int sm_count) {
+  if (experts < 1 || features < 1 || max_n < 1 || max_n > 32) return 0;   // wide tiles are never split
+  if (sm_count <= 0) sm_count = 148;
+  return split_counter_bytes(experts, features) + 2LL * sm_count * kTileM * narrow_tile_n(max_n) * 4;
+}
+
 extern "C" int pnv_group_mm_num_configs(void) { return kNumKinds; }
 
 extern "C" const char* pnv_group_mm_config_name(int config_id) {
@@ -858,8 +970,8 @@ constexpr int kNumFusedKinds = sizeof(kFusedKinds) / sizeof(kFusedKinds[0]);
 int group_mm_common(void* out, const FusedArgs* fused, const uint8_t* a_comp, const uint8_t* e_meta,
                     const uint8_t* sfa, const uint8_t* b_act, const uint8_t* sfb, const float* alphas,
                     const int32_t* counts, int experts, int features, int k, int max_n, int config_id,
-                    int cluster_m, int cluster_n, int sm_count, int pdl, pnv_stream_t stream,
-                    const char* display_name) {
+                    int cluster_m, int cluster_n, int sm_count, int pdl, void* workspace, int64_t workspace_bytes,
+                    pnv_stream_t stream, const char* display_name) {
   PNV_REQUIRE(out && a_comp && e_meta && sfa && b_act && sfb && alphas && counts, "null pointer argument");
   PNV_REQUIRE(experts >= 1 && features >= 1 && max_n >= 1, "experts, features and max_n must be positive");
   PNV_REQUIRE(experts <= kMaxExperts, "group_mm supports at most %d experts per call, got %d", kMaxExperts,
@@ -903,6 +1015,8 @@ int group_mm_common(void* out, const FusedArgs* fused, const uint8_t* a_comp, co
   p.sfb_rt = sf_row_atoms(max_n);
   p.stages = 0;
   p.prod_lanes = 1;
+  p.split_counters = nullptr;
+  p.split_partials = nullptr;
 
   // Tile geometry.  The variant names fix the widest token tile; when every expert's tokens fit one
   // narrow tile (max_n <= 32) the kernel runs 16- or 32-wide MMAs over 512-K stages with four issuer
@@ -915,6 +1029,14 @@ int group_mm_common(void* out, const FusedArgs* fused, const uint8_t* a_comp, co
   }
   const bool pair = kind.two_sm && !narrow;
   p.k_stages = ceil_div_i(k, stage_k);
+  if (narrow && workspace != nullptr && p.k_stages > 1) {
+    const int64_t need = pnv_group_mm_workspace_bytes(experts, features, max_n, sm_count);
+    PNV_REQUIRE(workspace_bytes >= need, "group_mm: the split-K workspace holds %lld bytes, %lld are needed",
+                (long long)workspace_bytes, (long long)need);
+    PNV_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 256 == 0, "group_mm: the workspace must be 256-byte aligned");
+    p.split_counters = reinterpret_cast<int*>(workspace);
+    p.split_partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + split_counter_bytes(experts, features));
+  }
 
   CUtensorMap map_a, map_b;
   if (int rc = make_map(&map_a, a_comp, (uint64_t)wd.k_ac / 2, (uint64_t)wd.m_ac, (uint64_t)experts,
@@ -973,9 +1095,10 @@ extern "C" int pnv_group_mm(void* out, const uint8_t* a_comp, const uint8_t* e_m
                             const uint8_t* b_act, const uint8_t* sfb, const float* alphas,
                             const int32_t* counts, int experts, int features, int k, int max_n,
                             int config_id, int cluster_m, int cluster_n, int sm_count, int pdl,
-                            pnv_stream_t stream) {
+                            void* workspace, int64_t workspace_bytes, pnv_stream_t stream) {
   return group_mm_common(out, nullptr, a_comp, e_meta, sfa, b_act, sfb, alphas, counts, experts, features, k,
-                         max_n, config_id, cluster_m, cluster_n, sm_count, pdl, stream, nullptr);
+                         max_n, config_id, cluster_m, cluster_n, sm_count, pdl, workspace, workspace_bytes, stream,
+                         nullptr);
 }
 
 extern "C" int pnv_group_mm_swiglu_num_configs(void) { return kNumFusedKinds; }
@@ -990,7 +1113,8 @@ extern "C" int pnv_group_mm_swiglu_quant(uint8_t* b_out, uint8_t* sfb_out, const
                                          const float* gscale, int gscale_per_expert, int experts,
                                          int features, int k, int max_n, int config_id, int cluster_m,
                                          int cluster_n, int act_kind, float beta, float linear_beta,
-                                         int sm_count, int pdl, pnv_stream_t stream) {
+                                         int sm_count, int pdl, void* workspace, int64_t workspace_bytes,
+                                         pnv_stream_t stream) {
   PNV_REQUIRE(b_out && sfb_out && gscale, "null pointer argument");
   PNV_REQUIRE(features % 128 == 0,
               "features (2N) must be a multiple of 128 (whole 64-row gate/up blocks per CTA), got %d", features);
@@ -1005,5 +1129,5 @@ extern "C" int pnv_group_mm_swiglu_quant(uint8_t* b_out, uint8_t* sfb_out, const
   PNV_REQUIRE(sf_numel(max_n, features / 2, experts) < (1LL << 31), "sfb_out must be smaller than 2 GiB");
   const FusedKind& fk = kFusedKinds[config_id];
   return group_mm_common(b_out, &f, a_comp, e_meta, sfa, b_act, sfb, alphas, counts, experts, features, k, max_n,
-                         fk.base_config, cluster_m, cluster_n, sm_count, pdl, stream, fk.name);
+                         fk.base_config, cluster_m, cluster_n, sm_count, pdl, workspace, workspace_bytes, stream, fk.name);
 }

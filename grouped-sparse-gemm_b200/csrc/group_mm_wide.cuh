@@ -12,23 +12,25 @@
 //                               halves.  Against the single-CTA form that halves the activation bytes an SM
 //                               has to pull from L2 per unit of math, which is what bounds these shapes.
 //
-// 24 warps per CTA:
+// 22 warps per CTA:
 //   warp 0   tile producer: TMA copies of the compressed weights and of the activations
 //   warp 1   side producer: bulk copies of the metadata, SFA and SFB atoms (they sit in global memory in
 //            the shape tensor memory wants)
 //   2 - 3    MMA issuers (of a pair: in the first CTA only), alternate tiles, each into its own accumulator
-//            stage: per pipeline stage the metadata tcgen05.cp and the MMAs, nothing else
-//   4 - 7    scale loaders, one per tensor-memory lane quarter: shared memory -> registers -> tcgen05.st into a
-//            ring of scale slots (one slot per pipeline stage): the image tcgen05.cp.32x128b.warpx4 would leave
-//   8 - 23   epilogue, four groups of four warps (one warp per lane quarter); a tile's chunks of token
+//            stage: per pipeline stage they wait for one barrier, issue the MMAs and commit
+//   4 - 5    copiers (one thread each, alternate pipeline stages; of a pair: in the first CTA only): tcgen05.cp of
+//            the stage's scale and metadata atoms from shared memory into the stage's slot of a ring in tensor
+//            memory, then a tcgen05.commit that tells the issuers the slot is filled.  The copies are
+//            asynchronous, so a copier spends a few dozen cycles per atom and the issuers none.  In the second
+//            CTA of a pair warp 4 only relays "my copies have landed" to the first CTA.
+//   6 - 21   epilogue, four groups of four warps (one warp per lane quarter); a tile's chunks of token
 //            columns are dealt round-robin to the groups
 //
-// Barriers per pipeline stage s: full[s] (this CTA's copies landed; its scale loaders wait on it),
-// sf_full[s] (scale loaders -> issuer: the scales are in tensor memory, which also says that the
-// stage's copies have landed, since the loaders saw full[s] first; of a pair, the second CTA's loaders
-// arrive on the first CTA's barrier), empty[s] (issuer's tcgen05.commit, delivered to both CTAs of a
-// pair, plus the CTA's four loaders -> producers).  Per accumulator stage: acc_full (commit, both CTAs),
-// acc_empty (all epilogue warps of the CTA or pair -> issuers).  Every wait is bounded.
+// Barriers per pipeline stage s: full[s] (this CTA's copies landed), peer_full[s] (pair: the second CTA's
+// copies landed, relayed to the first), sf_full[s] (copier's commit -> issuers: scales and metadata are in tensor
+// memory), empty[s] (issuer's tcgen05.commit, delivered to both CTAs of a pair -> producers).  Per accumulator
+// stage: acc_full (commit, both CTAs), acc_empty (all epilogue warps of the CTA or pair -> issuers).  Every
+// wait is bounded.
 
 template <int TILE_N, int STAGE_K, bool kPair>
 struct WideCfg {
@@ -36,7 +38,8 @@ struct WideCfg {
   static_assert(STAGE_K == 256 || STAGE_K == 512, "stage depths: 256, 512");
   static constexpr int kCtas = kPair ? 2 : 1;
   static constexpr int kEpilogueWarps = 16;
-  static constexpr int kThreads = (8 + kEpilogueWarps) * 32;
+  static constexpr int kFirstEpilogueWarp = 6;
+  static constexpr int kThreads = (kFirstEpilogueWarp + kEpilogueWarps) * 32;
   static constexpr int kAtoms = STAGE_K / 128;
   static constexpr int kARowBytes = STAGE_K / 4;
   static constexpr int kABytes = kTileM * kARowBytes;
@@ -56,20 +59,22 @@ struct WideCfg {
   static constexpr int kBarrierBytes = 1024;
   static constexpr int kMaxStages = 12;
   static constexpr int kAccStages = TILE_N == 256 ? 1 : 2;
-  static constexpr int kColE = 256;                          // tensor-memory columns: accumulators below 256
-  static constexpr int kColSf = 272;                         // ring of scale slots
+  // tensor-memory columns: accumulators below 256, then a ring of slots, one per pipeline stage, each holding
+  // the stage's weight scales, activation scales and metadata
+  static constexpr int kColSlots = 256;
   static constexpr int kSfbColsPerAtom = 4 * kSfbRowAtoms;
-  static constexpr int kSfSlotCols = kAtoms * (4 + kSfbColsPerAtom);
-  static constexpr int kSfSlots = (kTmemCols - kColSf) / kSfSlotCols;   // one per stage: caps the pipeline depth
+  static constexpr int kSlotSfb = 4 * kAtoms;                // column offsets inside a slot
+  static constexpr int kSlotE = kSlotSfb + kSfbColsPerAtom * kAtoms;
+  static constexpr int kSlotCols = kSlotE + 4 * kEAtoms;
+  static constexpr int kSlots = (kTmemCols - kColSlots) / kSlotCols;    // caps the pipeline depth
   static constexpr int kOffA = 0;
   static constexpr int kOffB = kABytes;
   static constexpr int kOffE = kOffB + kBBytes;
   static constexpr int kOffSfa = kOffE + kEBytes;
   static constexpr int kOffSfb = kOffSfa + kSfaBytes;
   static_assert(kStageBytes % 1024 == 0 && kOffB % 1024 == 0, "operand tiles must keep 1024-byte alignment");
-  static_assert(kAccStages * TILE_N <= kColE && kColE + 2 * 4 * kEAtoms <= kColSf && kSfSlots >= 2,
-                "tensor-memory column map overflows");
-  static_assert(8 * (3 * kMaxStages + 2 * kAccStages) + 16 <= kBarrierBytes, "barrier block overflows");
+  static_assert(kAccStages * TILE_N <= kColSlots && kSlots >= 2, "tensor-memory column map overflows");
+  static_assert(8 * (4 * kMaxStages + 2 * kAccStages) + 16 <= kBarrierBytes, "barrier block overflows");
 };
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
@@ -103,7 +108,7 @@ template <>
 __device__ __forceinline__ void tc_ld_cols<16>(uint32_t taddr, uint32_t (&r)[16]) { ptx::tc_ld_32x16(taddr, r); }
 
 template <int TILE_N, int STAGE_K, bool kFused, bool kPair>
-__global__ void __launch_bounds__(768, 1)
+__global__ void __launch_bounds__((6 + 16) * 32, 1)
 group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const Params p) {
   using C = WideCfg<TILE_N, STAGE_K, kPair>;
@@ -117,7 +122,8 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(after_stages + C::kOutBytes);
   uint64_t* empty_bar = full_bar + C::kMaxStages;
   uint64_t* sf_full = empty_bar + C::kMaxStages;
-  uint64_t* acc_full = sf_full + C::kMaxStages;
+  uint64_t* peer_full = sf_full + C::kMaxStages;
+  uint64_t* acc_full = peer_full + C::kMaxStages;
   uint64_t* acc_empty = acc_full + C::kAccStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + C::kAccStages);
   int* s_counts = reinterpret_cast<int*>(after_stages + C::kOutBytes + C::kBarrierBytes);
@@ -135,8 +141,9 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     ptx::prefetch_tensormap(&map_b);
     for (int s = 0; s < p.stages; ++s) {
       ptx::mbar_init(full_bar + s, 3);
-      ptx::mbar_init(empty_bar + s, 1 + 4);
-      ptx::mbar_init(sf_full + s, 4 * kCtas);
+      ptx::mbar_init(empty_bar + s, 1);
+      ptx::mbar_init(sf_full + s, 1);
+      ptx::mbar_init(peer_full + s, 1);
     }
     for (int a = 0; a < C::kAccStages; ++a) {
       ptx::mbar_init(acc_full + a, 1);
@@ -249,8 +256,8 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     // A tcgen05.mma holds its issuing thread for about as long as it executes, so whatever else that
     // thread does between two MMAs is time the tensor pipe idles.  Two issuers in two warps take alternate
     // tiles, each into its own accumulator stage; while one is between MMAs the other's are executing.
-    // Every tile's MMAs still come from one thread, in K order.  The issuer does no tile arithmetic: it
-    // counts its tiles once and then only waits, issues and commits.
+    // Every tile's MMAs still come from one thread, in K order.  The issuer does no tile arithmetic and no
+    // copies: it counts its tiles once and then only waits, issues and commits.
     constexpr int kIssuers = C::kAccStages == 2 ? 2 : 1;
     const int issuer = warp - 2;
     const int n_items = my_work_items<TILE_N>(s_counts, p.E, n_mu, unit, n_units, lane);
@@ -265,7 +272,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       auto skip_stages = [&](int n) {
 #pragma unroll 1
         for (int i = 0; i < n && ok; ++i) {
-          if (!ptx::mbar_wait_cluster(sf_full + stage, phase)) {
+          if (!ptx::mbar_wait(sf_full + stage, phase)) {
             atomicExch(&g_status, kMmaScaleTimeout);
             ok = false;
           }
@@ -277,12 +284,9 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       // stage-0 descriptors, split into the 32-bit halves: only the low half changes with the address
       const uint64_t d_a0 = ptx::smem_desc(ptx::smem_u32(stage_base) + C::kOffA, 8 * C::kARowBytes, 16, C::kASwizzle);
       const uint64_t d_b0 = ptx::smem_desc(ptx::smem_u32(stage_base) + C::kOffB, 1024, 16, 2);
-      const uint64_t d_e0 = ptx::smem_desc(ptx::smem_u32(stage_base) + C::kOffE, 128, 0, 0);
       const uint32_t lo_a0 = (uint32_t)d_a0, hi_a = (uint32_t)(d_a0 >> 32);
       const uint32_t lo_b0 = (uint32_t)d_b0, hi_b = (uint32_t)(d_b0 >> 32);
-      const uint32_t lo_e0 = (uint32_t)d_e0, hi_e = (uint32_t)(d_e0 >> 32);
-      const uint32_t e_cols = tmem_base + C::kColE + issuer * (4 * C::kEAtoms);   // private metadata columns
-      const uint32_t sf_cols0 = tmem_base + C::kColSf;
+      const uint32_t slots0 = tmem_base + C::kColSlots;
       const int last_atoms = p.n_kt - (p.k_stages - 1) * C::kAtoms;     // K-blocks of a tile's last stage
       for (int item = kIssuers == 2 ? issuer : 0; item < n_items && ok; item += kIssuers) {
         // a 64-wide tile's scales sit 0 or 2 columns into the 128-row atom (even offsets only: the MMA
@@ -293,7 +297,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           if (!walk.seek<TILE_N>(unit + (long long)item * n_units, mu, nt)) break;
           sfb_off = ((nt * TILE_N) & 127) >> 5;
         }
-        if (!ptx::mbar_wait_cluster(acc_empty + acc, acc_phase ^ 1)) {
+        if (!ptx::mbar_wait(acc_empty + acc, acc_phase ^ 1)) {
           atomicExch(&g_status, kMmaAccTimeout);
           ok = false;
           break;
@@ -303,7 +307,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 #pragma unroll 1
         for (int ks = 0; ks < p.k_stages; ++ks) {
           const int k_atoms = ks + 1 == p.k_stages ? last_atoms : C::kAtoms;
-          if (!ptx::mbar_wait_cluster(sf_full + stage, phase)) {
+          if (!ptx::mbar_wait(sf_full + stage, phase)) {
             atomicExch(&g_status, kMmaScaleTimeout);
             ok = false;
             break;
@@ -311,32 +315,17 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           ptx::tc_fence_after();
           // descriptors of this stage: the precomputed ones of stage 0 plus the stage's offset in
           // 16-byte units (the address field is the low 14 bits, so a 32-bit add cannot carry out)
-          const uint32_t la = lo_a0 + soff, le = lo_e0 + soff, lb = lo_b0 + soff;
-          const uint32_t sf_cols = sf_cols0 + stage * C::kSfSlotCols;
-          const uint32_t sfb_cols = sf_cols + C::kAtoms * 4 + sfb_off;
-          if (k_atoms == C::kAtoms) {
+          const uint32_t la = lo_a0 + soff, lb = lo_b0 + soff;
+          const uint32_t slot = slots0 + stage * C::kSlotCols;
+          const uint32_t sfb_cols = slot + C::kSlotSfb + sfb_off;
 #pragma unroll
-            for (int ea = 0; ea < C::kEAtoms; ++ea)
-              ptx::tc_cp_128x128b<kCtas>(e_cols + ea * 4, pack_desc(le + ea * 128, hi_e));
-#pragma unroll
-            for (int ka = 0; ka < C::kAtoms; ++ka)
+          for (int ka = 0; ka < C::kAtoms; ++ka)
+            if (ka < k_atoms)
               ptx::tc_mma_sp_nvf4<kCtas>(d_tmem, pack_desc(la + ka * 2, hi_a),
                                          pack_desc(lb + (ka >> 1) * (C::kBBoxBytes >> 4) + (ka & 1) * 4, hi_b), idesc,
-                                         (ks | ka) != 0 ? 1u : 0u, sf_cols + ka * 4,
-                                         sfb_cols + ka * C::kSfbColsPerAtom, e_cols + ka * 2);
-          } else {
-#pragma unroll
-            for (int ea = 0; ea < C::kEAtoms; ++ea)
-              if (2 * ea < k_atoms) ptx::tc_cp_128x128b<kCtas>(e_cols + ea * 4, pack_desc(le + ea * 128, hi_e));
-#pragma unroll
-            for (int ka = 0; ka < C::kAtoms; ++ka)
-              if (ka < k_atoms)
-                ptx::tc_mma_sp_nvf4<kCtas>(d_tmem, pack_desc(la + ka * 2, hi_a),
-                                           pack_desc(lb + (ka >> 1) * (C::kBBoxBytes >> 4) + (ka & 1) * 4, hi_b), idesc,
-                                           (ks | ka) != 0 ? 1u : 0u, sf_cols + ka * 4,
-                                           sfb_cols + ka * C::kSfbColsPerAtom, e_cols + ka * 2);
-          }
-          // stage and scale slot reusable (in both CTAs of a pair) once these MMAs and copies retire
+                                         (ks | ka) != 0 ? 1u : 0u, slot + ka * 4, sfb_cols + ka * C::kSfbColsPerAtom,
+                                         slot + C::kSlotE + ka * 2);
+          // shared-memory stage and tensor-memory slot reusable (in both CTAs of a pair) once these MMAs retire
           ptx::tc_commit_n<kCtas>(empty_bar + stage);
           soff += C::kStageBytes >> 4;
           if (++stage == p.stages) { stage = 0; soff = 0; phase ^= 1; }
@@ -353,42 +342,70 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       }
     }
     __syncwarp();
-  } else if (warp < 8) {
-    // =============================== scale loaders ===============================
+  } else if (warp == 4 || warp == 5) {
+    // =============================== copiers ===============================
+    // Copier c takes the pipeline stages c, c + 2, ... of this CTA's (or pair's) sequence; the host keeps the ring
+    // depth even, so each ring slot always belongs to the same copier and no barrier phase goes unobserved.
+    const int copier = warp - 4;
     const int n_items = my_work_items<TILE_N>(s_counts, p.E, n_mu, unit, n_units, lane);
     const long long n_stages = (long long)n_items * p.k_stages;
-    const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + C::kColSf;
-    int stage = 0;
-    uint32_t phase = 0;
+    if (lane == 0 && rank == 0) {
+      const uint64_t d_sfa0 = ptx::smem_desc(ptx::smem_u32(stage_base) + C::kOffSfa, 128, 0, 0);
+      const uint64_t d_sfb0 = ptx::smem_desc(ptx::smem_u32(stage_base) + C::kOffSfb, 128, 0, 0);
+      const uint64_t d_e0 = ptx::smem_desc(ptx::smem_u32(stage_base) + C::kOffE, 128, 0, 0);
+      const uint32_t lo_sfa0 = (uint32_t)d_sfa0, lo_sfb0 = (uint32_t)d_sfb0, lo_e0 = (uint32_t)d_e0;
+      const uint32_t hi = (uint32_t)(d_e0 >> 32);           // the three descriptors differ in the address only
+      const uint32_t slots0 = tmem_base + C::kColSlots;
+      const int last_atoms = p.n_kt - (p.k_stages - 1) * C::kAtoms;
+      int stage = copier, ks = copier % p.k_stages;
+      uint32_t phase = 0;
 #pragma unroll 1
-    for (long long g = 0; g < n_stages; ++g) {
-      if (!ptx::mbar_wait(full_bar + stage, phase)) {
-        atomicExch(&g_status, kScaleLoaderTimeout);
-        break;
-      }
-      const uint8_t* st = stage_base + stage * C::kStageBytes + lane * 16;
-      const uint32_t cols = lane_base + stage * C::kSfSlotCols;
+      for (long long g = copier; g < n_stages; g += 2) {
+        if (!ptx::mbar_wait(full_bar + stage, phase) || (kPair && !ptx::mbar_wait(peer_full + stage, phase))) {
+          atomicExch(&g_status, kScaleLoaderTimeout);
+          break;
+        }
+        ptx::tc_fence_after();
+        const int k_atoms = ks + 1 == p.k_stages ? last_atoms : C::kAtoms;
+        const uint32_t soff = (uint32_t)stage * (C::kStageBytes >> 4);
+        const uint32_t slot = slots0 + stage * C::kSlotCols;
 #pragma unroll
-      for (int ka = 0; ka < C::kAtoms; ++ka) {
-        ptx::tc_st_32x32_x4(cols + ka * 4, *reinterpret_cast<const uint4*>(st + C::kOffSfa + ka * 512));
+        for (int ka = 0; ka < C::kAtoms; ++ka) {
+          if (ka < k_atoms) {
+            ptx::tc_cp_32x128b_warpx4<kCtas>(slot + ka * 4, pack_desc(lo_sfa0 + soff + ka * 32, hi));
 #pragma unroll
-        for (int ra = 0; ra < C::kSfbRowAtoms; ++ra)
-          ptx::tc_st_32x32_x4(cols + C::kAtoms * 4 + ka * C::kSfbColsPerAtom + ra * 4,
-                              *reinterpret_cast<const uint4*>(st + C::kOffSfb + ra * C::kSfaBytes + ka * 512));
+            for (int ra = 0; ra < C::kSfbRowAtoms; ++ra)
+              ptx::tc_cp_32x128b_warpx4<kCtas>(slot + C::kSlotSfb + ka * C::kSfbColsPerAtom + ra * 4,
+                                               pack_desc(lo_sfb0 + soff + ra * (C::kSfaBytes >> 4) + ka * 32, hi));
+          }
+        }
+#pragma unroll
+        for (int ea = 0; ea < C::kEAtoms; ++ea)
+          if (2 * ea < k_atoms) ptx::tc_cp_128x128b<kCtas>(slot + C::kSlotE + ea * 4, pack_desc(lo_e0 + soff + ea * 128, hi));
+        ptx::tc_commit_local<kCtas>(sf_full + stage);     // arrives once the copies above have completed
+        ks += 2;
+        while (ks >= p.k_stages) ks -= p.k_stages;
+        stage += 2;
+        if (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
       }
-      ptx::tc_st_wait();
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if (kPair && rank != 0) ptx::mbar_arrive_cluster(sf_full + stage, 0);   // the issuers live in the first CTA
-        else ptx::mbar_arrive(sf_full + stage);
-        ptx::mbar_arrive(empty_bar + stage);   // the scales have left shared memory
+    } else if (kPair && lane == 0 && rank != 0 && copier == 0) {
+      // second CTA of a pair: tell the first when each stage's copies have landed here
+      int stage = 0;
+      uint32_t phase = 0;
+#pragma unroll 1
+      for (long long g = 0; g < n_stages; ++g) {
+        if (!ptx::mbar_wait(full_bar + stage, phase)) {
+          atomicExch(&g_status, kScaleLoaderTimeout);
+          break;
+        }
+        ptx::mbar_arrive_cluster(peer_full + stage, 0);
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
       }
-      if (++stage == p.stages) { stage = 0; phase ^= 1; }
     }
+    __syncwarp();
   } else {
     // =============================== epilogue ===============================
-    const int group = (warp - 8) >> 2;         // chunks of kChunk token columns are dealt to the four groups in turn
+    const int group = (warp - C::kFirstEpilogueWarp) >> 2;   // chunks of kChunk token columns are dealt to the four groups in turn
     const int sub = warp & 3;                  // tensor-memory lane quarter this warp may read
     const int m_local = sub * 32 + lane;       // accumulator row (output feature) held by this thread
     const bool vec_ok = (p.M % 8) == 0;        // 16-byte aligned output rows: needed by the bulk stores
@@ -404,7 +421,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       const uint32_t w4 = kBenignSf * 0x01010101u;
       constexpr unsigned kFillThreads = C::kEpilogueWarps * 32;
 #pragma unroll 1
-      for (unsigned c = blockIdx.x * kFillThreads + (threadIdx.x - 256); c < lines; c += gridDim.x * kFillThreads) {
+      for (unsigned c = blockIdx.x * kFillThreads + (threadIdx.x - C::kFirstEpilogueWarp * 32); c < lines; c += gridDim.x * kFillThreads) {
         const int rr = (int)(c & 31);
         unsigned a = c >> 5;
         const unsigned a_kt = a / (unsigned)p.f_n_kt;

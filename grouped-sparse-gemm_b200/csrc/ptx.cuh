@@ -101,34 +101,10 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t cta)
   asm volatile(
       "{\n\t.reg .b32 ra;\n\t"
       "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
-      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
+      "mbarrier.arrive.shared::cluster.b64 _, [ra];\n\t}"
       :
       : "r"(smem_u32(bar)), "r"(cta)
       : "memory");
-}
-// Wait whose acquire reaches the whole cluster: for barriers another CTA of the pair arrives on.
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-static __device__ __noinline__ bool mbar_wait_cluster_slow(uint64_t* bar, uint32_t parity) {
-#pragma unroll 1
-  for (uint32_t i = 0; i < kMaxPolls; ++i) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    if (i > 64) __nanosleep(128);
-  }
-  return false;
-}
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
-  if (mbar_try_wait_cluster(bar, parity)) return true;
-  return mbar_wait_cluster_slow(bar, parity);
 }
 
 // ---- TMA -----------------------------------------------------------------------------------------
@@ -243,6 +219,15 @@ template <int CTAS>
 __device__ __forceinline__ void tc_commit_n(uint64_t* bar) {
   if (CTAS == 2) tc_commit_pair(bar); else tc_commit(bar);
 }
+// Operations issued on a CTA pair, arrival on the issuing CTA's barrier only.
+template <int CTAS>
+__device__ __forceinline__ void tc_commit_local(uint64_t* bar) {
+  if (CTAS == 2)
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+  else
+    tc_commit(bar);
+}
 
 // Shared-memory matrix descriptor.  K-major operand: rows of (swizzle width) bytes, groups of 8
 // rows `sbo` bytes apart.  layout: 0 none, 2 128-byte, 4 64-byte, 6 32-byte swizzle.
@@ -268,8 +253,12 @@ __device__ __forceinline__ void tc_cp_128x128b(uint32_t taddr, uint64_t sdesc) {
     asm volatile("tcgen05.cp.cta_group::1.128x128b [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
 // 32 lines x 16 bytes, replicated into all four 32-lane quarters.
+template <int CTAS = 1>
 __device__ __forceinline__ void tc_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+  if (CTAS == 2)
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+  else
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
 
 // D[tmem] (+)= A_sparse[smem] * B[smem]^T with per-32-K UE4M3 scales; e2m1 operands.

@@ -45,8 +45,10 @@ struct PlanArgs {
   const int* src_tok;
   const int* src_route;
   const float* topk_w;
-  const uint8_t* q;
-  const uint8_t* q_sf;
+  const uint8_t* q;        // kFp4: codes of source row t at q + t * q_pitch
+  const uint8_t* q_sf;     //       its scales at q_sf + t * sf_pitch
+  long long q_pitch;
+  long long sf_pitch;
 };
 
 template <int kSrc>
@@ -96,8 +98,8 @@ quant_lines_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
         const long long slot = (long long)e * max_n + r;
         const long long t = plan.src_tok[slot];
         *reinterpret_cast<uint2*>(b_act + slot * (K / 2) + k0 / 2) =
-            __ldg(reinterpret_cast<const uint2*>(plan.q + t * (K / 2) + k0 / 2));
-        sf_copy = __ldg(plan.q_sf + t * KB + kb);
+            __ldg(reinterpret_cast<const uint2*>(plan.q + t * plan.q_pitch + k0 / 2));
+        sf_copy = __ldg(plan.q_sf + t * plan.sf_pitch + kb);
       }
       store_sf_line(line, sf_copy, lane);
       continue;
@@ -296,6 +298,48 @@ gated_act_kernel(const __nv_bfloat16* __restrict__ x2, long long rows, int N, in
   }
 }
 
+// Wire rows of the expert-parallel dispatch: one routed token row as it crosses the link,
+//   [K/2 bytes of e2m1 codes][K/32 UE4M3 scales][padding to 16 bytes][int32 expert id local to the receiver][12 bytes]
+// in fixed-capacity slabs of `slab` rows per destination rank.  Slot s of slab w is live when
+// s < slab_counts[w]; a dead slot only gets its expert id, -1, which the receiver's dispatch_plan
+// treats like any routing that is not for one of its experts.
+__host__ __device__ inline long long wire_row_bytes(int K) { return (long long)round_up_i(K / 2 + K / kSfBlock, 16) + 16; }
+
+template <class IdT>
+__global__ void __launch_bounds__(128)
+pack_wire_rows_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ q_sf, const IdT* __restrict__ ids,
+                      const int* __restrict__ slot_tok, const int* __restrict__ slot_route,
+                      const int* __restrict__ slab_counts, int slab, int experts_per_rank, int K,
+                      uint8_t* __restrict__ wire) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long long slot = blockIdx.x;
+  const int w = (int)(slot / slab);
+  const int s = (int)(slot - (long long)w * slab);
+  const long long row_bytes = wire_row_bytes(K);
+  uint8_t* row = wire + slot * row_bytes;
+  int* id_out = reinterpret_cast<int*>(row + row_bytes - 16);
+  if (s >= min(slab_counts[w], slab)) {
+    if (threadIdx.x == 0) *id_out = -1;
+    return;
+  }
+  const long long t = slot_tok[slot];
+  const int code_vecs = K / 32;                       // 16-byte words of codes
+  const uint4* src = reinterpret_cast<const uint4*>(q + t * (K / 2));
+  uint4* dst = reinterpret_cast<uint4*>(row);
+  for (int v = threadIdx.x; v < code_vecs; v += 128) dst[v] = __ldg(src + v);
+  const int KB = K / kSfBlock;
+  const uint8_t* sf_src = q_sf + t * KB;
+  uint8_t* sf_dst = row + K / 2;
+  if (KB % 16 == 0) {
+    for (int v = threadIdx.x; v < KB / 16; v += 128)
+      reinterpret_cast<uint4*>(sf_dst)[v] = __ldg(reinterpret_cast<const uint4*>(sf_src) + v);
+  } else {
+    for (int b = threadIdx.x; b < KB; b += 128) sf_dst[b] = __ldg(sf_src + b);
+  }
+  if (threadIdx.x == 0) *id_out = (int)((long long)ids[slot_route[slot]] - (long long)w * experts_per_rank);
+}
+
 int grid_for(long long warp_items, int sm_count) {
   long long blocks = (warp_items + kWarpsPerBlock - 1) / kWarpsPerBlock;
   long long cap = (long long)(sm_count > 0 ? sm_count : 148) * 8;   // 8 x 256 threads fill an SM
@@ -461,7 +505,7 @@ extern "C" int pnv_scatter_quant_act_planned(const void* a1, const int32_t* src_
   if (int rc = check_common(a1, gscale, counts, experts, cap, k, b_act, sfb, "K")) return rc;
   long long lines = sf_numel(cap, k, experts) / 16;
   GatedAct act{PNV_ACT_SILU, 1.f, -1.f, nullptr};
-  PlanArgs plan{src_tok, src_route, topk_weights, nullptr, nullptr};
+  PlanArgs plan{src_tok, src_route, topk_weights, nullptr, nullptr, 0, 0};
   PNV_CUDA(launch_pdl(quant_lines_kernel<kPlanned>, dim3(grid_for(lines, sm_count)), dim3(kThreads), 0,
                       (cudaStream_t)stream, pdl_enabled(), (const __nv_bfloat16*)a1, gscale, gscale_per_expert,
                       counts, experts, cap, k, 0, act, plan, b_act, sfb));
@@ -489,7 +533,7 @@ extern "C" int pnv_scatter_fp4_planned(const uint8_t* q, const uint8_t* q_sf, co
   if (int rc = check_common(q, &dummy, counts, experts, cap, k, b_act, sfb, "K")) return rc;
   long long lines = sf_numel(cap, k, experts) / 16;
   GatedAct act{PNV_ACT_SILU, 1.f, -1.f, nullptr};
-  PlanArgs plan{src_tok, nullptr, nullptr, q, q_sf};
+  PlanArgs plan{src_tok, nullptr, nullptr, q, q_sf, k / 2, k / kSfBlock};
   PNV_CUDA(launch_pdl(quant_lines_kernel<kFp4>, dim3(grid_for(lines, sm_count)), dim3(kThreads), 0,
                       (cudaStream_t)stream, pdl_enabled(), (const __nv_bfloat16*)nullptr, (const float*)nullptr, 0,
                       counts, experts, cap, k, 0, act, plan, b_act, sfb));
@@ -498,5 +542,53 @@ extern "C" int pnv_scatter_fp4_planned(const uint8_t* q, const uint8_t* q_sf, co
 
 extern "C" int pnv_set_silu_table(int enabled) {
   g_silu_table_on = enabled != 0;
+  return PNV_OK;
+}
+
+
+extern "C" int64_t pnv_wire_row_bytes(int k) {
+  if (k <= 0 || k % kSfBlock != 0) return 0;
+  return wire_row_bytes(k);
+}
+
+extern "C" int pnv_pack_wire_rows(const uint8_t* q, const uint8_t* q_sf, const void* topk_ids, int ids_are_int64,
+                                  const int32_t* slot_tok, const int32_t* slot_route, const int32_t* slab_counts,
+                                  int ranks, int slab, int experts_per_rank, int k, uint8_t* wire,
+                                  pnv_stream_t stream) {
+  PNV_REQUIRE(k > 0 && k % kSfBlock == 0, "K must be a multiple of %d, got %d", kSfBlock, k);
+  PNV_REQUIRE(ranks >= 1 && slab >= 1 && experts_per_rank >= 1, "ranks, slab and experts_per_rank must be positive");
+  PNV_REQUIRE((long long)ranks * slab < (1LL << 31), "ranks * slab must fit int32");
+  PNV_REQUIRE(q && q_sf && topk_ids && slot_tok && slot_route && slab_counts && wire, "null pointer argument");
+  PNV_REQUIRE((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(wire)) % 16 == 0 &&
+                  ((k / kSfBlock) % 16 != 0 || reinterpret_cast<uintptr_t>(q_sf) % 16 == 0),
+              "pack_wire_rows buffers must be 16-byte aligned");
+  cudaStream_t s = (cudaStream_t)stream;
+  const dim3 grid((unsigned)(ranks * slab)), block(128);
+  if (ids_are_int64)
+    PNV_CUDA(launch_pdl(pack_wire_rows_kernel<long long>, grid, block, 0, s, pdl_enabled(), q, q_sf,
+                        (const long long*)topk_ids, (const int*)slot_tok, (const int*)slot_route,
+                        (const int*)slab_counts, slab, experts_per_rank, k, wire));
+  else
+    PNV_CUDA(launch_pdl(pack_wire_rows_kernel<int>, grid, block, 0, s, pdl_enabled(), q, q_sf, (const int*)topk_ids,
+                        (const int*)slot_tok, (const int*)slot_route, (const int*)slab_counts, slab,
+                        experts_per_rank, k, wire));
+  return PNV_OK;
+}
+
+extern "C" int pnv_scatter_fp4_wire(const uint8_t* wire, const int32_t* src_tok, const int32_t* counts, int k,
+                                    int experts, int cap, uint8_t* b_act, uint8_t* sfb, int sm_count,
+                                    pnv_stream_t stream) {
+  PNV_REQUIRE(cap > 0, "cap must be positive");
+  PNV_REQUIRE(wire && src_tok, "null pointer argument");
+  PNV_REQUIRE(reinterpret_cast<uintptr_t>(wire) % 16 == 0, "wire rows must be 16-byte aligned");
+  float dummy = 0.f;
+  if (int rc = check_common(wire, &dummy, counts, experts, cap, k, b_act, sfb, "K")) return rc;
+  long long lines = sf_numel(cap, k, experts) / 16;
+  GatedAct act{PNV_ACT_SILU, 1.f, -1.f, nullptr};
+  const long long pitch = wire_row_bytes(k);
+  PlanArgs plan{src_tok, nullptr, nullptr, wire, wire + k / 2, pitch, pitch};
+  PNV_CUDA(launch_pdl(quant_lines_kernel<kFp4>, dim3(grid_for(lines, sm_count)), dim3(kThreads), 0,
+                      (cudaStream_t)stream, pdl_enabled(), (const __nv_bfloat16*)nullptr, (const float*)nullptr, 0,
+                      counts, experts, cap, k, 0, act, plan, b_act, sfb));
   return PNV_OK;
 }

@@ -39,7 +39,8 @@ __device__ __forceinline__ unsigned cmp_swap(unsigned mine, unsigned other, bool
 // totals: [segments][E] (nullptr for single-segment plans, which write the final outputs themselves)
 template <class IdT>
 __global__ void __launch_bounds__(kSeg)
-plan_sort_kernel(const IdT* __restrict__ ids, int n, int topk, int first, int E, int cap, int* __restrict__ totals,
+plan_sort_kernel(const IdT* __restrict__ ids, long long id_stride, int n, int topk, int first, int E, int cap,
+                 int* __restrict__ totals,
                  int* __restrict__ counts, int* __restrict__ route_dest, int* __restrict__ src_tok,
                  int* __restrict__ src_route) {
   __shared__ unsigned s_key[kSeg];
@@ -52,7 +53,7 @@ plan_sort_kernel(const IdT* __restrict__ ids, int n, int topk, int first, int E,
   for (int x = tid; x < E; x += kSeg) s_total[x] = 0;
   unsigned code = kNotLocal;
   if (seg0 + tid < n) {
-    const long long e = (long long)ids[seg0 + tid] - first;
+    const long long e = (long long)ids[(seg0 + tid) * id_stride] - first;
     if (e >= 0 && e < E) code = (unsigned)e;
   }
   unsigned key = (code << kSegBits) | (unsigned)tid;
@@ -151,7 +152,7 @@ plan_offsets_kernel(int* __restrict__ totals, int segments, int E, int cap, int*
 
 template <class IdT>
 __global__ void __launch_bounds__(256)
-plan_place_kernel(const IdT* __restrict__ ids, int n, int topk, int first, int E, int cap,
+plan_place_kernel(const IdT* __restrict__ ids, long long id_stride, int n, int topk, int first, int E, int cap,
                   const int* __restrict__ offsets, int* __restrict__ route_dest, int* __restrict__ src_tok,
                   int* __restrict__ src_route) {
   pdl_wait();
@@ -161,7 +162,7 @@ plan_place_kernel(const IdT* __restrict__ ids, int n, int topk, int first, int E
   const int in_seg = route_dest[i];
   int dest = -1;
   if (in_seg >= 0) {
-    const int e = (int)((long long)ids[i] - first);
+    const int e = (int)((long long)ids[i * id_stride] - first);
     const int r = in_seg + offsets[(long long)(i >> kSegBits) * E + e];
     if (r < cap) {
       dest = e * cap + r;
@@ -173,7 +174,7 @@ plan_place_kernel(const IdT* __restrict__ ids, int n, int topk, int first, int E
 }
 
 template <class IdT>
-int run_plan(const IdT* ids, int n, int topk, int first, int E, int cap, int* counts, int* route_dest,
+int run_plan(const IdT* ids, long long id_stride, int n, int topk, int first, int E, int cap, int* counts, int* route_dest,
              int* src_tok, int* src_route, int* scratch, cudaStream_t s) {
   const int segments = (n + kSeg - 1) / kSeg;
   if (segments == 0) {
@@ -183,15 +184,15 @@ int run_plan(const IdT* ids, int n, int topk, int first, int E, int cap, int* co
   const size_t smem = sizeof(int) * (size_t)E;     // static shared memory takes 4.1 KiB more: always below 48 KiB
   const bool pdl = pdl_enabled();
   if (segments == 1) {
-    PNV_CUDA(launch_pdl(plan_sort_kernel<IdT>, dim3(1), dim3(kSeg), smem, s, pdl, ids, n, topk, first, E, cap,
+    PNV_CUDA(launch_pdl(plan_sort_kernel<IdT>, dim3(1), dim3(kSeg), smem, s, pdl, ids, id_stride, n, topk, first, E, cap,
                         (int*)nullptr, counts, route_dest, src_tok, src_route));
     return PNV_OK;
   }
   PNV_REQUIRE(scratch != nullptr, "dispatch_plan: %d segments need a scratch buffer of segments * E ints", segments);
-  PNV_CUDA(launch_pdl(plan_sort_kernel<IdT>, dim3(segments), dim3(kSeg), smem, s, pdl, ids, n, topk, first, E, cap,
+  PNV_CUDA(launch_pdl(plan_sort_kernel<IdT>, dim3(segments), dim3(kSeg), smem, s, pdl, ids, id_stride, n, topk, first, E, cap,
                       scratch, counts, route_dest, src_tok, src_route));
   PNV_CUDA(launch_pdl(plan_offsets_kernel, dim3((E + 7) / 8), dim3(256), 0, s, pdl, scratch, segments, E, cap, counts));
-  PNV_CUDA(launch_pdl(plan_place_kernel<IdT>, dim3((n + 255) / 256), dim3(256), 0, s, pdl, ids, n, topk, first, E, cap,
+  PNV_CUDA(launch_pdl(plan_place_kernel<IdT>, dim3((n + 255) / 256), dim3(256), 0, s, pdl, ids, id_stride, n, topk, first, E, cap,
                       (const int*)scratch, route_dest, src_tok, src_route));
   return PNV_OK;
 }
@@ -335,18 +336,27 @@ int check_plan_args(const void* topk_ids, int64_t tokens, int topk, int num_loca
 }
 }  // namespace
 
-extern "C" int pnv_dispatch_plan(const void* topk_ids, int ids_are_int64, int64_t tokens, int topk, int first_expert,
-                                 int num_local_experts, int cap, int32_t* counts, int32_t* route_dest,
-                                 int32_t* src_tok, int32_t* src_route, int32_t* scratch, pnv_stream_t stream) {
+extern "C" int pnv_dispatch_plan_strided(const void* topk_ids, int ids_are_int64, int64_t id_stride, int64_t tokens,
+                                         int topk, int first_expert, int num_local_experts, int cap, int32_t* counts,
+                                         int32_t* route_dest, int32_t* src_tok, int32_t* src_route, int32_t* scratch,
+                                         pnv_stream_t stream) {
   if (int rc = check_plan_args(topk_ids, tokens, topk, num_local_experts, cap, counts, route_dest, src_tok, src_route))
     return rc;
+  PNV_REQUIRE(id_stride >= 1, "id_stride must be positive");
   const int n = (int)(tokens * topk);
   cudaStream_t s = (cudaStream_t)stream;
   if (ids_are_int64)
-    return run_plan(static_cast<const long long*>(topk_ids), n, topk, first_expert, num_local_experts, cap, counts,
-                    route_dest, src_tok, src_route, scratch, s);
-  return run_plan(static_cast<const int*>(topk_ids), n, topk, first_expert, num_local_experts, cap, counts, route_dest,
-                  src_tok, src_route, scratch, s);
+    return run_plan(static_cast<const long long*>(topk_ids), (long long)id_stride, n, topk, first_expert,
+                    num_local_experts, cap, counts, route_dest, src_tok, src_route, scratch, s);
+  return run_plan(static_cast<const int*>(topk_ids), (long long)id_stride, n, topk, first_expert, num_local_experts, cap,
+                  counts, route_dest, src_tok, src_route, scratch, s);
+}
+
+extern "C" int pnv_dispatch_plan(const void* topk_ids, int ids_are_int64, int64_t tokens, int topk, int first_expert,
+                                 int num_local_experts, int cap, int32_t* counts, int32_t* route_dest,
+                                 int32_t* src_tok, int32_t* src_route, int32_t* scratch, pnv_stream_t stream) {
+  return pnv_dispatch_plan_strided(topk_ids, ids_are_int64, 1, tokens, topk, first_expert, num_local_experts, cap, counts,
+                                   route_dest, src_tok, src_route, scratch, stream);
 }
 
 extern "C" int64_t pnv_dispatch_plan_noalloc_max_scratch_ints(void) { return kBuiltinScratchInts; }

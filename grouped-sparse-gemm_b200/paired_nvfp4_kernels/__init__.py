@@ -52,6 +52,10 @@ def _register():
                "-> (Tensor, Tensor)")
     lib.define("moe_finalize(Tensor(a!) out, Tensor fused, Tensor route_dest, Tensor? topk_weights) -> ()")
     lib.define("gather_rows(Tensor src, Tensor idx) -> Tensor")
+    lib.define("pack_wire_rows(Tensor q, Tensor q_sf, Tensor topk_ids, Tensor slot_tok, Tensor slot_route, "
+               "Tensor slab_counts, int slab, int experts_per_rank) -> Tensor")
+    lib.define("scatter_fp4_wire(Tensor wire, int k, Tensor src_tok, Tensor expert_num_tokens, int cap) "
+               "-> (Tensor, Tensor)")
     lib.define("group_mm(Tensor(a!) out, Tensor a_comp, Tensor e_meta, Tensor sfa, Tensor b_act, Tensor sfb, "
                "Tensor alphas, Tensor expert_num_tokens, int features, int k, "
                f"int config_id={DEFAULT_TACTIC[0]}, int cluster_m={DEFAULT_TACTIC[1]}, "
@@ -74,6 +78,8 @@ def _register():
     lib.impl("scatter_fp4_planned", ops.scatter_fp4_planned, "CUDA")
     lib.impl("moe_finalize", ops.moe_finalize, "CUDA")
     lib.impl("gather_rows", ops.gather_rows, "CUDA")
+    lib.impl("pack_wire_rows", ops.pack_wire_rows, "CUDA")
+    lib.impl("scatter_fp4_wire", ops.scatter_fp4_wire, "CUDA")
     lib.impl("group_mm", ops.group_mm, "CUDA")
     lib.impl("gated_act", ops.gated_act, "CUDA")
     lib.impl("group_mm_swiglu_quant", ops.group_mm_swiglu_quant, "CUDA")

@@ -9,7 +9,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libpaired_nvfp4_b200.so")
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 _p = ctypes.c_void_p
 _i = ctypes.c_int
@@ -30,6 +30,10 @@ SIGNATURES = {
     "pnv_scatter_quant_act": (_i, [_p, _p, _p, _p, _p, _i, _i64, _i, _i, _i, _p, _p, _i, _p]),
     "pnv_dispatch_plan_scratch_ints": (_i64, [_i64, _i]),
     "pnv_dispatch_plan": (_i, [_p, _i, _i64, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p]),
+    "pnv_dispatch_plan_strided": (_i, [_p, _i, _i64, _i64, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p]),
+    "pnv_wire_row_bytes": (_i64, [_i]),
+    "pnv_pack_wire_rows": (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p, _p]),
+    "pnv_scatter_fp4_wire": (_i, [_p, _p, _p, _i, _i, _i, _p, _p, _i, _p]),
     "pnv_dispatch_plan_noalloc_max_scratch_ints": (_i64, []),
     "pnv_dispatch_plan_noalloc": (_i, [_p, _i, _i64, _i, _i, _i, _i, _p, _p, _p, _p, _p]),
     "pnv_scatter_quant_act_planned": (_i, [_p, _p, _p, _p, _p, _i, _p, _i, _i, _i, _p, _p, _i, _p]),
@@ -41,10 +45,11 @@ SIGNATURES = {
     "pnv_gated_act": (_i, [_p, _i64, _i, _i, _i, _f, _f, _p, _p]),
     "pnv_group_mm_num_configs": (_i, []),
     "pnv_group_mm_config_name": (ctypes.c_char_p, [_i]),
-    "pnv_group_mm": (_i, [_p] * 8 + [_i] * 9 + [_p]),
+    "pnv_group_mm_workspace_bytes": (_i64, [_i, _i, _i, _i]),
+    "pnv_group_mm": (_i, [_p] * 8 + [_i] * 9 + [_p, _i64, _p]),
     "pnv_group_mm_swiglu_num_configs": (_i, []),
     "pnv_group_mm_swiglu_config_name": (ctypes.c_char_p, [_i]),
-    "pnv_group_mm_swiglu_quant": (_i, [_p] * 10 + [_i] * 9 + [_f, _f, _i, _i, _p]),
+    "pnv_group_mm_swiglu_quant": (_i, [_p] * 10 + [_i] * 9 + [_f, _f, _i, _i, _p, _i64, _p]),
 }
 
 

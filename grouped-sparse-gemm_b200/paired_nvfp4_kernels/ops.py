@@ -173,9 +173,14 @@ def scatter_quant_act(a1, flat_tok, dest_global, topk_weights, gscale, expert_nu
 
 
 def dispatch_plan(topk_ids, first_expert, num_local_experts, cap):
-    """csrc/ops.cu:374-411.  Returns (expert_num_tokens, route_dest, src_tok, src_route)."""
+    """csrc/ops.cu:374-411.  Returns (expert_num_tokens, route_dest, src_tok, src_route).
+
+    Beyond the reference's contiguous [T, topk] ids, a [T, 1] view with a row stride is accepted (one id per
+    row of a wider buffer: the expert ids inside the wire rows of an expert-parallel dispatch)."""
     _check(topk_ids.is_cuda, "topk_ids must be CUDA")
-    _check(topk_ids.dim() == 2 and topk_ids.is_contiguous(), "topk_ids must be contiguous [T, topk]")
+    _check(topk_ids.dim() == 2, "topk_ids must be [T, topk]")
+    strided = (not topk_ids.is_contiguous()) and topk_ids.size(1) == 1 and topk_ids.stride(0) >= 1
+    _check(topk_ids.is_contiguous() or strided, "topk_ids must be contiguous [T, topk] (or a strided [T, 1] view)")
     _check(topk_ids.dtype in (torch.int32, torch.int64), "topk_ids must be int32 or int64")
     E = int(num_local_experts)
     _check(1 <= E <= 4096, lambda: f"num_local_experts must be in [1, 4096], got {E}")
@@ -191,10 +196,10 @@ def dispatch_plan(topk_ids, first_expert, num_local_experts, cap):
     n_scratch = int(_lib.pnv_dispatch_plan_scratch_ints(T * topk, E))
     scratch = torch.empty((max(n_scratch, 1),), **i32)
     with torch.cuda.device(topk_ids.device):
-        _cabi.check(_lib.pnv_dispatch_plan(topk_ids.data_ptr(), 1 if topk_ids.dtype == torch.int64 else 0, T, topk,
-                                           int(first_expert), E, int(cap), counts.data_ptr(), route_dest.data_ptr(),
-                                           src_tok.data_ptr(), src_route.data_ptr(), scratch.data_ptr(),
-                                           _stream(topk_ids)))
+        _cabi.check(_lib.pnv_dispatch_plan_strided(
+            topk_ids.data_ptr(), 1 if topk_ids.dtype == torch.int64 else 0, topk_ids.stride(0) if strided else 1, T, topk,
+            int(first_expert), E, int(cap), counts.data_ptr(), route_dest.data_ptr(), src_tok.data_ptr(),
+            src_route.data_ptr(), scratch.data_ptr(), _stream(topk_ids)))
     return counts, route_dest, src_tok, src_route
 
 
@@ -270,6 +275,71 @@ def scatter_fp4_planned(q, q_sf, src_tok, expert_num_tokens, cap):
     return b_act, sfb
 
 
+def wire_row_bytes(k):
+    """Bytes of one wire row of the expert-parallel dispatch for hidden size k."""
+    return int(_lib.pnv_wire_row_bytes(int(k)))
+
+
+def pack_wire_rows(q, q_sf, topk_ids, slot_tok, slot_route, slab_counts, slab, experts_per_rank):
+    """quant_rows output -> wire rows in fixed-capacity slabs, one slab of `slab` rows per destination rank
+    (see pnv_pack_wire_rows).  slot_tok / slot_route / slab_counts are dispatch_plan's outputs for the routings
+    keyed by destination rank.  Returns uint8 [ranks * slab, wire_row_bytes(K)]."""
+    _check(q.is_cuda and q_sf.is_cuda and topk_ids.is_cuda and slot_tok.is_cuda and slot_route.is_cuda
+           and slab_counts.is_cuda, "inputs must be CUDA")
+    _check_arch(q)
+    _check(q.dim() == 2 and q.dtype == torch.uint8 and q.is_contiguous(), "q must be contiguous uint8 [T, K/2]")
+    K = q.size(1) * 2
+    _check(K % SF_BLOCK == 0, lambda: f"K must be a multiple of {SF_BLOCK}, got {K}")
+    _check(q_sf.dim() == 2 and q_sf.size(0) == q.size(0) and q_sf.size(1) == K // SF_BLOCK and q_sf.element_size() == 1
+           and q_sf.is_contiguous(), lambda: f"q_sf must be contiguous 1-byte [T, K/{SF_BLOCK}]")
+    _check(topk_ids.dtype in (torch.int32, torch.int64) and topk_ids.is_contiguous(), "topk_ids must be contiguous int32/int64")
+    ranks = slab_counts.numel()
+    _check(slab_counts.dtype == torch.int32 and slab_counts.is_contiguous(), "slab_counts must be contiguous int32 [ranks]")
+    _check(slab >= 1 and experts_per_rank >= 1, "slab and experts_per_rank must be positive")
+    _check(slot_tok.dtype == torch.int32 and slot_route.dtype == torch.int32 and slot_tok.is_contiguous()
+           and slot_route.is_contiguous() and slot_tok.numel() == ranks * slab and slot_route.numel() == ranks * slab,
+           "slot_tok and slot_route must be contiguous int32 [ranks * slab] (dispatch_plan output)")
+    wire = torch.empty((ranks * slab, wire_row_bytes(K)), dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        _cabi.check(_lib.pnv_pack_wire_rows(q.data_ptr(), q_sf.data_ptr(), topk_ids.data_ptr(),
+                                            1 if topk_ids.dtype == torch.int64 else 0, slot_tok.data_ptr(),
+                                            slot_route.data_ptr(), slab_counts.data_ptr(), ranks, int(slab),
+                                            int(experts_per_rank), K, wire.data_ptr(), _stream(q)))
+    return wire
+
+
+def wire_expert_ids(wire):
+    """The [rows, 1] int32 view of the expert ids inside wire rows (input of dispatch_plan on the receiver)."""
+    _check(wire.dim() == 2 and wire.dtype == torch.uint8 and wire.is_contiguous() and wire.size(1) % 16 == 0,
+           "wire must be contiguous uint8 [rows, wire_row_bytes(K)]")
+    rb = wire.size(1)
+    return wire.view(torch.int32)[:, rb // 4 - 4: rb // 4 - 3]
+
+
+def scatter_fp4_wire(wire, k, src_tok, expert_num_tokens, cap):
+    """Received wire rows -> group_mm's activation operands, as scatter_fp4_planned does for separate code and
+    scale tensors (csrc/ops.cu:502-541)."""
+    _check(wire.is_cuda and src_tok.is_cuda and expert_num_tokens.is_cuda, "inputs must be CUDA")
+    _check_arch(wire)
+    K = int(k)
+    _check(K % SF_BLOCK == 0, lambda: f"K must be a multiple of {SF_BLOCK}, got {K}")
+    _check(wire.dim() == 2 and wire.dtype == torch.uint8 and wire.is_contiguous() and wire.size(1) == wire_row_bytes(K),
+           "wire must be contiguous uint8 [rows, wire_row_bytes(K)]")
+    E = expert_num_tokens.numel()
+    _check(expert_num_tokens.dtype == torch.int32 and expert_num_tokens.is_contiguous(),
+           "expert_num_tokens must be contiguous int32 [E]")
+    _check(cap > 0, "cap must be positive")
+    _check(src_tok.dtype == torch.int32 and src_tok.is_contiguous() and src_tok.numel() == E * cap,
+           "src_tok must be contiguous int32 [E * cap] (dispatch_plan output)")
+    b_act = torch.empty((E, cap, K // 2), dtype=torch.uint8, device=wire.device)
+    sfb = torch.empty((_cabi.sf_numel(cap, K, E),), dtype=torch.uint8, device=wire.device)
+    with torch.cuda.device(wire.device):
+        _cabi.check(_lib.pnv_scatter_fp4_wire(wire.data_ptr(), src_tok.data_ptr(), expert_num_tokens.data_ptr(), K, E,
+                                              int(cap), b_act.data_ptr(), sfb.data_ptr(), _device_info(wire.device)[1],
+                                              _stream(wire)))
+    return b_act, sfb
+
+
 def moe_finalize(out, fused, route_dest, topk_weights):
     """csrc/ops.cu:548-575.  Mutates `out` in place."""
     _check(out.is_cuda and fused.is_cuda and route_dest.is_cuda, "inputs must be CUDA")
@@ -326,6 +396,30 @@ def gated_act(x2, interleaved=False, activation="silu", beta=1.0, linear_beta=-1
     return y
 
 
+_workspaces = {}
+
+
+def _split_workspace(t, experts, features, max_n):
+    """(pointer, bytes) of the split-K workspace for a group_mm launch on t's device and current stream, or
+    (None, 0) when the launch does not split.  The reference allocates its workspace inside the op as well
+    (csrc/group_mm.cuh:163-165); here it is kept per (device, stream), zeroed once, because every launch
+    leaves its counters zero.  Under stream capture a fresh zeroed buffer is made instead, so a graph never
+    shares the buffer with work outside it."""
+    sm = _device_info(t.device)[1]
+    need = int(_lib.pnv_group_mm_workspace_bytes(int(experts), int(features), int(max_n), sm))
+    if need == 0:
+        return None, 0
+    if torch.cuda.is_current_stream_capturing():
+        ws = torch.zeros((need,), dtype=torch.uint8, device=t.device)
+        return ws, need
+    key = (t.device.index, torch.cuda.current_stream(t.device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros((need,), dtype=torch.uint8, device=t.device)
+        _workspaces[key] = ws
+    return ws, need
+
+
 def group_mm_configs():
     """csrc/ops.cu:665-670."""
     return _cabi.group_mm_config_names()
@@ -358,10 +452,12 @@ def group_mm(out, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens, fe
     _check(sfa.numel() >= _cabi.sf_numel(M, K, E), "sfa is smaller than the SFA layout")
     _check(sfb.numel() >= _cabi.sf_numel(max_n, K, E), "sfb is smaller than the SFB layout")
     with torch.cuda.device(out.device):
+        ws, ws_bytes = _split_workspace(out, E, M, max_n)
         _cabi.check(_lib.pnv_group_mm(
             out.data_ptr(), a_comp.data_ptr(), e_meta.data_ptr(), sfa.data_ptr(), b_act.data_ptr(), sfb.data_ptr(),
             alphas.data_ptr(), expert_num_tokens.data_ptr(), E, M, K, max_n, int(config_id), int(cluster_m),
-            int(cluster_n), _device_info(out.device)[1], 1, _stream(out)))
+            int(cluster_n), _device_info(out.device)[1], 1, ws.data_ptr() if ws is not None else None, ws_bytes,
+            _stream(out)))
 
 
 def group_mm_swiglu_configs():
@@ -393,11 +489,13 @@ def group_mm_swiglu_quant(a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_to
     b_out = torch.empty((E, max_n, N // 2), dtype=torch.uint8, device=b_act.device)
     sfb_out = torch.empty((_cabi.sf_numel(max_n, N, E),), dtype=torch.uint8, device=b_act.device)
     with torch.cuda.device(b_act.device):
+        ws, ws_bytes = _split_workspace(b_act, E, M, max_n)
         _cabi.check(_lib.pnv_group_mm_swiglu_quant(
             b_out.data_ptr(), sfb_out.data_ptr(), a_comp.data_ptr(), e_meta.data_ptr(), sfa.data_ptr(),
             b_act.data_ptr(), sfb.data_ptr(), alphas.data_ptr(), expert_num_tokens.data_ptr(), gscale.data_ptr(),
             1 if gscale.numel() == E else 0, E, M, K, max_n, int(config_id), int(cluster_m), int(cluster_n), kind,
-            float(beta), float(linear_beta), _device_info(b_act.device)[1], 1, _stream(b_act)))
+            float(beta), float(linear_beta), _device_info(b_act.device)[1], 1,
+            ws.data_ptr() if ws is not None else None, ws_bytes, _stream(b_act)))
     return b_out, sfb_out
 
 

@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define PNV_ABI_VERSION 1
+#define PNV_ABI_VERSION 2
 
 #define PNV_OK 0
 #define PNV_ERR_INVALID_ARGUMENT 1 /* a shape / option the reference rejects with TORCH_CHECK */
@@ -115,6 +115,15 @@ int pnv_dispatch_plan(const void* topk_ids, int ids_are_int64, int64_t tokens, i
                       int num_local_experts, int cap, int32_t* counts, int32_t* route_dest,
                       int32_t* src_tok, int32_t* src_route, int32_t* scratch, pnv_stream_t stream);
 
+/* The same plan for expert ids that do not sit back to back: id i is read at topk_ids[i * id_stride] (stride in
+ * elements of the id type).  This is how a receiving rank plans straight from the wire rows of an
+ * expert-parallel dispatch (pnv_pack_wire_rows), whose expert ids sit one per row.  No counterpart in the
+ * reference, which leaves the exchange to its caller. */
+int pnv_dispatch_plan_strided(const void* topk_ids, int ids_are_int64, int64_t id_stride, int64_t tokens, int topk,
+                              int first_expert, int num_local_experts, int cap, int32_t* counts,
+                              int32_t* route_dest, int32_t* src_tok, int32_t* src_route, int32_t* scratch,
+                              pnv_stream_t stream);
+
 /* pnv_dispatch_plan without any allocation, by anyone.  It has no counterpart in the reference.
  * The plan's scratch (per-chunk expert totals) lives in an array built into the library instead of a
  * caller buffer, for callers that cannot obtain device memory at call time: a serving process that
@@ -153,15 +162,33 @@ int pnv_scatter_fp4_planned(const uint8_t* q, const uint8_t* q_sf, const int32_t
                             const int32_t* counts, int k, int experts, int cap, uint8_t* b_act,
                             uint8_t* sfb, int sm_count, pnv_stream_t stream);
 
+/* Expert-parallel dispatch in fixed-capacity slabs (no counterpart in the reference, which offers quant_rows /
+ * scatter_fp4_planned, csrc/quant.cuh:485-562, and leaves the exchange between them to the caller).
+ * A wire row is one routed token row as it crosses the link:
+ *   [k/2 bytes e2m1 codes][k/32 UE4M3 scales][padding to 16 bytes][int32 expert id local to the receiver][12 bytes]
+ * = pnv_wire_row_bytes(k) bytes.  The sender plans its routings by destination rank with
+ * pnv_dispatch_plan(topk_ids / experts_per_rank ..., num_local_experts = ranks, cap = slab): slot s of slab w
+ * is live when s < slab_counts[w] and then carries token slot_tok[w * slab + s] of routing
+ * slot_route[w * slab + s]; pnv_pack_wire_rows builds wire u8[ranks * slab, row bytes] from pnv_quant_rows
+ * output, writing expert id -1 into dead slots (their other bytes stay undefined).  After an equal-split
+ * all-to-all the receiver plans with pnv_dispatch_plan_strided on the ids inside the rows (dead slots fall
+ * out as "not local") and pnv_scatter_fp4_wire places codes and scales like pnv_scatter_fp4_planned. */
+int64_t pnv_wire_row_bytes(int k);
+int pnv_pack_wire_rows(const uint8_t* q, const uint8_t* q_sf, const void* topk_ids, int ids_are_int64,
+                       const int32_t* slot_tok, const int32_t* slot_route, const int32_t* slab_counts, int ranks,
+                       int slab, int experts_per_rank, int k, uint8_t* wire, pnv_stream_t stream);
+int pnv_scatter_fp4_wire(const uint8_t* wire, const int32_t* src_tok, const int32_t* counts, int k, int experts,
+                         int cap, uint8_t* b_act, uint8_t* sfb, int sm_count, pnv_stream_t stream);
+
 /* paired_nvfp4_moe_finalize (csrc/ops.cu:548-575 -> finalize_kernel, csrc/moe_routing.cuh:203-244).
  * out bf16[tokens, K] = sum over kept routings in top-k order of fused bf16[E * cap, K] rows
  * (route_dest i32[tokens, topk], -1 = dropped), weighted by topk_weights f32[tokens, topk] when given. */
 int pnv_moe_finalize(void* out, const void* fused, const int32_t* route_dest, const float* topk_weights,
                      int64_t tokens, int topk, int k, pnv_stream_t stream);
 
-/* Row gather for the expert-parallel exchange (no op of its own in the reference, which leaves the
- * permutation to the caller's framework; python/paired_nvfp4_kernels/__init__.py documents the plan
- * tensors it consumes): dst[i, :] = idx[i] >= 0 ? src[idx[i], :] : 0 for rows of row_bytes bytes
+/* Row gather for the expert-parallel exchange (no counterpart in the reference, which leaves the permutation
+ * either side of the exchange to the caller's framework; the plan tensors are those of dispatch_plan,
+ * csrc/ops.cu:374-411): dst[i, :] = idx[i] >= 0 ? src[idx[i], :] : 0 for rows of row_bytes bytes
  * (a multiple of 16; both buffers 16-byte aligned). */
 int pnv_gather_rows(const void* src, const int32_t* idx, int64_t n_idx, int64_t row_bytes, void* dst,
                     pnv_stream_t stream);
@@ -191,11 +218,20 @@ const char* pnv_group_mm_config_name(int config_id);
  * for t < counts[e]; every other row keeps the caller's bytes.  a_comp / e_meta / sfa are
  * pnv_compress outputs for (features, k); b_act / sfb a quantizer's outputs for (max_n, k).
  * pdl != 0 launches with programmatic dependent launch (the kernel waits on its stream
- * predecessor before its first dependent read; csrc/pdl.cuh:42-80). */
+ * predecessor before its first dependent read; csrc/pdl.cuh:42-80).
+ * workspace (the reference allocates its own inside the op, csrc/group_mm.cuh:163-165): NULL, or
+ * pnv_group_mm_workspace_bytes(experts, features, max_n, sm_count) bytes, 256-byte aligned, for splitting K
+ * across CTAs.  Only decode-sized problems (max_n <= 32) use it: the K stages of all tiles are dealt evenly
+ * to the SMs, a tile shared by several CTAs is summed from fp32 partials in K order by whichever arrives
+ * last (so the result does not depend on timing).  The first 4 * experts * ceil(features / 128) bytes are
+ * arrival counters: they must be zero before the first launch that uses the buffer, every launch leaves
+ * them zero, and two launches that may overlap on the GPU must not share a workspace. */
+int64_t pnv_group_mm_workspace_bytes(int experts, int features, int max_n, int sm_count);
 int pnv_group_mm(void* out, const uint8_t* a_comp, const uint8_t* e_meta, const uint8_t* sfa,
                  const uint8_t* b_act, const uint8_t* sfb, const float* alphas,
                  const int32_t* counts, int experts, int features, int k, int max_n, int config_id,
-                 int cluster_m, int cluster_n, int sm_count, int pdl, pnv_stream_t stream);
+                 int cluster_m, int cluster_n, int sm_count, int pdl, void* workspace,
+                 int64_t workspace_bytes, pnv_stream_t stream);
 
 /* paired_nvfp4_group_mm_swiglu_configs / paired_nvfp4_group_mm_swiglu_quant (csrc/ops.cu:585-658 ->
  * SwigluFp4Epilogue, csrc/sm100/swiglu_epilogue.cuh:52-236; variant table kSwigluMmKinds,
@@ -203,7 +239,8 @@ int pnv_group_mm(void* out, const uint8_t* a_comp, const uint8_t* e_meta, const 
  * rows, then the 32 matching up rows; features = 2N, a multiple of 128), with the gated activation
  * and GEMM2's input quantization fused into the epilogue: writes b_out u8[E, max_n, N/2] (rows
  * t >= counts[e] untouched) and sfb_out u8[pnv_sf_numel(max_n, N, E)] (every byte), byte-identical
- * to pnv_group_mm followed by pnv_silu_mul_quant_act(interleaved = 1) with the same gscale. */
+ * to pnv_group_mm followed by pnv_silu_mul_quant_act(interleaved = 1) with the same gscale (and the same
+ * workspace choice: splitting K changes the order of the fp32 sum).  workspace as for pnv_group_mm. */
 int pnv_group_mm_swiglu_num_configs(void);
 const char* pnv_group_mm_swiglu_config_name(int config_id);
 int pnv_group_mm_swiglu_quant(uint8_t* b_out, uint8_t* sfb_out, const uint8_t* a_comp,
@@ -212,7 +249,7 @@ int pnv_group_mm_swiglu_quant(uint8_t* b_out, uint8_t* sfb_out, const uint8_t* a
                               const float* gscale, int gscale_per_expert, int experts, int features,
                               int k, int max_n, int config_id, int cluster_m, int cluster_n,
                               int act_kind, float beta, float linear_beta, int sm_count, int pdl,
-                              pnv_stream_t stream);
+                              void* workspace, int64_t workspace_bytes, pnv_stream_t stream);
 
 #ifdef __cplusplus
 }

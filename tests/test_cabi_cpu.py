@@ -28,7 +28,7 @@ def test_library_exports_every_declared_symbol(pnk):
     for name in declared:
         assert hasattr(lib, name), f"{name} is declared but not exported"
     assert declared == set(_cabi.SIGNATURES), "ctypes binding and header disagree"
-    assert lib.pnv_abi_version() == 1
+    assert lib.pnv_abi_version() == 2
 
 
 def test_size_queries_match_oracle(pnk):

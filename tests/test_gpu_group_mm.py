@@ -117,6 +117,48 @@ def test_pair_kernels_on_odd_tile_counts(pnk):
         run_case(pnk, E=2, M=640 - 8, K=512, max_n=96, counts=[96, 33], config_id=cid, seed=22)
 
 
+SPLIT_CASES = [
+    # E, M, K, max_n, counts: decode-sized problems, where the K stages of all tiles are dealt evenly to the SMs
+    (2, 256, 4096, 16, [16, 5]),                  # 4 tiles x 8 stages over 32 CTAs: every CTA gets one stage of a tile
+    (8, 512, 2048, 8, [0, 0, 0, 7, 0, 0, 0, 0]),  # one active expert: most CTAs get an empty range
+    (1, 128, 2176, 32, [32]),                     # K = 4 stages + a short tail stage that is a unit of its own
+    (3, 384, 14336, 16, [16, 1, 9]),              # long K, tiles cut at arbitrary stages
+    (32, 4096, 7168, 1, [0] * 10 + [1] + [0] * 21),   # one token on one of 32 experts (an expert-parallel decode rank)
+]
+
+
+@pytest.mark.parametrize("E,M,K,max_n,counts", SPLIT_CASES)
+def test_split_k_matches_oracle_and_unsplit(pnk, E, M, K, max_n, counts):
+    """Through the operators the split is on (they keep a workspace per stream); through the C ABI with no
+    workspace it is off.  Both must meet the bar; twice in a row, to show the counters return to zero."""
+    from paired_nvfp4_kernels import _cabi
+    ops = torch.ops.paired_nvfp4
+    got_a, want, valid = run_case(pnk, E, M, K, max_n, counts, 7, seed=31)
+    got_b, _, _ = run_case(pnk, E, M, K, max_n, counts, 7, seed=31)
+    assert np.array_equal(got_a, got_b), "the split result must not depend on timing"
+    # the same launch without a workspace
+    packed, sf, _ = make_weights(E, M, K, 31, 1.0)
+    x = make_acts(E, max_n, K, 32)
+    cnt = np.asarray(counts, np.int32)
+    al = np.linspace(0.5, 2.0, E).astype(np.float32)
+    a_comp, e_meta, sfa = ops.compress(dev(packed), dev(sf), K)
+    b_act, sfb = ops.quant_act(bf16_tensor(x), dev(np.ones(1, np.float32)), dev(cnt), M)
+    out = torch.full((E, max_n, M), SENTINEL, dtype=torch.bfloat16, device="cuda")
+    al_t, cnt_t = dev(al), dev(cnt)
+    _cabi.check(_cabi.lib.pnv_group_mm(out.data_ptr(), a_comp.data_ptr(), e_meta.data_ptr(), sfa.data_ptr(),
+                                       b_act.data_ptr(), sfb.data_ptr(), al_t.data_ptr(), cnt_t.data_ptr(), E, M, K, max_n,
+                                       7, 1, 1, 0, 1, None, 0, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    plain = out.float().cpu().numpy()
+    assert (plain[~valid] == SENTINEL).all()
+    for e in range(E):
+        n = int(cnt[e])
+        if n:
+            assert orc.rel_frobenius(plain[e, :n], want[e, :n]) <= REL_FROB_TOL
+            # split and unsplit differ only in the order of the fp32 sum: at most an ulp of bf16 here and there
+            assert orc.rel_frobenius(got_a[e, :n], plain[e, :n]) <= 4e-3
+
+
 def test_bounded_wait_gives_up_and_reports(pnk):
     """The give-up path of the kernels' bounded waits, with nothing in flight: a wait on a barrier nobody
     arrives at must return, leave its code in the status word, and leave the context usable."""
