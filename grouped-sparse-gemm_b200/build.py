@@ -36,6 +36,7 @@ def build(force=False, ptxas_v=False, verbose=True):
            "-gencode", "arch=compute_100a,code=sm_100a", "-o", OUT]
     if ptxas_v or os.environ.get("PAIRED_NVFP4_PTXAS_V") == "1":
         cmd += ["-Xptxas", "-v"]
+    cmd += os.environ.get("PAIRED_NVFP4_NVCC_FLAGS", "").split()      # developer builds, e.g. -DPNV_WIDE_PROFILE
     cmd += [os.path.join(CSRC, s) for s in SOURCES]
     if verbose:
         print(" ".join(cmd), flush=True)

@@ -172,38 +172,48 @@ struct TileWalk {
 struct UnitWalk {
   TileWalk tw;
   bool split;
-  int ksn, grid;
-  long long total;   // split: K stages of all tiles
-  long long pos, hi; // split: this CTA's range; unsplit: pos is the next tile
+  unsigned ksn, grid;
+  // split: K stages of all tiles (the host bounds it below 2^31), and the cut: the first `rem` CTAs take
+  // `quot` + 1 stages, the others `quot` -- no division per lookup (a lone thread pays hundreds of cycles for one)
+  unsigned total, quot, rem;
+  unsigned pos, hi;  // split: this CTA's range; unsplit: pos is the next tile
   template <int TILE_N>
   __device__ void init(const int* s_counts, int E, int n_mt, int k_stages, long long n_tiles, bool split_) {
     tw.init<TILE_N>(s_counts, E, n_mt);
-    split = split_; ksn = k_stages; grid = (int)gridDim.x;
+    split = split_; ksn = (unsigned)k_stages; grid = gridDim.x;
     if (split) {
-      total = n_tiles * ksn;
+      total = (unsigned)n_tiles * ksn;
+      quot = total / grid;
+      rem = total - quot * grid;
       pos = range_lo(blockIdx.x);
       hi = range_lo(blockIdx.x + 1);
     } else {
-      total = 0; pos = blockIdx.x; hi = 0;
+      total = quot = rem = 0; pos = blockIdx.x; hi = 0;
     }
   }
-  __device__ long long range_lo(long long b) const { return total * b / grid; }
+  __device__ unsigned range_lo(unsigned b) const { return quot * b + min(b, rem); }
+  // the CTA whose range holds stage x (x < total)
+  __device__ unsigned owner(unsigned x) const {
+    const unsigned big = rem * (quot + 1);       // stages held by the CTAs with one extra
+    return x < big ? x / (quot + 1) : rem + (x - big) / quot;
+  }
   // next unit of this CTA; slot = workspace slot of a partial unit
   template <int TILE_N>
   __device__ bool next(long long& tile, int& mt, int& nt, int& ks0, int& ks1, int& slot) {
     if (!split) {
       if (!tw.seek<TILE_N>(pos, mt, nt)) return false;
-      tile = pos; ks0 = 0; ks1 = ksn; slot = 0;
+      tile = pos; ks0 = 0; ks1 = (int)ksn; slot = 0;
       pos += grid;
       return true;
     }
     if (pos >= hi) return false;
-    tile = pos / ksn;
-    ks0 = (int)(pos - tile * ksn);
-    ks1 = (int)min((long long)ksn, ks0 + (hi - pos));
+    const unsigned t = pos / ksn;
+    tile = t;
+    ks0 = (int)(pos - t * ksn);
+    ks1 = (int)min(ksn, (unsigned)ks0 + (hi - pos));
     slot = 2 * (int)blockIdx.x + (pos == range_lo(blockIdx.x) ? 0 : 1);
     tw.seek<TILE_N>(tile, mt, nt);     // inside the list by construction
-    pos += ks1 - ks0;
+    pos += (unsigned)(ks1 - ks0);
     return true;
   }
 };
@@ -518,14 +528,10 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           for (int i = 0; i < kCols; ++i) __stcg(mine + i * kTileM, __uint_as_float(r[i]));
           __threadfence();
           epilogue_bar_sync();
-          // the CTAs that share this tile, first to last in K: cut points are range_lo(c), c = 0 .. grid
-          const long long t_lo = tile * p.k_stages, t_hi = t_lo + p.k_stages;
-          long long c = t_lo * walk.grid / walk.total;
-          while (c > 0 && walk.range_lo(c) > t_lo) --c;
-          while (walk.range_lo(c + 1) <= t_lo) ++c;
-          int parts = 0;
-          for (long long d = c; d < walk.grid && walk.range_lo(d) < t_hi; ++d)
-            if (walk.range_lo(d + 1) > walk.range_lo(d)) ++parts;
+          // the CTAs that share this tile, first to last in K
+          const unsigned t_lo = (unsigned)tile * walk.ksn, t_hi = t_lo + walk.ksn;
+          const unsigned c_first = walk.owner(t_lo), c_last = walk.owner(t_hi - 1);
+          const int parts = (int)(c_last - c_first + 1);        // every CTA in between holds stages of the tile
           if (ep_tid == 0) {
             const int before = atomicAdd(p.split_counters + tile, 1);
             *s_last = before == parts - 1 ? 1 : 0;
@@ -536,10 +542,8 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           __threadfence();
 #pragma unroll
           for (int i = 0; i < kCols; ++i) r[i] = 0u;
-          for (long long d = c; d < walk.grid && walk.range_lo(d) < t_hi; ++d) {
-            const long long lo_d = walk.range_lo(d);
-            if (walk.range_lo(d + 1) <= lo_d) continue;
-            const int sl = 2 * (int)d + (max(lo_d, t_lo) == lo_d ? 0 : 1);
+          for (unsigned d = c_first; d <= c_last; ++d) {
+            const int sl = 2 * (int)d + (walk.range_lo(d) >= t_lo ? 0 : 1);     // head of d's range, or its tail
             const float* part = p.split_partials + (long long)sl * kSlotFloats + m_local;
 #pragma unroll
             for (int i = 0; i < kCols; ++i)
@@ -822,10 +826,13 @@ int launch_narrow(const CUtensorMap& map_a, const CUtensorMap& map_b, Params& p,
 // Pipeline depth of a wide-tile launch: what fits beside the epilogue staging, the barriers and the
 // counts, capped by the scale-slot ring in tensor memory.
 template <class C>
-int wide_stages(int experts) {
-  const int fixed = 1024 + C::kOutBytes + C::kBarrierBytes + 4 * experts;
-  const int n = std::min(std::min((int)C::kMaxStages, (int)C::kSlots), (kSmemLimit - fixed) / C::kStageBytes);
-  return n & ~1;     // even: the two copier threads own alternate ring slots
+int wide_stages(int experts, bool fused) {
+  const int fixed = 1024 + (fused ? C::kFusedOutBytes : 0) + C::kBarrierBytes + 4 * experts;
+  int n = std::min(std::min((int)C::kMaxStages, (int)C::kSlots), (kSmemLimit - fixed) / C::kStageBytes);
+#ifdef PNV_WIDE_MAX_STAGES      // developer builds: a shallower ring, to see how the time depends on its depth
+  n = std::min(n, PNV_WIDE_MAX_STAGES);
+#endif
+  return n;
 }
 
 template <int TILE_N, int STAGE_K, bool kFused, bool kPair>
@@ -833,12 +840,12 @@ int launch_wide_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const P
                      cudaStream_t stream) {
   using C = WideCfg<TILE_N, STAGE_K, kPair>;
   Params p = p_in;
-  const int stages = wide_stages<C>(p.E);
+  const int stages = wide_stages<C>(p.E, kFused);
   if (stages < 2)
     return fail(PNV_ERR_INVALID_ARGUMENT, "group_mm: not enough shared memory for a %dx%d pipeline", TILE_N, STAGE_K);
   p.stages = stages;
   p.prod_lanes = stages >= 8 ? 4 : stages >= 4 ? 2 : 1;
-  const size_t smem = 1024 + (size_t)stages * C::kStageBytes + C::kOutBytes + C::kBarrierBytes + 4 * (size_t)p.E;
+  const size_t smem = 1024 + (size_t)stages * C::kStageBytes + (kFused ? C::kFusedOutBytes : 0) + C::kBarrierBytes + 4 * (size_t)p.E;
   static KernelSetup setup;
   int max_pairs = 0;
   if (int rc = prepare_kernel(group_mm_wide_kernel<TILE_N, STAGE_K, kFused, kPair>, setup, C::kThreads, smem, kPair,
@@ -1029,7 +1036,9 @@ int group_mm_common(void* out, const FusedArgs* fused, const uint8_t* a_comp, co
   }
   const bool pair = kind.two_sm && !narrow;
   p.k_stages = ceil_div_i(k, stage_k);
-  if (narrow && workspace != nullptr && p.k_stages > 1) {
+  // the split schedule counts K stages in 32 bits
+  const bool split_fits = (long long)experts * p.n_mt * p.k_stages < (1LL << 30);
+  if (narrow && workspace != nullptr && p.k_stages > 1 && split_fits) {
     const int64_t need = pnv_group_mm_workspace_bytes(experts, features, max_n, sm_count);
     PNV_REQUIRE(workspace_bytes >= need, "group_mm: the split-K workspace holds %lld bytes, %lld are needed",
                 (long long)workspace_bytes, (long long)need);
@@ -1078,6 +1087,17 @@ int group_mm_common(void* out, const FusedArgs* fused, const uint8_t* a_comp, co
 
 }  // namespace
 }  // namespace pnv
+
+#ifdef PNV_WIDE_PROFILE
+// developer build only: read and clear the wide kernel's cycle counters (16 per CTA, 296 CTAs)
+extern "C" int pnv_debug_wide_profile(long long* out) {
+  PNV_CUDA(cudaDeviceSynchronize());
+  PNV_CUDA(cudaMemcpyFromSymbol(out, g_wide_prof, sizeof(long long) * 296 * 16));
+  static long long zeros[296 * 16] = {};
+  PNV_CUDA(cudaMemcpyToSymbol(g_wide_prof, zeros, sizeof(zeros)));
+  return PNV_OK;
+}
+#endif
 
 extern "C" int pnv_selftest_bounded_wait(int* gave_up_out) {
   PNV_REQUIRE(gave_up_out, "null pointer argument");

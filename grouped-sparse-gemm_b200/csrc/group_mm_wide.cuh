@@ -18,11 +18,11 @@
 //            the shape tensor memory wants)
 //   2 - 3    MMA issuers (of a pair: in the first CTA only), alternate tiles, each into its own accumulator
 //            stage: per pipeline stage they wait for one barrier, issue the MMAs and commit
-//   4 - 5    copiers (one thread each, alternate pipeline stages; of a pair: in the first CTA only): tcgen05.cp of
-//            the stage's scale and metadata atoms from shared memory into the stage's slot of a ring in tensor
-//            memory, then a tcgen05.commit that tells the issuers the slot is filled.  The copies are
-//            asynchronous, so a copier spends a few dozen cycles per atom and the issuers none.  In the second
-//            CTA of a pair warp 4 only relays "my copies have landed" to the first CTA.
+//   4 - 5    copiers (one thread each; of a pair: in the first CTA only): tcgen05.cp of every stage's scale and
+//            metadata atoms from shared memory into the stage's slot of a ring in tensor memory (warp 4 the weight
+//            scales and the metadata, warp 5 the activation scales), then a tcgen05.commit that tells the issuers
+//            the slot is filled.  The copies are asynchronous and off the issuers' instruction stream.  In the
+//            second CTA of a pair warp 4 only relays "my copies have landed" to the first CTA.
 //   6 - 21   epilogue, four groups of four warps (one warp per lane quarter); a tile's chunks of token
 //            columns are dealt round-robin to the groups
 //
@@ -55,7 +55,7 @@ struct WideCfg {
   static constexpr int kSfbBytes = kSfaBytes * kSfbRowAtoms;
   static constexpr int kStageBytes = kABytes + kBBytes + kEBytes + kSfaBytes + kSfbBytes;
   static constexpr int kChunk = TILE_N >= 128 ? 32 : 16;     // token columns an epilogue group takes at a time
-  static constexpr int kOutBytes = 4 * 8192;                 // one 8 KiB staging area per epilogue group
+  static constexpr int kFusedOutBytes = 4 * 8192;            // fused epilogue: one 8 KiB exchange area per group
   static constexpr int kBarrierBytes = 1024;
   static constexpr int kMaxStages = 12;
   static constexpr int kAccStages = TILE_N == 256 ? 1 : 2;
@@ -76,6 +76,19 @@ struct WideCfg {
   static_assert(kAccStages * TILE_N <= kColSlots && kSlots >= 2, "tensor-memory column map overflows");
   static_assert(8 * (4 * kMaxStages + 2 * kAccStages) + 16 <= kBarrierBytes, "barrier block overflows");
 };
+
+// Developer build only (-DPNV_WIDE_PROFILE): per-CTA cycle counters of the roles' waits, 16 per CTA, in a buffer
+// read back with pnv_debug_wide_profile.  Not compiled into the library otherwise.
+#ifdef PNV_WIDE_PROFILE
+__device__ long long g_wide_prof[296 * 16];
+#define PNV_PROF_T() clock64()
+#define PNV_PROF_ACC(var, t0) var += clock64() - (t0)
+#define PNV_PROF_SET(slot, v) g_wide_prof[blockIdx.x * 16 + (slot)] = (v)
+#else
+#define PNV_PROF_T() 0ll
+#define PNV_PROF_ACC(var, t0) ((void)(t0), (void)(var))
+#define PNV_PROF_SET(slot, v) ((void)(v))
+#endif
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -118,15 +131,16 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_base = smem;
   uint8_t* after_stages = stage_base + p.stages * C::kStageBytes;
+  constexpr int kOutBytes = kFused ? C::kFusedOutBytes : 0;     // the plain epilogue stores from registers
   uint8_t* s_out = after_stages;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(after_stages + C::kOutBytes);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(after_stages + kOutBytes);
   uint64_t* empty_bar = full_bar + C::kMaxStages;
   uint64_t* sf_full = empty_bar + C::kMaxStages;
   uint64_t* peer_full = sf_full + C::kMaxStages;
   uint64_t* acc_full = peer_full + C::kMaxStages;
   uint64_t* acc_empty = acc_full + C::kAccStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + C::kAccStages);
-  int* s_counts = reinterpret_cast<int*>(after_stages + C::kOutBytes + C::kBarrierBytes);
+  int* s_counts = reinterpret_cast<int*>(after_stages + kOutBytes + C::kBarrierBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -142,7 +156,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     for (int s = 0; s < p.stages; ++s) {
       ptx::mbar_init(full_bar + s, 3);
       ptx::mbar_init(empty_bar + s, 1);
-      ptx::mbar_init(sf_full + s, 1);
+      ptx::mbar_init(sf_full + s, 2);
       ptx::mbar_init(peer_full + s, 1);
     }
     for (int a = 0; a < C::kAccStages; ++a) {
@@ -185,6 +199,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       uint32_t turn = 0;
       int e = 0, mt = 0, n0 = 0, sfb_row_atoms = 1;
       const uint8_t *e_base = nullptr, *sfa_base = nullptr, *sfb_base = nullptr;
+      long long pf_wait = 0;
       while (ok) {
         while (ks >= p.k_stages) { ks -= p.k_stages; ++n; }
         if (n != cur_n) {                                  // a new tile: where it is, and its operand bases
@@ -205,11 +220,13 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         }
         const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
         const int b_boxes = (k_atoms + 1) / 2;
+        const long long tp0 = PNV_PROF_T();
         if (!ptx::mbar_wait(empty_bar + stage, turn ^ 1u)) {
           atomicExch(&g_status, tile_role ? kProducerEmptyTimeout : kSideProducerTimeout);
           ok = false;
           break;
         }
+        PNV_PROF_ACC(pf_wait, tp0);                             // waiting for a free stage
         uint8_t* st = stage_base + stage * C::kStageBytes;
         if (tile_role) {
           // with the 4-D activation map one copy fetches all of the stage's 256-K chunks (a box past the
@@ -244,6 +261,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         stage += p.prod_lanes;
         if (stage >= p.stages) { stage -= p.stages; turn ^= 1u; }
       }
+      if (threadIdx.x == 0) PNV_PROF_SET(0, pf_wait);
       if (!ok) {
         // give copies already in flight time to land before the CTA's shared memory is released
 #pragma unroll 1
@@ -269,7 +287,9 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       // Pass over the stages of a tile the other issuer takes.  Each one is waited for, not just
       // counted: a parity wait only tells two consecutive phases of a barrier apart, so an issuer
       // must see every turn of every slot, or after a long tile it would take an old phase for its own.
+      long long pf_skip = 0;
       auto skip_stages = [&](int n) {
+        const long long tk0 = PNV_PROF_T();
 #pragma unroll 1
         for (int i = 0; i < n && ok; ++i) {
           if (!ptx::mbar_wait(sf_full + stage, phase)) {
@@ -279,6 +299,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
         soff = (uint32_t)stage * (C::kStageBytes >> 4);
+        PNV_PROF_ACC(pf_skip, tk0);
       };
       if (kIssuers == 2 && issuer == 1 && n_items > 1) skip_stages(p.k_stages);
       // stage-0 descriptors, split into the 32-bit halves: only the low half changes with the address
@@ -288,6 +309,8 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       const uint32_t lo_b0 = (uint32_t)d_b0, hi_b = (uint32_t)(d_b0 >> 32);
       const uint32_t slots0 = tmem_base + C::kColSlots;
       const int last_atoms = p.n_kt - (p.k_stages - 1) * C::kAtoms;     // K-blocks of a tile's last stage
+      const long long ti0 = PNV_PROF_T();
+      long long pf_acc = 0, pf_slot = 0, pf_issue = 0, pf_loop = 0;
       for (int item = kIssuers == 2 ? issuer : 0; item < n_items && ok; item += kIssuers) {
         // a 64-wide tile's scales sit 0 or 2 columns into the 128-row atom (even offsets only: the MMA
         // faults on an odd scale column); wider tiles start at column 0 and need no tile coordinates
@@ -297,22 +320,27 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           if (!walk.seek<TILE_N>(unit + (long long)item * n_units, mu, nt)) break;
           sfb_off = ((nt * TILE_N) & 127) >> 5;
         }
+        const long long ta0 = PNV_PROF_T();
         if (!ptx::mbar_wait(acc_empty + acc, acc_phase ^ 1)) {
           atomicExch(&g_status, kMmaAccTimeout);
           ok = false;
           break;
         }
+        PNV_PROF_ACC(pf_acc, ta0);                              // waiting for a free accumulator
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * TILE_N;
 #pragma unroll 1
         for (int ks = 0; ks < p.k_stages; ++ks) {
           const int k_atoms = ks + 1 == p.k_stages ? last_atoms : C::kAtoms;
+          const long long ts0 = PNV_PROF_T();
           if (!ptx::mbar_wait(sf_full + stage, phase)) {
             atomicExch(&g_status, kMmaScaleTimeout);
             ok = false;
             break;
           }
+          PNV_PROF_ACC(pf_slot, ts0);                           // waiting for a filled slot (own tiles)
           ptx::tc_fence_after();
+          const long long tm0 = PNV_PROF_T();
           // descriptors of this stage: the precomputed ones of stage 0 plus the stage's offset in
           // 16-byte units (the address field is the low 14 bits, so a 32-bit add cannot carry out)
           const uint32_t la = lo_a0 + soff, lb = lo_b0 + soff;
@@ -327,6 +355,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                                          slot + C::kSlotE + ka * 2);
           // shared-memory stage and tensor-memory slot reusable (in both CTAs of a pair) once these MMAs retire
           ptx::tc_commit_n<kCtas>(empty_bar + stage);
+          PNV_PROF_ACC(pf_issue, tm0);                          // issuing MMAs + commit
           soff += C::kStageBytes >> 4;
           if (++stage == p.stages) { stage = 0; soff = 0; phase ^= 1; }
         }
@@ -340,12 +369,17 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           acc_phase ^= 1;
         }
       }
+      PNV_PROF_ACC(pf_loop, ti0);
+      if (issuer == 0) {   // issuer 0's waits and work (it takes every other tile), its whole loop, stages of the CTA
+        PNV_PROF_SET(1, pf_acc); PNV_PROF_SET(2, pf_slot); PNV_PROF_SET(3, pf_issue); PNV_PROF_SET(4, pf_loop);
+        PNV_PROF_SET(5, (long long)n_items * p.k_stages); PNV_PROF_SET(14, pf_skip);
+      }
     }
     __syncwarp();
   } else if (warp == 4 || warp == 5) {
     // =============================== copiers ===============================
-    // Copier c takes the pipeline stages c, c + 2, ... of this CTA's (or pair's) sequence; the host keeps the ring
-    // depth even, so each ring slot always belongs to the same copier and no barrier phase goes unobserved.
+    // Both copiers take every pipeline stage and split its atoms: copier 0 the weight scales and the metadata,
+    // copier 1 the activation scales.  Each commits on the stage's sf_full barrier (two arrivals).
     const int copier = warp - 4;
     const int n_items = my_work_items<TILE_N>(s_counts, p.E, n_mu, unit, n_units, lane);
     const long long n_stages = (long long)n_items * p.k_stages;
@@ -357,37 +391,46 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       const uint32_t hi = (uint32_t)(d_e0 >> 32);           // the three descriptors differ in the address only
       const uint32_t slots0 = tmem_base + C::kColSlots;
       const int last_atoms = p.n_kt - (p.k_stages - 1) * C::kAtoms;
-      int stage = copier, ks = copier % p.k_stages;
+      int stage = 0, ks = 0;
       uint32_t phase = 0;
+      long long pf_cwait = 0, pf_cissue = 0;
 #pragma unroll 1
-      for (long long g = copier; g < n_stages; g += 2) {
+      for (long long g = 0; g < n_stages; ++g) {
+        const long long tc0 = PNV_PROF_T();
         if (!ptx::mbar_wait(full_bar + stage, phase) || (kPair && !ptx::mbar_wait(peer_full + stage, phase))) {
           atomicExch(&g_status, kScaleLoaderTimeout);
           break;
         }
+        PNV_PROF_ACC(pf_cwait, tc0);                            // waiting for landed copies
         ptx::tc_fence_after();
+        const long long tc1 = PNV_PROF_T();
         const int k_atoms = ks + 1 == p.k_stages ? last_atoms : C::kAtoms;
         const uint32_t soff = (uint32_t)stage * (C::kStageBytes >> 4);
         const uint32_t slot = slots0 + stage * C::kSlotCols;
+        if (copier == 0) {
 #pragma unroll
-        for (int ka = 0; ka < C::kAtoms; ++ka) {
-          if (ka < k_atoms) {
-            ptx::tc_cp_32x128b_warpx4<kCtas>(slot + ka * 4, pack_desc(lo_sfa0 + soff + ka * 32, hi));
+          for (int ka = 0; ka < C::kAtoms; ++ka)
+            if (ka < k_atoms) ptx::tc_cp_32x128b_warpx4<kCtas>(slot + ka * 4, pack_desc(lo_sfa0 + soff + ka * 32, hi));
 #pragma unroll
-            for (int ra = 0; ra < C::kSfbRowAtoms; ++ra)
-              ptx::tc_cp_32x128b_warpx4<kCtas>(slot + C::kSlotSfb + ka * C::kSfbColsPerAtom + ra * 4,
-                                               pack_desc(lo_sfb0 + soff + ra * (C::kSfaBytes >> 4) + ka * 32, hi));
+          for (int ea = 0; ea < C::kEAtoms; ++ea)
+            if (2 * ea < k_atoms) ptx::tc_cp_128x128b<kCtas>(slot + C::kSlotE + ea * 4, pack_desc(lo_e0 + soff + ea * 128, hi));
+        } else {
+#pragma unroll
+          for (int ka = 0; ka < C::kAtoms; ++ka) {
+            if (ka < k_atoms) {
+#pragma unroll
+              for (int ra = 0; ra < C::kSfbRowAtoms; ++ra)
+                ptx::tc_cp_32x128b_warpx4<kCtas>(slot + C::kSlotSfb + ka * C::kSfbColsPerAtom + ra * 4,
+                                                 pack_desc(lo_sfb0 + soff + ra * (C::kSfaBytes >> 4) + ka * 32, hi));
+            }
           }
         }
-#pragma unroll
-        for (int ea = 0; ea < C::kEAtoms; ++ea)
-          if (2 * ea < k_atoms) ptx::tc_cp_128x128b<kCtas>(slot + C::kSlotE + ea * 4, pack_desc(lo_e0 + soff + ea * 128, hi));
         ptx::tc_commit_local<kCtas>(sf_full + stage);     // arrives once the copies above have completed
-        ks += 2;
-        while (ks >= p.k_stages) ks -= p.k_stages;
-        stage += 2;
-        if (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
+        PNV_PROF_ACC(pf_cissue, tc1);                           // issuing copies
+        if (++ks == p.k_stages) ks = 0;
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
       }
+      if (copier == 0) { PNV_PROF_SET(6, pf_cwait); PNV_PROF_SET(7, pf_cissue); }
     } else if (kPair && lane == 0 && rank != 0 && copier == 0) {
       // second CTA of a pair: tell the first when each stage's copies have landed here
       int stage = 0;
@@ -408,7 +451,6 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const int group = (warp - C::kFirstEpilogueWarp) >> 2;   // chunks of kChunk token columns are dealt to the four groups in turn
     const int sub = warp & 3;                  // tensor-memory lane quarter this warp may read
     const int m_local = sub * 32 + lane;       // accumulator row (output feature) held by this thread
-    const bool vec_ok = (p.M % 8) == 0;        // 16-byte aligned output rows: needed by the bulk stores
     uint8_t* gbuf = s_out + group * 8192;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -455,6 +497,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         else ptx::mbar_arrive(acc_empty + acc);
       }
     };
+    long long pf_ewait = 0, pf_ework = 0, pf_f0 = 0, pf_f1 = 0, pf_f2 = 0, pf_f3 = 0;
     for (long long w = unit;; w += n_units) {
       int mu, nt;
       if (!walk.seek<TILE_N>(w, mu, nt)) break;
@@ -464,56 +507,48 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       const bool mt_valid = mt < p.n_mt;       // the second CTA of the last pair of an odd tile count stores nothing
       const float alpha = p.alphas[e];
       const int n0 = nt * TILE_N;
+      const long long te0 = PNV_PROF_T();
       if (!ptx::mbar_wait(acc_full + acc, acc_phase)) {
         atomicExch(&g_status, kEpilogueTimeout);
         break;
       }
+      PNV_PROF_ACC(pf_ewait, te0);                              // waiting for an accumulator
+      const long long te1 = PNV_PROF_T();
       ptx::tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(sub * 32) << 16) + acc * TILE_N;
       bool released = false;
       if (!kFused) {
-        // Plain epilogue.  A group (four warps = all 128 features of the tile) takes kChunk token columns:
-        // scale, round to bf16 and transpose into the group's staging area as [token][128 features], rows of
-        // 256 bytes; then a few lanes issue one bulk copy shared -> global per live token row (256
-        // contiguous bytes; rows at or past counts[e] get no copy) and the warps go straight back to the
-        // next tensor-memory load.  The staging area is reused once the earlier copies have read it.
-        __nv_bfloat16* buf = reinterpret_cast<__nv_bfloat16*>(gbuf);
-        constexpr int kRowsPerWarp = kChunk / 4;
+        // Plain epilogue.  A warp holds 32 features x kChunk tokens of the accumulator; it scales, rounds to bf16
+        // and stores straight from registers, one instruction per token: 32 lanes x 2 bytes = 64 contiguous
+        // bytes of that token's output row (two whole 32-byte sectors; the neighbouring lane quarters of the same
+        // group fill the rest of the line at about the same time).  No shared memory, no barrier, nothing to wait
+        // for: the warp goes straight back to the next tensor-memory load.  Rows at or past counts[e] are skipped.
         __nv_bfloat16* out_e = p.out + (long long)e * p.max_n * p.M;
-        const int m0 = mt * kTileM;
-#pragma unroll 1
-        for (int c0 = group * kChunk; c0 < TILE_N && n0 + c0 < cnt; c0 += 4 * kChunk) {
-          uint32_t v[kChunk];
-          tc_ld_cols<kChunk>(t_row + c0, v);
-          ptx::tc_ld_wait();
-          if (c0 + 4 * kChunk >= TILE_N || n0 + c0 + 4 * kChunk >= cnt) { release_acc(); released = true; }
-          if (!mt_valid) continue;
-          if (vec_ok) {
-            if (lane < kRowsPerWarp) ptx::bulk_wait_read_all();
-            named_bar_sync(1 + group, 128);
+        const int m = mt * kTileM + m_local;
+        constexpr int kOwn = TILE_N / (4 * kChunk);       // chunks of a tile each group takes (1, or 2 for 256 tokens)
+        uint32_t v[kOwn][kChunk];
 #pragma unroll
-            for (int i = 0; i < kChunk; ++i)
-              buf[i * kTileM + m_local] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(v[i])));
-            ptx::fence_proxy_async_smem();
-            named_bar_sync(1 + group, 128);
-            if (lane < kRowsPerWarp) {
-              const int row = sub * kRowsPerWarp + lane;
-              const int n = n0 + c0 + row;
-              if (n < cnt) {
-                const int feats = min(kTileM, p.M - m0);
-                ptx::bulk_store(out_e + (long long)n * p.M + m0, buf + row * kTileM, (uint32_t)feats * 2u);
-              }
-              ptx::bulk_commit();
-            }
-          } else {
-            const int m = m0 + m_local;
-            if (m < p.M) {
+        for (int j = 0; j < kOwn; ++j) {
+          const int c0 = (group + 4 * j) * kChunk;
+          if (n0 + c0 < cnt) tc_ld_cols<kChunk>(t_row + c0, v[j]);     // the same for all lanes
+        }
+        ptx::tc_ld_wait();
+        release_acc();                                    // the issuers may reuse the accumulator while this warp stores
+        released = true;
 #pragma unroll
-              for (int i = 0; i < kChunk; ++i) {
-                const int n = n0 + c0 + i;
-                if (n < cnt) out_e[(long long)n * p.M + m] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(v[i])));
-              }
-            }
+        for (int j = 0; j < kOwn; ++j) {
+          const int c0 = (group + 4 * j) * kChunk;
+          const int live = (mt_valid && m < p.M) ? min(kChunk, cnt - (n0 + c0)) : 0;       // <= 0: nothing to store
+          unsigned short* dst = reinterpret_cast<unsigned short*>(out_e + (long long)(n0 + c0) * p.M + m);
+          const long long pitch = p.M;
+#pragma unroll
+          for (int i = 0; i < kChunk; i += 2) {
+            // two tokens per conversion (cvt.rn.bf16x2.f32: first argument in the low half)
+            const __nv_bfloat162 pr = __floats2bfloat162_rn(__fmul_rn(alpha, __uint_as_float(v[j][i])),
+                                                           __fmul_rn(alpha, __uint_as_float(v[j][i + 1])));
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(&pr);
+            if (i < live) dst[(long long)i * pitch] = (unsigned short)(w & 0xFFFFu);
+            if (i + 1 < live) dst[(long long)(i + 1) * pitch] = (unsigned short)(w >> 16);
           }
         }
       } else {
@@ -537,10 +572,13 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 #pragma unroll 1
         for (int c0 = group * kChunk; c0 < TILE_N && n0 + c0 < cnt; c0 += 4 * kChunk) {
           uint32_t v[kChunk];
+          const long long tf0 = PNV_PROF_T();
           tc_ld_cols<kChunk>(t_row + c0, v);
           ptx::tc_ld_wait();
           if (c0 + 4 * kChunk >= TILE_N || n0 + c0 + 4 * kChunk >= cnt) { release_acc(); released = true; }
-          if (!mt_valid) continue;
+          PNV_PROF_ACC(pf_f0, tf0);                // tensor-memory load
+          if (!mt_valid) continue;                 // the same for every thread of the CTA
+          const long long tf1 = PNV_PROF_T();
           float h[kChunk];
 #pragma unroll
           for (int i = 0; i < kChunk; ++i)
@@ -549,6 +587,8 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 #pragma unroll
           for (int k = 0; k < kHalf; ++k) x_mine[k * 32 + lane] = __float2bfloat16_rn(is_up ? h[2 * k] : h[2 * k + 1]);
           named_bar_sync(pair_bar, 64);
+          PNV_PROF_ACC(pf_f1, tf1);                // round, park for the partner, both pair barriers
+          const long long tf2 = PNV_PROF_T();
           float o[kHalf];
 #pragma unroll
           for (int k = 0; k < kHalf; ++k) o[k] = __bfloat162float(x_other[k * 32 + lane]);
@@ -564,6 +604,8 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             for (int k = 0; k < kHalf; ++k)
               y[k] = __float2bfloat16_rn(gated_act(is_up ? o[k] : h[2 * k], is_up ? h[2 * k + 1] : o[k], p.f_act));
           }
+          PNV_PROF_ACC(pf_f2, tf2);                // partner's values in, activation
+          const long long tf3 = PNV_PROF_T();
           __syncwarp();                          // every lane has finished reading the previous chunk's results
 #pragma unroll
           for (int k = 0; k < kHalf; ++k) y_mine[k * 32 + lane] = y[k];
@@ -593,13 +635,17 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
               if (hb == 0) p.f_sfb_out[sf_offset(e, n, kb, p.sfb_rt, p.f_n_kt)] = (uint8_t)sf_byte;
             }
           }
+          PNV_PROF_ACC(pf_f3, tf3);                // transpose, quantize, store
         }
       }
       if (!released) release_acc();
+      PNV_PROF_ACC(pf_ework, te1);                              // this group's share of the tile
       if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
     }
-    // shared memory may only be given back once the bulk copies out of it have read it
-    if (!kFused) ptx::bulk_wait_all();
+    if (group == 0 && sub == 0 && lane == 0) {
+      PNV_PROF_SET(8, pf_ewait); PNV_PROF_SET(9, pf_ework);
+      PNV_PROF_SET(10, pf_f0); PNV_PROF_SET(11, pf_f1); PNV_PROF_SET(12, pf_f2); PNV_PROF_SET(13, pf_f3);
+    }
   }
 
   ptx::tc_fence_before();

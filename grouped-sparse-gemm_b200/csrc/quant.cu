@@ -191,8 +191,34 @@ __device__ __forceinline__ uint4 block_codes(const BlockRegs& b, float inv) {
   return make_uint4(quant8(b.f[0], inv), quant8(b.f[1], inv), quant8(b.f[2], inv), quant8(b.f[3], inv));
 }
 
-// One warp per routing: the whole row, 32 K-blocks (1024 elements) at a time, one block per lane; a
-// row's four scales of one 128-K group are one aligned word of the swizzled layout.
+// One routed row by one warp: 32 K-blocks (1024 elements) at a time, one block per lane; a row's four scales
+// of one 128-K group are one aligned word of the swizzled layout.  `w` is the (already bf16-rounded) router
+// weight when `weighted`.
+__device__ __forceinline__ void quantize_routed_row(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                                                    uint8_t* __restrict__ sf_row, int KB, float gs, bool weighted,
+                                                    float w, int lane) {
+  for (int kb0 = 0; kb0 < KB; kb0 += 32) {
+    const int kb = kb0 + lane;
+    uint32_t sf_byte = kBenignSf;   // blocks past K keep the benign byte in the layout's slop
+    if (kb < KB) {
+      BlockRegs b;
+      load_block(src + kb * 4, b);
+      if (weighted) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+          for (int z = 0; z < 8; ++z) b.f[q][z] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(b.f[q][z], w)));
+      }
+      float inv;
+      block_scale(block_amax(b), gs, sf_byte, inv);
+      dst[kb] = block_codes(b, inv);
+    }
+    const uint32_t word = gather_sf_word(sf_byte);
+    if ((lane & 3) == 0 && kb < KB) *reinterpret_cast<uint32_t*>(sf_row + (kb >> 2) * 512) = word;
+  }
+}
+
+// scatter_quant_act: one warp per routing of the flat plan.
 __global__ void __launch_bounds__(kThreads)
 scatter_quant_kernel(const __nv_bfloat16* __restrict__ a1, const long long* __restrict__ flat_tok,
                      const long long* __restrict__ dest_global, const float* __restrict__ topk_w,
@@ -215,28 +241,44 @@ scatter_quant_kernel(const __nv_bfloat16* __restrict__ a1, const long long* __re
     const float gs = gscale_per_expert ? gscale[e] : gscale[0];
     const bool weighted = topk_w != nullptr;
     const float w = weighted ? __bfloat162float(__float2bfloat16_rn(topk_w[i])) : 1.f;
-    const uint4* src = reinterpret_cast<const uint4*>(a1 + flat_tok[i] * K);
-    uint4* dst = reinterpret_cast<uint4*>(b_act + dest * (K / 2));
-    uint8_t* sf_row = sfb + sf_offset(e, r, 0, n_rt, n_kt);   // K-block kb of this row: + (kb >> 2) * 512 + (kb & 3)
-    for (int kb0 = 0; kb0 < KB; kb0 += 32) {
-      const int kb = kb0 + lane;
-      uint32_t sf_byte = kBenignSf;   // blocks past K keep the benign byte in the layout's slop
-      if (kb < KB) {
-        BlockRegs b;
-        load_block(src + kb * 4, b);
-        if (weighted) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-#pragma unroll
-            for (int z = 0; z < 8; ++z) b.f[q][z] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(b.f[q][z], w)));
-        }
-        float inv;
-        block_scale(block_amax(b), gs, sf_byte, inv);
-        dst[kb] = block_codes(b, inv);
-      }
-      const uint32_t word = gather_sf_word(sf_byte);
-      if ((lane & 3) == 0 && kb < KB) *reinterpret_cast<uint32_t*>(sf_row + (kb >> 2) * 512) = word;
+    quantize_routed_row(reinterpret_cast<const uint4*>(a1 + flat_tok[i] * K),
+                        reinterpret_cast<uint4*>(b_act + dest * (K / 2)), sfb + sf_offset(e, r, 0, n_rt, n_kt), KB, gs,
+                        weighted, w, lane);
+  }
+}
+
+// scatter_quant_act_planned: one warp per row slot (e, r) of the batched operand; slots at or past counts[e] are
+// skipped (their scales keep the benign fill laid down before the launch).
+__global__ void __launch_bounds__(kThreads)
+scatter_planned_rows_kernel(const __nv_bfloat16* __restrict__ a1, const int* __restrict__ src_tok,
+                            const int* __restrict__ src_route, const float* __restrict__ topk_w,
+                            const float* __restrict__ gscale, int gscale_per_expert, const int* __restrict__ counts,
+                            int K, int E, int cap, uint8_t* __restrict__ b_act, uint8_t* __restrict__ sfb) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int KB = K / kSfBlock;
+  const int n_rt = sf_row_atoms(cap);
+  const int n_kt = sf_k_atoms(K);
+  const int lane = threadIdx.x & 31;
+  const unsigned slots = (unsigned)E * (unsigned)cap;
+  const unsigned warp0 = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const unsigned nwarps = gridDim.x * kWarpsPerBlock;
+  for (unsigned slot = warp0; slot < slots; slot += nwarps) {
+    const int e = (int)(slot / (unsigned)cap);
+    const int r = (int)(slot - (unsigned)e * (unsigned)cap);
+    if (r >= min(counts[e], cap)) {
+      // jump to the next expert's first slot that this warp owns
+      const unsigned next = (unsigned)(e + 1) * (unsigned)cap;
+      const unsigned skip = (next - slot + nwarps - 1) / nwarps;
+      slot += (skip - 1) * nwarps;
+      continue;
     }
+    const float gs = gscale_per_expert ? gscale[e] : gscale[0];
+    const bool weighted = topk_w != nullptr;
+    const float w = weighted ? __bfloat162float(__float2bfloat16_rn(topk_w[src_route[slot]])) : 1.f;
+    quantize_routed_row(reinterpret_cast<const uint4*>(a1 + (long long)src_tok[slot] * K),
+                        reinterpret_cast<uint4*>(b_act + (long long)slot * (K / 2)), sfb + sf_offset(e, r, 0, n_rt, n_kt),
+                        KB, gs, weighted, w, lane);
   }
 }
 
@@ -503,12 +545,13 @@ extern "C" int pnv_scatter_quant_act_planned(const void* a1, const int32_t* src_
   PNV_REQUIRE(cap > 0, "cap must be positive");
   PNV_REQUIRE(src_tok && src_route, "null pointer argument");
   if (int rc = check_common(a1, gscale, counts, experts, cap, k, b_act, sfb, "K")) return rc;
-  long long lines = sf_numel(cap, k, experts) / 16;
-  GatedAct act{PNV_ACT_SILU, 1.f, -1.f, nullptr};
-  PlanArgs plan{src_tok, src_route, topk_weights, nullptr, nullptr, 0, 0};
-  PNV_CUDA(launch_pdl(quant_lines_kernel<kPlanned>, dim3(grid_for(lines, sm_count)), dim3(kThreads), 0,
-                      (cudaStream_t)stream, pdl_enabled(), (const __nv_bfloat16*)a1, gscale, gscale_per_expert,
-                      counts, experts, cap, k, 0, act, plan, b_act, sfb));
+  PNV_REQUIRE((long long)experts * cap < (1LL << 31), "E * cap must fit int32");
+  cudaStream_t s = (cudaStream_t)stream;
+  // benign fill first, then one warp per live row writes its scales over it
+  PNV_CUDA(cudaMemsetAsync(sfb, kBenignSf, (size_t)sf_numel(cap, k, experts), s));
+  PNV_CUDA(launch_pdl(scatter_planned_rows_kernel, dim3(grid_for((long long)experts * cap, sm_count)), dim3(kThreads), 0, s,
+                      false, (const __nv_bfloat16*)a1, (const int*)src_tok, (const int*)src_route, topk_weights, gscale,
+                      gscale_per_expert, (const int*)counts, k, experts, cap, b_act, sfb));
   return PNV_OK;
 }
 

@@ -109,11 +109,10 @@ def built_archs():
 
 
 def is_available():
-    """True iff the current CUDA device is an sm_100 part and the ops are registered."""
-    if _current_sm() != _LOADED_SM:
-        return False
-    ns = getattr(torch.ops, "paired_nvfp4", None)
-    return ns is not None and hasattr(ns, "group_mm") and hasattr(ns, "compress")
+    """Can the ops run here?  Needs a CUDA device of the architecture the library was built for (the
+    operators themselves are registered at import, or the import would have failed)."""
+    return _current_sm() == _LOADED_SM and all(
+        hasattr(torch.ops.paired_nvfp4, op) for op in ("compress", "quant_act", "group_mm"))
 
 
 def group_mm_configs():
@@ -121,18 +120,18 @@ def group_mm_configs():
     return list(torch.ops.paired_nvfp4.group_mm_configs())
 
 
-def _is_2sm(config_name):
-    return config_name.split("_")[1] == "2sm"   # sparse_<sm mode>_<TileM>x<TileN>
+def _needs_cta_pair(config_name):
+    """Variant names read <kind>_<1sm|2sm>_<rows>x<tokens>[_k512]; "2sm" variants run on pairs of CTAs."""
+    fields = config_name.split("_")
+    return len(fields) > 1 and fields[1] == "2sm"
 
 
 def valid_clusters(config_name, max_product=16):
-    """Legal (cluster_m, cluster_n) pairs for one tile variant (2SM names need an even cluster_m)."""
-    out = []
-    for cm in _CLUSTER_DIMS:
-        if _is_2sm(config_name) and cm % 2:
-            continue
-        out.extend((cm, cn) for cn in _CLUSTER_DIMS if cm * cn <= max_product)
-    return out
+    """(cluster_m, cluster_n) pairs the op accepts for one tile variant: both from {1, 2, 4}, product at most
+    max_product, and an even cluster_m where the variant runs on CTA pairs."""
+    pair = _needs_cta_pair(config_name)
+    return [(cm, cn) for cm in _CLUSTER_DIMS for cn in _CLUSTER_DIMS
+            if cm * cn <= max_product and not (pair and cm % 2 == 1)]
 
 
 def all_tactics(max_cluster_product=16):
@@ -152,12 +151,14 @@ def interleave_gate_up_rows(n, device=None):
 
 
 def fused_swiglu_tactics(max_cluster_product=16):
-    """Candidate (config_id, cluster_m, cluster_n) for group_mm_swiglu_quant."""
-    ns = torch.ops.paired_nvfp4
-    if not hasattr(ns, "group_mm_swiglu_configs"):
+    """Candidate (config_id, cluster_m, cluster_n) for group_mm_swiglu_quant; empty if the fused op is absent."""
+    configs = getattr(torch.ops.paired_nvfp4, "group_mm_swiglu_configs", None)
+    if configs is None:
         return []
-    return [(cid, cm, cn) for cid, name in enumerate(ns.group_mm_swiglu_configs())
-            for cm, cn in valid_clusters(name, max_cluster_product)]
+    tactics = []
+    for cid, name in enumerate(configs()):
+        tactics.extend((cid, cm, cn) for cm, cn in valid_clusters(name, max_cluster_product))
+    return tactics
 
 
 def suggest_tactic(max_n):

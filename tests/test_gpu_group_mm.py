@@ -123,7 +123,7 @@ SPLIT_CASES = [
     (8, 512, 2048, 8, [0, 0, 0, 7, 0, 0, 0, 0]),  # one active expert: most CTAs get an empty range
     (1, 128, 2176, 32, [32]),                     # K = 4 stages + a short tail stage that is a unit of its own
     (3, 384, 14336, 16, [16, 1, 9]),              # long K, tiles cut at arbitrary stages
-    (32, 4096, 7168, 1, [0] * 10 + [1] + [0] * 21),   # one token on one of 32 experts (an expert-parallel decode rank)
+    (8, 1024, 7168, 1, [0, 0, 0, 1, 0, 0, 0, 0]),   # one token on one expert (an expert-parallel decode rank)
 ]
 
 
