@@ -10,7 +10,7 @@ second, long enough for the clock sampler to see them; the line says how many).
 Headline workload (every N, so that a 1-2-4-8 series is one curve): c4, the expert-parallel DeepSeek-V3-shaped
 layer - 256 experts sharded over the N ranks, 8192 tokens per rank, top-8.  A pass is the whole layer: slab
 plan -> quant_rows -> pack_wire_rows -> all-to-all -> dispatch_plan -> scatter_fp4_wire -> group_mm (gate_up,
-fused SwiGLU + quantize) -> group_mm (down) -> gather_rows -> all-to-all -> moe_finalize, with fresh routing
+fused SwiGLU + quantize) -> zero_rows + group_mm_rows (down, rows straight into return order) -> all-to-all -> moe_finalize, with fresh routing
 work inside the pass.  At N = 1 the two all-to-alls are the identity and everything else is the same code.
 `value` is dense-equivalent TFLOP/s of the two grouped GEMMs over the kept rows of all ranks, inputs resident
 in HBM; `e2e` is the same with the tokens in pinned host memory (copy in, layer, copy out, inside the timed
@@ -644,7 +644,7 @@ def run_cpu_baseline(host_sample, inputs, counts, layer, budget_s=12.0):
 # ------------------------------------------------------------------------------------------------
 
 EP_PHASES = ("send_plan", "quant_rows", "pack_wire_rows", "all_to_all_dispatch", "dispatch_plan", "scatter_fp4_wire",
-             "group_mm_gate_up", "group_mm_down", "gather_rows", "all_to_all_combine", "moe_finalize")
+             "group_mm_gate_up", "zero_rows", "group_mm_down", "all_to_all_combine", "moe_finalize")
 
 
 def run_expert_parallel(args, wl_name, wl, rank, world, local_rank, device):
@@ -817,7 +817,7 @@ def run_expert_parallel(args, wl_name, wl, rank, world, local_rank, device):
         "roofline": dominant, "rooflines": {"group_mm_gate_up": r13, "group_mm_down": r2},
         "ep_parity": parity, "cpu_baseline": None, "e2e": e2e,
         # our kernels per pass: 2 x dispatch_plan (3 launches each), quant_rows, pack_wire_rows, scatter_fp4_wire, 2 x group_mm,
-        # gather_rows, moe_finalize (the all-to-alls are NCCL's)
+        # zero_rows, moe_finalize (the all-to-alls are NCCL's)
         "gpu_launches": 13 * passes * args.steps,
         "clocks": clocks.summary(),
     }

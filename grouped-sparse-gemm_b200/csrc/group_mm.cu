@@ -110,6 +110,9 @@ struct Params {
   const float* alphas;
   const int* counts;
   __nv_bfloat16* out;
+  // plain epilogue: token row (e, n) is written to output row row_map[e * max_n + n] of a [rows, M] output,
+  // and not at all where the map is negative; nullptr = row e * max_n + n
+  const int* row_map;
   int E, M, K, max_n;
   int n_mt;          // ceil(M / 128)
   int k_stages;      // ceil(K / STAGE_K)
@@ -495,7 +498,7 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       ptx::tc_fence_after();
       const float alpha = p.alphas[e];
       const int n0 = nt * TILE_N;
-      __nv_bfloat16* out_e = p.out + (long long)e * p.max_n * p.M;
+      const long long row_e = (long long)e * p.max_n;
       // Issuers whose partial accumulators hold something for this unit.  Every issuer has K-blocks in a full
       // stage; in the (shorter) last stage of a tile the later issuers may have none, and a unit that is just
       // that stage never touched their accumulators.
@@ -628,9 +631,11 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           for (int j = 0; j < 4; ++j) {
             const int row = (ep_tid >> 4) + 8 * j;
             const int n = n0 + c0 + row;
-            if (n < cnt && m < p.M)
-              *reinterpret_cast<uint4*>(out_e + (long long)n * p.M + m) =
-                  *reinterpret_cast<const uint4*>(buf + row * kOutRow + col);
+            if (n < cnt && m < p.M) {
+              const long long to = p.row_map ? (long long)p.row_map[row_e + n] : row_e + n;
+              if (to >= 0)
+                *reinterpret_cast<uint4*>(p.out + to * p.M + m) = *reinterpret_cast<const uint4*>(buf + row * kOutRow + col);
+            }
           }
           ++chunk;
         } else {
@@ -639,8 +644,10 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
             for (int i = 0; i < (TILE_N < 32 ? TILE_N : 32); ++i) {
               const int n = n0 + c0 + i;
-              if (n < cnt)
-                out_e[(long long)n * p.M + m] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(r[i])));
+              if (n < cnt) {
+                const long long to = p.row_map ? (long long)p.row_map[row_e + n] : row_e + n;
+                if (to >= 0) p.out[to * p.M + m] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(r[i])));
+              }
             }
           }
         }
@@ -974,7 +981,7 @@ const FusedKind kFusedKinds[] = {
 };
 constexpr int kNumFusedKinds = sizeof(kFusedKinds) / sizeof(kFusedKinds[0]);
 
-int group_mm_common(void* out, const FusedArgs* fused, const uint8_t* a_comp, const uint8_t* e_meta,
+int group_mm_common(void* out, const int32_t* row_map, const FusedArgs* fused, const uint8_t* a_comp, const uint8_t* e_meta,
                     const uint8_t* sfa, const uint8_t* b_act, const uint8_t* sfb, const float* alphas,
                     const int32_t* counts, int experts, int features, int k, int max_n, int config_id,
                     int cluster_m, int cluster_n, int sm_count, int pdl, void* workspace, int64_t workspace_bytes,
@@ -1008,6 +1015,7 @@ int group_mm_common(void* out, const FusedArgs* fused, const uint8_t* a_comp, co
   Params p;
   p.e_meta = e_meta; p.sfa = sfa; p.sfb = sfb; p.alphas = alphas; p.counts = counts;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.row_map = row_map;
   p.f_b_out = nullptr; p.f_sfb_out = nullptr; p.f_gscale = nullptr; p.f_gpe = 0; p.f_n = 0; p.f_n_kt = 0;
   p.f_act = GatedAct{PNV_ACT_SILU, 1.f, -1.f, nullptr};
   if (fused != nullptr) {
@@ -1116,7 +1124,18 @@ extern "C" int pnv_group_mm(void* out, const uint8_t* a_comp, const uint8_t* e_m
                             const int32_t* counts, int experts, int features, int k, int max_n,
                             int config_id, int cluster_m, int cluster_n, int sm_count, int pdl,
                             void* workspace, int64_t workspace_bytes, pnv_stream_t stream) {
-  return group_mm_common(out, nullptr, a_comp, e_meta, sfa, b_act, sfb, alphas, counts, experts, features, k,
+  return group_mm_common(out, nullptr, nullptr, a_comp, e_meta, sfa, b_act, sfb, alphas, counts, experts, features, k,
+                         max_n, config_id, cluster_m, cluster_n, sm_count, pdl, workspace, workspace_bytes, stream,
+                         nullptr);
+}
+
+extern "C" int pnv_group_mm_rows(void* out, const int32_t* row_map, const uint8_t* a_comp, const uint8_t* e_meta,
+                                 const uint8_t* sfa, const uint8_t* b_act, const uint8_t* sfb, const float* alphas,
+                                 const int32_t* counts, int experts, int features, int k, int max_n, int config_id,
+                                 int cluster_m, int cluster_n, int sm_count, int pdl, void* workspace,
+                                 int64_t workspace_bytes, pnv_stream_t stream) {
+  PNV_REQUIRE(row_map, "null pointer argument");
+  return group_mm_common(out, row_map, nullptr, a_comp, e_meta, sfa, b_act, sfb, alphas, counts, experts, features, k,
                          max_n, config_id, cluster_m, cluster_n, sm_count, pdl, workspace, workspace_bytes, stream,
                          nullptr);
 }
@@ -1148,6 +1167,6 @@ extern "C" int pnv_group_mm_swiglu_quant(uint8_t* b_out, uint8_t* sfb_out, const
   PNV_REQUIRE(experts >= 1 && max_n >= 1, "experts and max_n must be positive");
   PNV_REQUIRE(sf_numel(max_n, features / 2, experts) < (1LL << 31), "sfb_out must be smaller than 2 GiB");
   const FusedKind& fk = kFusedKinds[config_id];
-  return group_mm_common(b_out, &f, a_comp, e_meta, sfa, b_act, sfb, alphas, counts, experts, features, k, max_n,
+  return group_mm_common(b_out, nullptr, &f, a_comp, e_meta, sfa, b_act, sfb, alphas, counts, experts, features, k, max_n,
                          fk.base_config, cluster_m, cluster_n, sm_count, pdl, workspace, workspace_bytes, stream, fk.name);
 }

@@ -454,6 +454,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     uint8_t* gbuf = s_out + group * 8192;
     int acc = 0;
     uint32_t acc_phase = 0;
+    int flip = 0;                              // fused epilogue: which of the two exchange areas the next chunk uses
     if (kFused) {
       // Benign fill of GEMM2's scale buffer: every byte the epilogues will not write (rows at or
       // past counts[e], K-block slop) becomes 0x38.  All CTAs share the lines; live slots are
@@ -523,52 +524,81 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         // bytes of that token's output row (two whole 32-byte sectors; the neighbouring lane quarters of the same
         // group fill the rest of the line at about the same time).  No shared memory, no barrier, nothing to wait
         // for: the warp goes straight back to the next tensor-memory load.  Rows at or past counts[e] are skipped.
-        __nv_bfloat16* out_e = p.out + (long long)e * p.max_n * p.M;
+        const long long row_e = (long long)e * p.max_n;
         const int m = mt * kTileM + m_local;
         constexpr int kOwn = TILE_N / (4 * kChunk);       // chunks of a tile each group takes (1, or 2 for 256 tokens)
-        uint32_t v[kOwn][kChunk];
+        const bool mine = mt_valid && m < p.M;
+        const long long pitch = p.M;
+        // the warp's share of the tile, scaled and rounded, two tokens to a register (cvt.rn.bf16x2.f32: first
+        // argument in the low half): kept packed so that two chunks fit under this kernel's register cap
+        uint32_t pk[kOwn][kChunk / 2];
 #pragma unroll
         for (int j = 0; j < kOwn; ++j) {
           const int c0 = (group + 4 * j) * kChunk;
-          if (n0 + c0 < cnt) tc_ld_cols<kChunk>(t_row + c0, v[j]);     // the same for all lanes
+          if (n0 + c0 < cnt) {                            // the same for all lanes
+            uint32_t v[kChunk];
+            tc_ld_cols<kChunk>(t_row + c0, v);
+            ptx::tc_ld_wait();
+#pragma unroll
+            for (int i = 0; i < kChunk; i += 2) {
+              const __nv_bfloat162 pr = __floats2bfloat162_rn(__fmul_rn(alpha, __uint_as_float(v[i])),
+                                                             __fmul_rn(alpha, __uint_as_float(v[i + 1])));
+              pk[j][i / 2] = *reinterpret_cast<const uint32_t*>(&pr);
+            }
+          }
         }
-        ptx::tc_ld_wait();
         release_acc();                                    // the issuers may reuse the accumulator while this warp stores
         released = true;
 #pragma unroll
         for (int j = 0; j < kOwn; ++j) {
           const int c0 = (group + 4 * j) * kChunk;
-          const int live = (mt_valid && m < p.M) ? min(kChunk, cnt - (n0 + c0)) : 0;       // <= 0: nothing to store
-          unsigned short* dst = reinterpret_cast<unsigned short*>(out_e + (long long)(n0 + c0) * p.M + m);
-          const long long pitch = p.M;
+          const int rows = cnt - (n0 + c0);               // live token rows from c0 on
+          if (rows <= 0) continue;
+          if (p.row_map == nullptr) {
+            const int live = mine ? min(kChunk, rows) : 0;
+            unsigned short* dst = reinterpret_cast<unsigned short*>(p.out + (row_e + n0 + c0) * p.M + m);
 #pragma unroll
-          for (int i = 0; i < kChunk; i += 2) {
-            // two tokens per conversion (cvt.rn.bf16x2.f32: first argument in the low half)
-            const __nv_bfloat162 pr = __floats2bfloat162_rn(__fmul_rn(alpha, __uint_as_float(v[j][i])),
-                                                           __fmul_rn(alpha, __uint_as_float(v[j][i + 1])));
-            const uint32_t w = *reinterpret_cast<const uint32_t*>(&pr);
-            if (i < live) dst[(long long)i * pitch] = (unsigned short)(w & 0xFFFFu);
-            if (i + 1 < live) dst[(long long)(i + 1) * pitch] = (unsigned short)(w >> 16);
+            for (int i = 0; i < kChunk; i += 2) {
+              const uint32_t w = pk[j][i / 2];
+              if (i < live) dst[(long long)i * pitch] = (unsigned short)(w & 0xFFFFu);
+              if (i + 1 < live) dst[(long long)(i + 1) * pitch] = (unsigned short)(w >> 16);
+            }
+          } else {
+            // lane i holds the output row of the chunk's token i (kChunk <= 32); -1 past the live rows
+            const int to_lane = lane < rows ? p.row_map[row_e + n0 + c0 + lane] : -1;
+            unsigned short* base = reinterpret_cast<unsigned short*>(p.out) + m;
+#pragma unroll
+            for (int i = 0; i < kChunk; i += 2) {
+              const uint32_t w = pk[j][i / 2];
+              const int to0 = __shfl_sync(0xffffffffu, to_lane, i), to1 = __shfl_sync(0xffffffffu, to_lane, i + 1);
+              if (mine && to0 >= 0) base[(long long)to0 * pitch] = (unsigned short)(w & 0xFFFFu);
+              if (mine && to1 >= 0) base[(long long)to1 * pitch] = (unsigned short)(w >> 16);
+            }
           }
         }
       } else {
         // Fused epilogue.  The weight rows are interleaved in 64-row blocks (32 gate rows, then the 32
         // matching up rows), so of a warp pair (lane quarters 0-1 or 2-3) one warp holds the gates and the
         // other the ups of the same 32 output features: exactly one quantization block per token.  The
-        // pair splits the chunk's tokens: the gate warp finishes the even ones, the up warp the odd ones.
-        // Each parks the values its partner needs ([token pair][feature], 64-byte rows), computes the
-        // activation for its own tokens from its registers and the partner's parked values, transposes the
-        // results through a private corner of shared memory, and then two adjacent lanes quantize one
-        // (token, 32-feature block): 16 features each, the block amax by one shuffle.
+        // pair splits the chunk's tokens: the gate warp finishes the first half, the up warp the second.
+        // Each parks the half its partner needs (bf16 pairs, [token pair][feature]; two areas used in turn, so
+        // one barrier per chunk is enough) and computes the activation for its own tokens.  Everything after
+        // that stays in registers, a feature per lane: the block amax is a warp-wide integer max of the bf16
+        // magnitudes, lane t works out the scale of token t and hands the multiplier back by shuffle, every
+        // lane rounds its feature to e2m1 (eight tokens' codes to a register), and three exchange steps
+        // inside each group of eight lanes transpose token and feature, so that a lane ends up with one
+        // aligned word of one token's codes.
         constexpr int kHalf = kChunk / 2;                    // tokens each warp of a pair finishes
+        constexpr int kPk = kHalf / 2;                       // ... as bf16 pairs
         const bool is_up = (sub & 1) != 0;
         const int par = is_up ? 1 : 0;
-        __nv_bfloat16* pbuf = reinterpret_cast<__nv_bfloat16*>(gbuf + (sub >> 1) * 4096);
-        __nv_bfloat16* x_mine = pbuf + par * (kHalf * 32);         // what this warp parks for its partner
-        __nv_bfloat16* x_other = pbuf + (1 - par) * (kHalf * 32);
-        __nv_bfloat16* y_mine = pbuf + 1024 + par * (kHalf * 32);  // this warp's results, [own token][feature]
+        uint32_t* xbuf = reinterpret_cast<uint32_t*>(gbuf + (sub >> 1) * 4096);
         const int pair_bar = 1 + group * 2 + (sub >> 1);
-        float gs = p.f_gpe ? p.f_gscale[e] : p.f_gscale[0];
+        const float gs = p.f_gpe ? p.f_gscale[e] : p.f_gscale[0];
+        const bool table = p.f_act.kind == PNV_ACT_SILU && p.f_act.silu_tab != nullptr;
+        const int kb = mt * 2 + (sub >> 1);                  // 32-feature block of the N-wide output
+        uint8_t* code_col = p.f_b_out + kb * 16 + (lane >> 3) * 4;
+        const long long code_pitch = p.f_n / 2;
 #pragma unroll 1
         for (int c0 = group * kChunk; c0 < TILE_N && n0 + c0 < cnt; c0 += 4 * kChunk) {
           uint32_t v[kChunk];
@@ -579,63 +609,109 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           PNV_PROF_ACC(pf_f0, tf0);                // tensor-memory load
           if (!mt_valid) continue;                 // the same for every thread of the CTA
           const long long tf1 = PNV_PROF_T();
-          float h[kChunk];
+          // bf16(alpha * acc), two tokens to a word (token 2k in the low half)
+          uint32_t hp[kChunk / 2];
 #pragma unroll
-          for (int i = 0; i < kChunk; ++i)
-            h[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(v[i]))));
-          named_bar_sync(pair_bar, 64);          // the partner has read what was parked for the previous chunk
+          for (int k = 0; k < kChunk / 2; ++k) {
+            const __nv_bfloat162 pr = __floats2bfloat162_rn(__fmul_rn(alpha, __uint_as_float(v[2 * k])),
+                                                           __fmul_rn(alpha, __uint_as_float(v[2 * k + 1])));
+            hp[k] = *reinterpret_cast<const uint32_t*>(&pr);
+          }
+          uint32_t* area = xbuf + flip * (2 * kPk * 32);
+          uint32_t* x_mine = area + par * (kPk * 32);
+          const uint32_t* x_other = area + (1 - par) * (kPk * 32);
+          flip ^= 1;
 #pragma unroll
-          for (int k = 0; k < kHalf; ++k) x_mine[k * 32 + lane] = __float2bfloat16_rn(is_up ? h[2 * k] : h[2 * k + 1]);
+          for (int k = 0; k < kPk; ++k) x_mine[k * 32 + lane] = is_up ? hp[k] : hp[kPk + k];
+          // own halves: gates of the first half of the chunk, or ups of the second
+          uint32_t own[kPk];
+#pragma unroll
+          for (int k = 0; k < kPk; ++k) own[k] = is_up ? hp[kPk + k] : hp[k];
+          float sv[kHalf];
+          if (table && !is_up) {                   // the gate warp's lookups are in flight across the barrier
+#pragma unroll
+            for (int k = 0; k < kPk; ++k) {
+              sv[2 * k] = __uint_as_float((uint32_t)__ldg(p.f_act.silu_tab + (own[k] & 0xFFFFu)) << 16);
+              sv[2 * k + 1] = __uint_as_float((uint32_t)__ldg(p.f_act.silu_tab + (own[k] >> 16)) << 16);
+            }
+          }
           named_bar_sync(pair_bar, 64);
-          PNV_PROF_ACC(pf_f1, tf1);                // round, park for the partner, both pair barriers
+          PNV_PROF_ACC(pf_f1, tf1);                // round, park for the partner, the pair barrier
           const long long tf2 = PNV_PROF_T();
-          float o[kHalf];
+          uint32_t oth[kPk];
 #pragma unroll
-          for (int k = 0; k < kHalf; ++k) o[k] = __bfloat162float(x_other[k * 32 + lane]);
-          __nv_bfloat16 y[kHalf];
-          if (p.f_act.kind == PNV_ACT_SILU && p.f_act.silu_tab != nullptr) {
-            float sv[kHalf];
+          for (int k = 0; k < kPk; ++k) oth[k] = x_other[k * 32 + lane];
+          uint32_t yp[kPk];                        // results, bf16 pairs again
+          if (table) {
+            if (is_up) {
 #pragma unroll
-            for (int k = 0; k < kHalf; ++k) sv[k] = silu_lookup(is_up ? o[k] : h[2 * k], p.f_act.silu_tab);
+              for (int k = 0; k < kPk; ++k) {
+                sv[2 * k] = __uint_as_float((uint32_t)__ldg(p.f_act.silu_tab + (oth[k] & 0xFFFFu)) << 16);
+                sv[2 * k + 1] = __uint_as_float((uint32_t)__ldg(p.f_act.silu_tab + (oth[k] >> 16)) << 16);
+              }
+            }
 #pragma unroll
-            for (int k = 0; k < kHalf; ++k) y[k] = __float2bfloat16_rn(__fmul_rn(sv[k], is_up ? h[2 * k + 1] : o[k]));
+            for (int k = 0; k < kPk; ++k) {
+              const uint32_t u = is_up ? own[k] : oth[k];
+              const __nv_bfloat162 pr = __floats2bfloat162_rn(__fmul_rn(sv[2 * k], bf16_lo(u)), __fmul_rn(sv[2 * k + 1], bf16_hi(u)));
+              yp[k] = *reinterpret_cast<const uint32_t*>(&pr);
+            }
           } else {
 #pragma unroll
-            for (int k = 0; k < kHalf; ++k)
-              y[k] = __float2bfloat16_rn(gated_act(is_up ? o[k] : h[2 * k], is_up ? h[2 * k + 1] : o[k], p.f_act));
+            for (int k = 0; k < kPk; ++k) {
+              const uint32_t g = is_up ? oth[k] : own[k], u = is_up ? own[k] : oth[k];
+              const __nv_bfloat162 pr = __floats2bfloat162_rn(gated_act(bf16_lo(g), bf16_lo(u), p.f_act),
+                                                             gated_act(bf16_hi(g), bf16_hi(u), p.f_act));
+              yp[k] = *reinterpret_cast<const uint32_t*>(&pr);
+            }
           }
           PNV_PROF_ACC(pf_f2, tf2);                // partner's values in, activation
           const long long tf3 = PNV_PROF_T();
-          __syncwarp();                          // every lane has finished reading the previous chunk's results
+          // block amax of own token t, left in lane t: bf16 magnitudes order like their bit patterns (NaN, which
+          // fmaxf would skip, counts as zero)
+          uint32_t amax_bits = 0;
 #pragma unroll
-          for (int k = 0; k < kHalf; ++k) y_mine[k * 32 + lane] = y[k];
-          __syncwarp();
-          // quantize: lanes 2k and 2k + 1 share own token k (chunk token 2k + par)
-          const int k = lane >> 1, hb = lane & 1;
-          if (k < kHalf) {
-            const int n = n0 + c0 + 2 * k + par;
-            const uint4* src = reinterpret_cast<const uint4*>(y_mine + k * 32 + hb * 16);
-            float f[2][8];
-            float amax = 0.f;
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-              unpack8(src[q], f[q]);
-#pragma unroll
-              for (int z = 0; z < 8; ++z) amax = fmaxf(amax, fabsf(f[q][z]));
-            }
-            amax = fmaxf(amax, __shfl_xor_sync(kHalf == 16 ? 0xffffffffu : 0x0000ffffu, amax, 1));
-            uint32_t sf_byte;
-            float inv;
-            block_scale(amax, gs, sf_byte, inv);
-            if (n < cnt) {
-              const int kb = mt * 2 + (sub >> 1);  // 32-feature block of the N-wide output
-              const long long row = (long long)e * p.max_n + n;
-              *reinterpret_cast<uint2*>(p.f_b_out + row * (p.f_n / 2) + kb * 16 + hb * 8) =
-                  make_uint2(quant8(f[0], inv), quant8(f[1], inv));
-              if (hb == 0) p.f_sfb_out[sf_offset(e, n, kb, p.sfb_rt, p.f_n_kt)] = (uint8_t)sf_byte;
-            }
+          for (int k = 0; k < kPk; ++k) {
+            uint32_t lo = yp[k] & 0x7FFFu, hi = (yp[k] >> 16) & 0x7FFFu;
+            lo = lo > 0x7F80u ? 0u : lo;
+            hi = hi > 0x7F80u ? 0u : hi;
+            const uint32_t mlo = __reduce_max_sync(0xffffffffu, lo), mhi = __reduce_max_sync(0xffffffffu, hi);
+            amax_bits = lane == 2 * k ? mlo : amax_bits;
+            amax_bits = lane == 2 * k + 1 ? mhi : amax_bits;
           }
-          PNV_PROF_ACC(pf_f3, tf3);                // transpose, quantize, store
+          uint32_t sf_byte;
+          float inv_mine;
+          block_scale(__uint_as_float(amax_bits << 16), gs, sf_byte, inv_mine);
+          // this lane's feature of every own token -> e2m1, token i of each eight in nibble i
+          uint32_t codes[(kHalf + 7) / 8];
+#pragma unroll
+          for (int r = 0; r < (kHalf + 7) / 8; ++r) codes[r] = 0u;
+#pragma unroll
+          for (int k = 0; k < kPk; ++k) {
+            const float i0 = __shfl_sync(0xffffffffu, inv_mine, 2 * k), i1 = __shfl_sync(0xffffffffu, inv_mine, 2 * k + 1);
+            codes[k >> 2] |= cvt_e2m1x2(__fmul_rn(bf16_lo(yp[k]), i0), __fmul_rn(bf16_hi(yp[k]), i1)) << (8 * (k & 3));
+          }
+          // 8 x 8 nibble transpose inside each group of eight lanes: afterwards lane 8 g + j holds, for own token j
+          // (and 8 + j), the codes of features 8 g .. 8 g + 7 in order - word g of that token's 16 bytes
+#pragma unroll
+          for (int r = 0; r < (kHalf + 7) / 8; ++r) {
+            uint32_t x = codes[r], y;
+            y = __shfl_xor_sync(0xffffffffu, x, 1);
+            x = (lane & 1) ? ((x & 0xF0F0F0F0u) | ((y & 0xF0F0F0F0u) >> 4)) : ((x & 0x0F0F0F0Fu) | ((y & 0x0F0F0F0Fu) << 4));
+            y = __shfl_xor_sync(0xffffffffu, x, 2);
+            x = (lane & 2) ? ((x & 0xFF00FF00u) | ((y & 0xFF00FF00u) >> 8)) : ((x & 0x00FF00FFu) | ((y & 0x00FF00FFu) << 8));
+            y = __shfl_xor_sync(0xffffffffu, x, 4);
+            x = (lane & 4) ? ((x & 0xFFFF0000u) | (y >> 16)) : ((x & 0x0000FFFFu) | (y << 16));
+            const int t = 8 * r + (lane & 7);                 // own token of this word
+            const int n = n0 + c0 + par * kHalf + t;
+            if (t < kHalf && n < cnt)
+              *reinterpret_cast<uint32_t*>(code_col + ((long long)e * p.max_n + n) * code_pitch) = x;
+          }
+          {
+            const int n = n0 + c0 + par * kHalf + lane;       // lane t holds the scale of own token t
+            if (lane < kHalf && n < cnt) p.f_sfb_out[sf_offset(e, n, kb, p.sfb_rt, p.f_n_kt)] = (uint8_t)sf_byte;
+          }
+          PNV_PROF_ACC(pf_f3, tf3);                // amax, scale, quantize, transpose, store
         }
       }
       if (!released) release_acc();

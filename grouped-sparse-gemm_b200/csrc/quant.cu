@@ -36,26 +36,13 @@ __device__ __forceinline__ void store_sf_line(uint8_t* line, uint32_t my_byte, i
 // Where a live row's values come from.
 //   kPlain   x is [E, max_n, K]
 //   kGated   x is [E, max_n, 2K] holding gate and up; the gated activation is applied first
-//   kPlanned x is token-order [T, K]; row (e, r) is token src_tok[e*max_n + r], optionally scaled by
-//            the router weight of routing src_route[e*max_n + r] (bf16(float(x) * float(bf16(w))))
-//   kFp4     rows are already quantized: q [T, K/2] codes and q_sf [T, K/32] scales are copied
-enum LineSource : int { kPlain = 0, kGated = 1, kPlanned = 2, kFp4 = 3 };
-
-struct PlanArgs {
-  const int* src_tok;
-  const int* src_route;
-  const float* topk_w;
-  const uint8_t* q;        // kFp4: codes of source row t at q + t * q_pitch
-  const uint8_t* q_sf;     //       its scales at q_sf + t * sf_pitch
-  long long q_pitch;
-  long long sf_pitch;
-};
+enum LineSource : int { kPlain = 0, kGated = 1 };
 
 template <int kSrc>
 __global__ void __launch_bounds__(kThreads)
 quant_lines_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gscale,
                    int gscale_per_expert, const int* __restrict__ counts, int E, int max_n, int K,
-                   int interleaved, GatedAct act, PlanArgs plan, uint8_t* __restrict__ b_act,
+                   int interleaved, GatedAct act, uint8_t* __restrict__ b_act,
                    uint8_t* __restrict__ sfb) {
   pdl_wait();
   pdl_launch_dependents();
@@ -91,36 +78,14 @@ quant_lines_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
     const int k0 = kb * kSfBlock + (j & 1) * 16;
     uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
     float f0[8], f1[8];
-    if (kSrc == kFp4) {
-      // byte copy of an already quantized row: 8 code bytes per lane, the scale as stored
-      uint32_t sf_copy = kBenignSf;
-      if (live) {
-        const long long slot = (long long)e * max_n + r;
-        const long long t = plan.src_tok[slot];
-        *reinterpret_cast<uint2*>(b_act + slot * (K / 2) + k0 / 2) =
-            __ldg(reinterpret_cast<const uint2*>(plan.q + t * plan.q_pitch + k0 / 2));
-        sf_copy = __ldg(plan.q_sf + t * plan.sf_pitch + kb);
-      }
-      store_sf_line(line, sf_copy, lane);
-      continue;
-    }
     if (live) {
       const long long row = (long long)e * max_n + r;
-      if (kSrc == kPlain || kSrc == kPlanned) {
-        const long long src_row = kSrc == kPlanned ? (long long)plan.src_tok[row] : row;
-        const uint4* p = reinterpret_cast<const uint4*>(x + src_row * K + k0);
+      if (kSrc == kPlain) {
+        const uint4* p = reinterpret_cast<const uint4*>(x + row * K + k0);
         v0 = __ldg(p);
         v1 = __ldg(p + 1);
         unpack8(v0, f0);
         unpack8(v1, f1);
-        if (kSrc == kPlanned && plan.topk_w != nullptr) {
-          const float w = __bfloat162float(__float2bfloat16_rn(plan.topk_w[plan.src_route[row]]));
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            f0[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(f0[i], w)));
-            f1[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(f1[i], w)));
-          }
-        }
       } else {
         const __nv_bfloat16* base = x + row * (2LL * K);
         const int gate_off = interleaved ? kb * 64 + (j & 1) * 16 : k0;
@@ -279,6 +244,47 @@ scatter_planned_rows_kernel(const __nv_bfloat16* __restrict__ a1, const int* __r
     quantize_routed_row(reinterpret_cast<const uint4*>(a1 + (long long)src_tok[slot] * K),
                         reinterpret_cast<uint4*>(b_act + (long long)slot * (K / 2)), sfb + sf_offset(e, r, 0, n_rt, n_kt),
                         KB, gs, weighted, w, lane);
+  }
+}
+
+// scatter_fp4_planned / scatter_fp4_wire: already quantized rows into the batched operands, one warp per row slot.
+// Codes are copied 16 bytes per lane; the row's scales go from natural order into the swizzled layout four
+// K-blocks (one aligned word of both layouts) at a time.  Slots at or past counts[e] are skipped; their scales
+// keep the benign fill laid down before the launch.
+__global__ void __launch_bounds__(kThreads)
+scatter_fp4_rows_kernel(const uint8_t* __restrict__ q, long long q_pitch, const uint8_t* __restrict__ q_sf,
+                        long long sf_pitch, const int* __restrict__ src_tok, const int* __restrict__ counts, int K, int E,
+                        int cap, uint8_t* __restrict__ b_act, uint8_t* __restrict__ sfb) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int KB = K / kSfBlock;
+  const int n_rt = sf_row_atoms(cap);
+  const int n_kt = sf_k_atoms(K);
+  const int lane = threadIdx.x & 31;
+  const unsigned slots = (unsigned)E * (unsigned)cap;
+  const unsigned warp0 = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const unsigned nwarps = gridDim.x * kWarpsPerBlock;
+  const bool words = (KB % 4) == 0 && (sf_pitch % 4) == 0 && (reinterpret_cast<uintptr_t>(q_sf) % 4) == 0;
+  for (unsigned slot = warp0; slot < slots; slot += nwarps) {
+    const int e = (int)(slot / (unsigned)cap);
+    const int r = (int)(slot - (unsigned)e * (unsigned)cap);
+    if (r >= min(counts[e], cap)) {
+      const unsigned next = (unsigned)(e + 1) * (unsigned)cap;       // on to the next expert's first slot of this warp
+      slot += ((next - slot + nwarps - 1) / nwarps - 1) * nwarps;
+      continue;
+    }
+    const long long t = src_tok[slot];
+    const uint4* src = reinterpret_cast<const uint4*>(q + t * q_pitch);
+    uint4* dst = reinterpret_cast<uint4*>(b_act + (long long)slot * (K / 2));
+    for (int v = lane; v < K / 32; v += 32) dst[v] = __ldg(src + v);
+    const uint8_t* sf_src = q_sf + t * sf_pitch;
+    uint8_t* sf_row = sfb + sf_offset(e, r, 0, n_rt, n_kt);        // K-block kb of this row: + (kb >> 2) * 512 + (kb & 3)
+    if (words) {
+      for (int w = lane; w < KB / 4; w += 32)
+        *reinterpret_cast<uint32_t*>(sf_row + w * 512) = __ldg(reinterpret_cast<const uint32_t*>(sf_src) + w);
+    } else {
+      for (int kb = lane; kb < KB; kb += 32) sf_row[(kb >> 2) * 512 + (kb & 3)] = __ldg(sf_src + kb);
+    }
   }
 }
 
@@ -478,7 +484,7 @@ extern "C" int pnv_quant_act(const void* x, const float* gscale, int gscale_per_
   GatedAct act{PNV_ACT_SILU, 1.f, -1.f, nullptr};
   PNV_CUDA(launch_pdl(quant_lines_kernel<kPlain>, dim3(grid_for(lines, sm_count)), dim3(kThreads), 0,
                       (cudaStream_t)stream, pdl_enabled(), (const __nv_bfloat16*)x, gscale,
-                      gscale_per_expert, counts, experts, max_n, k, 0, act, PlanArgs{}, b_act, sfb));
+                      gscale_per_expert, counts, experts, max_n, k, 0, act, b_act, sfb));
   return PNV_OK;
 }
 
@@ -494,7 +500,7 @@ extern "C" int pnv_silu_mul_quant_act(const void* x2, const float* gscale, int g
   long long lines = sf_numel(max_n, n, experts) / 16;
   PNV_CUDA(launch_pdl(quant_lines_kernel<kGated>, dim3(grid_for(lines, sm_count)), dim3(kThreads), 0,
                       (cudaStream_t)stream, pdl_enabled(), (const __nv_bfloat16*)x2, gscale,
-                      gscale_per_expert, counts, experts, max_n, n, interleaved ? 1 : 0, act, PlanArgs{},
+                      gscale_per_expert, counts, experts, max_n, n, interleaved ? 1 : 0, act,
                       b_act, sfb));
   return PNV_OK;
 }
@@ -567,20 +573,32 @@ extern "C" int pnv_quant_rows(const void* x, const float* gscale, int64_t tokens
   return PNV_OK;
 }
 
+namespace {
+int scatter_fp4_rows(const uint8_t* q, long long q_pitch, const uint8_t* q_sf, long long sf_pitch, const int32_t* src_tok,
+                     const int32_t* counts, int k, int experts, int cap, uint8_t* b_act, uint8_t* sfb, int sm_count,
+                     cudaStream_t s) {
+  float dummy = 0.f;
+  if (int rc = check_common(q, &dummy, counts, experts, cap, k, b_act, sfb, "K")) return rc;
+  PNV_REQUIRE((long long)experts * cap < (1LL << 31), "E * cap must fit int32");
+  PNV_REQUIRE((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(b_act) | (uintptr_t)q_pitch) % 16 == 0,
+              "code rows must be 16-byte aligned");
+  // benign fill first, then one warp per live row writes its scales over it
+  PNV_CUDA(cudaMemsetAsync(sfb, kBenignSf, (size_t)sf_numel(cap, k, experts), s));
+  PNV_CUDA(launch_pdl(scatter_fp4_rows_kernel, dim3(grid_for((long long)experts * cap, sm_count)), dim3(kThreads), 0, s,
+                      false, q, q_pitch, q_sf, sf_pitch, (const int*)src_tok, (const int*)counts, k, experts, cap, b_act,
+                      sfb));
+  return PNV_OK;
+}
+}  // namespace
+
 extern "C" int pnv_scatter_fp4_planned(const uint8_t* q, const uint8_t* q_sf, const int32_t* src_tok,
                                        const int32_t* counts, int k, int experts, int cap, uint8_t* b_act,
                                        uint8_t* sfb, int sm_count, pnv_stream_t stream) {
   PNV_REQUIRE(cap > 0, "cap must be positive");
   PNV_REQUIRE(q && q_sf && src_tok, "null pointer argument");
-  float dummy = 0.f;
-  if (int rc = check_common(q, &dummy, counts, experts, cap, k, b_act, sfb, "K")) return rc;
-  long long lines = sf_numel(cap, k, experts) / 16;
-  GatedAct act{PNV_ACT_SILU, 1.f, -1.f, nullptr};
-  PlanArgs plan{src_tok, nullptr, nullptr, q, q_sf, k / 2, k / kSfBlock};
-  PNV_CUDA(launch_pdl(quant_lines_kernel<kFp4>, dim3(grid_for(lines, sm_count)), dim3(kThreads), 0,
-                      (cudaStream_t)stream, pdl_enabled(), (const __nv_bfloat16*)nullptr, (const float*)nullptr, 0,
-                      counts, experts, cap, k, 0, act, plan, b_act, sfb));
-  return PNV_OK;
+  PNV_REQUIRE(k > 0 && k % kSfBlock == 0, "K must be a multiple of %d, got %d", kSfBlock, k);
+  return scatter_fp4_rows(q, k / 2, q_sf, k / kSfBlock, src_tok, counts, k, experts, cap, b_act, sfb, sm_count,
+                          (cudaStream_t)stream);
 }
 
 extern "C" int pnv_set_silu_table(int enabled) {
@@ -623,15 +641,8 @@ extern "C" int pnv_scatter_fp4_wire(const uint8_t* wire, const int32_t* src_tok,
                                     pnv_stream_t stream) {
   PNV_REQUIRE(cap > 0, "cap must be positive");
   PNV_REQUIRE(wire && src_tok, "null pointer argument");
-  PNV_REQUIRE(reinterpret_cast<uintptr_t>(wire) % 16 == 0, "wire rows must be 16-byte aligned");
-  float dummy = 0.f;
-  if (int rc = check_common(wire, &dummy, counts, experts, cap, k, b_act, sfb, "K")) return rc;
-  long long lines = sf_numel(cap, k, experts) / 16;
-  GatedAct act{PNV_ACT_SILU, 1.f, -1.f, nullptr};
+  PNV_REQUIRE(k > 0 && k % kSfBlock == 0, "K must be a multiple of %d, got %d", kSfBlock, k);
   const long long pitch = wire_row_bytes(k);
-  PlanArgs plan{src_tok, nullptr, nullptr, wire, wire + k / 2, pitch, pitch};
-  PNV_CUDA(launch_pdl(quant_lines_kernel<kFp4>, dim3(grid_for(lines, sm_count)), dim3(kThreads), 0,
-                      (cudaStream_t)stream, pdl_enabled(), (const __nv_bfloat16*)nullptr, (const float*)nullptr, 0,
-                      counts, experts, cap, k, 0, act, plan, b_act, sfb));
-  return PNV_OK;
+  return scatter_fp4_rows(wire, pitch, wire + k / 2, pitch, src_tok, counts, k, experts, cap, b_act, sfb, sm_count,
+                          (cudaStream_t)stream);
 }

@@ -60,6 +60,11 @@ def _register():
                "Tensor alphas, Tensor expert_num_tokens, int features, int k, "
                f"int config_id={DEFAULT_TACTIC[0]}, int cluster_m={DEFAULT_TACTIC[1]}, "
                f"int cluster_n={DEFAULT_TACTIC[2]}) -> ()")
+    lib.define("group_mm_rows(Tensor(a!) out, Tensor row_map, Tensor a_comp, Tensor e_meta, Tensor sfa, Tensor b_act, "
+               "Tensor sfb, Tensor alphas, Tensor expert_num_tokens, int features, int k, "
+               f"int config_id={DEFAULT_TACTIC[0]}, int cluster_m={DEFAULT_TACTIC[1]}, "
+               f"int cluster_n={DEFAULT_TACTIC[2]}) -> ()")
+    lib.define("zero_rows(Tensor(a!) dst, Tensor flags) -> ()")
     lib.define("group_mm_configs() -> str[]")
     lib.define("group_mm_swiglu_quant(Tensor a_comp, Tensor e_meta, Tensor sfa, Tensor b_act, Tensor sfb, "
                "Tensor alphas, Tensor expert_num_tokens, Tensor gscale, int features, int k, int config_id=0, "
@@ -81,6 +86,8 @@ def _register():
     lib.impl("pack_wire_rows", ops.pack_wire_rows, "CUDA")
     lib.impl("scatter_fp4_wire", ops.scatter_fp4_wire, "CUDA")
     lib.impl("group_mm", ops.group_mm, "CUDA")
+    lib.impl("group_mm_rows", ops.group_mm_rows, "CUDA")
+    lib.impl("zero_rows", ops.zero_rows, "CUDA")
     lib.impl("gated_act", ops.gated_act, "CUDA")
     lib.impl("group_mm_swiglu_quant", ops.group_mm_swiglu_quant, "CUDA")
     lib.impl("group_mm_configs", ops.group_mm_configs, "CompositeExplicitAutograd")

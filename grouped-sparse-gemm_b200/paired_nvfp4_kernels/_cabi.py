@@ -47,6 +47,8 @@ SIGNATURES = {
     "pnv_group_mm_config_name": (ctypes.c_char_p, [_i]),
     "pnv_group_mm_workspace_bytes": (_i64, [_i, _i, _i, _i]),
     "pnv_group_mm": (_i, [_p] * 8 + [_i] * 9 + [_p, _i64, _p]),
+    "pnv_group_mm_rows": (_i, [_p] * 9 + [_i] * 9 + [_p, _i64, _p]),
+    "pnv_zero_rows": (_i, [_p, _p, _i64, _i64, _p]),
     "pnv_group_mm_swiglu_num_configs": (_i, []),
     "pnv_group_mm_swiglu_config_name": (ctypes.c_char_p, [_i]),
     "pnv_group_mm_swiglu_quant": (_i, [_p] * 10 + [_i] * 9 + [_f, _f, _i, _i, _p, _i64, _p]),

@@ -10,7 +10,8 @@ routing.  A forward pass is
                NVFP4 codes + scales + the expert id local to the receiver; dead slots carry id -1
     dispatch   ONE equal-split all-to-all of the slabs
     local FFN  dispatch_plan on the ids inside the received rows -> scatter_fp4_wire -> group_mm
-               (gate_up, fused SwiGLU + quantize) -> group_mm (down) -> gather_rows into slot order
+               (gate_up, fused SwiGLU + quantize) -> group_mm_rows (down; every expert output row is written
+               straight into the slot it came from) + zero_rows for the slots no expert kept
     combine    ONE equal-split all-to-all back (bf16 rows)
     finalize   out[t] = sum_j w[t, j] * returned_row(t, j)
 
@@ -106,12 +107,13 @@ class ExpertParallelFFN:
         b2, sfb2 = ops.group_mm_swiglu_quant(self.w13[0], self.w13[1], self.w13[2], b1, sfb1, self.al1, counts, self.g2,
                                              2 * I, H, self.fused_config, self.fused_cluster_m, 1, "silu", 1.0, -1.0)
         mark("group_mm_gate_up")
-        y = torch.empty((E, cap, H), dtype=torch.bfloat16, device=wire.device)
-        ops.group_mm(y, self.w2[0], self.w2[1], self.w2[2], b2, sfb2, self.al2, counts, H, I, self.config_id,
-                     self.cluster_m, 1)
+        # the receiver's plan has one routing per wire row, so its src_tok is the slot every expert row came from
+        back = torch.empty((wire.size(0), H), dtype=torch.bfloat16, device=wire.device)
+        ops.zero_rows(back, route_dest.view(-1))             # dead and dropped slots return zero rows
+        mark("zero_rows")
+        ops.group_mm_rows(back, src_tok, self.w2[0], self.w2[1], self.w2[2], b2, sfb2, self.al2, counts, H, I,
+                          self.config_id, self.cluster_m, 1)
         mark("group_mm_down")
-        back = ops.gather_rows(y.view(E * cap, H), route_dest.view(-1))   # dead and dropped slots return zero rows
-        mark("gather_rows")
         return back, counts
 
     def forward(self, x, topk_ids, topk_weights, out=None, mark: Optional[Callable[[str], None]] = None):

@@ -425,17 +425,22 @@ def group_mm_configs():
     return _cabi.group_mm_config_names()
 
 
-def group_mm(out, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens, features, k, config_id=0,
-             cluster_m=2, cluster_n=1):
-    """csrc/ops.cu:672-735.  Mutates `out` in place."""
+def _group_mm(out, row_map, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens, features, k, config_id,
+              cluster_m, cluster_n):
     ts = (out, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens)
     _check(all(t.is_cuda for t in ts), "all tensors must be CUDA")
     _check_arch(out)
-    _check(out.dim() == 3 and b_act.dim() == 3 and a_comp.dim() == 3 and e_meta.dim() == 3,
-           "out, b_act, a_comp and e_meta must be 3D")
+    _check(b_act.dim() == 3 and a_comp.dim() == 3 and e_meta.dim() == 3, "b_act, a_comp and e_meta must be 3D")
     E, M, K, max_n = a_comp.size(0), int(features), int(k), b_act.size(1)
-    _check(out.size(0) == E and b_act.size(0) == E and e_meta.size(0) == E, "expert dim mismatch")
-    _check(out.size(1) == max_n and out.size(2) == M, "out must be [E, max_n, features]")
+    _check(b_act.size(0) == E and e_meta.size(0) == E, "expert dim mismatch")
+    if row_map is None:
+        _check(out.dim() == 3, "out must be 3D")
+        _check(out.size(0) == E, "expert dim mismatch")
+        _check(out.size(1) == max_n and out.size(2) == M, "out must be [E, max_n, features]")
+    else:
+        _check(out.dim() == 2 and out.size(1) == M, "out must be [rows, features]")
+        _check(row_map.is_cuda and row_map.dtype == torch.int32 and row_map.is_contiguous()
+               and row_map.numel() == E * max_n, "row_map must be contiguous int32 [E * max_n]")
     _check(b_act.size(2) == K // 2, "b_act must be [E, max_n, K/2]")
     _check(out.dtype == torch.bfloat16, "out must be bf16")
     _check(a_comp.dtype == torch.uint8 and e_meta.dtype == torch.uint8 and b_act.dtype == torch.uint8
@@ -453,11 +458,41 @@ def group_mm(out, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens, fe
     _check(sfb.numel() >= _cabi.sf_numel(max_n, K, E), "sfb is smaller than the SFB layout")
     with torch.cuda.device(out.device):
         ws, ws_bytes = _split_workspace(out, E, M, max_n)
-        _cabi.check(_lib.pnv_group_mm(
-            out.data_ptr(), a_comp.data_ptr(), e_meta.data_ptr(), sfa.data_ptr(), b_act.data_ptr(), sfb.data_ptr(),
-            alphas.data_ptr(), expert_num_tokens.data_ptr(), E, M, K, max_n, int(config_id), int(cluster_m),
-            int(cluster_n), _device_info(out.device)[1], 1, ws.data_ptr() if ws is not None else None, ws_bytes,
-            _stream(out)))
+        tail = (a_comp.data_ptr(), e_meta.data_ptr(), sfa.data_ptr(), b_act.data_ptr(), sfb.data_ptr(),
+                alphas.data_ptr(), expert_num_tokens.data_ptr(), E, M, K, max_n, int(config_id), int(cluster_m),
+                int(cluster_n), _device_info(out.device)[1], 1, ws.data_ptr() if ws is not None else None, ws_bytes,
+                _stream(out))
+        if row_map is None:
+            _cabi.check(_lib.pnv_group_mm(out.data_ptr(), *tail))
+        else:
+            _cabi.check(_lib.pnv_group_mm_rows(out.data_ptr(), row_map.data_ptr(), *tail))
+
+
+def group_mm(out, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens, features, k, config_id=0,
+             cluster_m=2, cluster_n=1):
+    """csrc/ops.cu:672-735.  Mutates `out` in place."""
+    _group_mm(out, None, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens, features, k, config_id,
+              cluster_m, cluster_n)
+
+
+def group_mm_rows(out, row_map, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens, features, k, config_id=0,
+                  cluster_m=2, cluster_n=1):
+    """group_mm whose token row (e, t) lands in row row_map[e * max_n + t] of out [rows, features] (skipped where
+    negative).  Mutates `out` in place; rows no kept token maps to are left alone."""
+    _group_mm(out, row_map, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens, features, k, config_id,
+              cluster_m, cluster_n)
+
+
+def zero_rows(dst, flags):
+    """dst[i] = 0 where flags[i] < 0; the other rows are left alone.  Mutates `dst` in place."""
+    _check(dst.is_cuda and flags.is_cuda, "inputs must be CUDA")
+    _check(dst.dim() == 2 and dst.is_contiguous(), "dst must be contiguous [rows, width]")
+    _check(flags.dtype == torch.int32 and flags.is_contiguous() and flags.numel() == dst.size(0),
+           "flags must be contiguous int32 [rows]")
+    row_bytes = dst.size(1) * dst.element_size()
+    _check(row_bytes % 16 == 0, lambda: f"rows must be a multiple of 16 bytes, got {row_bytes}")
+    with torch.cuda.device(dst.device):
+        _cabi.check(_lib.pnv_zero_rows(dst.data_ptr(), flags.data_ptr(), dst.size(0), row_bytes, _stream(dst)))
 
 
 def group_mm_swiglu_configs():

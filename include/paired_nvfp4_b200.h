@@ -193,6 +193,11 @@ int pnv_moe_finalize(void* out, const void* fused, const int32_t* route_dest, co
 int pnv_gather_rows(const void* src, const int32_t* idx, int64_t n_idx, int64_t row_bytes, void* dst,
                     pnv_stream_t stream);
 
+/* Rows whose flag is negative become zero, the others are left alone (dst [rows, row_bytes], row_bytes a
+ * multiple of 16).  With pnv_group_mm_rows this stands in for pnv_gather_rows on the way back from the experts:
+ * the GEMM writes every kept row straight into return order, this zeroes the slots no row lands on. */
+int pnv_zero_rows(void* dst, const int32_t* flags, int64_t rows, int64_t row_bytes, pnv_stream_t stream);
+
 /* The unfused gated activation the quantizer above folds in (gated_act, csrc/layout.cuh:204-216;
  * device replica ref_silu_mul_kernel, csrc/testing/selftest.cu:750-760): y bf16[rows, n] from
  * x2 bf16[rows, 2n].  pnv_silu_mul_quant_act == pnv_gated_act followed by pnv_quant_act, byte for
@@ -232,6 +237,17 @@ int pnv_group_mm(void* out, const uint8_t* a_comp, const uint8_t* e_meta, const 
                  const int32_t* counts, int experts, int features, int k, int max_n, int config_id,
                  int cluster_m, int cluster_n, int sm_count, int pdl, void* workspace,
                  int64_t workspace_bytes, pnv_stream_t stream);
+
+/* pnv_group_mm with the output rows permuted on the way out (no counterpart in the reference, whose caller
+ * permutes the expert outputs after the GEMM): token row (e, t), t < counts[e], is written to row
+ * row_map[e * max_n + t] of out bf16[rows, features] and not at all where the map is negative; map entries of rows
+ * at or past counts[e] are not read.  The caller guarantees 0 <= row_map[...] < rows for the rows it keeps.  With
+ * the src_tok of the dispatch_plan that placed the rows (topk = 1) the outputs land in the plan's input order. */
+int pnv_group_mm_rows(void* out, const int32_t* row_map, const uint8_t* a_comp, const uint8_t* e_meta,
+                      const uint8_t* sfa, const uint8_t* b_act, const uint8_t* sfb, const float* alphas,
+                      const int32_t* counts, int experts, int features, int k, int max_n, int config_id,
+                      int cluster_m, int cluster_n, int sm_count, int pdl, void* workspace,
+                      int64_t workspace_bytes, pnv_stream_t stream);
 
 /* paired_nvfp4_group_mm_swiglu_configs / paired_nvfp4_group_mm_swiglu_quant (csrc/ops.cu:585-658 ->
  * SwigluFp4Epilogue, csrc/sm100/swiglu_epilogue.cuh:52-236; variant table kSwigluMmKinds,

@@ -57,6 +57,17 @@ class CpuOps:
         for e in range(o.shape[0]):
             out[e, :int(cnt[e])] = _from_bits(orc.f32_to_bf16_bits(o[e, :int(cnt[e])]))
 
+    def group_mm_rows(self, out, row_map, w, _e, _s, b2, sfb2, alphas, counts, features, k, cfg, cm, cn):
+        o = orc.group_mm(_np(w), _np(b2), _np(sfb2), _np(alphas), _np(counts))
+        cnt, to = _np(counts), _np(row_map).reshape(o.shape[0], -1)
+        for e in range(o.shape[0]):
+            for r in range(int(cnt[e])):
+                if to[e, r] >= 0:
+                    out[int(to[e, r])] = _from_bits(orc.f32_to_bf16_bits(o[e, r]))
+
+    def zero_rows(self, dst, flags):
+        dst[flags < 0] = 0
+
     def gather_rows(self, src, idx):
         i = idx.long()
         out = src[i.clamp(min=0)].clone()

@@ -117,6 +117,48 @@ def test_pair_kernels_on_odd_tile_counts(pnk):
         run_case(pnk, E=2, M=640 - 8, K=512, max_n=96, counts=[96, 33], config_id=cid, seed=22)
 
 
+ROW_MAP_CASES = [
+    # E, M, K, max_n, counts, config ids
+    (3, 384, 768, 200, [200, 0, 77], (0, 1, 3, 5, 8)),       # wide kernels, single CTA and pairs, odd tile count
+    (2, 250, 512, 300, [300, 150], (1, 2)),                  # 256-token tiles (two chunks per group); M tail
+    (4, 512, 2048, 16, [16, 0, 3, 9], (7,)),                 # narrow kernel, K split across CTAs
+    (2, 202, 1024, 32, [32, 20], (7,)),                      # narrow kernel, scalar store path (M % 8 != 0)
+]
+
+
+@pytest.mark.parametrize("E,M,K,max_n,counts,cids", ROW_MAP_CASES)
+def test_group_mm_rows_permutes_the_output(pnk, E, M, K, max_n, counts, cids):
+    """group_mm_rows == group_mm followed by a row permutation: kept rows land where the map says, bit for bit;
+    rows mapped to -1 and rows no token maps to keep the caller's bytes."""
+    ops = torch.ops.paired_nvfp4
+    packed, sf, _ = make_weights(E, M, K, 31)
+    x = make_acts(E, max_n, K, 32)
+    cnt = np.asarray(counts, np.int32)
+    a_comp, e_meta, sfa = ops.compress(dev(packed), dev(sf), K)
+    b_act, sfb = ops.quant_act(bf16_tensor(x), dev(np.ones(1, np.float32)), dev(cnt), M)
+    al = dev(np.linspace(0.5, 2.0, E).astype(np.float32))
+    rng = np.random.default_rng(33)
+    rows = E * max_n + 5
+    to = rng.permutation(rows)[:E * max_n].astype(np.int32)
+    to[rng.random(E * max_n) < 0.1] = -1                      # some kept rows are not wanted
+    live = (np.arange(max_n)[None, :] < cnt[:, None]).reshape(-1)
+    to_dev = dev(np.where(live, to, np.int32(2 ** 30)))       # entries of rows past counts[e] are never read
+    for cid in cids:
+        name = pnk.group_mm_configs()[cid]
+        cm, cn = pnk.valid_clusters(name)[0]
+        plain = torch.full((E, max_n, M), SENTINEL, dtype=torch.bfloat16, device="cuda")
+        ops.group_mm(plain, a_comp, e_meta, sfa, b_act, sfb, al, dev(cnt), M, K, cid, cm, cn)
+        out = torch.full((rows, M), SENTINEL, dtype=torch.bfloat16, device="cuda")
+        ops.group_mm_rows(out, to_dev, a_comp, e_meta, sfa, b_act, sfb, al, dev(cnt), M, K, cid, cm, cn)
+        torch.cuda.synchronize()
+        want = torch.full((rows, M), SENTINEL, dtype=torch.bfloat16, device="cuda")
+        keep = torch.from_numpy(live & (to >= 0)).cuda()
+        want[torch.from_numpy(to).cuda().long()[keep]] = plain.view(E * max_n, M)[keep]
+        assert torch.equal(out, want), name
+    from paired_nvfp4_kernels import ops as pyops
+    assert pyops.group_mm_device_status() == 0
+
+
 SPLIT_CASES = [
     # E, M, K, max_n, counts: decode-sized problems, where the K stages of all tiles are dealt evenly to the SMs
     (2, 256, 4096, 16, [16, 5]),                  # 4 tiles x 8 stages over 32 CTAs: every CTA gets one stage of a tile

@@ -91,8 +91,9 @@ def test_planned_scatter_equals_flat_scatter_and_oracle(ops, T, K, Etot, rank, w
     assert np.array_equal(u8(b_p)[valid], u8(b_f)[valid]) and np.array_equal(u8(sf_p), u8(sf_f))
 
 
-def test_fp4_wire_pair_equals_scatter_quant(ops):
-    T, K, E, cap, topk = 500, 512, 16, 48, 4
+@pytest.mark.parametrize("T,K,E,cap,topk", [(500, 512, 16, 48, 4), (70, 96, 4, 20, 2), (120, 7168, 8, 40, 3),
+                                            (64, 1056, 2, 130, 2)])
+def test_fp4_wire_pair_equals_scatter_quant(ops, T, K, E, cap, topk):
     rng = np.random.default_rng(9)
     ids = route(T, topk, E, 9)
     a1 = orc.f32_to_bf16_bits(rng.standard_normal((T, K)).astype(np.float32))
@@ -146,3 +147,19 @@ def test_gather_rows(rows, width, dtype):
     assert ops.gather_rows(src, idx[:0]).shape == (0, width)
     with pytest.raises(RuntimeError, match="multiple of 16"):
         ops.gather_rows(src[:, :4].contiguous(), idx)
+
+
+@pytest.mark.parametrize("rows,width,dtype", [(37, 16, torch.uint8), (203, 7168, torch.bfloat16), (8, 264, torch.bfloat16)])
+def test_zero_rows(rows, width, dtype):
+    import paired_nvfp4_kernels  # noqa: F401
+    ops = torch.ops.paired_nvfp4
+    g = torch.Generator(device="cpu").manual_seed(rows + width)
+    dst = torch.randint(1, 255, (rows, width), generator=g, dtype=torch.uint8).to(dtype).cuda()
+    flags = torch.randint(-1, 3, (rows,), generator=g, dtype=torch.int32).cuda()
+    want = dst.clone()
+    want[flags < 0] = 0
+    ops.zero_rows(dst, flags)
+    assert torch.equal(dst, want)
+    ops.zero_rows(dst[:0], flags[:0])
+    with pytest.raises(RuntimeError, match="multiple of 16"):
+        ops.zero_rows(dst[:, :4].contiguous(), flags)
