@@ -80,6 +80,9 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-sub-workloads", action="store_true", help="N = 1: skip the c2 / c3 entries of `workloads`")
     ap.add_argument("--unfused", action="store_true", help="separate silu_mul_quant_act launch instead of the fused GEMM1 epilogue")
+    ap.add_argument("--passes", type=int, default=None,
+                    help="passes per step (default: as many as make the timed steps last half a second); "
+                         "small values keep a profiler capture short")
     ap.add_argument("--slab-headroom", type=float, default=1.125, help="expert-parallel slab rows over the mean load")
     return ap.parse_args()
 
@@ -207,7 +210,7 @@ class Layer:
         names = _cabi.group_mm_config_names()
         self.cluster_m = 2 if names[self.cfg].split("_")[1] == "2sm" else 1
         # fused variant with the same tile as the chosen group_mm variant
-        self.fused_cfg = {6: 0, 7: 0, 4: 1, 5: 2, 0: 3, 1: 3, 2: 4, 3: 4, 8: 4}[self.cfg]
+        self.fused_cfg = {6: 0, 7: 0, 4: 1, 5: 2, 0: 3, 1: 5, 2: 4, 3: 4, 8: 4}[self.cfg]
         self.fused_cluster_m = 2 if _cabi.group_mm_swiglu_config_names()[self.fused_cfg].split("_")[1] == "2sm" else 1
         self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
         E, H, I, cap = self.E, self.H, self.I, self.cap
@@ -422,7 +425,7 @@ def run_local_workload(wl_name, wl, device, args, steps, warmup, sample_clocks=N
         layer.step(stream, c=i)
     e1.record()
     torch.cuda.synchronize()
-    passes = passes_for(e0.elapsed_time(e1) / 3 * 1e-3, steps)
+    passes = args.passes or passes_for(e0.elapsed_time(e1) / 3 * 1e-3, steps)
     for i in range(warmup * passes):
         layer.step(stream, c=i)
     # every pass carries its phase events; steps are timed as a whole
@@ -663,7 +666,7 @@ def run_expert_parallel(args, wl_name, wl, rank, world, local_rank, device):
     cfg = wl["config_id"] if args.config_id is None else args.config_id
     names = _cabi.group_mm_config_names()
     cluster_m = 2 if names[cfg].split("_")[1] == "2sm" else 1
-    fused_cfg = {6: 0, 7: 0, 4: 1, 5: 2, 0: 3, 1: 3, 2: 4, 3: 4, 8: 4}[cfg]
+    fused_cfg = {6: 0, 7: 0, 4: 1, 5: 2, 0: 3, 1: 5, 2: 4, 3: 4, 8: 4}[cfg]
     fused_cm = 2 if _cabi.group_mm_swiglu_config_names()[fused_cfg].split("_")[1] == "2sm" else 1
 
     def barrier():
@@ -724,7 +727,7 @@ def run_expert_parallel(args, wl_name, wl, rank, world, local_rank, device):
     est = torch.tensor([e0.elapsed_time(e1) / 3 * 1e-3], device=device)
     if world > 1:
         dist.all_reduce(est, op=dist.ReduceOp.MAX)
-    passes = passes_for(float(est.item()), args.steps)
+    passes = args.passes or passes_for(float(est.item()), args.steps)
     warm = max(args.warmup, 3)
     for i in range(warm * passes):
         one_pass(i)

@@ -834,7 +834,7 @@ int launch_narrow(const CUtensorMap& map_a, const CUtensorMap& map_b, Params& p,
 // counts, capped by the scale-slot ring in tensor memory.
 template <class C>
 int wide_stages(int experts, bool fused) {
-  const int fixed = 1024 + (fused ? C::kFusedOutBytes : 0) + C::kBarrierBytes + 4 * experts;
+  const int fixed = 1024 + (fused ? C::kFusedOutBytes : C::kPlainOutBytes) + C::kBarrierBytes + 4 * experts;
   int n = std::min(std::min((int)C::kMaxStages, (int)C::kSlots), (kSmemLimit - fixed) / C::kStageBytes);
 #ifdef PNV_WIDE_MAX_STAGES      // developer builds: a shallower ring, to see how the time depends on its depth
   n = std::min(n, PNV_WIDE_MAX_STAGES);
@@ -852,7 +852,8 @@ int launch_wide_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const P
     return fail(PNV_ERR_INVALID_ARGUMENT, "group_mm: not enough shared memory for a %dx%d pipeline", TILE_N, STAGE_K);
   p.stages = stages;
   p.prod_lanes = stages >= 8 ? 4 : stages >= 4 ? 2 : 1;
-  const size_t smem = 1024 + (size_t)stages * C::kStageBytes + (kFused ? C::kFusedOutBytes : 0) + C::kBarrierBytes + 4 * (size_t)p.E;
+  const size_t smem = 1024 + (size_t)stages * C::kStageBytes + (kFused ? C::kFusedOutBytes : C::kPlainOutBytes) +
+                      C::kBarrierBytes + 4 * (size_t)p.E;
   static KernelSetup setup;
   int max_pairs = 0;
   if (int rc = prepare_kernel(group_mm_wide_kernel<TILE_N, STAGE_K, kFused, kPair>, setup, C::kThreads, smem, kPair,
@@ -977,7 +978,7 @@ struct FusedKind { const char* name; bool two_sm; int base_config; };
 const FusedKind kFusedKinds[] = {
     {"fused_2sm_256x64_k512", true, 6}, {"fused_2sm_256x64", true, 4},
     {"fused_1sm_128x64", false, 5},     {"fused_2sm_256x128", true, 0},
-    {"fused_1sm_128x128", false, 2},
+    {"fused_1sm_128x128", false, 2},    {"fused_2sm_256x256", true, 1},
 };
 constexpr int kNumFusedKinds = sizeof(kFusedKinds) / sizeof(kFusedKinds[0]);
 

@@ -17,7 +17,8 @@
 //   warp 1   side producer: bulk copies of the metadata, SFA and SFB atoms (they sit in global memory in
 //            the shape tensor memory wants)
 //   2 - 3    MMA issuers (of a pair: in the first CTA only), alternate tiles, each into its own accumulator
-//            stage: per pipeline stage they wait for one barrier, issue the MMAs and commit
+//            stage: per pipeline stage they wait for one barrier, issue the MMAs and commit.  With one
+//            accumulator stage (256 tokens) there is one issuer.
 //   4 - 5    copiers (one thread each; of a pair: in the first CTA only): tcgen05.cp of every stage's scale and
 //            metadata atoms from shared memory into the stage's slot of a ring in tensor memory (warp 4 the weight
 //            scales and the metadata, warp 5 the activation scales), then a tcgen05.commit that tells the issuers
@@ -29,8 +30,8 @@
 // Barriers per pipeline stage s: full[s] (this CTA's copies landed), peer_full[s] (pair: the second CTA's
 // copies landed, relayed to the first), sf_full[s] (copier's commit -> issuers: scales and metadata are in tensor
 // memory), empty[s] (issuer's tcgen05.commit, delivered to both CTAs of a pair -> producers).  Per accumulator
-// stage: acc_full (commit, both CTAs), acc_empty (all epilogue warps of the CTA or pair -> issuers).  Every
-// wait is bounded.
+// stage: acc_full (commit, both CTAs), acc_empty (all epilogue warps of the CTA or pair -> issuers).  Every wait
+// is bounded.
 
 template <int TILE_N, int STAGE_K, bool kPair>
 struct WideCfg {
@@ -53,9 +54,17 @@ struct WideCfg {
   static constexpr int kSfaBytes = 512 * kAtoms;
   static constexpr int kSfbRowAtoms = TILE_N > 128 ? 2 : 1;  // every CTA holds the scales of all TILE_N tokens
   static constexpr int kSfbBytes = kSfaBytes * kSfbRowAtoms;
+  // a pipeline stage in shared memory: [weights | activations | metadata | weight scales | activation scales]
   static constexpr int kStageBytes = kABytes + kBBytes + kEBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kOffA = 0;
+  static constexpr int kOffB = kABytes;
+  static constexpr int kOffE = kOffB + kBBytes;
+  static constexpr int kOffSfa = kOffE + kEBytes;
+  static constexpr int kOffSfb = kOffSfa + kSfaBytes;
   static constexpr int kChunk = TILE_N >= 128 ? 32 : 16;     // token columns an epilogue group takes at a time
   static constexpr int kFusedOutBytes = 4 * 8192;            // fused epilogue: one 8 KiB exchange area per group
+  static constexpr int kPlainWarpWords = 8 * 36;             // plain epilogue: 8 token pairs x 32 features (+ 4 words of padding) per warp
+  static constexpr int kPlainOutBytes = kEpilogueWarps * kPlainWarpWords * 4;
   static constexpr int kBarrierBytes = 1024;
   static constexpr int kMaxStages = 12;
   static constexpr int kAccStages = TILE_N == 256 ? 1 : 2;
@@ -67,11 +76,6 @@ struct WideCfg {
   static constexpr int kSlotE = kSlotSfb + kSfbColsPerAtom * kAtoms;
   static constexpr int kSlotCols = kSlotE + 4 * kEAtoms;
   static constexpr int kSlots = (kTmemCols - kColSlots) / kSlotCols;    // caps the pipeline depth
-  static constexpr int kOffA = 0;
-  static constexpr int kOffB = kABytes;
-  static constexpr int kOffE = kOffB + kBBytes;
-  static constexpr int kOffSfa = kOffE + kEBytes;
-  static constexpr int kOffSfb = kOffSfa + kSfaBytes;
   static_assert(kStageBytes % 1024 == 0 && kOffB % 1024 == 0, "operand tiles must keep 1024-byte alignment");
   static_assert(kAccStages * TILE_N <= kColSlots && kSlots >= 2, "tensor-memory column map overflows");
   static_assert(8 * (4 * kMaxStages + 2 * kAccStages) + 16 <= kBarrierBytes, "barrier block overflows");
@@ -100,8 +104,8 @@ __device__ __forceinline__ uint64_t pack_desc(uint32_t lo, uint32_t hi) {
   return d;
 }
 
-// Work items (tiles) position `unit` of `n_units` will process: items unit, unit + n_units, ... of the
-// list every role walks.  Warp-collective.
+// Work items (tiles) position `unit` of `n_units` will process: items unit, unit + n_units, ... of the list
+// every role walks.  Warp-collective.
 template <int TILE_N>
 __device__ __forceinline__ int my_work_items(const int* cnt, int E, int per_token_tile, int unit, int n_units, int lane) {
   long long sum = 0;
@@ -112,6 +116,28 @@ __device__ __forceinline__ int my_work_items(const int* cnt, int E, int per_toke
   return (long long)unit < total ? (int)((total - unit + n_units - 1) / n_units) : 0;
 }
 
+// The tiles of one unit (a CTA, or a CTA pair), in the order every role walks them: tiles unit, unit + units, ...
+// of the (expert, token tile, M unit) order, so that units working at the same time share token rows through L2.
+// next() moves to the following tile and says whether there was one.
+template <int TILE_N>
+struct UnitTiles {
+  int e, mu, nt;                 // the current tile: expert, M unit, token tile
+  TileWalk walk;
+  long long w;
+  int n_units;
+  __device__ void init(const int* s_counts, int E, int n_mu, int unit, int n_units_) {
+    walk.init<TILE_N>(s_counts, E, n_mu);
+    w = unit;
+    n_units = n_units_;
+  }
+  __device__ bool next() {
+    if (!walk.seek<TILE_N>(w, mu, nt)) return false;
+    w += n_units;
+    e = walk.e;
+    return true;
+  }
+};
+
 // tensor memory -> registers, kChunk (16 or 32) consecutive columns of this warp's lane quarter
 template <int N>
 __device__ __forceinline__ void tc_ld_cols(uint32_t taddr, uint32_t (&r)[N]);
@@ -119,19 +145,22 @@ template <>
 __device__ __forceinline__ void tc_ld_cols<32>(uint32_t taddr, uint32_t (&r)[32]) { ptx::tc_ld_32x32(taddr, r); }
 template <>
 __device__ __forceinline__ void tc_ld_cols<16>(uint32_t taddr, uint32_t (&r)[16]) { ptx::tc_ld_32x16(taddr, r); }
+template <>
+__device__ __forceinline__ void tc_ld_cols<8>(uint32_t taddr, uint32_t (&r)[8]) { ptx::tc_ld_32x8(taddr, r); }
 
 template <int TILE_N, int STAGE_K, bool kFused, bool kPair>
 __global__ void __launch_bounds__((6 + 16) * 32, 1)
 group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const Params p) {
   using C = WideCfg<TILE_N, STAGE_K, kPair>;
+  using Tiles = UnitTiles<TILE_N>;
   constexpr int kCtas = C::kCtas;
   constexpr int kChunk = C::kChunk;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_base = smem;
   uint8_t* after_stages = stage_base + p.stages * C::kStageBytes;
-  constexpr int kOutBytes = kFused ? C::kFusedOutBytes : 0;     // the plain epilogue stores from registers
+  constexpr int kOutBytes = kFused ? C::kFusedOutBytes : C::kPlainOutBytes;
   uint8_t* s_out = after_stages;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(after_stages + kOutBytes);
   uint64_t* empty_bar = full_bar + C::kMaxStages;
@@ -179,9 +208,6 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  TileWalk walk;
-  walk.init<TILE_N>(s_counts, p.E, n_mu);
-
   if (warp < 2) {
     // =============================== producers ===============================
     // In each producer warp p.prod_lanes lanes work side by side, lane i on pipeline slots i, i + lanes, ...:
@@ -194,6 +220,8 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const int slot_lane = tile_role ? lane : lane >> 1;     // which of the side-by-side pipeline slots
     const int part = lane & 1;                              // bulk-copy warp: 0 metadata, 1 scales
     if (slot_lane < p.prod_lanes) {
+      Tiles tiles;
+      tiles.init(s_counts, p.E, n_mu, unit, n_units);
       bool ok = true;
       int n = 0, ks = slot_lane, stage = slot_lane, cur_n = -1;     // prod_lanes <= stages (host)
       uint32_t turn = 0;
@@ -203,14 +231,14 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       while (ok) {
         while (ks >= p.k_stages) { ks -= p.k_stages; ++n; }
         if (n != cur_n) {                                  // a new tile: where it is, and its operand bases
-          int mu, nt;
-          if (!walk.seek<TILE_N>(unit + (long long)n * n_units, mu, nt)) break;
-          cur_n = n;
-          e = walk.e;
-          n0 = nt * TILE_N;
+          bool any = true;
+          while (cur_n < n && (any = tiles.next())) ++cur_n;
+          if (!any) break;
+          e = tiles.e;
+          n0 = tiles.nt * TILE_N;
           // the second CTA of a pair takes the odd M tile; past the last tile it re-reads the last one (its
           // results are never stored), so every copy stays inside the expert's operands
-          mt = kPair ? min(2 * mu + (int)rank, p.n_mt - 1) : mu;
+          mt = kPair ? min(2 * tiles.mu + (int)rank, p.n_mt - 1) : tiles.mu;
           if (!tile_role) {
             sfb_base = p.sfb + (((long long)e * p.sfb_rt + (n0 >> 7)) * p.n_kt) * 512;
             sfb_row_atoms = TILE_N > 128 ? min(2, p.sfb_rt - (n0 >> 7)) : 1;
@@ -220,6 +248,9 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         }
         const int k_atoms = min(C::kAtoms, p.n_kt - ks * C::kAtoms);
         const int b_boxes = (k_atoms + 1) / 2;
+        const int e_atoms = (k_atoms + 1) / 2;
+        const uint32_t sf_bytes = 512u * k_atoms;
+        uint8_t* st = stage_base + stage * C::kStageBytes;
         const long long tp0 = PNV_PROF_T();
         if (!ptx::mbar_wait(empty_bar + stage, turn ^ 1u)) {
           atomicExch(&g_status, tile_role ? kProducerEmptyTimeout : kSideProducerTimeout);
@@ -227,7 +258,6 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           break;
         }
         PNV_PROF_ACC(pf_wait, tp0);                             // waiting for a free stage
-        uint8_t* st = stage_base + stage * C::kStageBytes;
         if (tile_role) {
           // with the 4-D activation map one copy fetches all of the stage's 256-K chunks (a box past the
           // last chunk is zero-filled and still counts its full size)
@@ -241,21 +271,17 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
               ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + stage,
                                ks * (STAGE_K / 2) + b * 128, nb, e);
           }
+        } else if (part == 0) {
+          ptx::mbar_arrive_expect_tx(full_bar + stage, e_atoms * 2048);
+          for (int ea = 0; ea < e_atoms; ++ea)
+            ptx::bulk_load(st + C::kOffE + ea * 2048,
+                           e_base + (long long)(ks * C::kEAtoms + ea) * p.e_m_atoms * 2048, 2048, full_bar + stage);
         } else {
-          const int e_atoms = (k_atoms + 1) / 2;
-          const uint32_t sf_bytes = 512u * k_atoms;
-          if (part == 0) {
-            ptx::mbar_arrive_expect_tx(full_bar + stage, e_atoms * 2048);
-            for (int ea = 0; ea < e_atoms; ++ea)
-              ptx::bulk_load(st + C::kOffE + ea * 2048,
-                             e_base + (long long)(ks * C::kEAtoms + ea) * p.e_m_atoms * 2048, 2048, full_bar + stage);
-          } else {
-            ptx::mbar_arrive_expect_tx(full_bar + stage, sf_bytes * (1 + sfb_row_atoms));
-            ptx::bulk_load(st + C::kOffSfa, sfa_base + ks * (C::kAtoms * 512), sf_bytes, full_bar + stage);
-            for (int ra = 0; ra < sfb_row_atoms; ++ra)
-              ptx::bulk_load(st + C::kOffSfb + ra * C::kSfaBytes,
-                             sfb_base + ((long long)ra * p.n_kt + ks * C::kAtoms) * 512, sf_bytes, full_bar + stage);
-          }
+          ptx::mbar_arrive_expect_tx(full_bar + stage, sf_bytes * (1 + sfb_row_atoms));
+          ptx::bulk_load(st + C::kOffSfa, sfa_base + ks * (C::kAtoms * 512), sf_bytes, full_bar + stage);
+          for (int ra = 0; ra < sfb_row_atoms; ++ra)
+            ptx::bulk_load(st + C::kOffSfb + ra * C::kSfaBytes,
+                           sfb_base + ((long long)ra * p.n_kt + ks * C::kAtoms) * 512, sf_bytes, full_bar + stage);
         }
         ks += p.prod_lanes;
         stage += p.prod_lanes;
@@ -274,13 +300,15 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     // A tcgen05.mma holds its issuing thread for about as long as it executes, so whatever else that
     // thread does between two MMAs is time the tensor pipe idles.  Two issuers in two warps take alternate
     // tiles, each into its own accumulator stage; while one is between MMAs the other's are executing.
-    // Every tile's MMAs still come from one thread, in K order.  The issuer does no tile arithmetic and no
-    // copies: it counts its tiles once and then only waits, issues and commits.
+    // Every tile's MMAs still come from one thread, in K order.  The issuer does no copies: it counts its
+    // tiles once and then only waits, issues and commits.
     constexpr int kIssuers = C::kAccStages == 2 ? 2 : 1;
     const int issuer = warp - 2;
     const int n_items = my_work_items<TILE_N>(s_counts, p.E, n_mu, unit, n_units, lane);
     if (lane == 0 && issuer < kIssuers && rank == 0) {
       constexpr uint32_t idesc = ptx::mma_sp_nvf4_idesc(TILE_N, kTileM * kCtas);
+      Tiles tiles;
+      tiles.init(s_counts, p.E, n_mu, unit, n_units);
       int stage = 0, acc = kIssuers == 2 ? issuer : 0;
       uint32_t phase = 0, acc_phase = 0, soff = 0;
       bool ok = true;
@@ -302,7 +330,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         PNV_PROF_ACC(pf_skip, tk0);
       };
       if (kIssuers == 2 && issuer == 1 && n_items > 1) skip_stages(p.k_stages);
-      // stage-0 descriptors, split into the 32-bit halves: only the low half changes with the address
+      // first-tile descriptors, split into the 32-bit halves: only the low half changes with the address
       const uint64_t d_a0 = ptx::smem_desc(ptx::smem_u32(stage_base) + C::kOffA, 8 * C::kARowBytes, 16, C::kASwizzle);
       const uint64_t d_b0 = ptx::smem_desc(ptx::smem_u32(stage_base) + C::kOffB, 1024, 16, 2);
       const uint32_t lo_a0 = (uint32_t)d_a0, hi_a = (uint32_t)(d_a0 >> 32);
@@ -316,9 +344,11 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         // faults on an odd scale column); wider tiles start at column 0 and need no tile coordinates
         uint32_t sfb_off = 0;
         if (TILE_N < 128) {
-          int mu, nt;
-          if (!walk.seek<TILE_N>(unit + (long long)item * n_units, mu, nt)) break;
-          sfb_off = ((nt * TILE_N) & 127) >> 5;
+          // (two issuers: each walks every tile and uses every other one)
+          bool any = true;
+          for (int s = item < kIssuers ? item + 1 : kIssuers; s > 0 && any; --s) any = tiles.next();
+          if (!any) break;
+          sfb_off = ((tiles.nt * TILE_N) & 127) >> 5;
         }
         const long long ta0 = PNV_PROF_T();
         if (!ptx::mbar_wait(acc_empty + acc, acc_phase ^ 1)) {
@@ -383,7 +413,9 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const int copier = warp - 4;
     const int n_items = my_work_items<TILE_N>(s_counts, p.E, n_mu, unit, n_units, lane);
     const long long n_stages = (long long)n_items * p.k_stages;
-    if (lane == 0 && rank == 0) {
+    if (lane == 0 && (rank == 0 || (kPair && copier == 0))) {
+      // of a pair's second CTA only warp 4 works here: it tells the first CTA when each stage's copies have landed
+      const bool relay = rank != 0;
       const uint64_t d_sfa0 = ptx::smem_desc(ptx::smem_u32(stage_base) + C::kOffSfa, 128, 0, 0);
       const uint64_t d_sfb0 = ptx::smem_desc(ptx::smem_u32(stage_base) + C::kOffSfb, 128, 0, 0);
       const uint64_t d_e0 = ptx::smem_desc(ptx::smem_u32(stage_base) + C::kOffE, 128, 0, 0);
@@ -397,53 +429,44 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 #pragma unroll 1
       for (long long g = 0; g < n_stages; ++g) {
         const long long tc0 = PNV_PROF_T();
-        if (!ptx::mbar_wait(full_bar + stage, phase) || (kPair && !ptx::mbar_wait(peer_full + stage, phase))) {
+        if (!ptx::mbar_wait(full_bar + stage, phase) || (kPair && !relay && !ptx::mbar_wait(peer_full + stage, phase))) {
           atomicExch(&g_status, kScaleLoaderTimeout);
           break;
         }
         PNV_PROF_ACC(pf_cwait, tc0);                            // waiting for landed copies
-        ptx::tc_fence_after();
-        const long long tc1 = PNV_PROF_T();
-        const int k_atoms = ks + 1 == p.k_stages ? last_atoms : C::kAtoms;
-        const uint32_t soff = (uint32_t)stage * (C::kStageBytes >> 4);
-        const uint32_t slot = slots0 + stage * C::kSlotCols;
-        if (copier == 0) {
-#pragma unroll
-          for (int ka = 0; ka < C::kAtoms; ++ka)
-            if (ka < k_atoms) ptx::tc_cp_32x128b_warpx4<kCtas>(slot + ka * 4, pack_desc(lo_sfa0 + soff + ka * 32, hi));
-#pragma unroll
-          for (int ea = 0; ea < C::kEAtoms; ++ea)
-            if (2 * ea < k_atoms) ptx::tc_cp_128x128b<kCtas>(slot + C::kSlotE + ea * 4, pack_desc(lo_e0 + soff + ea * 128, hi));
+        if (relay) {
+          ptx::mbar_arrive_cluster(peer_full + stage, 0);
         } else {
+          ptx::tc_fence_after();
+          const long long tc1 = PNV_PROF_T();
+          const int k_atoms = ks + 1 == p.k_stages ? last_atoms : C::kAtoms;
+          const uint32_t soff = (uint32_t)stage * (C::kStageBytes >> 4);
+          const uint32_t slot = slots0 + stage * C::kSlotCols;
+          if (copier == 0) {
 #pragma unroll
-          for (int ka = 0; ka < C::kAtoms; ++ka) {
-            if (ka < k_atoms) {
+            for (int ka = 0; ka < C::kAtoms; ++ka)
+              if (ka < k_atoms) ptx::tc_cp_32x128b_warpx4<kCtas>(slot + ka * 4, pack_desc(lo_sfa0 + soff + ka * 32, hi));
 #pragma unroll
-              for (int ra = 0; ra < C::kSfbRowAtoms; ++ra)
-                ptx::tc_cp_32x128b_warpx4<kCtas>(slot + C::kSlotSfb + ka * C::kSfbColsPerAtom + ra * 4,
-                                                 pack_desc(lo_sfb0 + soff + ra * (C::kSfaBytes >> 4) + ka * 32, hi));
+            for (int ea = 0; ea < C::kEAtoms; ++ea)
+              if (2 * ea < k_atoms) ptx::tc_cp_128x128b<kCtas>(slot + C::kSlotE + ea * 4, pack_desc(lo_e0 + soff + ea * 128, hi));
+          } else {
+#pragma unroll
+            for (int ka = 0; ka < C::kAtoms; ++ka) {
+              if (ka < k_atoms) {
+#pragma unroll
+                for (int ra = 0; ra < C::kSfbRowAtoms; ++ra)
+                  ptx::tc_cp_32x128b_warpx4<kCtas>(slot + C::kSlotSfb + ka * C::kSfbColsPerAtom + ra * 4,
+                                                   pack_desc(lo_sfb0 + soff + ra * (C::kSfaBytes >> 4) + ka * 32, hi));
+              }
             }
           }
+          ptx::tc_commit_local<kCtas>(sf_full + stage);     // arrives once the copies above have completed
+          PNV_PROF_ACC(pf_cissue, tc1);                           // issuing copies
         }
-        ptx::tc_commit_local<kCtas>(sf_full + stage);     // arrives once the copies above have completed
-        PNV_PROF_ACC(pf_cissue, tc1);                           // issuing copies
         if (++ks == p.k_stages) ks = 0;
         if (++stage == p.stages) { stage = 0; phase ^= 1; }
       }
-      if (copier == 0) { PNV_PROF_SET(6, pf_cwait); PNV_PROF_SET(7, pf_cissue); }
-    } else if (kPair && lane == 0 && rank != 0 && copier == 0) {
-      // second CTA of a pair: tell the first when each stage's copies have landed here
-      int stage = 0;
-      uint32_t phase = 0;
-#pragma unroll 1
-      for (long long g = 0; g < n_stages; ++g) {
-        if (!ptx::mbar_wait(full_bar + stage, phase)) {
-          atomicExch(&g_status, kScaleLoaderTimeout);
-          break;
-        }
-        ptx::mbar_arrive_cluster(peer_full + stage, 0);
-        if (++stage == p.stages) { stage = 0; phase ^= 1; }
-      }
+      if (copier == 0 && !relay) { PNV_PROF_SET(6, pf_cwait); PNV_PROF_SET(7, pf_cissue); }
     }
     __syncwarp();
   } else {
@@ -499,10 +522,10 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       }
     };
     long long pf_ewait = 0, pf_ework = 0, pf_f0 = 0, pf_f1 = 0, pf_f2 = 0, pf_f3 = 0;
-    for (long long w = unit;; w += n_units) {
-      int mu, nt;
-      if (!walk.seek<TILE_N>(w, mu, nt)) break;
-      const int e = walk.e;
+    Tiles tiles;
+    tiles.init(s_counts, p.E, n_mu, unit, n_units);
+    while (tiles.next()) {
+      const int e = tiles.e, mu = tiles.mu, nt = tiles.nt;
       const int cnt = s_counts[e];
       const int mt = kPair ? 2 * mu + (int)rank : mu;
       const bool mt_valid = mt < p.n_mt;       // the second CTA of the last pair of an odd tile count stores nothing
@@ -519,23 +542,28 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       const uint32_t t_row = tmem_base + ((uint32_t)(sub * 32) << 16) + acc * TILE_N;
       bool released = false;
       if (!kFused) {
-        // Plain epilogue.  A warp holds 32 features x kChunk tokens of the accumulator; it scales, rounds to bf16
-        // and stores straight from registers, one instruction per token: 32 lanes x 2 bytes = 64 contiguous
-        // bytes of that token's output row (two whole 32-byte sectors; the neighbouring lane quarters of the same
-        // group fill the rest of the line at about the same time).  No shared memory, no barrier, nothing to wait
-        // for: the warp goes straight back to the next tensor-memory load.  Rows at or past counts[e] are skipped.
+        // Plain epilogue.  A warp holds 32 features x kChunk tokens of the accumulator: it scales and rounds them to
+        // bf16, hands the accumulator back, and then stores - when the output rows are 16-byte aligned, through a
+        // warp-private transpose in shared memory (no barrier beyond the warp's own), else one token row at a time
+        // straight from registers (64 contiguous bytes per instruction).  Rows at or past counts[e] are skipped.
         const long long row_e = (long long)e * p.max_n;
         const int m = mt * kTileM + m_local;
         constexpr int kOwn = TILE_N / (4 * kChunk);       // chunks of a tile each group takes (1, or 2 for 256 tokens)
         const bool mine = mt_valid && m < p.M;
         const long long pitch = p.M;
-        // the warp's share of the tile, scaled and rounded, two tokens to a register (cvt.rn.bf16x2.f32: first
-        // argument in the low half): kept packed so that two chunks fit under this kernel's register cap
-        uint32_t pk[kOwn][kChunk / 2];
+        const bool wide_rows = (p.M & 7) == 0;            // output rows are 16-byte aligned
+        uint32_t* tbuf = reinterpret_cast<uint32_t*>(s_out) + (warp - C::kFirstEpilogueWarp) * C::kPlainWarpWords;
+        // One chunk at a time: load, (after the warp's last chunk) hand the accumulator back, scale and round two
+        // tokens to a register (cvt.rn.bf16x2.f32: first argument in the low half), store.  A chunk's stores are
+        // issued and forgotten, so taking the first chunk all the way before loading the second delays the
+        // hand-back by little, and the two chunks never sit in registers together (that spilled, and the spill
+        // traffic to L2 was of the order of the output itself).
 #pragma unroll
         for (int j = 0; j < kOwn; ++j) {
           const int c0 = (group + 4 * j) * kChunk;
-          if (n0 + c0 < cnt) {                            // the same for all lanes
+          const int rows = cnt - (n0 + c0);               // live token rows from c0 on; the same for all lanes
+          uint32_t pk[kChunk / 2];
+          if (rows > 0) {
             uint32_t v[kChunk];
             tc_ld_cols<kChunk>(t_row + c0, v);
             ptx::tc_ld_wait();
@@ -543,23 +571,49 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             for (int i = 0; i < kChunk; i += 2) {
               const __nv_bfloat162 pr = __floats2bfloat162_rn(__fmul_rn(alpha, __uint_as_float(v[i])),
                                                              __fmul_rn(alpha, __uint_as_float(v[i + 1])));
-              pk[j][i / 2] = *reinterpret_cast<const uint32_t*>(&pr);
+              pk[i / 2] = *reinterpret_cast<const uint32_t*>(&pr);
             }
           }
-        }
-        release_acc();                                    // the issuers may reuse the accumulator while this warp stores
-        released = true;
-#pragma unroll
-        for (int j = 0; j < kOwn; ++j) {
-          const int c0 = (group + 4 * j) * kChunk;
-          const int rows = cnt - (n0 + c0);               // live token rows from c0 on
+          if (j == kOwn - 1) {                            // the issuers may reuse the accumulator while this warp stores
+            release_acc();
+            released = true;
+          }
           if (rows <= 0) continue;
-          if (p.row_map == nullptr) {
+          if (wide_rows) {
+            // 16 tokens at a time through a private corner of shared memory ([token pair][feature] words, rows
+            // padded to 36 words so that neither side has bank conflicts): lane (k, f) = (lane / 4, lane % 4)
+            // reads features 8 f .. 8 f + 7 of token pair k and stores 16 bytes per token, so one instruction
+            // writes 64 contiguous bytes of each of eight output rows instead of 64 bytes of one.
+            const int pr_row = lane >> 2, fg = lane & 3;
+            const int m8 = mt * kTileM + sub * 32 + fg * 8;
+            const bool mine8 = mt_valid && m8 < p.M;
+#pragma unroll
+            for (int h = 0; h < kChunk / 16; ++h) {
+              __syncwarp();
+#pragma unroll
+              for (int q = 0; q < 8; ++q) tbuf[q * 36 + lane] = pk[h * 8 + q];
+              __syncwarp();
+              const uint4 a = *reinterpret_cast<const uint4*>(tbuf + pr_row * 36 + fg * 8);
+              const uint4 b = *reinterpret_cast<const uint4*>(tbuf + pr_row * 36 + fg * 8 + 4);
+              const uint4 lo = make_uint4(__byte_perm(a.x, a.y, 0x5410), __byte_perm(a.z, a.w, 0x5410),
+                                          __byte_perm(b.x, b.y, 0x5410), __byte_perm(b.z, b.w, 0x5410));
+              const uint4 hi = make_uint4(__byte_perm(a.x, a.y, 0x7632), __byte_perm(a.z, a.w, 0x7632),
+                                          __byte_perm(b.x, b.y, 0x7632), __byte_perm(b.z, b.w, 0x7632));
+              const int t0 = h * 16 + 2 * pr_row;          // this lane's even token inside the chunk
+              long long to0 = t0 < rows ? row_e + n0 + c0 + t0 : -1, to1 = t0 + 1 < rows ? to0 + 1 : -1;
+              if (p.row_map != nullptr) {
+                if (to0 >= 0) to0 = p.row_map[to0];
+                if (to1 >= 0) to1 = p.row_map[row_e + n0 + c0 + t0 + 1];
+              }
+              if (mine8 && to0 >= 0) *reinterpret_cast<uint4*>(p.out + to0 * pitch + m8) = lo;
+              if (mine8 && to1 >= 0) *reinterpret_cast<uint4*>(p.out + to1 * pitch + m8) = hi;
+            }
+          } else if (p.row_map == nullptr) {
             const int live = mine ? min(kChunk, rows) : 0;
             unsigned short* dst = reinterpret_cast<unsigned short*>(p.out + (row_e + n0 + c0) * p.M + m);
 #pragma unroll
             for (int i = 0; i < kChunk; i += 2) {
-              const uint32_t w = pk[j][i / 2];
+              const uint32_t w = pk[i / 2];
               if (i < live) dst[(long long)i * pitch] = (unsigned short)(w & 0xFFFFu);
               if (i + 1 < live) dst[(long long)(i + 1) * pitch] = (unsigned short)(w >> 16);
             }
@@ -569,7 +623,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             unsigned short* base = reinterpret_cast<unsigned short*>(p.out) + m;
 #pragma unroll
             for (int i = 0; i < kChunk; i += 2) {
-              const uint32_t w = pk[j][i / 2];
+              const uint32_t w = pk[i / 2];
               const int to0 = __shfl_sync(0xffffffffu, to_lane, i), to1 = __shfl_sync(0xffffffffu, to_lane, i + 1);
               if (mine && to0 >= 0) base[(long long)to0 * pitch] = (unsigned short)(w & 0xFFFFu);
               if (mine && to1 >= 0) base[(long long)to1 * pitch] = (unsigned short)(w >> 16);
@@ -601,32 +655,32 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const long long code_pitch = p.f_n / 2;
 #pragma unroll 1
         for (int c0 = group * kChunk; c0 < TILE_N && n0 + c0 < cnt; c0 += 4 * kChunk) {
-          uint32_t v[kChunk];
+          // the half of the chunk this warp finishes and the half it parks for its partner, as two loads (the
+          // column offsets differ between the gate and the up warp, the register indices do not)
+          uint32_t v_own[kHalf], v_oth[kHalf];
           const long long tf0 = PNV_PROF_T();
-          tc_ld_cols<kChunk>(t_row + c0, v);
+          tc_ld_cols<kHalf>(t_row + c0 + par * kHalf, v_own);
+          tc_ld_cols<kHalf>(t_row + c0 + (1 - par) * kHalf, v_oth);
           ptx::tc_ld_wait();
           if (c0 + 4 * kChunk >= TILE_N || n0 + c0 + 4 * kChunk >= cnt) { release_acc(); released = true; }
           PNV_PROF_ACC(pf_f0, tf0);                // tensor-memory load
           if (!mt_valid) continue;                 // the same for every thread of the CTA
           const long long tf1 = PNV_PROF_T();
-          // bf16(alpha * acc), two tokens to a word (token 2k in the low half)
-          uint32_t hp[kChunk / 2];
-#pragma unroll
-          for (int k = 0; k < kChunk / 2; ++k) {
-            const __nv_bfloat162 pr = __floats2bfloat162_rn(__fmul_rn(alpha, __uint_as_float(v[2 * k])),
-                                                           __fmul_rn(alpha, __uint_as_float(v[2 * k + 1])));
-            hp[k] = *reinterpret_cast<const uint32_t*>(&pr);
-          }
           uint32_t* area = xbuf + flip * (2 * kPk * 32);
           uint32_t* x_mine = area + par * (kPk * 32);
           const uint32_t* x_other = area + (1 - par) * (kPk * 32);
           flip ^= 1;
-#pragma unroll
-          for (int k = 0; k < kPk; ++k) x_mine[k * 32 + lane] = is_up ? hp[k] : hp[kPk + k];
-          // own halves: gates of the first half of the chunk, or ups of the second
+          // bf16(alpha * acc), two tokens to a word (the even token in the low half)
           uint32_t own[kPk];
 #pragma unroll
-          for (int k = 0; k < kPk; ++k) own[k] = is_up ? hp[kPk + k] : hp[k];
+          for (int k = 0; k < kPk; ++k) {
+            const __nv_bfloat162 po = __floats2bfloat162_rn(__fmul_rn(alpha, __uint_as_float(v_oth[2 * k])),
+                                                           __fmul_rn(alpha, __uint_as_float(v_oth[2 * k + 1])));
+            x_mine[k * 32 + lane] = *reinterpret_cast<const uint32_t*>(&po);
+            const __nv_bfloat162 pr = __floats2bfloat162_rn(__fmul_rn(alpha, __uint_as_float(v_own[2 * k])),
+                                                           __fmul_rn(alpha, __uint_as_float(v_own[2 * k + 1])));
+            own[k] = *reinterpret_cast<const uint32_t*>(&pr);
+          }
           float sv[kHalf];
           if (table && !is_up) {                   // the gate warp's lookups are in flight across the barrier
 #pragma unroll

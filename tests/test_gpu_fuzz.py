@@ -63,7 +63,7 @@ def test_fused_gate_up_random_shapes(seed):
         K = int(rng.choice([32, 256, 320, 768, 1024, 2048]))
         max_n = 1024 if big else int(rng.choice([8, 16, 24, 33, 64, 100, 200, 257]))
         counts = rng.integers(0, max_n + 1, E).astype(np.int32)
-        fcfg = int(rng.integers(0, 5))
+        fcfg = int(rng.integers(0, 6))
         act = ["silu", "situ"][int(rng.integers(0, 2))]
         beta, lb = (1.702, 1.0) if act == "situ" else (1.0, -1.0)
         packed, sf, _ = make_weights(E, M, K, 3000 * seed + it, 1.0)
@@ -79,7 +79,7 @@ def test_fused_gate_up_random_shapes(seed):
         cm = 2 if "2sm" in name else 1
         fb, fsf = ops.group_mm_swiglu_quant(a_comp, e_meta, sfa, b_act, sfb, dev(al), dev(counts), dev(g2), M, K, fcfg,
                                             cm, 1, act, beta, lb)
-        base = {0: 6, 1: 4, 2: 5, 3: 0, 4: 2}[fcfg]
+        base = {0: 6, 1: 4, 2: 5, 3: 0, 4: 2, 5: 1}[fcfg]
         out = torch.zeros((E, max_n, M), dtype=torch.bfloat16, device="cuda")
         ops.group_mm(out, a_comp, e_meta, sfa, b_act, sfb, dev(al), dev(counts), M, K, base, cm, 1)
         y = ops.gated_act(out, True, act, beta, lb)

@@ -94,6 +94,18 @@ def test_many_long_tiles_per_cta(pnk, config_id):
              wscale=0.05)
 
 
+@pytest.mark.parametrize("config_id", [0, 1])
+@pytest.mark.parametrize("K", [768, 2048, 3072])
+def test_pair_kernels_over_many_ragged_experts(pnk, config_id, K):
+    # many experts with ragged counts (some empty, one full, one with a single token) on the pair kernels: more
+    # tiles than CTA pairs, M not a multiple of the pair's 256 rows, K loops shorter and longer than the ring
+    rng = np.random.default_rng(K)
+    counts = rng.integers(0, 601, 28)
+    counts[[3, 4, 17]] = 0
+    counts[5], counts[6] = 600, 1
+    run_case(pnk, E=28, M=768 - 24, K=K, max_n=600, counts=counts.tolist(), config_id=config_id, seed=K, wscale=0.05)
+
+
 def test_gscale_and_alpha_undo_each_other(pnk):
     E, M, K, max_n = 4, 256, 512, 48
     x_amax = 4.5

@@ -39,6 +39,7 @@ CASES = [
     (64, 128, 1, 16, [16]),                 # one 128-row tile, small-batch path
     (2048, 1024, 2, 16, [9, 16]),           # decode-like
     (192, 768, 2, 130, [130, 64]),
+    (384, 1536, 9, 520, [520, 0, 300, 1, 257, 128, 519, 33, 256]),   # many ragged experts, several token tiles each
 ]
 
 
@@ -52,10 +53,10 @@ def test_fused_equals_unfused_bytes(pnk, N, K, E, max_n, counts, act, beta, lbet
     names = ops.group_mm_swiglu_configs()
     # the reference's four names and ids, then this build's addition
     assert names[:4] == ["fused_2sm_256x64_k512", "fused_2sm_256x64", "fused_1sm_128x64", "fused_2sm_256x128"]
-    assert names[4:] == ["fused_1sm_128x128"]
+    assert names[4:] == ["fused_1sm_128x128", "fused_2sm_256x256"]
     # unfused chain on the same interleaved weight; the GEMM tile choice does not change a single bit of its
     # accumulation order per output element, but compare like with like anyway
-    base_cfg = {0: 6, 1: 4, 2: 5, 3: 0, 4: 2}
+    base_cfg = {0: 6, 1: 4, 2: 5, 3: 0, 4: 2, 5: 1}
     for cid, cm, cn in pnk.fused_swiglu_tactics():
         out1 = torch.zeros(E, max_n, 2 * N, dtype=torch.bfloat16, device="cuda")
         ops.group_mm(out1, o["a_comp"], o["e_meta"], o["sfa"], o["b_act"], o["sfb"], o["al"], o["cnt"], 2 * N, K,
