@@ -54,16 +54,16 @@ WORKLOADS = {
                 cap=16, routing="one", seed=1006, config_id=7, wstd=0.02),
     # Qwen3-30B-A3B MoE, prefill: 16384 tokens, top-8 of 128, cap 2048
     "c3": dict(desc="prefill Qwen3-30B-A3B-shaped MoE", E=128, hidden=2048, inter=768, cap=2048,
-               routing="topk", tokens=16384, topk=8, seed=1002, config_id=0, wstd=0.02),
+               routing="topk", tokens=16384, topk=8, seed=1002, config_id=1, wstd=0.02),
     # DeepSeek-V3 MoE, expert parallel: 8192 tokens per rank, top-8 of 256
     "c4": dict(desc="DeepSeek-V3-shaped MoE, expert parallel", E=256, hidden=7168, inter=2048, cap=1024,
-               routing="topk", tokens=8192, topk=8, seed=1003, config_id=0, wstd=0.02),
+               routing="topk", tokens=8192, topk=8, seed=1003, config_id=1, wstd=0.02),
     # the per-rank shape of c4 at 8 ranks (32 local experts, 65536 routed rows), without the exchange
     "c4r8": dict(desc="DeepSeek-V3-shaped MoE, one rank's expert shard at 8 ranks", E=32, hidden=7168, inter=2048,
-                 cap=4096, routing="topk", tokens=8192, topk=8, seed=1005, config_id=0, wstd=0.02),
+                 cap=4096, routing="topk", tokens=8192, topk=8, seed=1005, config_id=1, wstd=0.02),
     # skewed routing: Zipf(1.2) expert popularity, top-4 of 128 over 8192 tokens, cap 4096
     "c5": dict(desc="skewed-routing MoE (Zipf 1.2)", E=128, hidden=3072, inter=3072, cap=4096,
-               routing="zipf", tokens=8192, topk=4, seed=1004, config_id=0, wstd=0.02),
+               routing="zipf", tokens=8192, topk=4, seed=1004, config_id=1, wstd=0.02),
 }
 METRIC = "moe_expert_ffn_group_mm_dense_equiv_tflops"
 
@@ -83,6 +83,9 @@ def parse_args():
     ap.add_argument("--passes", type=int, default=None,
                     help="passes per step (default: as many as make the timed steps last half a second); "
                          "small values keep a profiler capture short")
+    ap.add_argument("--exchange", default="direct", choices=["direct", "nccl"],
+                    help="N > 1: 'direct' = the producing kernels store wire rows and expert outputs straight into the "
+                         "other ranks' buffers (peer memory); 'nccl' = an all-to-all either side of the local FFN")
     ap.add_argument("--slab-headroom", type=float, default=1.125, help="expert-parallel slab rows over the mean load")
     return ap.parse_args()
 
@@ -687,10 +690,13 @@ def run_expert_parallel(args, wl_name, wl, rank, world, local_rank, device):
         dist.all_reduce(g1, op=dist.ReduceOp.MIN)
     al1 = (1.0 / g1).expand(E_local).contiguous()
 
-    def make_ffn(w, g2, al2):
+    direct = world > 1 and args.exchange == "direct"
+    peers = ep.PeerBuffers(world, rank, slab, H, int(_cabi.lib.pnv_wire_row_bytes(H)), device) if direct else None
+
+    def make_ffn(w, g2, al2, peers=None):
         return ep.ExpertParallelFFN((w["a13"], w["e13"], w["s13"]), (w["a2"], w["e2"], w["s2"]), H, I, cap, al1, al2, g1, g2,
                                     slab, fused_config=fused_cfg, config_id=cfg, cluster_m=cluster_m, fused_cluster_m=fused_cm, world=world,
-                                    rank=rank)
+                                    rank=rank, peers=peers)
 
     # second quantizer's scales from the activation range of one unfused pass over the received rows
     ones = torch.ones(E_local, device=device)
@@ -707,7 +713,7 @@ def run_expert_parallel(args, wl_name, wl, rank, world, local_rank, device):
     g2 = (6.0 * 448.0 / amax.clamp(min=1e-6)).contiguous()
     al2 = (1.0 / g2).contiguous()
     del h, y, b1, sfb1, wire, recv, probe
-    ffns = [make_ffn(w, g2, al2) for w in weights]
+    ffns = [make_ffn(w, g2, al2, peers) for w in weights]
     out = torch.empty((T, H), dtype=torch.bfloat16, device=device)
 
     def one_pass(i, mark=None):
@@ -798,6 +804,8 @@ def run_expert_parallel(args, wl_name, wl, rank, world, local_rank, device):
         e2e = dict(value=flops_pass / (ms_e2e * 1e-3) / 1e12, unit="TFLOP/s", ms_per_pass=ms_e2e,
                    h2d_bytes_per_step=host_x.numel() * 2 * world * passes, d2h_bytes_per_step=host_out.numel() * 2 * world * passes,
                    passes=n, mode="eager operator calls, host-synchronised per pass")
+    if peers is not None:
+        peers.close()          # a collective: before the other ranks leave
     if rank != 0:
         return None
     rb = _cabi.lib.pnv_wire_row_bytes(H)
@@ -810,8 +818,12 @@ def run_expert_parallel(args, wl_name, wl, rank, world, local_rank, device):
                    "routed_rows_kept_rank0": kept, "slab_rows": slab, "routings_dropped_by_slab_rank0": slab_drops,
                    "tile_config": names[cfg], "fused_swiglu_epilogue": True, "parallelism": f"ep{world}",
                    "passes_per_step": passes,
-                   "exchange": "one equal-split NCCL all_to_all_single each way: NVFP4 wire rows out, bf16 rows back; "
-                               "routing planned on the device inside every pass" if world > 1 else
+                   "exchange": ("direct: pack_wire_rows stores NVFP4 wire rows into the receivers' buffers and the down "
+                                "GEMM's epilogue stores bf16 expert outputs into the senders' buffers over NVLink (peer memory, "
+                                "plain stores); two one-element all-reduces per pass order them; the phases named all_to_all_* "
+                                "are those fences" if direct else
+                                "one equal-split NCCL all_to_all_single each way: NVFP4 wire rows out, bf16 rows back; "
+                                "routing planned on the device inside every pass") if world > 1 else
                                "N = 1: both all-to-alls are the identity, everything else is the N > 1 pass",
                    "l2": "inputs larger than L2" + ("; two weight copies alternate" if copies > 1 else "")},
         "layer_us": pass_s * 1e6, "step_ms_mean": float(step_ms.mean()), "step_ms_p10": float(np.percentile(step_ms, 10)),

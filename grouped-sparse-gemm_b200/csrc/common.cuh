@@ -77,6 +77,34 @@ __host__ __device__ inline long long sf_offset(int g, int r, int kb, int n_rt, i
   return atom * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (kb & 3);
 }
 
+// ---- outputs spread over several buffers ---------------------------------------------------------
+//
+// Row q of a logical [n * rows_per_part, width] output lives at row q % rows_per_part of buffer q / rows_per_part.
+// The buffers may be another GPU's memory mapped into this process (peer access): the expert-parallel exchange
+// lets the producing kernel store every row straight into the buffer of the rank that wants it.
+constexpr int kMaxRowParts = 16;
+struct RowParts {
+  void* base[kMaxRowParts];
+  int n;                 // 0: a single buffer, addressed the ordinary way
+  int rows_per_part;
+};
+inline int make_row_parts(void* const* parts, int n_parts, long long rows_per_part, RowParts& out) {
+  PNV_REQUIRE(parts != nullptr, "null pointer argument");
+  PNV_REQUIRE(n_parts >= 1 && n_parts <= kMaxRowParts, "between 1 and %d output parts, got %d", kMaxRowParts, n_parts);
+  PNV_REQUIRE(rows_per_part >= 1 && rows_per_part < (1LL << 31), "bad rows_per_part");
+  for (int i = 0; i < kMaxRowParts; ++i) out.base[i] = i < n_parts ? parts[i] : nullptr;
+  for (int i = 0; i < n_parts; ++i)
+    PNV_REQUIRE(parts[i] != nullptr && reinterpret_cast<uintptr_t>(parts[i]) % 16 == 0, "output part %d is null or not 16-byte aligned", i);
+  out.n = n_parts;
+  out.rows_per_part = (int)rows_per_part;
+  return PNV_OK;
+}
+// Address of byte 0 of row q (rows of `pitch` bytes).
+__device__ __forceinline__ uint8_t* part_row(const RowParts& parts, long long q, long long pitch) {
+  const int w = (int)(q / parts.rows_per_part);
+  return static_cast<uint8_t*>(parts.base[w]) + (q - (long long)w * parts.rows_per_part) * pitch;
+}
+
 // ---- programmatic dependent launch -----------------------------------------------------------
 
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

@@ -113,6 +113,7 @@ struct Params {
   // plain epilogue: token row (e, n) is written to output row row_map[e * max_n + n] of a [rows, M] output,
   // and not at all where the map is negative; nullptr = row e * max_n + n
   const int* row_map;
+  RowParts out_parts;  // with a row map: the output rows spread over several buffers (n = 0: all in `out`)
   int E, M, K, max_n;
   int n_mt;          // ceil(M / 128)
   int k_stages;      // ceil(K / STAGE_K)
@@ -136,6 +137,12 @@ struct Params {
   int f_n_kt;              // scale K-atoms of the N-wide output
   GatedAct f_act;
 };
+
+// Where output row `to` of a row-mapped launch starts.
+__device__ __forceinline__ __nv_bfloat16* mapped_row(const Params& p, long long to) {
+  if (p.out_parts.n == 0) return p.out + to * p.M;
+  return reinterpret_cast<__nv_bfloat16*>(part_row(p.out_parts, to, 2LL * p.M));
+}
 
 // The walk over (expert, n tile, m tile) shared by all roles.
 struct TileWalk {
@@ -634,7 +641,8 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             if (n < cnt && m < p.M) {
               const long long to = p.row_map ? (long long)p.row_map[row_e + n] : row_e + n;
               if (to >= 0)
-                *reinterpret_cast<uint4*>(p.out + to * p.M + m) = *reinterpret_cast<const uint4*>(buf + row * kOutRow + col);
+                *reinterpret_cast<uint4*>((p.row_map ? mapped_row(p, to) : p.out + to * p.M) + m) =
+                    *reinterpret_cast<const uint4*>(buf + row * kOutRow + col);
             }
           }
           ++chunk;
@@ -646,7 +654,8 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               const int n = n0 + c0 + i;
               if (n < cnt) {
                 const long long to = p.row_map ? (long long)p.row_map[row_e + n] : row_e + n;
-                if (to >= 0) p.out[to * p.M + m] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(r[i])));
+                if (to >= 0)
+                  (p.row_map ? mapped_row(p, to) : p.out + to * p.M)[m] = __float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(r[i])));
               }
             }
           }
@@ -982,12 +991,12 @@ const FusedKind kFusedKinds[] = {
 };
 constexpr int kNumFusedKinds = sizeof(kFusedKinds) / sizeof(kFusedKinds[0]);
 
-int group_mm_common(void* out, const int32_t* row_map, const FusedArgs* fused, const uint8_t* a_comp, const uint8_t* e_meta,
+int group_mm_common(void* out, const int32_t* row_map, const RowParts* out_parts, const FusedArgs* fused, const uint8_t* a_comp, const uint8_t* e_meta,
                     const uint8_t* sfa, const uint8_t* b_act, const uint8_t* sfb, const float* alphas,
                     const int32_t* counts, int experts, int features, int k, int max_n, int config_id,
                     int cluster_m, int cluster_n, int sm_count, int pdl, void* workspace, int64_t workspace_bytes,
                     pnv_stream_t stream, const char* display_name) {
-  PNV_REQUIRE(out && a_comp && e_meta && sfa && b_act && sfb && alphas && counts, "null pointer argument");
+  PNV_REQUIRE((out || out_parts) && a_comp && e_meta && sfa && b_act && sfb && alphas && counts, "null pointer argument");
   PNV_REQUIRE(experts >= 1 && features >= 1 && max_n >= 1, "experts, features and max_n must be positive");
   PNV_REQUIRE(experts <= kMaxExperts, "group_mm supports at most %d experts per call, got %d", kMaxExperts,
               experts);
@@ -1017,6 +1026,7 @@ int group_mm_common(void* out, const int32_t* row_map, const FusedArgs* fused, c
   p.e_meta = e_meta; p.sfa = sfa; p.sfb = sfb; p.alphas = alphas; p.counts = counts;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.row_map = row_map;
+  p.out_parts = out_parts ? *out_parts : RowParts{};
   p.f_b_out = nullptr; p.f_sfb_out = nullptr; p.f_gscale = nullptr; p.f_gpe = 0; p.f_n = 0; p.f_n_kt = 0;
   p.f_act = GatedAct{PNV_ACT_SILU, 1.f, -1.f, nullptr};
   if (fused != nullptr) {
@@ -1125,7 +1135,7 @@ extern "C" int pnv_group_mm(void* out, const uint8_t* a_comp, const uint8_t* e_m
                             const int32_t* counts, int experts, int features, int k, int max_n,
                             int config_id, int cluster_m, int cluster_n, int sm_count, int pdl,
                             void* workspace, int64_t workspace_bytes, pnv_stream_t stream) {
-  return group_mm_common(out, nullptr, nullptr, a_comp, e_meta, sfa, b_act, sfb, alphas, counts, experts, features, k,
+  return group_mm_common(out, nullptr, nullptr, nullptr, a_comp, e_meta, sfa, b_act, sfb, alphas, counts, experts, features, k,
                          max_n, config_id, cluster_m, cluster_n, sm_count, pdl, workspace, workspace_bytes, stream,
                          nullptr);
 }
@@ -1136,9 +1146,23 @@ extern "C" int pnv_group_mm_rows(void* out, const int32_t* row_map, const uint8_
                                  int cluster_m, int cluster_n, int sm_count, int pdl, void* workspace,
                                  int64_t workspace_bytes, pnv_stream_t stream) {
   PNV_REQUIRE(row_map, "null pointer argument");
-  return group_mm_common(out, row_map, nullptr, a_comp, e_meta, sfa, b_act, sfb, alphas, counts, experts, features, k,
+  return group_mm_common(out, row_map, nullptr, nullptr, a_comp, e_meta, sfa, b_act, sfb, alphas, counts, experts, features, k,
                          max_n, config_id, cluster_m, cluster_n, sm_count, pdl, workspace, workspace_bytes, stream,
                          nullptr);
+}
+
+extern "C" int pnv_group_mm_rows_parts(void* const* out_parts, int n_parts, int64_t rows_per_part, const int32_t* row_map,
+                                       const uint8_t* a_comp, const uint8_t* e_meta, const uint8_t* sfa,
+                                       const uint8_t* b_act, const uint8_t* sfb, const float* alphas,
+                                       const int32_t* counts, int experts, int features, int k, int max_n, int config_id,
+                                       int cluster_m, int cluster_n, int sm_count, int pdl, void* workspace,
+                                       int64_t workspace_bytes, pnv_stream_t stream) {
+  PNV_REQUIRE(row_map, "null pointer argument");
+  RowParts parts;
+  if (int rc = make_row_parts(out_parts, n_parts, rows_per_part, parts)) return rc;
+  return group_mm_common(nullptr, row_map, &parts, nullptr, a_comp, e_meta, sfa, b_act, sfb, alphas, counts, experts,
+                         features, k, max_n, config_id, cluster_m, cluster_n, sm_count, pdl, workspace, workspace_bytes,
+                         stream, nullptr);
 }
 
 extern "C" int pnv_group_mm_swiglu_num_configs(void) { return kNumFusedKinds; }
@@ -1168,6 +1192,6 @@ extern "C" int pnv_group_mm_swiglu_quant(uint8_t* b_out, uint8_t* sfb_out, const
   PNV_REQUIRE(experts >= 1 && max_n >= 1, "experts and max_n must be positive");
   PNV_REQUIRE(sf_numel(max_n, features / 2, experts) < (1LL << 31), "sfb_out must be smaller than 2 GiB");
   const FusedKind& fk = kFusedKinds[config_id];
-  return group_mm_common(b_out, nullptr, &f, a_comp, e_meta, sfa, b_act, sfb, alphas, counts, experts, features, k, max_n,
+  return group_mm_common(b_out, nullptr, nullptr, &f, a_comp, e_meta, sfa, b_act, sfb, alphas, counts, experts, features, k, max_n,
                          fk.base_config, cluster_m, cluster_n, sm_count, pdl, workspace, workspace_bytes, stream, fk.name);
 }

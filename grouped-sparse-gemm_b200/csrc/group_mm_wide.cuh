@@ -605,8 +605,13 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 if (to0 >= 0) to0 = p.row_map[to0];
                 if (to1 >= 0) to1 = p.row_map[row_e + n0 + c0 + t0 + 1];
               }
-              if (mine8 && to0 >= 0) *reinterpret_cast<uint4*>(p.out + to0 * pitch + m8) = lo;
-              if (mine8 && to1 >= 0) *reinterpret_cast<uint4*>(p.out + to1 * pitch + m8) = hi;
+              if (p.row_map != nullptr) {
+                if (mine8 && to0 >= 0) *reinterpret_cast<uint4*>(mapped_row(p, to0) + m8) = lo;
+                if (mine8 && to1 >= 0) *reinterpret_cast<uint4*>(mapped_row(p, to1) + m8) = hi;
+              } else {
+                if (mine8 && to0 >= 0) *reinterpret_cast<uint4*>(p.out + to0 * pitch + m8) = lo;
+                if (mine8 && to1 >= 0) *reinterpret_cast<uint4*>(p.out + to1 * pitch + m8) = hi;
+              }
             }
           } else if (p.row_map == nullptr) {
             const int live = mine ? min(kChunk, rows) : 0;
@@ -620,13 +625,12 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           } else {
             // lane i holds the output row of the chunk's token i (kChunk <= 32); -1 past the live rows
             const int to_lane = lane < rows ? p.row_map[row_e + n0 + c0 + lane] : -1;
-            unsigned short* base = reinterpret_cast<unsigned short*>(p.out) + m;
 #pragma unroll
             for (int i = 0; i < kChunk; i += 2) {
               const uint32_t w = pk[i / 2];
               const int to0 = __shfl_sync(0xffffffffu, to_lane, i), to1 = __shfl_sync(0xffffffffu, to_lane, i + 1);
-              if (mine && to0 >= 0) base[(long long)to0 * pitch] = (unsigned short)(w & 0xFFFFu);
-              if (mine && to1 >= 0) base[(long long)to1 * pitch] = (unsigned short)(w >> 16);
+              if (mine && to0 >= 0) reinterpret_cast<unsigned short*>(mapped_row(p, to0))[m] = (unsigned short)(w & 0xFFFFu);
+              if (mine && to1 >= 0) reinterpret_cast<unsigned short*>(mapped_row(p, to1))[m] = (unsigned short)(w >> 16);
             }
           }
         }

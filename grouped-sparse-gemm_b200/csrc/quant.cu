@@ -358,14 +358,15 @@ __global__ void __launch_bounds__(128)
 pack_wire_rows_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ q_sf, const IdT* __restrict__ ids,
                       const int* __restrict__ slot_tok, const int* __restrict__ slot_route,
                       const int* __restrict__ slab_counts, int slab, int experts_per_rank, int K,
-                      uint8_t* __restrict__ wire) {
+                      uint8_t* __restrict__ wire, const RowParts parts) {
   pdl_wait();
   pdl_launch_dependents();
   const long long slot = blockIdx.x;
   const int w = (int)(slot / slab);
   const int s = (int)(slot - (long long)w * slab);
   const long long row_bytes = wire_row_bytes(K);
-  uint8_t* row = wire + slot * row_bytes;
+  // (with parts: slab w goes to buffer w, which may be the receiving rank's own memory)
+  uint8_t* row = parts.n ? static_cast<uint8_t*>(parts.base[w]) + s * row_bytes : wire + slot * row_bytes;
   int* id_out = reinterpret_cast<int*>(row + row_bytes - 16);
   if (s >= min(slab_counts[w], slab)) {
     if (threadIdx.x == 0) *id_out = -1;
@@ -612,14 +613,15 @@ extern "C" int64_t pnv_wire_row_bytes(int k) {
   return wire_row_bytes(k);
 }
 
-extern "C" int pnv_pack_wire_rows(const uint8_t* q, const uint8_t* q_sf, const void* topk_ids, int ids_are_int64,
-                                  const int32_t* slot_tok, const int32_t* slot_route, const int32_t* slab_counts,
-                                  int ranks, int slab, int experts_per_rank, int k, uint8_t* wire,
-                                  pnv_stream_t stream) {
+namespace {
+int pack_wire_rows_common(const uint8_t* q, const uint8_t* q_sf, const void* topk_ids, int ids_are_int64,
+                          const int32_t* slot_tok, const int32_t* slot_route, const int32_t* slab_counts, int ranks,
+                          int slab, int experts_per_rank, int k, uint8_t* wire, const RowParts& parts,
+                          pnv_stream_t stream) {
   PNV_REQUIRE(k > 0 && k % kSfBlock == 0, "K must be a multiple of %d, got %d", kSfBlock, k);
   PNV_REQUIRE(ranks >= 1 && slab >= 1 && experts_per_rank >= 1, "ranks, slab and experts_per_rank must be positive");
   PNV_REQUIRE((long long)ranks * slab < (1LL << 31), "ranks * slab must fit int32");
-  PNV_REQUIRE(q && q_sf && topk_ids && slot_tok && slot_route && slab_counts && wire, "null pointer argument");
+  PNV_REQUIRE(q && q_sf && topk_ids && slot_tok && slot_route && slab_counts, "null pointer argument");
   PNV_REQUIRE((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(wire)) % 16 == 0 &&
                   ((k / kSfBlock) % 16 != 0 || reinterpret_cast<uintptr_t>(q_sf) % 16 == 0),
               "pack_wire_rows buffers must be 16-byte aligned");
@@ -628,12 +630,33 @@ extern "C" int pnv_pack_wire_rows(const uint8_t* q, const uint8_t* q_sf, const v
   if (ids_are_int64)
     PNV_CUDA(launch_pdl(pack_wire_rows_kernel<long long>, grid, block, 0, s, pdl_enabled(), q, q_sf,
                         (const long long*)topk_ids, (const int*)slot_tok, (const int*)slot_route,
-                        (const int*)slab_counts, slab, experts_per_rank, k, wire));
+                        (const int*)slab_counts, slab, experts_per_rank, k, wire, parts));
   else
     PNV_CUDA(launch_pdl(pack_wire_rows_kernel<int>, grid, block, 0, s, pdl_enabled(), q, q_sf, (const int*)topk_ids,
                         (const int*)slot_tok, (const int*)slot_route, (const int*)slab_counts, slab,
-                        experts_per_rank, k, wire));
+                        experts_per_rank, k, wire, parts));
   return PNV_OK;
+}
+}  // namespace
+
+extern "C" int pnv_pack_wire_rows(const uint8_t* q, const uint8_t* q_sf, const void* topk_ids, int ids_are_int64,
+                                  const int32_t* slot_tok, const int32_t* slot_route, const int32_t* slab_counts,
+                                  int ranks, int slab, int experts_per_rank, int k, uint8_t* wire,
+                                  pnv_stream_t stream) {
+  PNV_REQUIRE(wire, "null pointer argument");
+  RowParts none{};
+  return pack_wire_rows_common(q, q_sf, topk_ids, ids_are_int64, slot_tok, slot_route, slab_counts, ranks, slab,
+                               experts_per_rank, k, wire, none, stream);
+}
+
+extern "C" int pnv_pack_wire_rows_parts(const uint8_t* q, const uint8_t* q_sf, const void* topk_ids, int ids_are_int64,
+                                        const int32_t* slot_tok, const int32_t* slot_route,
+                                        const int32_t* slab_counts, int ranks, int slab, int experts_per_rank, int k,
+                                        void* const* wire_parts, pnv_stream_t stream) {
+  RowParts parts;
+  if (int rc = make_row_parts(wire_parts, ranks, slab, parts)) return rc;
+  return pack_wire_rows_common(q, q_sf, topk_ids, ids_are_int64, slot_tok, slot_route, slab_counts, ranks, slab,
+                               experts_per_rank, k, nullptr, parts, stream);
 }
 
 extern "C" int pnv_scatter_fp4_wire(const uint8_t* wire, const int32_t* src_tok, const int32_t* counts, int k,

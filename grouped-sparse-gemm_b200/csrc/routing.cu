@@ -314,12 +314,12 @@ gather_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ idx, u
 // group_mm_rows (expert output rows written straight into return order) this stands in for gather_rows:
 // the slots no expert row lands on (dropped and dead ones) still return zeros.
 __global__ void __launch_bounds__(256)
-zero_rows_kernel(const int* __restrict__ flags, long long rows, uint4* __restrict__ dst, int vecs) {
+zero_rows_kernel(const int* __restrict__ flags, long long rows, uint4* __restrict__ dst, int vecs, const RowParts parts) {
   pdl_wait();
   pdl_launch_dependents();
   const long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (r >= rows || flags[r] >= 0) return;
-  uint4* out = dst + r * vecs;
+  uint4* out = parts.n ? reinterpret_cast<uint4*>(part_row(parts, r, (long long)vecs * 16)) : dst + r * vecs;
   for (int v = threadIdx.x & 31; v < vecs; v += 32) out[v] = make_uint4(0u, 0u, 0u, 0u);
 }
 
@@ -439,14 +439,30 @@ extern "C" int pnv_gather_rows(const void* src, const int32_t* idx, int64_t n_id
   return PNV_OK;
 }
 
-extern "C" int pnv_zero_rows(void* dst, const int32_t* flags, int64_t rows, int64_t row_bytes, pnv_stream_t stream) {
+namespace {
+int zero_rows_common(void* dst, const RowParts& parts, const int32_t* flags, int64_t rows, int64_t row_bytes,
+                     pnv_stream_t stream) {
   PNV_REQUIRE(rows >= 0 && rows < (1LL << 33), "bad row count");
   PNV_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0 && row_bytes / 16 < (1LL << 31),
               "row_bytes must be a positive multiple of 16, got %lld", (long long)row_bytes);
   if (rows == 0) return PNV_OK;
-  PNV_REQUIRE(dst && flags, "null pointer argument");
+  PNV_REQUIRE(flags, "null pointer argument");
   PNV_REQUIRE(reinterpret_cast<uintptr_t>(dst) % 16 == 0, "zero_rows buffer must be 16-byte aligned");
   PNV_CUDA(launch_pdl(zero_rows_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, (cudaStream_t)stream,
-                      pdl_enabled(), (const int*)flags, (long long)rows, (uint4*)dst, (int)(row_bytes / 16)));
+                      pdl_enabled(), (const int*)flags, (long long)rows, (uint4*)dst, (int)(row_bytes / 16), parts));
   return PNV_OK;
+}
+}  // namespace
+
+extern "C" int pnv_zero_rows(void* dst, const int32_t* flags, int64_t rows, int64_t row_bytes, pnv_stream_t stream) {
+  PNV_REQUIRE(dst || rows == 0, "null pointer argument");
+  RowParts none{};
+  return zero_rows_common(dst, none, flags, rows, row_bytes, stream);
+}
+
+extern "C" int pnv_zero_rows_parts(void* const* parts, int n_parts, int64_t rows_per_part, const int32_t* flags,
+                                   int64_t row_bytes, pnv_stream_t stream) {
+  RowParts rp;
+  if (int rc = make_row_parts(parts, n_parts, rows_per_part, rp)) return rc;
+  return zero_rows_common(nullptr, rp, flags, (int64_t)n_parts * rows_per_part, row_bytes, stream);
 }

@@ -65,6 +65,13 @@ def _register():
                f"int config_id={DEFAULT_TACTIC[0]}, int cluster_m={DEFAULT_TACTIC[1]}, "
                f"int cluster_n={DEFAULT_TACTIC[2]}) -> ()")
     lib.define("zero_rows(Tensor(a!) dst, Tensor flags) -> ()")
+    lib.define("group_mm_rows_parts(Tensor(a!)[] out_parts, Tensor row_map, Tensor a_comp, Tensor e_meta, Tensor sfa, "
+               "Tensor b_act, Tensor sfb, Tensor alphas, Tensor expert_num_tokens, int features, int k, "
+               f"int config_id={DEFAULT_TACTIC[0]}, int cluster_m={DEFAULT_TACTIC[1]}, "
+               f"int cluster_n={DEFAULT_TACTIC[2]}) -> ()")
+    lib.define("zero_rows_parts(Tensor(a!)[] parts, Tensor flags) -> ()")
+    lib.define("pack_wire_rows_parts(Tensor q, Tensor q_sf, Tensor topk_ids, Tensor slot_tok, Tensor slot_route, "
+               "Tensor slab_counts, int slab, int experts_per_rank, Tensor(a!)[] wire_parts) -> ()")
     lib.define("group_mm_configs() -> str[]")
     lib.define("group_mm_swiglu_quant(Tensor a_comp, Tensor e_meta, Tensor sfa, Tensor b_act, Tensor sfb, "
                "Tensor alphas, Tensor expert_num_tokens, Tensor gscale, int features, int k, int config_id=0, "
@@ -88,6 +95,9 @@ def _register():
     lib.impl("group_mm", ops.group_mm, "CUDA")
     lib.impl("group_mm_rows", ops.group_mm_rows, "CUDA")
     lib.impl("zero_rows", ops.zero_rows, "CUDA")
+    lib.impl("group_mm_rows_parts", ops.group_mm_rows_parts, "CUDA")
+    lib.impl("zero_rows_parts", ops.zero_rows_parts, "CUDA")
+    lib.impl("pack_wire_rows_parts", ops.pack_wire_rows_parts, "CUDA")
     lib.impl("gated_act", ops.gated_act, "CUDA")
     lib.impl("group_mm_swiglu_quant", ops.group_mm_swiglu_quant, "CUDA")
     lib.impl("group_mm_configs", ops.group_mm_configs, "CompositeExplicitAutograd")

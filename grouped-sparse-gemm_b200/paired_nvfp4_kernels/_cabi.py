@@ -33,6 +33,7 @@ SIGNATURES = {
     "pnv_dispatch_plan_strided": (_i, [_p, _i, _i64, _i64, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p]),
     "pnv_wire_row_bytes": (_i64, [_i]),
     "pnv_pack_wire_rows": (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p, _p]),
+    "pnv_pack_wire_rows_parts": (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p, _p]),
     "pnv_scatter_fp4_wire": (_i, [_p, _p, _p, _i, _i, _i, _p, _p, _i, _p]),
     "pnv_dispatch_plan_noalloc_max_scratch_ints": (_i64, []),
     "pnv_dispatch_plan_noalloc": (_i, [_p, _i, _i64, _i, _i, _i, _i, _p, _p, _p, _p, _p]),
@@ -48,7 +49,13 @@ SIGNATURES = {
     "pnv_group_mm_workspace_bytes": (_i64, [_i, _i, _i, _i]),
     "pnv_group_mm": (_i, [_p] * 8 + [_i] * 9 + [_p, _i64, _p]),
     "pnv_group_mm_rows": (_i, [_p] * 9 + [_i] * 9 + [_p, _i64, _p]),
+    "pnv_peer_buffer_alloc": (_i, [_i64, _p, _p]),
+    "pnv_peer_buffer_open": (_i, [_p, _p]),
+    "pnv_peer_buffer_close": (_i, [_p]),
+    "pnv_peer_buffer_free": (_i, [_p]),
     "pnv_zero_rows": (_i, [_p, _p, _i64, _i64, _p]),
+    "pnv_zero_rows_parts": (_i, [_p, _i, _i64, _p, _i64, _p]),
+    "pnv_group_mm_rows_parts": (_i, [_p, _i, _i64] + [_p] * 8 + [_i] * 9 + [_p, _i64, _p]),
     "pnv_group_mm_swiglu_num_configs": (_i, []),
     "pnv_group_mm_swiglu_config_name": (ctypes.c_char_p, [_i]),
     "pnv_group_mm_swiglu_quant": (_i, [_p] * 10 + [_i] * 9 + [_f, _f, _i, _i, _p, _i64, _p]),

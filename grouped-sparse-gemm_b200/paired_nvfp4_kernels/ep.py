@@ -21,9 +21,17 @@ single-GPU path.  The price is the padding of the slabs: `slab` must cover the b
 (a routing that does not fit is dropped like one past an expert's capacity; the caller sees it as a
 -1 in the returned slot map).
 
-The all-to-alls are torch.distributed's (NCCL over NVLink on GPUs, gloo in the CPU tests); this
-module holds the order of operations and the exchange, the kernels are torch.ops.paired_nvfp4.* (or,
-in the CPU tests, a stand-in object with the same methods).  The reference leaves this step to its
+Two exchanges.  The plain one: torch.distributed's all-to-all (NCCL over NVLink on GPUs, gloo in the
+CPU tests) either side of the local FFN.  The direct one (PeerBuffers, one node, GPUs with peer
+access): every rank's receive and return buffers are opened in every other rank's process, and the
+kernels that produce the rows store them where they are wanted - pack_wire_rows_parts writes slab w
+into rank w's receive buffer, group_mm_rows_parts writes every expert output row into the return
+buffer of the rank that sent the token, while the tensor cores work on the next tiles.  Nothing is
+copied a second time and no all-to-all runs; two small all-reduces per pass order the stores against
+their readers (rows landed before the receiver plans; outputs landed before the sender combines).
+
+This module holds the order of operations and the exchange, the kernels are
+torch.ops.paired_nvfp4.* (or, in the CPU tests, a stand-in object with the same methods).  The reference leaves this step to its
 caller (the serving framework's fused-MoE layer); dispatch_plan / moe_finalize are the ops it
 provides either side of it (csrc/ops.cu:374-411, 548-575).
 """
@@ -51,6 +59,107 @@ class _TorchOps:
         return getattr(self._ns, name)
 
 
+class _RawCuda:
+    """A device pointer as an object torch.as_tensor understands (the CUDA array interface)."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+class PeerBuffers:
+    """The receive and return buffers of every rank, visible to all of them.
+
+    recv[r] uint8 [world * slab, wire row bytes]: slab s holds the wire rows rank s sent to rank r.
+    ret[r]  bf16  [world * slab, hidden]:         slab w holds the expert outputs of the rows rank r sent to rank w.
+    Index r is the owner.  Each rank allocates its own pair through the library (plain cudaMalloc, so that the
+    interprocess handle names exactly that allocation), the 64-byte handles are all-gathered, and every rank maps
+    the others' buffers into its own device's address space (pnv_peer_buffer_open: cudaIpcOpenMemHandle with lazy
+    peer access).  One node, GPUs with peer access.
+
+    close() is a collective (it ends with a barrier): every rank unmaps the others' buffers, then frees its own."""
+
+    def __init__(self, world, rank, slab, hidden, row_bytes, device, group=None, local_only=False):
+        import ctypes
+        from . import _cabi
+        self._cabi, self._lib = _cabi, _cabi.lib
+        self.world, self.rank, self.slab, self.group = world, rank, slab, group
+        self.device = torch.device(device)
+        rows = world * slab
+        self._sizes = (rows * row_bytes, rows * hidden * 2)
+        self._own_ptrs, self._opened, handles = [], [], []
+        with torch.cuda.device(self.device):
+            for nbytes in self._sizes:
+                ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+                _cabi.check(self._lib.pnv_peer_buffer_alloc(nbytes, ctypes.byref(ptr), handle))
+                self._own_ptrs.append(ptr.value)
+                handles.append(handle.raw)
+        self.recv_own = self._view(self._own_ptrs[0], 0).view(rows, row_bytes)
+        self.ret_own = self._view(self._own_ptrs[1], 1).view(torch.bfloat16).view(rows, hidden)
+        # dead slots are recognised by the id inside the row: start with all of them dead
+        self.recv_own.view(torch.int32)[:, row_bytes // 4 - 4].fill_(-1)
+        self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.recv, self.ret = [None] * world, [None] * world
+        self.recv[rank], self.ret[rank] = self.recv_own, self.ret_own
+        if local_only:                      # tests: all ranks in one process link their buffers themselves
+            return
+        torch.cuda.synchronize(self.device)
+        everyone = [None] * world
+        dist.all_gather_object(everyone, handles, group=group)
+        with torch.cuda.device(self.device):
+            for r in range(world):
+                if r == rank:
+                    continue
+                views = []
+                for which, handle in enumerate(everyone[r]):
+                    ptr = ctypes.c_void_p()
+                    _cabi.check(self._lib.pnv_peer_buffer_open(handle, ctypes.byref(ptr)))
+                    self._opened.append(ptr.value)
+                    views.append(self._view(ptr.value, which))
+                self.recv[r] = views[0].view(rows, row_bytes)
+                self.ret[r] = views[1].view(torch.bfloat16).view(rows, hidden)
+        dist.barrier(group=group)
+
+    def _view(self, ptr, which):
+        # no device argument: torch takes the device from the pointer itself and never copies
+        return torch.as_tensor(_RawCuda(ptr, self._sizes[which]))
+
+    def recv_parts(self):
+        """Where this rank's slab for rank w goes: slab `rank` of rank w's receive buffer."""
+        s, r = self.slab, self.rank
+        return [self.recv[w][r * s:(r + 1) * s] for w in range(self.world)]
+
+    def ret_parts(self):
+        """Where the outputs of the rows rank w sent here go: slab `rank` of rank w's return buffer."""
+        s, r = self.slab, self.rank
+        return [self.ret[w][r * s:(r + 1) * s] for w in range(self.world)]
+
+    def fence(self):
+        """Every rank's stores issued so far have landed before anything enqueued after this runs, on every
+        rank: a one-element all-reduce on the current stream (kernels complete, and with them their stores to
+        peer memory, before the collective that follows them in the stream starts)."""
+        if self.world > 1 and dist.is_initialized():
+            dist.all_reduce(self._token, group=self.group)
+
+    def close(self):
+        if self._lib is None:
+            return
+        collective = self.world > 1 and dist.is_initialized() and self._opened
+        torch.cuda.synchronize(self.device)
+        if collective:
+            dist.barrier(group=self.group)          # nobody stores into anybody's buffers any more
+        self.recv, self.ret, self.recv_own, self.ret_own = [], [], None, None
+        with torch.cuda.device(self.device):
+            for ptr in self._opened:
+                self._cabi.check(self._lib.pnv_peer_buffer_close(ptr))
+            self._opened = []
+            if collective:
+                dist.barrier(group=self.group)      # every mapping of this rank's buffers is gone
+            for ptr in self._own_ptrs:
+                self._cabi.check(self._lib.pnv_peer_buffer_free(ptr))
+            self._own_ptrs = []
+        self._lib = None
+
+
 class ExpertParallelFFN:
     """The expert FFN of one rank (its shard of the experts) behind dispatch / combine.
 
@@ -59,7 +168,7 @@ class ExpertParallelFFN:
 
     def __init__(self, w13, w2, hidden, inter, cap, alphas1, alphas2, gscale1, gscale2, slab, fused_config=3,
                  config_id=0, cluster_m=2, fused_cluster_m=None, group=None, ops=None, world=None, rank=None,
-                 exchange=None):
+                 exchange=None, peers=None):
         self.w13, self.w2 = w13, w2            # (a_comp, e_meta, sfa) each
         self.hidden, self.inter, self.cap, self.slab = hidden, inter, cap, slab
         self.al1, self.al2, self.g1, self.g2 = alphas1, alphas2, gscale1, gscale2
@@ -71,6 +180,7 @@ class ExpertParallelFFN:
         self.rank = rank if rank is not None else dist.get_rank(group)
         self.num_local = w13[0].size(0)
         self._exchange = exchange              # tests: a stand-in for the all-to-all
+        self.peers = peers                     # PeerBuffers: the direct exchange instead of the all-to-alls
 
     # ---- the two halves either side of the exchanges -----------------------------------------------
 
@@ -116,9 +226,63 @@ class ExpertParallelFFN:
         mark("group_mm_down")
         return back, counts
 
+    # ---- the direct exchange: the same pass with the rows stored where they are wanted ----------------
+
+    def send_direct(self, x, topk_ids, mark=None):
+        """plan + quantize + pack, the wire rows going straight into the receivers' buffers.  -> slot map."""
+        ops, mark = self.ops, mark or (lambda name: None)
+        dest_rank = torch.div(topk_ids, self.num_local, rounding_mode="floor")
+        slab_counts, route_slot, slot_tok, slot_route = ops.dispatch_plan(dest_rank, 0, self.world, self.slab)
+        mark("send_plan")
+        q, q_sf = ops.quant_rows(x, self.g1)
+        mark("quant_rows")
+        ops.pack_wire_rows_parts(q, q_sf, topk_ids, slot_tok, slot_route, slab_counts, self.slab, self.num_local,
+                                 self.peers.recv_parts())
+        mark("pack_wire_rows")
+        return route_slot
+
+    def local_ffn_direct(self, mark=None):
+        """The local FFN on this rank's receive buffer, expert outputs stored into the senders' return buffers."""
+        ops, mark = self.ops, mark or (lambda name: None)
+        E, H, I, cap = self.num_local, self.hidden, self.inter, self.cap
+        wire = self.peers.recv_own
+        ids = ops.wire_expert_ids(wire)
+        counts, route_dest, src_tok, _ = ops.dispatch_plan(ids, 0, E, cap)
+        mark("dispatch_plan")
+        b1, sfb1 = ops.scatter_fp4_wire(wire, H, src_tok, counts, cap)
+        mark("scatter_fp4_wire")
+        b2, sfb2 = ops.group_mm_swiglu_quant(self.w13[0], self.w13[1], self.w13[2], b1, sfb1, self.al1, counts, self.g2,
+                                             2 * I, H, self.fused_config, self.fused_cluster_m, 1, "silu", 1.0, -1.0)
+        mark("group_mm_gate_up")
+        parts = self.peers.ret_parts()
+        # live rows this rank had no room for come back as zeros; dead slots are never read by their sender
+        dropped = torch.where(ids.reshape(-1) >= 0, route_dest.view(-1), torch.zeros_like(route_dest.view(-1)))
+        ops.zero_rows_parts(parts, dropped)
+        mark("zero_rows")
+        ops.group_mm_rows_parts(parts, src_tok, self.w2[0], self.w2[1], self.w2[2], b2, sfb2, self.al2, counts, H, I,
+                                self.config_id, self.cluster_m, 1)
+        mark("group_mm_down")
+        return counts
+
+    def forward_direct(self, x, topk_ids, topk_weights, out=None, mark=None):
+        mark = mark or (lambda name: None)
+        route_slot = self.send_direct(x, topk_ids, mark)
+        self.peers.fence()                     # every rank's wire rows are in place
+        mark("all_to_all_dispatch")
+        counts = self.local_ffn_direct(mark)
+        self.peers.fence()                     # every rank's expert outputs are in place
+        mark("all_to_all_combine")
+        if out is None:
+            out = torch.empty((x.size(0), self.hidden), dtype=torch.bfloat16, device=x.device)
+        self.ops.moe_finalize(out, self.peers.ret_own, route_slot, topk_weights)
+        mark("moe_finalize")
+        return out, counts, route_slot
+
     def forward(self, x, topk_ids, topk_weights, out=None, mark: Optional[Callable[[str], None]] = None):
         """x bf16 [tokens, hidden], topk_ids int32/int64 [tokens, topk] (global expert ids), topk_weights
         float32 [tokens, topk] or None.  Returns (out, local expert counts, slot map of this rank's routings)."""
+        if self.peers is not None:
+            return self.forward_direct(x, topk_ids, topk_weights, out, mark)
         mark = mark or (lambda name: None)
         wire, route_slot = self.plan_and_pack(x, topk_ids, mark)
         recv = self.exchange(wire)

@@ -3,6 +3,8 @@ into the C ABI.  Mirrors the reference's op layer (csrc/ops.cu) schema for schem
 argument meaning, output shapes and error substrings.  Every forward op only enqueues work on the
 current CUDA stream of the tensors' device; nothing synchronises or reads device memory.
 """
+import ctypes
+
 import torch
 
 from . import _cabi
@@ -280,10 +282,7 @@ def wire_row_bytes(k):
     return int(_lib.pnv_wire_row_bytes(int(k)))
 
 
-def pack_wire_rows(q, q_sf, topk_ids, slot_tok, slot_route, slab_counts, slab, experts_per_rank):
-    """quant_rows output -> wire rows in fixed-capacity slabs, one slab of `slab` rows per destination rank
-    (see pnv_pack_wire_rows).  slot_tok / slot_route / slab_counts are dispatch_plan's outputs for the routings
-    keyed by destination rank.  Returns uint8 [ranks * slab, wire_row_bytes(K)]."""
+def _check_pack_args(q, q_sf, topk_ids, slot_tok, slot_route, slab_counts, slab, experts_per_rank):
     _check(q.is_cuda and q_sf.is_cuda and topk_ids.is_cuda and slot_tok.is_cuda and slot_route.is_cuda
            and slab_counts.is_cuda, "inputs must be CUDA")
     _check_arch(q)
@@ -299,6 +298,23 @@ def pack_wire_rows(q, q_sf, topk_ids, slot_tok, slot_route, slab_counts, slab, e
     _check(slot_tok.dtype == torch.int32 and slot_route.dtype == torch.int32 and slot_tok.is_contiguous()
            and slot_route.is_contiguous() and slot_tok.numel() == ranks * slab and slot_route.numel() == ranks * slab,
            "slot_tok and slot_route must be contiguous int32 [ranks * slab] (dispatch_plan output)")
+    return K, ranks
+
+
+def _parts_array(parts, rows, width, dtype, what):
+    """A host array of the parts' device pointers, after shape checks (each part [rows, width] of dtype)."""
+    _check(1 <= len(parts) <= 16, lambda: f"{what}: between 1 and 16 parts, got {len(parts)}")
+    for t in parts:
+        _check(t.is_cuda and t.dtype == dtype and t.dim() == 2 and t.is_contiguous() and t.size(0) == rows
+               and t.size(1) == width, lambda: f"{what}: every part must be contiguous CUDA {dtype} [{rows}, {width}]")
+    return (ctypes.c_void_p * len(parts))(*[t.data_ptr() for t in parts])
+
+
+def pack_wire_rows(q, q_sf, topk_ids, slot_tok, slot_route, slab_counts, slab, experts_per_rank):
+    """quant_rows output -> wire rows in fixed-capacity slabs, one slab of `slab` rows per destination rank
+    (see pnv_pack_wire_rows).  slot_tok / slot_route / slab_counts are dispatch_plan's outputs for the routings
+    keyed by destination rank.  Returns uint8 [ranks * slab, wire_row_bytes(K)]."""
+    K, ranks = _check_pack_args(q, q_sf, topk_ids, slot_tok, slot_route, slab_counts, slab, experts_per_rank)
     wire = torch.empty((ranks * slab, wire_row_bytes(K)), dtype=torch.uint8, device=q.device)
     with torch.cuda.device(q.device):
         _cabi.check(_lib.pnv_pack_wire_rows(q.data_ptr(), q_sf.data_ptr(), topk_ids.data_ptr(),
@@ -306,6 +322,19 @@ def pack_wire_rows(q, q_sf, topk_ids, slot_tok, slot_route, slab_counts, slab, e
                                             slot_route.data_ptr(), slab_counts.data_ptr(), ranks, int(slab),
                                             int(experts_per_rank), K, wire.data_ptr(), _stream(q)))
     return wire
+
+
+def pack_wire_rows_parts(q, q_sf, topk_ids, slot_tok, slot_route, slab_counts, slab, experts_per_rank, wire_parts):
+    """pack_wire_rows with slab w written into wire_parts[w] (uint8 [slab, wire_row_bytes(K)] each, possibly another
+    GPU's memory opened in this process): the pack is then the dispatch.  Mutates the parts."""
+    K, ranks = _check_pack_args(q, q_sf, topk_ids, slot_tok, slot_route, slab_counts, slab, experts_per_rank)
+    _check(len(wire_parts) == ranks, lambda: f"one wire part per destination rank: {ranks}, got {len(wire_parts)}")
+    arr = _parts_array(wire_parts, int(slab), wire_row_bytes(K), torch.uint8, "pack_wire_rows_parts")
+    with torch.cuda.device(q.device):
+        _cabi.check(_lib.pnv_pack_wire_rows_parts(q.data_ptr(), q_sf.data_ptr(), topk_ids.data_ptr(),
+                                                  1 if topk_ids.dtype == torch.int64 else 0, slot_tok.data_ptr(),
+                                                  slot_route.data_ptr(), slab_counts.data_ptr(), ranks, int(slab),
+                                                  int(experts_per_rank), K, arr, _stream(q)))
 
 
 def wire_expert_ids(wire):
@@ -426,23 +455,28 @@ def group_mm_configs():
 
 
 def _group_mm(out, row_map, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens, features, k, config_id,
-              cluster_m, cluster_n):
-    ts = (out, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens)
+              cluster_m, cluster_n, out_parts=None):
+    ts = (a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens) + (() if out_parts is not None else (out,))
     _check(all(t.is_cuda for t in ts), "all tensors must be CUDA")
-    _check_arch(out)
+    _check_arch(b_act)
     _check(b_act.dim() == 3 and a_comp.dim() == 3 and e_meta.dim() == 3, "b_act, a_comp and e_meta must be 3D")
     E, M, K, max_n = a_comp.size(0), int(features), int(k), b_act.size(1)
     _check(b_act.size(0) == E and e_meta.size(0) == E, "expert dim mismatch")
+    parts_arr = None
     if row_map is None:
         _check(out.dim() == 3, "out must be 3D")
         _check(out.size(0) == E, "expert dim mismatch")
         _check(out.size(1) == max_n and out.size(2) == M, "out must be [E, max_n, features]")
     else:
-        _check(out.dim() == 2 and out.size(1) == M, "out must be [rows, features]")
         _check(row_map.is_cuda and row_map.dtype == torch.int32 and row_map.is_contiguous()
                and row_map.numel() == E * max_n, "row_map must be contiguous int32 [E * max_n]")
+        if out_parts is None:
+            _check(out.dim() == 2 and out.size(1) == M, "out must be [rows, features]")
+        else:
+            _check(len(out_parts) >= 1, "at least one output part")
+            parts_arr = _parts_array(out_parts, out_parts[0].size(0), M, torch.bfloat16, "group_mm_rows_parts")
     _check(b_act.size(2) == K // 2, "b_act must be [E, max_n, K/2]")
-    _check(out.dtype == torch.bfloat16, "out must be bf16")
+    _check(out_parts is not None or out.dtype == torch.bfloat16, "out must be bf16")
     _check(a_comp.dtype == torch.uint8 and e_meta.dtype == torch.uint8 and b_act.dtype == torch.uint8
            and sfa.element_size() == 1 and sfb.element_size() == 1,
            "a_comp, e_meta and b_act must be uint8; sfa, sfb 1-byte")
@@ -456,16 +490,19 @@ def _group_mm(out, row_map, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_
                    "(check the features / k arguments)")
     _check(sfa.numel() >= _cabi.sf_numel(M, K, E), "sfa is smaller than the SFA layout")
     _check(sfb.numel() >= _cabi.sf_numel(max_n, K, E), "sfb is smaller than the SFB layout")
-    with torch.cuda.device(out.device):
-        ws, ws_bytes = _split_workspace(out, E, M, max_n)
+    with torch.cuda.device(b_act.device):
+        ws, ws_bytes = _split_workspace(b_act, E, M, max_n)
         tail = (a_comp.data_ptr(), e_meta.data_ptr(), sfa.data_ptr(), b_act.data_ptr(), sfb.data_ptr(),
                 alphas.data_ptr(), expert_num_tokens.data_ptr(), E, M, K, max_n, int(config_id), int(cluster_m),
-                int(cluster_n), _device_info(out.device)[1], 1, ws.data_ptr() if ws is not None else None, ws_bytes,
-                _stream(out))
+                int(cluster_n), _device_info(b_act.device)[1], 1, ws.data_ptr() if ws is not None else None, ws_bytes,
+                _stream(b_act))
         if row_map is None:
             _cabi.check(_lib.pnv_group_mm(out.data_ptr(), *tail))
-        else:
+        elif parts_arr is None:
             _cabi.check(_lib.pnv_group_mm_rows(out.data_ptr(), row_map.data_ptr(), *tail))
+        else:
+            _cabi.check(_lib.pnv_group_mm_rows_parts(parts_arr, len(out_parts), out_parts[0].size(0), row_map.data_ptr(),
+                                                     *tail))
 
 
 def group_mm(out, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens, features, k, config_id=0,
@@ -481,6 +518,27 @@ def group_mm_rows(out, row_map, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_
     negative).  Mutates `out` in place; rows no kept token maps to are left alone."""
     _group_mm(out, row_map, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens, features, k, config_id,
               cluster_m, cluster_n)
+
+
+def group_mm_rows_parts(out_parts, row_map, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens, features, k,
+                        config_id=0, cluster_m=2, cluster_n=1):
+    """group_mm_rows whose logical output [len(out_parts) * rows, features] is spread over out_parts (bf16
+    [rows, features] each, possibly other GPUs' memory opened in this process).  Mutates the parts."""
+    _group_mm(None, row_map, a_comp, e_meta, sfa, b_act, sfb, alphas, expert_num_tokens, features, k, config_id,
+              cluster_m, cluster_n, out_parts=list(out_parts))
+
+
+def zero_rows_parts(parts, flags):
+    """zero_rows over a parts table: flags [len(parts) * rows]; row q is row q % rows of parts[q // rows]."""
+    _check(len(parts) >= 1 and flags.is_cuda, "inputs must be CUDA")
+    rows, width = parts[0].size(0), parts[0].size(1)
+    arr = _parts_array(parts, rows, width, parts[0].dtype, "zero_rows_parts")
+    _check(flags.dtype == torch.int32 and flags.is_contiguous() and flags.numel() == len(parts) * rows,
+           "flags must be contiguous int32 [parts * rows]")
+    row_bytes = width * parts[0].element_size()
+    _check(row_bytes % 16 == 0, lambda: f"rows must be a multiple of 16 bytes, got {row_bytes}")
+    with torch.cuda.device(flags.device):
+        _cabi.check(_lib.pnv_zero_rows_parts(arr, len(parts), rows, flags.data_ptr(), row_bytes, _stream(flags)))
 
 
 def zero_rows(dst, flags):

@@ -38,6 +38,20 @@ typedef struct CUstream_st* pnv_stream_t;
 int pnv_abi_version(void);
 const char* pnv_last_error(void);
 
+/* Buffers for the direct expert-parallel exchange, where the *_parts entry points below store rows straight into
+ * another rank's memory (one node, GPUs with peer access; no counterpart in the reference).  Set-up time only.
+ *   pnv_peer_buffer_alloc  cudaMalloc on the current device + the 64-byte interprocess handle of the allocation
+ *   pnv_peer_buffer_open   in ANOTHER process: maps the allocation into the current device's address space
+ *                          (cudaIpcOpenMemHandle with lazy peer access), so that kernels launched on the current
+ *                          device can store into it
+ *   pnv_peer_buffer_close  unmaps an opened buffer;  pnv_peer_buffer_free  frees an allocated one (after every
+ *                          process that opened it has closed it) */
+#define PNV_PEER_HANDLE_BYTES 64
+int pnv_peer_buffer_alloc(int64_t bytes, void** ptr_out, void* handle_out);
+int pnv_peer_buffer_open(const void* handle, void** ptr_out);
+int pnv_peer_buffer_close(void* ptr);
+int pnv_peer_buffer_free(void* ptr);
+
 /* Device status word of the group_mm launches on the current device since the last read: 0 when every
  * bounded wait inside the kernels completed, otherwise the code of a wait that gave up (its launch's
  * results are then undefined).  Every wait inside the kernels is bounded so that a lost copy or a logic
@@ -177,6 +191,13 @@ int64_t pnv_wire_row_bytes(int k);
 int pnv_pack_wire_rows(const uint8_t* q, const uint8_t* q_sf, const void* topk_ids, int ids_are_int64,
                        const int32_t* slot_tok, const int32_t* slot_route, const int32_t* slab_counts, int ranks,
                        int slab, int experts_per_rank, int k, uint8_t* wire, pnv_stream_t stream);
+/* pnv_pack_wire_rows with slab w written to wire_parts[w] (a HOST array of `ranks` device pointers, at most 16,
+ * each to slab * row bytes): with peer memory of the receiving ranks mapped into this process the pack is the
+ * dispatch, the rows cross NVLink as the kernel stores them. */
+int pnv_pack_wire_rows_parts(const uint8_t* q, const uint8_t* q_sf, const void* topk_ids, int ids_are_int64,
+                             const int32_t* slot_tok, const int32_t* slot_route, const int32_t* slab_counts,
+                             int ranks, int slab, int experts_per_rank, int k, void* const* wire_parts,
+                             pnv_stream_t stream);
 int pnv_scatter_fp4_wire(const uint8_t* wire, const int32_t* src_tok, const int32_t* counts, int k, int experts,
                          int cap, uint8_t* b_act, uint8_t* sfb, int sm_count, pnv_stream_t stream);
 
@@ -197,6 +218,11 @@ int pnv_gather_rows(const void* src, const int32_t* idx, int64_t n_idx, int64_t 
  * multiple of 16).  With pnv_group_mm_rows this stands in for pnv_gather_rows on the way back from the experts:
  * the GEMM writes every kept row straight into return order, this zeroes the slots no row lands on. */
 int pnv_zero_rows(void* dst, const int32_t* flags, int64_t rows, int64_t row_bytes, pnv_stream_t stream);
+
+/* pnv_zero_rows over the same kind of parts table as pnv_group_mm_rows_parts: flags has n_parts * rows_per_part
+ * entries, row q is row q % rows_per_part of parts[q / rows_per_part]. */
+int pnv_zero_rows_parts(void* const* parts, int n_parts, int64_t rows_per_part, const int32_t* flags,
+                        int64_t row_bytes, pnv_stream_t stream);
 
 /* The unfused gated activation the quantizer above folds in (gated_act, csrc/layout.cuh:204-216;
  * device replica ref_silu_mul_kernel, csrc/testing/selftest.cu:750-760): y bf16[rows, n] from
@@ -248,6 +274,17 @@ int pnv_group_mm_rows(void* out, const int32_t* row_map, const uint8_t* a_comp, 
                       const int32_t* counts, int experts, int features, int k, int max_n, int config_id,
                       int cluster_m, int cluster_n, int sm_count, int pdl, void* workspace,
                       int64_t workspace_bytes, pnv_stream_t stream);
+
+/* pnv_group_mm_rows whose output rows are spread over n_parts buffers (1..16): row q of the logical
+ * [n_parts * rows_per_part, features] output is row q % rows_per_part of out_parts[q / rows_per_part].  out_parts is a
+ * HOST array of device pointers (16-byte aligned); they may be peer memory of other GPUs mapped into this process, so
+ * that an expert-parallel rank stores every expert output row straight into the buffer of the rank that sent the
+ * token (plain stores over NVLink; the caller orders them against the reader with its own barrier). */
+int pnv_group_mm_rows_parts(void* const* out_parts, int n_parts, int64_t rows_per_part, const int32_t* row_map,
+                            const uint8_t* a_comp, const uint8_t* e_meta, const uint8_t* sfa, const uint8_t* b_act,
+                            const uint8_t* sfb, const float* alphas, const int32_t* counts, int experts,
+                            int features, int k, int max_n, int config_id, int cluster_m, int cluster_n,
+                            int sm_count, int pdl, void* workspace, int64_t workspace_bytes, pnv_stream_t stream);
 
 /* paired_nvfp4_group_mm_swiglu_configs / paired_nvfp4_group_mm_swiglu_quant (csrc/ops.cu:585-658 ->
  * SwigluFp4Epilogue, csrc/sm100/swiglu_epilogue.cuh:52-236; variant table kSwigluMmKinds,

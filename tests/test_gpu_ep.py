@@ -3,7 +3,9 @@ holding all experts computes for the same tokens (row placement inside an expert
 result, and moe_finalize sums in top-k order).  Three forms: one rank (the exchange is the identity, everything
 else - slab plan, wire rows, plan on the strided ids, placement, return order - is the real path), two ranks
 emulated on one GPU (both ranks' halves run one after the other, the all-to-all is a slab swap in Python), and two
-real ranks over NCCL (skipped on a single-GPU box)."""
+real ranks over NCCL (skipped on a single-GPU box).  The last two also with the direct exchange, where the producing
+kernels store wire rows and expert outputs straight into the other rank's buffers (on one GPU: into the other
+emulated rank's buffers; on two: into peer memory opened through CUDA IPC)."""
 import os
 import socket
 import sys
@@ -46,14 +48,14 @@ def _tokens(rank, device):
     return x, ids, w
 
 
-def _ffn(ops, ep, w13, w2, lo, hi, device, world, rank, exchange=None, slab=SLAB):
+def _ffn(ops, ep, w13, w2, lo, hi, device, world, rank, exchange=None, slab=SLAB, peers=None):
     a13 = ops.compress(w13[0][lo:hi].contiguous(), w13[1][lo:hi].contiguous(), H)
     a2 = ops.compress(w2[0][lo:hi].contiguous(), w2[1][lo:hi].contiguous(), I)
     n = hi - lo
     one = torch.ones(1, device=device)
     ones = torch.ones(n, device=device)
     return ep.ExpertParallelFFN(a13, a2, H, I, CAP, ones, ones, one, ones, slab, fused_config=3, config_id=0, cluster_m=2,
-                                world=world, rank=rank, exchange=exchange)
+                                world=world, rank=rank, exchange=exchange, peers=peers)
 
 
 def _single(world, device=None):
@@ -185,7 +187,73 @@ def test_two_ranks_emulated_on_one_gpu(slab):
     assert np.array_equal(got, want)
 
 
-def _worker(rank, world, port, out_dir):
+def test_pack_wire_rows_parts_equals_pack_wire_rows():
+    import paired_nvfp4_kernels  # noqa: F401
+    from paired_nvfp4_kernels import ops as pyops
+    ops = torch.ops.paired_nvfp4
+    dev = torch.device("cuda", 0)
+    K, tokens, topk, world, epr, slab = 512, 50, 3, 4, 2, 64
+    rng = np.random.default_rng(3)
+    x = torch.from_numpy(rng.standard_normal((tokens, K)).astype(np.float32)).to(torch.bfloat16).to(dev)
+    ids = torch.from_numpy(np.stack([rng.permutation(world * epr)[:topk] for _ in range(tokens)]).astype(np.int64)).to(dev)
+    q, q_sf = ops.quant_rows(x, torch.full((1,), 3.5, device=dev))
+    slab_counts, _, slot_tok, slot_route = ops.dispatch_plan(torch.div(ids, epr, rounding_mode="floor"), 0, world, slab)
+    wire = ops.pack_wire_rows(q, q_sf, ids, slot_tok, slot_route, slab_counts, slab, epr)
+    parts = [torch.zeros((slab, pyops.wire_row_bytes(K)), dtype=torch.uint8, device=dev) for _ in range(world)]
+    ops.pack_wire_rows_parts(q, q_sf, ids, slot_tok, slot_route, slab_counts, slab, epr, parts)
+    torch.cuda.synchronize()
+    live = (torch.arange(slab, device=dev)[None, :] < slab_counts[:, None]).reshape(-1)
+    got = torch.cat(parts)
+    used = K // 2 + K // 32                               # the bytes after the scales are padding, but for the id
+    assert torch.equal(got[live][:, :used], wire[live][:, :used])
+    assert torch.equal(pyops.wire_expert_ids(got), pyops.wire_expert_ids(wire))     # dead slots carry -1 in both
+
+
+@pytest.mark.parametrize("slab", [SLAB, 80])
+def test_two_ranks_emulated_direct_exchange(slab):
+    """The direct exchange with both ranks in one process: each rank's kernels store into the other's buffers."""
+    import paired_nvfp4_kernels  # noqa: F401
+    from paired_nvfp4_kernels import ep
+    from paired_nvfp4_kernels import ops as pyops
+    ops = torch.ops.paired_nvfp4
+    device = torch.device("cuda", 0)
+    world, epr = 2, E // 2
+    w13, w2 = _weights(device)
+    pbs = [ep.PeerBuffers(world, r, slab, H, pyops.wire_row_bytes(H), device, local_only=True) for r in range(world)]
+    for pb in pbs:
+        pb.recv, pb.ret = [p.recv_own for p in pbs], [p.ret_own for p in pbs]
+        pb.ret_own.fill_(float("nan"))       # every row a sender reads must have been written by somebody
+    ffns = [_ffn(ops, ep, w13, w2, r * epr, (r + 1) * epr, device, world, r, slab=slab, peers=pbs[r]) for r in range(world)]
+    toks = [_tokens(r, device) for r in range(world)]
+    slots = [ffns[r].send_direct(toks[r][0], toks[r][1]) for r in range(world)]
+    counts = [ffns[r].local_ffn_direct() for r in range(world)]
+    outs = []
+    for r in range(world):
+        out = torch.empty((T, H), dtype=torch.bfloat16, device=device)
+        ops.moe_finalize(out, pbs[r].ret_own, slots[r], toks[r][2])
+        outs.append(out)
+    torch.cuda.synchronize()
+    # the all-to-all form of the same pass is the yardstick (itself checked against the single-GPU path above)
+    ref = [_ffn(ops, ep, w13, w2, r * epr, (r + 1) * epr, device, world, r, slab=slab) for r in range(world)]
+    sent = [ref[r].plan_and_pack(toks[r][0], toks[r][1]) for r in range(world)]
+
+    def swap(per_rank):
+        return [torch.cat([per_rank[s][r * slab:(r + 1) * slab] for s in range(world)]).contiguous() for r in range(world)]
+
+    backs = [ref[r].local_ffn(rv) for r, rv in enumerate(swap([s[0] for s in sent]))]
+    ret = swap([b[0] for b in backs])
+    for r in range(world):
+        want = torch.empty((T, H), dtype=torch.bfloat16, device=device)
+        ops.moe_finalize(want, ret[r], sent[r][1], toks[r][2])
+        torch.cuda.synchronize()
+        assert torch.equal(slots[r], sent[r][1]) and torch.equal(counts[r], backs[r][1])
+        assert torch.equal(outs[r].view(torch.int16), want.view(torch.int16))
+        assert not torch.isnan(outs[r].float()).any()
+    for pb in pbs:
+        pb.close()
+
+
+def _worker(rank, world, port, out_dir, direct=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -198,10 +266,17 @@ def _worker(rank, world, port, out_dir):
         ops = torch.ops.paired_nvfp4
         w13, w2 = _weights(device)
         epr = E // world
-        ffn = _ffn(ops, ep, w13, w2, rank * epr, (rank + 1) * epr, device, world, rank)
+        peers = None
+        if direct:
+            from paired_nvfp4_kernels import ops as pyops
+            peers = ep.PeerBuffers(world, rank, SLAB, H, pyops.wire_row_bytes(H), device)
+        ffn = _ffn(ops, ep, w13, w2, rank * epr, (rank + 1) * epr, device, world, rank, peers=peers)
         x, ids, w = _tokens(rank, device)
-        out, counts, _ = ffn.forward(x, ids, w)
+        for _ in range(3 if direct else 1):      # direct: the buffers are reused pass after pass
+            out, counts, _ = ffn.forward(x, ids, w)
         torch.cuda.synchronize()
+        if peers is not None:
+            peers.close()
         np.save(os.path.join(out_dir, f"ep{rank}.npy"), out.view(torch.int16).cpu().numpy())
         np.save(os.path.join(out_dir, f"cnt{rank}.npy"), counts.cpu().numpy())
     finally:
@@ -209,12 +284,13 @@ def _worker(rank, world, port, out_dir):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_rank_forward_matches_single_gpu(tmp_path):
+@pytest.mark.parametrize("direct", [False, True])
+def test_two_rank_forward_matches_single_gpu(tmp_path, direct):
     world = 2
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, str(tmp_path), direct), nprocs=world, join=True)
     want, want_counts = _single(world)
     got = np.concatenate([np.load(tmp_path / f"ep{r}.npy") for r in range(world)])
     got_counts = np.concatenate([np.load(tmp_path / f"cnt{r}.npy") for r in range(world)])

@@ -150,7 +150,7 @@ def test_group_mm_rows_permutes_the_output(pnk, E, M, K, max_n, counts, cids):
     b_act, sfb = ops.quant_act(bf16_tensor(x), dev(np.ones(1, np.float32)), dev(cnt), M)
     al = dev(np.linspace(0.5, 2.0, E).astype(np.float32))
     rng = np.random.default_rng(33)
-    rows = E * max_n + 5
+    rows = (E * max_n + 5 + 3) // 4 * 4                       # a multiple of four: the parts form cuts it in four
     to = rng.permutation(rows)[:E * max_n].astype(np.int32)
     to[rng.random(E * max_n) < 0.1] = -1                      # some kept rows are not wanted
     live = (np.arange(max_n)[None, :] < cnt[:, None]).reshape(-1)
@@ -167,6 +167,11 @@ def test_group_mm_rows_permutes_the_output(pnk, E, M, K, max_n, counts, cids):
         keep = torch.from_numpy(live & (to >= 0)).cuda()
         want[torch.from_numpy(to).cuda().long()[keep]] = plain.view(E * max_n, M)[keep]
         assert torch.equal(out, want), name
+        # the same output cut into four separately allocated buffers
+        parts = [torch.full((rows // 4, M), SENTINEL, dtype=torch.bfloat16, device="cuda") for _ in range(4)]
+        ops.group_mm_rows_parts(parts, to_dev, a_comp, e_meta, sfa, b_act, sfb, al, dev(cnt), M, K, cid, cm, cn)
+        torch.cuda.synchronize()
+        assert torch.equal(torch.cat(parts), want), name + " (parts)"
     from paired_nvfp4_kernels import ops as pyops
     assert pyops.group_mm_device_status() == 0
 

@@ -163,3 +163,15 @@ def test_zero_rows(rows, width, dtype):
     ops.zero_rows(dst[:0], flags[:0])
     with pytest.raises(RuntimeError, match="multiple of 16"):
         ops.zero_rows(dst[:, :4].contiguous(), flags)
+
+
+def test_zero_rows_parts():
+    import paired_nvfp4_kernels  # noqa: F401
+    ops = torch.ops.paired_nvfp4
+    g = torch.Generator(device="cpu").manual_seed(5)
+    parts = [torch.randint(1, 255, (21, 64), generator=g, dtype=torch.uint8).cuda() for _ in range(3)]
+    flags = torch.randint(-1, 3, (63,), generator=g, dtype=torch.int32).cuda()
+    want = torch.cat(parts).clone()
+    want[flags < 0] = 0
+    ops.zero_rows_parts(parts, flags)
+    assert torch.equal(torch.cat(parts), want)
