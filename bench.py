@@ -42,8 +42,10 @@ FALLBACK_HBM_GBS = 6650.0      # earlier measurement on this pool, used only wit
 NOMINAL_SPARSE_FP4_TFLOPS = 18000.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate_up group_mm launch, from the ncu captures summarised
-# under profiles/ (same workload, so no scaling); None where no capture exists
-NCU_TRAFFIC_BYTES = {"c2": 328.10e6, "c3": 337.87e6}
+# under profiles/ (c2, c3: the same workload; c4: a capture of 32 of the 256 experts with the same rows per expert,
+# times 8 - the traffic is the weights and rows of the experts, so it grows with their number); None where no
+# capture exists
+NCU_TRAFFIC_BYTES = {"c2": 332.6e6, "c3": 347.6e6, "c4": 8 * 382.3e6}
 
 WORKLOADS = {
     # Mixtral-8x7B expert FFN, decode: per-expert counts uniform in [1, 16]
@@ -83,6 +85,9 @@ def parse_args():
     ap.add_argument("--passes", type=int, default=None,
                     help="passes per step (default: as many as make the timed steps last half a second); "
                          "small values keep a profiler capture short")
+    ap.add_argument("--experts", type=int, default=None,
+                    help="run a routed workload with this many experts and proportionally fewer tokens (the same "
+                         "rows per expert): a smaller copy of the workload for profiler captures")
     ap.add_argument("--exchange", default="direct", choices=["direct", "nccl"],
                     help="N > 1: 'direct' = the producing kernels store wire rows and expert outputs straight into the "
                          "other ranks' buffers (peer memory); 'nccl' = an all-to-all either side of the local FFN")
@@ -768,7 +773,7 @@ def run_expert_parallel(args, wl_name, wl, rank, world, local_rank, device):
         one_pass(i, mark=lambda name, it=it: next(it).record())
     barrier()
     phases = {n: float(np.mean([ev[j].elapsed_time(ev[j + 1]) for ev in evs])) * 1e3 for j, n in enumerate(EP_PHASES)}
-    r13, r2 = gemm_rooflines(wl_name, H, I, kept, int((counts > 0).sum().item()), True,
+    r13, r2 = gemm_rooflines(wl_name if world == 1 and args.experts is None else None, H, I, kept, int((counts > 0).sum().item()), True,
                              phases["group_mm_gate_up"] * 1e-6, phases["group_mm_down"] * 1e-6)
     dominant = r13 if r13["launch_us"] >= r2["launch_us"] else r2
 
@@ -900,6 +905,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     wl_name = args.workload or "c4"
     wl = WORKLOADS[wl_name]
+    if args.experts is not None:
+        assert wl["routing"] in ("topk", "zipf") and 0 < args.experts <= wl["E"], "--experts: a routed workload, at most its own count"
+        wl = dict(wl, E=args.experts, tokens=max(1, wl["tokens"] * args.experts // wl["E"]),
+                  desc=f"{wl['desc']} (cut to {args.experts} experts for a profiler capture)")
 
     if args.impl == "reference":
         return run_reference_arm(args, wl_name, wl, rank)
