@@ -124,6 +124,7 @@ struct Params {
   int stages;        // pipeline depth in use (<= Cfg::kStages)
   int b_4d;          // map_b is the 4-D view [E][K/256][max_n][128 B] and one copy fetches a whole stage
   int prod_lanes;    // wide kernel: lanes of each producer warp that issue copies side by side
+  int b_tail;        // wide kernel: a second activation map with a 64-token box exists (narrow tail tiles)
   // narrow kernel, split K (nullptr = every tile on one CTA): per-tile arrival counters (all zero before and
   // after a launch) followed by two partial-accumulator slots per CTA
   int* split_counters;
@@ -285,8 +286,12 @@ group_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     for (int o = 16; o > 0; o >>= 1) n_tiles += __shfl_xor_sync(0xffffffffu, n_tiles, o);
   }
 
+  // K is split only when whole tiles would leave SMs idle or the last wave thin (fewer than 1.5 tiles per CTA):
+  // with more tiles than that the partial sums and their reduction cost more than the imbalance they remove
+  // (measured on an 8-expert decode step: 63.5 / 37.1 us split against 58.9 / 35.2 us whole)
   UnitWalk walk;
-  walk.init<TILE_N>(s_counts, p.E, p.n_mt, p.k_stages, n_tiles, p.split_counters != nullptr);
+  walk.init<TILE_N>(s_counts, p.E, p.n_mt, p.k_stages, n_tiles,
+                    p.split_counters != nullptr && 2 * n_tiles < 3LL * (long long)gridDim.x);
   long long tile;
   int mt, nt, ks0, ks1, slot;
 
@@ -852,8 +857,8 @@ int wide_stages(int experts, bool fused) {
 }
 
 template <int TILE_N, int STAGE_K, bool kFused, bool kPair>
-int launch_wide_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p_in, int sm_count, bool pdl,
-                     cudaStream_t stream) {
+int launch_wide_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_b_tail, const Params& p_in,
+                     int sm_count, bool pdl, cudaStream_t stream) {
   using C = WideCfg<TILE_N, STAGE_K, kPair>;
   Params p = p_in;
   const int stages = wide_stages<C>(p.E, kFused);
@@ -869,6 +874,7 @@ int launch_wide_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const P
                               &max_pairs))
     return rc;
   const long long token_tiles = (long long)p.E * ceil_div_i(p.max_n, TILE_N);
+  PNV_REQUIRE(token_tiles * p.n_mt < (1LL << 31), "group_mm: too many tiles for one launch");      // the device walk is 32-bit
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[2];
   int n_attr = 0;
@@ -899,15 +905,16 @@ int launch_wide_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const P
   cfg.stream = stream;
   cfg.attrs = attr;
   cfg.numAttrs = n_attr;
-  PNV_CUDA(cudaLaunchKernelEx(&cfg, group_mm_wide_kernel<TILE_N, STAGE_K, kFused, kPair>, map_a, map_b, p));
+  PNV_CUDA(cudaLaunchKernelEx(&cfg, group_mm_wide_kernel<TILE_N, STAGE_K, kFused, kPair>, map_a, map_b, map_b_tail, p));
   return PNV_OK;
 }
 
 template <int TILE_N, int STAGE_K, bool kPair>
-int launch_wide(const CUtensorMap& map_a, const CUtensorMap& map_b, Params& p, int sm_count, bool pdl,
-                cudaStream_t stream) {
-  if (p.f_b_out != nullptr) return launch_wide_impl<TILE_N, STAGE_K, true, kPair>(map_a, map_b, p, sm_count, pdl, stream);
-  return launch_wide_impl<TILE_N, STAGE_K, false, kPair>(map_a, map_b, p, sm_count, pdl, stream);
+int launch_wide(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_b_tail, Params& p, int sm_count,
+                bool pdl, cudaStream_t stream) {
+  if (p.f_b_out != nullptr)
+    return launch_wide_impl<TILE_N, STAGE_K, true, kPair>(map_a, map_b, map_b_tail, p, sm_count, pdl, stream);
+  return launch_wide_impl<TILE_N, STAGE_K, false, kPair>(map_a, map_b, map_b_tail, p, sm_count, pdl, stream);
 }
 
 // Tile variants.  The first eight names and ids are the reference's.  "1sm" variants run one CTA per
@@ -1041,6 +1048,7 @@ int group_mm_common(void* out, const int32_t* row_map, const RowParts* out_parts
   p.sfb_rt = sf_row_atoms(max_n);
   p.stages = 0;
   p.prod_lanes = 1;
+  p.b_tail = 0;
   p.split_counters = nullptr;
   p.split_partials = nullptr;
 
@@ -1066,7 +1074,7 @@ int group_mm_common(void* out, const int32_t* row_map, const RowParts* out_parts
     p.split_partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + split_counter_bytes(experts, features));
   }
 
-  CUtensorMap map_a, map_b;
+  CUtensorMap map_a, map_b, map_b_tail;
   if (int rc = make_map(&map_a, a_comp, (uint64_t)wd.k_ac / 2, (uint64_t)wd.m_ac, (uint64_t)experts,
                         (uint32_t)stage_k / 4, (uint32_t)kTileM,
                         stage_k == 512 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B))
@@ -1082,6 +1090,16 @@ int group_mm_common(void* out, const int32_t* row_map, const RowParts* out_parts
                                CU_TENSOR_MAP_SWIZZLE_128B)) {
     return rc;
   }
+  // narrow tail tiles: tiles of 128 tokens or more, activations through the 4-D map
+  map_b_tail = map_b;
+#ifndef PNV_NO_TAIL_TILES      // developer builds: every tile at full width, for comparisons
+  if (!narrow && tile_n >= 128 && p.b_4d) {
+    if (int rc = make_map_b4(&map_b_tail, b_act, (uint64_t)k / 2, (uint64_t)max_n, (uint64_t)experts,
+                             (uint32_t)(pair ? 32 : 64), (uint32_t)stage_k / 256))
+      return rc;
+    p.b_tail = 1;
+  }
+#endif
 
   cudaStream_t s = (cudaStream_t)stream;
   const bool use_pdl = pdl != 0 && pdl_enabled();
@@ -1090,15 +1108,15 @@ int group_mm_common(void* out, const int32_t* row_map, const RowParts* out_parts
     return launch_narrow<32, 512, 4>(map_a, map_b, p, sm_count, use_pdl, s);
   }
   switch (tile_n * 1000 + stage_k + (pair ? 1 : 0)) {
-    case 64256: return launch_wide<64, 256, false>(map_a, map_b, p, sm_count, use_pdl, s);
-    case 64257: return launch_wide<64, 256, true>(map_a, map_b, p, sm_count, use_pdl, s);
-    case 64512: return launch_wide<64, 512, false>(map_a, map_b, p, sm_count, use_pdl, s);
-    case 64513: return launch_wide<64, 512, true>(map_a, map_b, p, sm_count, use_pdl, s);
-    case 128256: return launch_wide<128, 256, false>(map_a, map_b, p, sm_count, use_pdl, s);
-    case 128257: return launch_wide<128, 256, true>(map_a, map_b, p, sm_count, use_pdl, s);
-    case 128512: return launch_wide<128, 512, false>(map_a, map_b, p, sm_count, use_pdl, s);
-    case 256256: return launch_wide<256, 256, false>(map_a, map_b, p, sm_count, use_pdl, s);
-    case 256257: return launch_wide<256, 256, true>(map_a, map_b, p, sm_count, use_pdl, s);
+    case 64256: return launch_wide<64, 256, false>(map_a, map_b, map_b_tail, p, sm_count, use_pdl, s);
+    case 64257: return launch_wide<64, 256, true>(map_a, map_b, map_b_tail, p, sm_count, use_pdl, s);
+    case 64512: return launch_wide<64, 512, false>(map_a, map_b, map_b_tail, p, sm_count, use_pdl, s);
+    case 64513: return launch_wide<64, 512, true>(map_a, map_b, map_b_tail, p, sm_count, use_pdl, s);
+    case 128256: return launch_wide<128, 256, false>(map_a, map_b, map_b_tail, p, sm_count, use_pdl, s);
+    case 128257: return launch_wide<128, 256, true>(map_a, map_b, map_b_tail, p, sm_count, use_pdl, s);
+    case 128512: return launch_wide<128, 512, false>(map_a, map_b, map_b_tail, p, sm_count, use_pdl, s);
+    case 256256: return launch_wide<256, 256, false>(map_a, map_b, map_b_tail, p, sm_count, use_pdl, s);
+    case 256257: return launch_wide<256, 256, true>(map_a, map_b, map_b_tail, p, sm_count, use_pdl, s);
     default: break;
   }
   return fail(PNV_ERR_UNSUPPORTED, "group_mm: no kernel for tile %dx%d%s", tile_n, stage_k, pair ? " (pair)" : "");

@@ -12,6 +12,11 @@
 //                               halves.  Against the single-CTA form that halves the activation bytes an SM
 //                               has to pull from L2 per unit of math, which is what bounds these shapes.
 //
+// Tail tiles.  The last token tile of an expert is often nearly empty (256 +- 16 rows per expert leave every other
+// expert a second tile of a dozen rows).  When it holds at most 64 live rows - and the launch has the tensor map for
+// it (K a multiple of 256, tiles of 128 tokens or more) - the tile runs 64 tokens wide: a quarter or half of the
+// activation bytes, one scale row-atom, MMAs a quarter or half as long.  Every role derives the width from counts[].
+//
 // 22 warps per CTA:
 //   warp 0   tile producer: TMA copies of the compressed weights and of the activations
 //   warp 1   side producer: bulk copies of the metadata, SFA and SFB atoms (they sit in global memory in
@@ -61,6 +66,9 @@ struct WideCfg {
   static constexpr int kOffE = kOffB + kBBytes;
   static constexpr int kOffSfa = kOffE + kEBytes;
   static constexpr int kOffSfb = kOffSfa + kSfaBytes;
+  static constexpr int kTailN = 64;                          // width of a narrow tail tile
+  static constexpr int kTailBRows = kTailN / kCtas;
+  static constexpr int kTailBBoxBytes = kTailBRows * 128;
   static constexpr int kChunk = TILE_N >= 128 ? 32 : 16;     // token columns an epilogue group takes at a time
   static constexpr int kFusedOutBytes = 4 * 8192;            // fused epilogue: one 8 KiB exchange area per group
   static constexpr int kPlainWarpWords = 8 * 36;             // plain epilogue: 8 token pairs x 32 features (+ 4 words of padding) per warp
@@ -122,21 +130,36 @@ __device__ __forceinline__ int my_work_items(const int* cnt, int E, int per_toke
 template <int TILE_N>
 struct UnitTiles {
   int e, mu, nt;                 // the current tile: expert, M unit, token tile
-  TileWalk walk;
-  long long w;
-  int n_units;
-  __device__ void init(const int* s_counts, int E, int n_mu, int unit, int n_units_) {
-    walk.init<TILE_N>(s_counts, E, n_mu);
-    w = unit;
-    n_units = n_units_;
+  // 32-bit walk (the host bounds the tile count of a launch): next tile index, first tile of expert e_next,
+  // tiles of that expert
+  const int* cnt;
+  int E, n_mu, e_next, n_units;
+  unsigned w, base, tiles_e;
+  __device__ void init(const int* s_counts, int E_, int n_mu_, int unit, int n_units_) {
+    cnt = s_counts; E = E_; n_mu = n_mu_; e_next = 0; n_units = n_units_;
+    w = (unsigned)unit; base = 0;
+    tiles_e = (unsigned)n_mu * (unsigned)ceil_div_i(cnt[0], TILE_N);
   }
   __device__ bool next() {
-    if (!walk.seek<TILE_N>(w, mu, nt)) return false;
-    w += n_units;
-    e = walk.e;
+    while (w - base >= tiles_e) {
+      base += tiles_e;
+      if (++e_next >= E) return false;
+      tiles_e = (unsigned)n_mu * (unsigned)ceil_div_i(cnt[e_next], TILE_N);
+    }
+    const unsigned local = w - base;
+    nt = (int)(local / (unsigned)n_mu);
+    mu = (int)(local - (unsigned)nt * (unsigned)n_mu);
+    e = e_next;
+    w += (unsigned)n_units;
     return true;
   }
 };
+
+// Does the tile at token offset n0 of an expert with cnt rows run as a narrow tail tile?
+template <int TILE_N>
+__device__ __forceinline__ bool narrow_tail(const Params& p, int cnt, int n0) {
+  return TILE_N >= 128 && p.b_tail != 0 && cnt - n0 <= 64;
+}
 
 // tensor memory -> registers, kChunk (16 or 32) consecutive columns of this warp's lane quarter
 template <int N>
@@ -151,7 +174,7 @@ __device__ __forceinline__ void tc_ld_cols<8>(uint32_t taddr, uint32_t (&r)[8]) 
 template <int TILE_N, int STAGE_K, bool kFused, bool kPair>
 __global__ void __launch_bounds__((6 + 16) * 32, 1)
 group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                     const Params p) {
+                     const __grid_constant__ CUtensorMap map_b_tail, const Params p) {
   using C = WideCfg<TILE_N, STAGE_K, kPair>;
   using Tiles = UnitTiles<TILE_N>;
   constexpr int kCtas = C::kCtas;
@@ -182,6 +205,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&map_a);
     ptx::prefetch_tensormap(&map_b);
+    ptx::prefetch_tensormap(&map_b_tail);
     for (int s = 0; s < p.stages; ++s) {
       ptx::mbar_init(full_bar + s, 3);
       ptx::mbar_init(empty_bar + s, 1);
@@ -226,6 +250,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       int n = 0, ks = slot_lane, stage = slot_lane, cur_n = -1;     // prod_lanes <= stages (host)
       uint32_t turn = 0;
       int e = 0, mt = 0, n0 = 0, sfb_row_atoms = 1;
+      bool tail = false;
       const uint8_t *e_base = nullptr, *sfa_base = nullptr, *sfb_base = nullptr;
       long long pf_wait = 0;
       while (ok) {
@@ -239,9 +264,10 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           // the second CTA of a pair takes the odd M tile; past the last tile it re-reads the last one (its
           // results are never stored), so every copy stays inside the expert's operands
           mt = kPair ? min(2 * tiles.mu + (int)rank, p.n_mt - 1) : tiles.mu;
+          tail = narrow_tail<TILE_N>(p, s_counts[e], n0);
           if (!tile_role) {
             sfb_base = p.sfb + (((long long)e * p.sfb_rt + (n0 >> 7)) * p.n_kt) * 512;
-            sfb_row_atoms = TILE_N > 128 ? min(2, p.sfb_rt - (n0 >> 7)) : 1;
+            sfb_row_atoms = (TILE_N > 128 && !tail) ? min(2, p.sfb_rt - (n0 >> 7)) : 1;
             e_base = p.e_meta + (((long long)e * p.e_k_atoms) * p.e_m_atoms + mt) * 2048;
             sfa_base = p.sfa + (((long long)e * p.n_mt + mt) * p.n_kt) * 512;
           }
@@ -261,10 +287,13 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         if (tile_role) {
           // with the 4-D activation map one copy fetches all of the stage's 256-K chunks (a box past the
           // last chunk is zero-filled and still counts its full size)
-          const int nb = n0 + (int)rank * C::kBRows;      // this CTA's share of the token rows
-          ptx::mbar_arrive_expect_tx(full_bar + stage, C::kABytes + (p.b_4d ? C::kBBoxes : b_boxes) * C::kBBoxBytes);
+          const int nb = n0 + (int)rank * (tail ? C::kTailBRows : C::kBRows);      // this CTA's share of the token rows
+          ptx::mbar_arrive_expect_tx(full_bar + stage, C::kABytes + (p.b_4d ? C::kBBoxes : b_boxes) *
+                                                                      (tail ? C::kTailBBoxBytes : C::kBBoxBytes));
           ptx::tma_load_3d(st + C::kOffA, &map_a, full_bar + stage, ks * C::kARowBytes, mt * kTileM, e);
-          if (p.b_4d) {
+          if (tail) {               // (only with the 4-D maps)
+            ptx::tma_load_4d(st + C::kOffB, &map_b_tail, full_bar + stage, 0, nb, ks * C::kBBoxes, e);
+          } else if (p.b_4d) {
             ptx::tma_load_4d(st + C::kOffB, &map_b, full_bar + stage, 0, nb, ks * C::kBBoxes, e);
           } else {
             for (int b = 0; b < b_boxes; ++b)
@@ -306,7 +335,8 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const int issuer = warp - 2;
     const int n_items = my_work_items<TILE_N>(s_counts, p.E, n_mu, unit, n_units, lane);
     if (lane == 0 && issuer < kIssuers && rank == 0) {
-      constexpr uint32_t idesc = ptx::mma_sp_nvf4_idesc(TILE_N, kTileM * kCtas);
+      constexpr uint32_t idesc_full = ptx::mma_sp_nvf4_idesc(TILE_N, kTileM * kCtas);
+      constexpr uint32_t idesc_tail = ptx::mma_sp_nvf4_idesc(C::kTailN, kTileM * kCtas);
       Tiles tiles;
       tiles.init(s_counts, p.E, n_mu, unit, n_units);
       int stage = 0, acc = kIssuers == 2 ? issuer : 0;
@@ -343,12 +373,17 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         // a 64-wide tile's scales sit 0 or 2 columns into the 128-row atom (even offsets only: the MMA
         // faults on an odd scale column); wider tiles start at column 0 and need no tile coordinates
         uint32_t sfb_off = 0;
-        if (TILE_N < 128) {
+        uint32_t idesc = idesc_full, bbox16 = C::kBBoxBytes >> 4;
+        if (TILE_N < 128 || p.b_tail != 0) {
           // (two issuers: each walks every tile and uses every other one)
           bool any = true;
           for (int s = item < kIssuers ? item + 1 : kIssuers; s > 0 && any; --s) any = tiles.next();
           if (!any) break;
-          sfb_off = ((tiles.nt * TILE_N) & 127) >> 5;
+          if (TILE_N < 128) sfb_off = ((tiles.nt * TILE_N) & 127) >> 5;
+          if (narrow_tail<TILE_N>(p, s_counts[tiles.e], tiles.nt * TILE_N)) {
+            idesc = idesc_tail;
+            bbox16 = C::kTailBBoxBytes >> 4;
+          }
         }
         const long long ta0 = PNV_PROF_T();
         if (!ptx::mbar_wait(acc_empty + acc, acc_phase ^ 1)) {
@@ -380,7 +415,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           for (int ka = 0; ka < C::kAtoms; ++ka)
             if (ka < k_atoms)
               ptx::tc_mma_sp_nvf4<kCtas>(d_tmem, pack_desc(la + ka * 2, hi_a),
-                                         pack_desc(lb + (ka >> 1) * (C::kBBoxBytes >> 4) + (ka & 1) * 4, hi_b), idesc,
+                                         pack_desc(lb + (ka >> 1) * bbox16 + (ka & 1) * 4, hi_b), idesc,
                                          (ks | ka) != 0 ? 1u : 0u, slot + ka * 4, sfb_cols + ka * C::kSfbColsPerAtom,
                                          slot + C::kSlotE + ka * 2);
           // shared-memory stage and tensor-memory slot reusable (in both CTAs of a pair) once these MMAs retire
@@ -409,7 +444,9 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   } else if (warp == 4 || warp == 5) {
     // =============================== copiers ===============================
     // Both copiers take every pipeline stage and split its atoms: copier 0 the weight scales and the metadata,
-    // copier 1 the activation scales.  Each commits on the stage's sf_full barrier (two arrivals).
+    // copier 1 the activation scales.  Each commits on the stage's sf_full barrier (two arrivals).  The copiers
+    // do not walk the tiles: a narrow tail tile loads one activation-scale row atom instead of two, and the copy of
+    // the other (whatever an older stage left there) lands in columns its 64-token MMAs never read.
     const int copier = warp - 4;
     const int n_items = my_work_items<TILE_N>(s_counts, p.E, n_mu, unit, n_units, lane);
     const long long n_stages = (long long)n_items * p.k_stages;
@@ -426,6 +463,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       int stage = 0, ks = 0;
       uint32_t phase = 0;
       long long pf_cwait = 0, pf_cissue = 0;
+
 #pragma unroll 1
       for (long long g = 0; g < n_stages; ++g) {
         const long long tc0 = PNV_PROF_T();
@@ -546,11 +584,9 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         // bf16, hands the accumulator back, and then stores - when the output rows are 16-byte aligned, through a
         // warp-private transpose in shared memory (no barrier beyond the warp's own), else one token row at a time
         // straight from registers (64 contiguous bytes per instruction).  Rows at or past counts[e] are skipped.
-        const long long row_e = (long long)e * p.max_n;
         const int m = mt * kTileM + m_local;
         constexpr int kOwn = TILE_N / (4 * kChunk);       // chunks of a tile each group takes (1, or 2 for 256 tokens)
         const bool mine = mt_valid && m < p.M;
-        const long long pitch = p.M;
         const bool wide_rows = (p.M & 7) == 0;            // output rows are 16-byte aligned
         uint32_t* tbuf = reinterpret_cast<uint32_t*>(s_out) + (warp - C::kFirstEpilogueWarp) * C::kPlainWarpWords;
         // One chunk at a time: load, (after the warp's last chunk) hand the accumulator back, scale and round two
@@ -589,33 +625,37 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             const bool mine8 = mt_valid && m8 < p.M;
 #pragma unroll
             for (int h = 0; h < kChunk / 16; ++h) {
+              // where this lane's two tokens go (nullptr: not stored), before the values take up registers
+              const int t0 = h * 16 + 2 * pr_row;          // this lane's even token inside the chunk
+              __nv_bfloat16 *d0 = nullptr, *d1 = nullptr;
+              if (mine8 && t0 < rows) {
+                const long long src = (long long)e * p.max_n + (n0 + c0 + t0);
+                if (p.row_map == nullptr) {
+                  d0 = p.out + src * p.M + m8;
+                  if (t0 + 1 < rows) d1 = d0 + p.M;
+                } else {
+                  const int r0 = p.row_map[src], r1 = t0 + 1 < rows ? p.row_map[src + 1] : -1;
+                  if (r0 >= 0) d0 = mapped_row(p, r0) + m8;
+                  if (r1 >= 0) d1 = mapped_row(p, r1) + m8;
+                }
+              }
               __syncwarp();
 #pragma unroll
               for (int q = 0; q < 8; ++q) tbuf[q * 36 + lane] = pk[h * 8 + q];
               __syncwarp();
               const uint4 a = *reinterpret_cast<const uint4*>(tbuf + pr_row * 36 + fg * 8);
               const uint4 b = *reinterpret_cast<const uint4*>(tbuf + pr_row * 36 + fg * 8 + 4);
-              const uint4 lo = make_uint4(__byte_perm(a.x, a.y, 0x5410), __byte_perm(a.z, a.w, 0x5410),
-                                          __byte_perm(b.x, b.y, 0x5410), __byte_perm(b.z, b.w, 0x5410));
-              const uint4 hi = make_uint4(__byte_perm(a.x, a.y, 0x7632), __byte_perm(a.z, a.w, 0x7632),
-                                          __byte_perm(b.x, b.y, 0x7632), __byte_perm(b.z, b.w, 0x7632));
-              const int t0 = h * 16 + 2 * pr_row;          // this lane's even token inside the chunk
-              long long to0 = t0 < rows ? row_e + n0 + c0 + t0 : -1, to1 = t0 + 1 < rows ? to0 + 1 : -1;
-              if (p.row_map != nullptr) {
-                if (to0 >= 0) to0 = p.row_map[to0];
-                if (to1 >= 0) to1 = p.row_map[row_e + n0 + c0 + t0 + 1];
-              }
-              if (p.row_map != nullptr) {
-                if (mine8 && to0 >= 0) *reinterpret_cast<uint4*>(mapped_row(p, to0) + m8) = lo;
-                if (mine8 && to1 >= 0) *reinterpret_cast<uint4*>(mapped_row(p, to1) + m8) = hi;
-              } else {
-                if (mine8 && to0 >= 0) *reinterpret_cast<uint4*>(p.out + to0 * pitch + m8) = lo;
-                if (mine8 && to1 >= 0) *reinterpret_cast<uint4*>(p.out + to1 * pitch + m8) = hi;
-              }
+              if (d0 != nullptr)
+                *reinterpret_cast<uint4*>(d0) = make_uint4(__byte_perm(a.x, a.y, 0x5410), __byte_perm(a.z, a.w, 0x5410),
+                                                           __byte_perm(b.x, b.y, 0x5410), __byte_perm(b.z, b.w, 0x5410));
+              if (d1 != nullptr)
+                *reinterpret_cast<uint4*>(d1) = make_uint4(__byte_perm(a.x, a.y, 0x7632), __byte_perm(a.z, a.w, 0x7632),
+                                                           __byte_perm(b.x, b.y, 0x7632), __byte_perm(b.z, b.w, 0x7632));
             }
           } else if (p.row_map == nullptr) {
             const int live = mine ? min(kChunk, rows) : 0;
-            unsigned short* dst = reinterpret_cast<unsigned short*>(p.out + (row_e + n0 + c0) * p.M + m);
+            const long long pitch = p.M;
+            unsigned short* dst = reinterpret_cast<unsigned short*>(p.out + ((long long)e * p.max_n + n0 + c0) * pitch + m);
 #pragma unroll
             for (int i = 0; i < kChunk; i += 2) {
               const uint32_t w = pk[i / 2];
@@ -624,7 +664,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             }
           } else {
             // lane i holds the output row of the chunk's token i (kChunk <= 32); -1 past the live rows
-            const int to_lane = lane < rows ? p.row_map[row_e + n0 + c0 + lane] : -1;
+            const int to_lane = lane < rows ? p.row_map[(long long)e * p.max_n + n0 + c0 + lane] : -1;
 #pragma unroll
             for (int i = 0; i < kChunk; i += 2) {
               const uint32_t w = pk[i / 2];

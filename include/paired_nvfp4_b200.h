@@ -252,7 +252,8 @@ const char* pnv_group_mm_config_name(int config_id);
  * predecessor before its first dependent read; csrc/pdl.cuh:42-80).
  * workspace (the reference allocates its own inside the op, csrc/group_mm.cuh:163-165): NULL, or
  * pnv_group_mm_workspace_bytes(experts, features, max_n, sm_count) bytes, 256-byte aligned, for splitting K
- * across CTAs.  Only decode-sized problems (max_n <= 32) use it: the K stages of all tiles are dealt evenly
+ * across CTAs.  Only decode-sized problems (max_n <= 32) with fewer than 1.5 tiles per SM (decided on the device
+ * from the counts) use it: the K stages of all tiles are dealt evenly
  * to the SMs, a tile shared by several CTAs is summed from fp32 partials in K order by whichever arrives
  * last (so the result does not depend on timing).  The first 4 * experts * ceil(features / 128) bytes are
  * arrival counters: they must be zero before the first launch that uses the buffer, every launch leaves
