@@ -697,25 +697,14 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const int kb = mt * 2 + (sub >> 1);                  // 32-feature block of the N-wide output
         uint8_t* code_col = p.f_b_out + kb * 16 + (lane >> 3) * 4;
         const long long code_pitch = p.f_n / 2;
-#pragma unroll 1
-        for (int c0 = group * kChunk; c0 < TILE_N && n0 + c0 < cnt; c0 += 4 * kChunk) {
-          // the half of the chunk this warp finishes and the half it parks for its partner, as two loads (the
-          // column offsets differ between the gate and the up warp, the register indices do not)
+        // tensor memory -> registers for one chunk: the half this warp finishes stays (bf16 pairs, the even token
+        // in the low half), the half its partner finishes is parked in shared memory; two loads, because the column
+        // offsets differ between the gate and the up warp and the register indices must not
+        auto load_park = [&](int c0, uint32_t* x_mine, uint32_t (&own)[kPk]) {
           uint32_t v_own[kHalf], v_oth[kHalf];
-          const long long tf0 = PNV_PROF_T();
           tc_ld_cols<kHalf>(t_row + c0 + par * kHalf, v_own);
           tc_ld_cols<kHalf>(t_row + c0 + (1 - par) * kHalf, v_oth);
           ptx::tc_ld_wait();
-          if (c0 + 4 * kChunk >= TILE_N || n0 + c0 + 4 * kChunk >= cnt) { release_acc(); released = true; }
-          PNV_PROF_ACC(pf_f0, tf0);                // tensor-memory load
-          if (!mt_valid) continue;                 // the same for every thread of the CTA
-          const long long tf1 = PNV_PROF_T();
-          uint32_t* area = xbuf + flip * (2 * kPk * 32);
-          uint32_t* x_mine = area + par * (kPk * 32);
-          const uint32_t* x_other = area + (1 - par) * (kPk * 32);
-          flip ^= 1;
-          // bf16(alpha * acc), two tokens to a word (the even token in the low half)
-          uint32_t own[kPk];
 #pragma unroll
           for (int k = 0; k < kPk; ++k) {
             const __nv_bfloat162 po = __floats2bfloat162_rn(__fmul_rn(alpha, __uint_as_float(v_oth[2 * k])),
@@ -725,27 +714,29 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                                                            __fmul_rn(alpha, __uint_as_float(v_own[2 * k + 1])));
             own[k] = *reinterpret_cast<const uint32_t*>(&pr);
           }
-          float sv[kHalf];
-          if (table && !is_up) {                   // the gate warp's lookups are in flight across the barrier
+        };
+        // the gate warp's SiLU lookups for its own tokens (issued before the barrier, so they are in flight across it)
+        auto gate_lookups = [&](const uint32_t (&own)[kPk], float (&sv)[kHalf]) {
 #pragma unroll
-            for (int k = 0; k < kPk; ++k) {
-              sv[2 * k] = __uint_as_float((uint32_t)__ldg(p.f_act.silu_tab + (own[k] & 0xFFFFu)) << 16);
-              sv[2 * k + 1] = __uint_as_float((uint32_t)__ldg(p.f_act.silu_tab + (own[k] >> 16)) << 16);
-            }
+          for (int k = 0; k < kPk; ++k) {
+            sv[2 * k] = __uint_as_float((uint32_t)__ldg(p.f_act.silu_tab + (own[k] & 0xFFFFu)) << 16);
+            sv[2 * k + 1] = __uint_as_float((uint32_t)__ldg(p.f_act.silu_tab + (own[k] >> 16)) << 16);
           }
-          named_bar_sync(pair_bar, 64);
-          PNV_PROF_ACC(pf_f1, tf1);                // round, park for the partner, the pair barrier
+        };
+        // everything after the exchange for one chunk: activation, block scale, codes, stores
+        auto finish = [&](int c0, const uint32_t (&own)[kPk], const uint32_t* x_other, float (&sv)[kHalf], bool have_sv) {
           const long long tf2 = PNV_PROF_T();
           uint32_t oth[kPk];
 #pragma unroll
           for (int k = 0; k < kPk; ++k) oth[k] = x_other[k * 32 + lane];
           uint32_t yp[kPk];                        // results, bf16 pairs again
           if (table) {
-            if (is_up) {
+            if (is_up || !have_sv) {
 #pragma unroll
               for (int k = 0; k < kPk; ++k) {
-                sv[2 * k] = __uint_as_float((uint32_t)__ldg(p.f_act.silu_tab + (oth[k] & 0xFFFFu)) << 16);
-                sv[2 * k + 1] = __uint_as_float((uint32_t)__ldg(p.f_act.silu_tab + (oth[k] >> 16)) << 16);
+                const uint32_t gk = is_up ? oth[k] : own[k];
+                sv[2 * k] = __uint_as_float((uint32_t)__ldg(p.f_act.silu_tab + (gk & 0xFFFFu)) << 16);
+                sv[2 * k + 1] = __uint_as_float((uint32_t)__ldg(p.f_act.silu_tab + (gk >> 16)) << 16);
               }
             }
 #pragma unroll
@@ -810,6 +801,55 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             if (lane < kHalf && n < cnt) p.f_sfb_out[sf_offset(e, n, kb, p.sfb_rt, p.f_n_kt)] = (uint8_t)sf_byte;
           }
           PNV_PROF_ACC(pf_f3, tf3);                // amax, scale, quantize, transpose, store
+        };
+        if (TILE_N == 256) {
+          // Two chunks per warp and one accumulator stage: both chunks leave tensor memory first (own halves in
+          // registers, partner halves in the two exchange areas) and the accumulator goes back to the issuer
+          // before any of the arithmetic.  Two pair barriers per tile: the partner has finished reading the
+          // previous tile's areas; this tile's are filled.
+          const int cA = group * kChunk, cB = cA + 4 * kChunk;
+          const bool liveA = n0 + cA < cnt, liveB = n0 + cB < cnt;
+          if (mt_valid && liveA) {
+            const long long tf0 = PNV_PROF_T();
+            uint32_t* area0 = xbuf;
+            uint32_t* area1 = xbuf + 2 * kPk * 32;
+            uint32_t ownA[kPk], ownB[kPk];
+            float sv[kHalf];
+            named_bar_sync(pair_bar, 64);
+            load_park(cA, area0 + par * (kPk * 32), ownA);
+            if (liveB) load_park(cB, area1 + par * (kPk * 32), ownB);
+            release_acc();
+            released = true;
+            PNV_PROF_ACC(pf_f0, tf0);              // tensor-memory loads, packing, parking
+            const long long tf1 = PNV_PROF_T();
+            if (table && !is_up) gate_lookups(ownA, sv);
+            named_bar_sync(pair_bar, 64);
+            PNV_PROF_ACC(pf_f1, tf1);              // the pair barrier
+            finish(cA, ownA, area0 + (1 - par) * (kPk * 32), sv, true);
+            if (liveB) finish(cB, ownB, area1 + (1 - par) * (kPk * 32), sv, false);
+          }
+        } else {
+#pragma unroll 1
+          for (int c0 = group * kChunk; c0 < TILE_N && n0 + c0 < cnt; c0 += 4 * kChunk) {
+            const long long tf0 = PNV_PROF_T();
+            uint32_t* area = xbuf + flip * (2 * kPk * 32);
+            flip ^= 1;
+            uint32_t own[kPk];
+            float sv[kHalf];
+            if (!mt_valid) {                       // the same for every thread of the CTA: nothing to compute or store
+              release_acc();
+              released = true;
+              break;
+            }
+            load_park(c0, area + par * (kPk * 32), own);
+            if (c0 + 4 * kChunk >= TILE_N || n0 + c0 + 4 * kChunk >= cnt) { release_acc(); released = true; }
+            PNV_PROF_ACC(pf_f0, tf0);              // tensor-memory loads, packing, parking
+            const long long tf1 = PNV_PROF_T();
+            if (table && !is_up) gate_lookups(own, sv);
+            named_bar_sync(pair_bar, 64);
+            PNV_PROF_ACC(pf_f1, tf1);              // the pair barrier
+            finish(c0, own, area + (1 - par) * (kPk * 32), sv, true);
+          }
         }
       }
       if (!released) release_acc();
