@@ -10,7 +10,9 @@
 //                               of the token rows into its own shared memory with ordinary TMA copies (no
 //                               cluster multicast anywhere), and the tensor cores of both SMs read the two
 //                               halves.  Against the single-CTA form that halves the activation bytes an SM
-//                               has to pull from L2 per unit of math, which is what bounds these shapes.
+//                               has to pull from L2 per unit of math, which is what bounds these shapes.  Both
+//                               CTAs' tile loads count their bytes on the first CTA's barrier (.cta_group::2
+//                               tiled loads), the second CTA's small bulk copies are relayed by a remote arrive.
 //
 // Tail tiles.  The last token tile of an expert is often nearly empty (256 +- 16 rows per expert leave every other
 // expert a second tile of a dozen rows).  When it holds at most 64 live rows - and the launch has the tensor map for
@@ -288,17 +290,35 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           // with the 4-D activation map one copy fetches all of the stage's 256-K chunks (a box past the
           // last chunk is zero-filled and still counts its full size)
           const int nb = n0 + (int)rank * (tail ? C::kTailBRows : C::kBRows);      // this CTA's share of the token rows
-          ptx::mbar_arrive_expect_tx(full_bar + stage, C::kABytes + (p.b_4d ? C::kBBoxes : b_boxes) *
-                                                                      (tail ? C::kTailBBoxBytes : C::kBBoxBytes));
-          ptx::tma_load_3d(st + C::kOffA, &map_a, full_bar + stage, ks * C::kARowBytes, mt * kTileM, e);
-          if (tail) {               // (only with the 4-D maps)
-            ptx::tma_load_4d(st + C::kOffB, &map_b_tail, full_bar + stage, 0, nb, ks * C::kBBoxes, e);
-          } else if (p.b_4d) {
-            ptx::tma_load_4d(st + C::kOffB, &map_b, full_bar + stage, 0, nb, ks * C::kBBoxes, e);
+          const uint32_t tile_bytes = C::kABytes + (p.b_4d ? C::kBBoxes : b_boxes) * (tail ? C::kTailBBoxBytes : C::kBBoxBytes);
+          if (kPair) {
+            // The tiles of BOTH CTAs are counted on the first CTA's barrier (the second CTA's loads name it as
+            // theirs: .cta_group::2), so nothing has to relay "the big copies have landed" across the pair; the
+            // first CTA expects both CTAs' bytes (the boxes are the same size), the second only arrives.
+            if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar + stage, 2 * tile_bytes);
+            else ptx::mbar_arrive(full_bar + stage);
+            ptx::tma_load_3d_pair(st + C::kOffA, &map_a, full_bar + stage, 0, ks * C::kARowBytes, mt * kTileM, e);
+            if (tail) {             // (only with the 4-D maps)
+              ptx::tma_load_4d_pair(st + C::kOffB, &map_b_tail, full_bar + stage, 0, 0, nb, ks * C::kBBoxes, e);
+            } else if (p.b_4d) {
+              ptx::tma_load_4d_pair(st + C::kOffB, &map_b, full_bar + stage, 0, 0, nb, ks * C::kBBoxes, e);
+            } else {
+              for (int b = 0; b < b_boxes; ++b)
+                ptx::tma_load_3d_pair(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + stage, 0,
+                                      ks * (STAGE_K / 2) + b * 128, nb, e);
+            }
           } else {
-            for (int b = 0; b < b_boxes; ++b)
-              ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + stage,
-                               ks * (STAGE_K / 2) + b * 128, nb, e);
+            ptx::mbar_arrive_expect_tx(full_bar + stage, tile_bytes);
+            ptx::tma_load_3d(st + C::kOffA, &map_a, full_bar + stage, ks * C::kARowBytes, mt * kTileM, e);
+            if (tail) {             // (only with the 4-D maps)
+              ptx::tma_load_4d(st + C::kOffB, &map_b_tail, full_bar + stage, 0, nb, ks * C::kBBoxes, e);
+            } else if (p.b_4d) {
+              ptx::tma_load_4d(st + C::kOffB, &map_b, full_bar + stage, 0, nb, ks * C::kBBoxes, e);
+            } else {
+              for (int b = 0; b < b_boxes; ++b)
+                ptx::tma_load_3d(st + C::kOffB + b * C::kBBoxBytes, &map_b, full_bar + stage,
+                                 ks * (STAGE_K / 2) + b * 128, nb, e);
+            }
           }
         } else if (part == 0) {
           ptx::mbar_arrive_expect_tx(full_bar + stage, e_atoms * 2048);

@@ -137,6 +137,35 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
       : "memory");
 }
 
+// The same loads from a CTA of a pair whose completion is counted on the barrier at the same offset in CTA
+// `bar_cta` of the pair (.cta_group::2 lets the mbarrier of a tiled load live in the peer CTA; the data still lands
+// in the issuing CTA's shared memory; no multicast).  The pair's first CTA can then wait on one barrier for both
+// CTAs' tiles.
+__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* map, uint64_t* bar, uint32_t bar_cta,
+                                                 int c0, int c1, int c2) {
+  asm volatile(
+      "{\n\t.reg .b32 ra;\n\t"
+      "mapa.shared::cluster.u32 ra, %2, %6;\n\t"
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [ra];\n\t}"
+      :
+      : "r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2),
+        "r"(bar_cta)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_pair(void* dst, const CUtensorMap* map, uint64_t* bar, uint32_t bar_cta,
+                                                 int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "{\n\t.reg .b32 ra;\n\t"
+      "mapa.shared::cluster.u32 ra, %2, %7;\n\t"
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [ra];\n\t}"
+      :
+      : "r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2),
+        "r"(c3), "r"(bar_cta)
+      : "memory");
+}
+
 // Contiguous bulk copy global -> shared; both addresses 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile(
