@@ -635,7 +635,43 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             released = true;
           }
           if (rows <= 0) continue;
-          if (wide_rows) {
+          if (wide_rows && p.out_parts.n > 0) {
+            // Rows bound for other GPUs' buffers.  The four warps of the group (one lane quarter = 32 features
+            // each) put their slices side by side in shared memory ([token pair][128 feature words], 16 tokens at a
+            // time), so that a store instruction carries 256 contiguous bytes of an output row (16 lanes x 16
+            // bytes, two rows per instruction) instead of 64: fewer, larger writes on the link.  Two group
+            // barriers per pass; every warp of the group sees the same chunks, so they arrive together.
+            uint32_t* gst = reinterpret_cast<uint32_t*>(s_out) + group * (4 * C::kPlainWarpWords);
+            const int pr_row = ((warp - C::kFirstEpilogueWarp) & 3) * 2 + (lane >> 4), fg = lane & 15;
+            const int m8 = mt * kTileM + fg * 8;
+            const bool mine8 = mt_valid && m8 < p.M;
+            const int first = (fg >> 2) & 1;             // which half of its 32 bytes a lane reads first (bank spread)
+#pragma unroll
+            for (int h = 0; h < kChunk / 16; ++h) {
+              const int t0 = h * 16 + 2 * pr_row;
+              __nv_bfloat16 *d0 = nullptr, *d1 = nullptr;
+              if (mine8 && t0 < rows) {
+                const long long src = (long long)e * p.max_n + (n0 + c0 + t0);
+                const int r0 = p.row_map[src], r1 = t0 + 1 < rows ? p.row_map[src + 1] : -1;
+                if (r0 >= 0) d0 = mapped_row(p, r0) + m8;
+                if (r1 >= 0) d1 = mapped_row(p, r1) + m8;
+              }
+              named_bar_sync(1 + group, 128);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) gst[q * 128 + sub * 32 + lane] = pk[h * 8 + q];
+              named_bar_sync(1 + group, 128);
+              const uint32_t* src = gst + pr_row * 128 + fg * 8;
+              const uint4 x0 = *reinterpret_cast<const uint4*>(src + first * 4);
+              const uint4 x1 = *reinterpret_cast<const uint4*>(src + (1 - first) * 4);
+              const uint4 a = first ? x1 : x0, b = first ? x0 : x1;
+              if (d0 != nullptr)
+                *reinterpret_cast<uint4*>(d0) = make_uint4(__byte_perm(a.x, a.y, 0x5410), __byte_perm(a.z, a.w, 0x5410),
+                                                           __byte_perm(b.x, b.y, 0x5410), __byte_perm(b.z, b.w, 0x5410));
+              if (d1 != nullptr)
+                *reinterpret_cast<uint4*>(d1) = make_uint4(__byte_perm(a.x, a.y, 0x7632), __byte_perm(a.z, a.w, 0x7632),
+                                                           __byte_perm(b.x, b.y, 0x7632), __byte_perm(b.z, b.w, 0x7632));
+            }
+          } else if (wide_rows) {
             // 16 tokens at a time through a private corner of shared memory ([token pair][feature] words, rows
             // padded to 36 words so that neither side has bank conflicts): lane (k, f) = (lane / 4, lane % 4)
             // reads features 8 f .. 8 f + 7 of token pair k and stores 16 bytes per token, so one instruction
