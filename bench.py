@@ -696,7 +696,12 @@ def run_expert_parallel(args, wl_name, wl, rank, world, local_rank, device):
     al1 = (1.0 / g1).expand(E_local).contiguous()
 
     direct = world > 1 and args.exchange == "direct"
-    peers = ep.PeerBuffers(world, rank, slab, H, int(_cabi.lib.pnv_wire_row_bytes(H)), device) if direct else None
+    peers, exchange_note = None, ""
+    if direct:
+        try:      # raises on every rank or on none
+            peers = ep.PeerBuffers(world, rank, slab, H, int(_cabi.lib.pnv_wire_row_bytes(H)), device)
+        except RuntimeError as ex:
+            direct, exchange_note = False, f" ({ex}; fell back to the all-to-alls)"
 
     def make_ffn(w, g2, al2, peers=None):
         return ep.ExpertParallelFFN((w["a13"], w["e13"], w["s13"]), (w["a2"], w["e2"], w["s2"]), H, I, cap, al1, al2, g1, g2,
@@ -853,7 +858,7 @@ def run_expert_parallel(args, wl_name, wl, rank, world, local_rank, device):
                                 "plain stores); two one-element all-reduces per pass order them; the phases named all_to_all_* "
                                 "are those fences" if direct else
                                 "one equal-split NCCL all_to_all_single each way: NVFP4 wire rows out, bf16 rows back; "
-                                "routing planned on the device inside every pass") if world > 1 else
+                                "routing planned on the device inside every pass" + exchange_note) if world > 1 else
                                "N = 1: both all-to-alls are the identity, everything else is the N > 1 pass",
                    "l2": "inputs larger than L2" + ("; two weight copies alternate" if copies > 1 else "")},
         "layer_us": pass_s * 1e6, "step_ms_mean": float(step_ms.mean()), "step_ms_p10": float(np.percentile(step_ms, 10)),

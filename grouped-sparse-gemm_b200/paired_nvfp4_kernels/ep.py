@@ -87,37 +87,57 @@ class PeerBuffers:
         rows = world * slab
         self._sizes = (rows * row_bytes, rows * hidden * 2)
         self._own_ptrs, self._opened, handles = [], [], []
-        with torch.cuda.device(self.device):
-            for nbytes in self._sizes:
-                ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
-                _cabi.check(self._lib.pnv_peer_buffer_alloc(nbytes, ctypes.byref(ptr), handle))
-                self._own_ptrs.append(ptr.value)
-                handles.append(handle.raw)
-        self.recv_own = self._view(self._own_ptrs[0], 0).view(rows, row_bytes)
-        self.ret_own = self._view(self._own_ptrs[1], 1).view(torch.bfloat16).view(rows, hidden)
-        # dead slots are recognised by the id inside the row: start with all of them dead
-        self.recv_own.view(torch.int32)[:, row_bytes // 4 - 4].fill_(-1)
-        self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._collective = world > 1 and not local_only
         self.recv, self.ret = [None] * world, [None] * world
-        self.recv[rank], self.ret[rank] = self.recv_own, self.ret_own
+        self.recv_own = self.ret_own = None
+        # A failure on one rank (no memory, no peer path, interprocess handles not permitted) must not leave the
+        # others inside a collective: every rank goes through the same collectives whatever happened to it, the
+        # outcome is agreed on at the end, and then every rank raises or none does.
+        error = None
+        try:
+            with torch.cuda.device(self.device):
+                for nbytes in self._sizes:
+                    ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+                    _cabi.check(self._lib.pnv_peer_buffer_alloc(nbytes, ctypes.byref(ptr), handle))
+                    self._own_ptrs.append(ptr.value)
+                    handles.append(handle.raw)
+            self.recv_own = self._view(self._own_ptrs[0], 0).view(rows, row_bytes)
+            self.ret_own = self._view(self._own_ptrs[1], 1).view(torch.bfloat16).view(rows, hidden)
+            # dead slots are recognised by the id inside the row: start with all of them dead
+            self.recv_own.view(torch.int32)[:, row_bytes // 4 - 4].fill_(-1)
+            self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self.recv[rank], self.ret[rank] = self.recv_own, self.ret_own
+            torch.cuda.synchronize(self.device)
+        except Exception as ex:          # noqa: BLE001  (reported below, on every rank)
+            error = f"rank {rank}: {ex}"
         if local_only:                      # tests: all ranks in one process link their buffers themselves
+            if error:
+                raise RuntimeError(error)
             return
-        torch.cuda.synchronize(self.device)
         everyone = [None] * world
-        dist.all_gather_object(everyone, handles, group=group)
-        with torch.cuda.device(self.device):
-            for r in range(world):
-                if r == rank:
-                    continue
-                views = []
-                for which, handle in enumerate(everyone[r]):
-                    ptr = ctypes.c_void_p()
-                    _cabi.check(self._lib.pnv_peer_buffer_open(handle, ctypes.byref(ptr)))
-                    self._opened.append(ptr.value)
-                    views.append(self._view(ptr.value, which))
-                self.recv[r] = views[0].view(rows, row_bytes)
-                self.ret[r] = views[1].view(torch.bfloat16).view(rows, hidden)
-        dist.barrier(group=group)
+        dist.all_gather_object(everyone, (handles, error), group=group)
+        if not any(err for _, err in everyone):
+            try:
+                with torch.cuda.device(self.device):
+                    for r in range(world):
+                        if r == rank:
+                            continue
+                        views = []
+                        for which, handle in enumerate(everyone[r][0]):
+                            ptr = ctypes.c_void_p()
+                            _cabi.check(self._lib.pnv_peer_buffer_open(handle, ctypes.byref(ptr)))
+                            self._opened.append(ptr.value)
+                            views.append(self._view(ptr.value, which))
+                        self.recv[r] = views[0].view(rows, row_bytes)
+                        self.ret[r] = views[1].view(torch.bfloat16).view(rows, hidden)
+            except Exception as ex:      # noqa: BLE001
+                error = f"rank {rank}: {ex}"
+        outcome = [None] * world
+        dist.all_gather_object(outcome, error, group=group)
+        errors = [err for _, err in everyone if err] + [err for err in outcome if err]
+        if errors:
+            self.close()
+            raise RuntimeError("direct exchange unavailable: " + "; ".join(sorted(set(errors))))
 
     def _view(self, ptr, which):
         # no device argument: torch takes the device from the pointer itself and never copies
@@ -141,21 +161,23 @@ class PeerBuffers:
             dist.all_reduce(self._token, group=self.group)
 
     def close(self):
+        """Unmap the other ranks' buffers, then free this rank's.  A collective (two barriers) unless the buffers
+        were linked inside one process."""
         if self._lib is None:
             return
-        collective = self.world > 1 and dist.is_initialized() and self._opened
+        collective = self._collective and dist.is_initialized()
         torch.cuda.synchronize(self.device)
         if collective:
             dist.barrier(group=self.group)          # nobody stores into anybody's buffers any more
         self.recv, self.ret, self.recv_own, self.ret_own = [], [], None, None
         with torch.cuda.device(self.device):
             for ptr in self._opened:
-                self._cabi.check(self._lib.pnv_peer_buffer_close(ptr))
+                self._lib.pnv_peer_buffer_close(ptr)
             self._opened = []
             if collective:
                 dist.barrier(group=self.group)      # every mapping of this rank's buffers is gone
             for ptr in self._own_ptrs:
-                self._cabi.check(self._lib.pnv_peer_buffer_free(ptr))
+                self._lib.pnv_peer_buffer_free(ptr)
             self._own_ptrs = []
         self._lib = None
 
