@@ -253,13 +253,18 @@ def test_two_ranks_emulated_direct_exchange(slab):
         pb.close()
 
 
-def _worker(rank, world, port, out_dir, direct=False):
+def _worker(rank, world, port, out_dir, direct=False, one_gpu=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
-    torch.cuda.set_device(rank)
-    device = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    if one_gpu:          # both ranks on GPU 0, the fences over gloo (NCCL wants a GPU per rank)
+        torch.cuda.set_device(0)
+        device = torch.device("cuda", 0)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    else:
+        torch.cuda.set_device(rank)
+        device = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
     try:
         import paired_nvfp4_kernels  # noqa: F401
         from paired_nvfp4_kernels import ep
@@ -291,6 +296,23 @@ def test_two_rank_forward_matches_single_gpu(tmp_path, direct):
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     mp.spawn(_worker, args=(world, port, str(tmp_path), direct), nprocs=world, join=True)
+    want, want_counts = _single(world)
+    got = np.concatenate([np.load(tmp_path / f"ep{r}.npy") for r in range(world)])
+    got_counts = np.concatenate([np.load(tmp_path / f"cnt{r}.npy") for r in range(world)])
+    assert np.array_equal(got_counts, want_counts)
+    assert np.array_equal(got, want)
+
+
+def test_two_processes_one_gpu_direct_exchange(tmp_path):
+    """The direct exchange between two real processes that share GPU 0: buffers allocated by the library, their
+    interprocess handles exchanged and opened in the other process, rows stored straight into the other rank's
+    buffers, three passes over the same buffers.  (No kernel of one process waits for the other: the fences are
+    host-side collectives.)"""
+    world = 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_worker, args=(world, port, str(tmp_path), True, True), nprocs=world, join=True)
     want, want_counts = _single(world)
     got = np.concatenate([np.load(tmp_path / f"ep{r}.npy") for r in range(world)])
     got_counts = np.concatenate([np.load(tmp_path / f"cnt{r}.npy") for r in range(world)])
