@@ -34,8 +34,8 @@
 //   6 - 21   epilogue, four groups of four warps (one warp per lane quarter); a tile's chunks of token
 //            columns are dealt round-robin to the groups
 //
-// Barriers per pipeline stage s: full[s] (this CTA's copies landed), peer_full[s] (pair: the second CTA's
-// copies landed, relayed to the first), sf_full[s] (copier's commit -> issuers: scales and metadata are in tensor
+// Barriers per pipeline stage s: full[s] (this CTA's copies landed; in a pair's first CTA it also counts the
+// second CTA's tile loads), peer_full[s] (pair: the second CTA's bulk copies landed, relayed to the first), sf_full[s] (copier's commit -> issuers: scales and metadata are in tensor
 // memory), empty[s] (issuer's tcgen05.commit, delivered to both CTAs of a pair -> producers).  Per accumulator
 // stage: acc_full (commit, both CTAs), acc_empty (all epilogue warps of the CTA or pair -> issuers).  Every wait
 // is bounded.
