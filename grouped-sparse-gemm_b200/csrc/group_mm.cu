@@ -37,6 +37,7 @@
 
 #include <algorithm>
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -856,10 +857,10 @@ int wide_stages(int experts, bool fused) {
   return n;
 }
 
-template <int TILE_N, int STAGE_K, bool kFused, bool kPair>
+template <int TILE_N, int STAGE_K, bool kFused, bool kPair, bool kDblTails = false>
 int launch_wide_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_b_tail, const Params& p_in,
                      int sm_count, bool pdl, cudaStream_t stream) {
-  using C = WideCfg<TILE_N, STAGE_K, kPair>;
+  using C = WideCfg<TILE_N, STAGE_K, kPair, kDblTails>;
   Params p = p_in;
   const int stages = wide_stages<C>(p.E, kFused);
   if (stages < 2)
@@ -870,7 +871,7 @@ int launch_wide_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const C
                       C::kBarrierBytes + 4 * (size_t)p.E;
   static KernelSetup setup;
   int max_pairs = 0;
-  if (int rc = prepare_kernel(group_mm_wide_kernel<TILE_N, STAGE_K, kFused, kPair>, setup, C::kThreads, smem, kPair,
+  if (int rc = prepare_kernel(group_mm_wide_kernel<TILE_N, STAGE_K, kFused, kPair, kDblTails>, setup, C::kThreads, smem, kPair,
                               &max_pairs))
     return rc;
   const long long token_tiles = (long long)p.E * ceil_div_i(p.max_n, TILE_N);
@@ -905,13 +906,23 @@ int launch_wide_impl(const CUtensorMap& map_a, const CUtensorMap& map_b, const C
   cfg.stream = stream;
   cfg.attrs = attr;
   cfg.numAttrs = n_attr;
-  PNV_CUDA(cudaLaunchKernelEx(&cfg, group_mm_wide_kernel<TILE_N, STAGE_K, kFused, kPair>, map_a, map_b, map_b_tail, p));
+  PNV_CUDA(cudaLaunchKernelEx(&cfg, group_mm_wide_kernel<TILE_N, STAGE_K, kFused, kPair, kDblTails>, map_a, map_b, map_b_tail, p));
   return PNV_OK;
 }
 
 template <int TILE_N, int STAGE_K, bool kPair>
 int launch_wide(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_b_tail, Params& p, int sm_count,
                 bool pdl, cudaStream_t stream) {
+  // Pairs with 256-token tiles: when no expert can hold more than four token tiles, narrow tail tiles are a
+  // large enough share of the work for the double-tail-item variant to pay for its overhead on the other items
+  // (measured: 256 rows per expert -9 % on the down GEMM, 2048 rows per expert +3 %).
+  if constexpr (kPair && TILE_N == 256) {
+    if (p.b_tail != 0 && p.max_n <= 4 * TILE_N) {
+      if (p.f_b_out != nullptr)
+        return launch_wide_impl<TILE_N, STAGE_K, true, kPair, true>(map_a, map_b, map_b_tail, p, sm_count, pdl, stream);
+      return launch_wide_impl<TILE_N, STAGE_K, false, kPair, true>(map_a, map_b, map_b_tail, p, sm_count, pdl, stream);
+    }
+  }
   if (p.f_b_out != nullptr)
     return launch_wide_impl<TILE_N, STAGE_K, true, kPair>(map_a, map_b, map_b_tail, p, sm_count, pdl, stream);
   return launch_wide_impl<TILE_N, STAGE_K, false, kPair>(map_a, map_b, map_b_tail, p, sm_count, pdl, stream);
@@ -1062,6 +1073,10 @@ int group_mm_common(void* out, const int32_t* row_map, const RowParts* out_parts
     stage_k = 512;
   }
   const bool pair = kind.two_sm && !narrow;
+  // The 256 x 256 pair kernel takes 512-K stages (three large ones instead of six) when K is long: every stage
+  // costs the lone issuing threads the same few hundred cycles whatever it holds, and a long K loop keeps a short
+  // ring busy (measured: K = 7168 -5 to -12 %, K = 3072 -10 %; K = 2048 +4 %, K = 768 +3 %).
+  if (pair && tile_n == 256 && stage_k == 256 && k >= 3072) stage_k = 512;
   p.k_stages = ceil_div_i(k, stage_k);
   // the split schedule counts K stages in 32 bits
   const bool split_fits = (long long)experts * p.n_mt * p.k_stages < (1LL << 30);
@@ -1117,6 +1132,7 @@ int group_mm_common(void* out, const int32_t* row_map, const RowParts* out_parts
     case 128512: return launch_wide<128, 512, false>(map_a, map_b, map_b_tail, p, sm_count, use_pdl, s);
     case 256256: return launch_wide<256, 256, false>(map_a, map_b, map_b_tail, p, sm_count, use_pdl, s);
     case 256257: return launch_wide<256, 256, true>(map_a, map_b, map_b_tail, p, sm_count, use_pdl, s);
+    case 256513: return launch_wide<256, 512, true>(map_a, map_b, map_b_tail, p, sm_count, use_pdl, s);
     default: break;
   }
   return fail(PNV_ERR_UNSUPPORTED, "group_mm: no kernel for tile %dx%d%s", tile_n, stage_k, pair ? " (pair)" : "");

@@ -40,7 +40,7 @@
 // stage: acc_full (commit, both CTAs), acc_empty (all epilogue warps of the CTA or pair -> issuers).  Every wait
 // is bounded.
 
-template <int TILE_N, int STAGE_K, bool kPair>
+template <int TILE_N, int STAGE_K, bool kPair, bool kDblTails = false>
 struct WideCfg {
   static_assert(TILE_N == 64 || TILE_N == 128 || TILE_N == 256, "wide tile widths: 64, 128, 256");
   static_assert(STAGE_K == 256 || STAGE_K == 512, "stage depths: 256, 512");
@@ -84,11 +84,36 @@ struct WideCfg {
   static constexpr int kSfbColsPerAtom = 4 * kSfbRowAtoms;
   static constexpr int kSlotSfb = 4 * kAtoms;                // column offsets inside a slot
   static constexpr int kSlotE = kSlotSfb + kSfbColsPerAtom * kAtoms;
-  static constexpr int kSlotCols = kSlotE + 4 * kEAtoms;
+  // Double tail items (CTA pairs, 256-token tiles).  A narrow tail tile costs a pipeline stage per
+  // 256 K like any other tile although it moves half the bytes and a quarter of the math, so such a tile is
+  // multiplied against TWO M units per work item: the stage then holds both units' weights, metadata and weight
+  // scales next to the one 64-token activation box, and the item writes two 64-column accumulators.  Half as many
+  // stages per tail tile, and the activation box is fetched once for two units.  The support costs every item a few
+  // instructions in roles whose instruction streams bound the pipeline, so it is a kernel variant of its own
+  // (kDblTails), which the host picks when experts hold few token tiles.  The layout of such a stage:
+  static constexpr bool kTailDouble = kDblTails && kPair && TILE_N == 256;
+  static constexpr int kDblOffA1 = kABytes;                              // second unit's weights
+  static constexpr int kDblOffB = 2 * kABytes;
+  static constexpr int kDblOffE = kDblOffB + kBBoxes * kTailBBoxBytes;   // metadata, unit after unit
+  static constexpr int kDblOffSfa = kDblOffE + 2 * kEBytes;              // weight scales, unit after unit
+  static constexpr int kDblOffSfb = kDblOffSfa + 2 * kSfaBytes;          // activation scales (one row atom)
+  static constexpr int kDblBytes = kDblOffSfb + kSfaBytes;
+  // ... and of its tensor-memory slot: [SFA unit 0 | SFA unit 1 | SFB | E unit 0 | E unit 1]
+  static constexpr int kDblSlotSfa1 = 4 * kAtoms;
+  static constexpr int kDblSlotSfb = 8 * kAtoms;
+  static constexpr int kDblSlotE = kDblSlotSfb + 4 * kAtoms;
+  static constexpr int kDblSlotE1 = kDblSlotE + 4 * kEAtoms;
+  static constexpr int kDblSlotCols = kDblSlotE1 + 4 * kEAtoms;
+  static constexpr int kSlotCols = kTailDouble ? (kDblSlotCols > kSlotE + 4 * kEAtoms ? kDblSlotCols : kSlotE + 4 * kEAtoms)
+                                               : kSlotE + 4 * kEAtoms;
   static constexpr int kSlots = (kTmemCols - kColSlots) / kSlotCols;    // caps the pipeline depth
   static_assert(kStageBytes % 1024 == 0 && kOffB % 1024 == 0, "operand tiles must keep 1024-byte alignment");
   static_assert(kAccStages * TILE_N <= kColSlots && kSlots >= 2, "tensor-memory column map overflows");
-  static_assert(8 * (4 * kMaxStages + 2 * kAccStages) + 16 <= kBarrierBytes, "barrier block overflows");
+  static_assert(!kTailDouble || (kDblBytes <= kStageBytes && kDblOffB % 1024 == 0 && 2 * kTailN <= TILE_N),
+                "a double tail stage must fit the ordinary stage");
+  // the barriers take the first half of the barrier block, the per-stage item kinds sit in the second
+  static_assert(8 * (4 * kMaxStages + 2 * kAccStages) + 16 <= kBarrierBytes / 2 && 4 * kMaxStages <= kBarrierBytes / 2,
+                "barrier block overflows");
 };
 
 // Developer build only (-DPNV_WIDE_PROFILE): per-CTA cycle counters of the roles' waits, 16 per CTA, in a buffer
@@ -114,43 +139,65 @@ __device__ __forceinline__ uint64_t pack_desc(uint32_t lo, uint32_t hi) {
   return d;
 }
 
-// Work items (tiles) position `unit` of `n_units` will process: items unit, unit + n_units, ... of the list
-// every role walks.  Warp-collective.
+// Work items of an expert with c token rows: one per (token tile, M unit) - except that, with double tail items, the
+// narrow tail tile (at most 64 live rows) takes one item per TWO M units.  full = the items of the ordinary tiles.
 template <int TILE_N>
-__device__ __forceinline__ int my_work_items(const int* cnt, int E, int per_token_tile, int unit, int n_units, int lane) {
-  long long sum = 0;
-  for (int e = lane; e < E; e += 32) sum += ceil_div_i(cnt[e], TILE_N);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  const long long total = sum * per_token_tile;
-  return (long long)unit < total ? (int)((total - unit + n_units - 1) / n_units) : 0;
+__device__ __forceinline__ unsigned expert_items(int c, int n_mu, bool dbl_tails, unsigned& full) {
+  const unsigned nt = (unsigned)ceil_div_i(c, TILE_N);
+  const bool tail = dbl_tails && c > 0 && c - (int)(nt - 1u) * TILE_N <= 64;
+  full = (unsigned)n_mu * (nt - (tail ? 1u : 0u));
+  return full + (tail ? (unsigned)(n_mu + 1) >> 1 : 0u);
 }
 
-// The tiles of one unit (a CTA, or a CTA pair), in the order every role walks them: tiles unit, unit + units, ...
-// of the (expert, token tile, M unit) order, so that units working at the same time share token rows through L2.
-// next() moves to the following tile and says whether there was one.
+// Work items position `unit` of `n_units` will process: items unit, unit + n_units, ... of the list every role
+// walks.  Warp-collective.
+template <int TILE_N>
+__device__ __forceinline__ int my_work_items(const int* cnt, int E, int n_mu, bool dbl_tails, int unit, int n_units, int lane) {
+  long long sum = 0;
+  for (int e = lane; e < E; e += 32) {
+    unsigned full;
+    sum += expert_items<TILE_N>(cnt[e], n_mu, dbl_tails, full);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  return (long long)unit < sum ? (int)((sum - unit + n_units - 1) / n_units) : 0;
+}
+
+// The work items of one unit (a CTA, or a CTA pair), in the order every role walks them: items unit, unit + units,
+// ... of the (expert, token tile, M unit) order, so that units working at the same time share token rows through L2.
+// next() moves to the following item and says whether there was one.
 template <int TILE_N>
 struct UnitTiles {
-  int e, mu, nt;                 // the current tile: expert, M unit, token tile
-  // 32-bit walk (the host bounds the tile count of a launch): next tile index, first tile of expert e_next,
-  // tiles of that expert
+  int e, mu, nt;                 // the current item: expert, (first) M unit, token tile
+  bool dbl;                      // ... a narrow tail tile against M units mu and mu + 1
+  // 32-bit walk (the host bounds the tile count of a launch): next item index, first item of expert e_next.  The
+  // item count of an expert is recomputed from its row count whenever it is needed (a few instructions per item)
+  // rather than carried along in registers.
   const int* cnt;
   int E, n_mu, e_next, n_units;
-  unsigned w, base, tiles_e;
-  __device__ void init(const int* s_counts, int E_, int n_mu_, int unit, int n_units_) {
-    cnt = s_counts; E = E_; n_mu = n_mu_; e_next = 0; n_units = n_units_;
-    w = (unsigned)unit; base = 0;
-    tiles_e = (unsigned)n_mu * (unsigned)ceil_div_i(cnt[0], TILE_N);
+  bool dbl_tails;
+  unsigned w, base;
+  __device__ void init(const int* s_counts, int E_, int n_mu_, bool dbl_tails_, int unit, int n_units_) {
+    cnt = s_counts; E = E_; n_mu = n_mu_; e_next = 0; n_units = n_units_; dbl_tails = dbl_tails_;
+    w = (unsigned)unit; base = 0; dbl = false;
   }
   __device__ bool next() {
-    while (w - base >= tiles_e) {
-      base += tiles_e;
+    unsigned full, items = expert_items<TILE_N>(cnt[e_next], n_mu, dbl_tails, full);
+    while (w - base >= items) {
+      base += items;
       if (++e_next >= E) return false;
-      tiles_e = (unsigned)n_mu * (unsigned)ceil_div_i(cnt[e_next], TILE_N);
+      items = expert_items<TILE_N>(cnt[e_next], n_mu, dbl_tails, full);
     }
     const unsigned local = w - base;
-    nt = (int)(local / (unsigned)n_mu);
-    mu = (int)(local - (unsigned)nt * (unsigned)n_mu);
+    if (local < full) {
+      nt = (int)(local / (unsigned)n_mu);
+      mu = (int)(local - (unsigned)nt * (unsigned)n_mu);
+      dbl = false;
+    } else {                      // (only with dbl_tails: otherwise full == items)
+      nt = (cnt[e_next] - 1) / TILE_N;
+      mu = 2 * (int)(local - full);
+      dbl = true;
+    }
     e = e_next;
     w += (unsigned)n_units;
     return true;
@@ -173,11 +220,11 @@ __device__ __forceinline__ void tc_ld_cols<16>(uint32_t taddr, uint32_t (&r)[16]
 template <>
 __device__ __forceinline__ void tc_ld_cols<8>(uint32_t taddr, uint32_t (&r)[8]) { ptx::tc_ld_32x8(taddr, r); }
 
-template <int TILE_N, int STAGE_K, bool kFused, bool kPair>
+template <int TILE_N, int STAGE_K, bool kFused, bool kPair, bool kDblTails>
 __global__ void __launch_bounds__((6 + 16) * 32, 1)
 group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const __grid_constant__ CUtensorMap map_b_tail, const Params p) {
-  using C = WideCfg<TILE_N, STAGE_K, kPair>;
+  using C = WideCfg<TILE_N, STAGE_K, kPair, kDblTails>;
   using Tiles = UnitTiles<TILE_N>;
   constexpr int kCtas = C::kCtas;
   constexpr int kChunk = C::kChunk;
@@ -194,6 +241,9 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   uint64_t* acc_full = peer_full + C::kMaxStages;
   uint64_t* acc_empty = acc_full + C::kAccStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + C::kAccStages);
+  // per pipeline stage: does it belong to a double tail item?  Written by the metadata producer before its
+  // arrival on the stage's full barrier, read by the copiers after their wait on it.
+  volatile int* s_kind = reinterpret_cast<volatile int*>(after_stages + kOutBytes + C::kBarrierBytes / 2);
   int* s_counts = reinterpret_cast<int*>(after_stages + kOutBytes + C::kBarrierBytes);
 
   const int warp = threadIdx.x >> 5;
@@ -203,6 +253,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const int unit = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int n_units = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   const int n_mu = kPair ? (p.n_mt + 1) / 2 : p.n_mt;      // work items per token tile: M tiles, or pairs of them
+  const bool dbl_tails = C::kTailDouble && p.b_tail != 0;  // narrow tail tiles take two M units per work item
 
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&map_a);
@@ -247,12 +298,12 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const int part = lane & 1;                              // bulk-copy warp: 0 metadata, 1 scales
     if (slot_lane < p.prod_lanes) {
       Tiles tiles;
-      tiles.init(s_counts, p.E, n_mu, unit, n_units);
+      tiles.init(s_counts, p.E, n_mu, dbl_tails, unit, n_units);
       bool ok = true;
       int n = 0, ks = slot_lane, stage = slot_lane, cur_n = -1;     // prod_lanes <= stages (host)
       uint32_t turn = 0;
-      int e = 0, mt = 0, n0 = 0, sfb_row_atoms = 1;
-      bool tail = false;
+      int e = 0, mt = 0, mt1 = 0, n0 = 0, sfb_row_atoms = 1;
+      bool tail = false, dbl = false;
       const uint8_t *e_base = nullptr, *sfa_base = nullptr, *sfb_base = nullptr;
       long long pf_wait = 0;
       while (ok) {
@@ -267,6 +318,9 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           // results are never stored), so every copy stays inside the expert's operands
           mt = kPair ? min(2 * tiles.mu + (int)rank, p.n_mt - 1) : tiles.mu;
           tail = narrow_tail<TILE_N>(p, s_counts[e], n0);
+          // a double tail item: the second M unit's tile (again clamped: past the last unit its results are dropped)
+          dbl = C::kTailDouble && tiles.dbl;
+          mt1 = dbl ? min(2 * (tiles.mu + 1) + (int)rank, p.n_mt - 1) : mt;
           if (!tile_role) {
             sfb_base = p.sfb + (((long long)e * p.sfb_rt + (n0 >> 7)) * p.n_kt) * 512;
             sfb_row_atoms = (TILE_N > 128 && !tail) ? min(2, p.sfb_rt - (n0 >> 7)) : 1;
@@ -290,7 +344,8 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           // with the 4-D activation map one copy fetches all of the stage's 256-K chunks (a box past the
           // last chunk is zero-filled and still counts its full size)
           const int nb = n0 + (int)rank * (tail ? C::kTailBRows : C::kBRows);      // this CTA's share of the token rows
-          const uint32_t tile_bytes = C::kABytes + (p.b_4d ? C::kBBoxes : b_boxes) * (tail ? C::kTailBBoxBytes : C::kBBoxBytes);
+          const uint32_t tile_bytes = (dbl ? 2 * C::kABytes : C::kABytes) +
+                                      (p.b_4d ? C::kBBoxes : b_boxes) * (tail ? C::kTailBBoxBytes : C::kBBoxBytes);
           if (kPair) {
             // The tiles of BOTH CTAs are counted on the first CTA's barrier (the second CTA's loads name it as
             // theirs: .cta_group::2), so nothing has to relay "the big copies have landed" across the pair; the
@@ -298,7 +353,10 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar + stage, 2 * tile_bytes);
             else ptx::mbar_arrive(full_bar + stage);
             ptx::tma_load_3d_pair(st + C::kOffA, &map_a, full_bar + stage, 0, ks * C::kARowBytes, mt * kTileM, e);
-            if (tail) {             // (only with the 4-D maps)
+            if (dbl) {              // both units' weights, then the one narrow activation box
+              ptx::tma_load_3d_pair(st + C::kDblOffA1, &map_a, full_bar + stage, 0, ks * C::kARowBytes, mt1 * kTileM, e);
+              ptx::tma_load_4d_pair(st + C::kDblOffB, &map_b_tail, full_bar + stage, 0, 0, nb, ks * C::kBBoxes, e);
+            } else if (tail) {      // (only with the 4-D maps)
               ptx::tma_load_4d_pair(st + C::kOffB, &map_b_tail, full_bar + stage, 0, 0, nb, ks * C::kBBoxes, e);
             } else if (p.b_4d) {
               ptx::tma_load_4d_pair(st + C::kOffB, &map_b, full_bar + stage, 0, 0, nb, ks * C::kBBoxes, e);
@@ -321,10 +379,23 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             }
           }
         } else if (part == 0) {
-          ptx::mbar_arrive_expect_tx(full_bar + stage, e_atoms * 2048);
-          for (int ea = 0; ea < e_atoms; ++ea)
-            ptx::bulk_load(st + C::kOffE + ea * 2048,
-                           e_base + (long long)(ks * C::kEAtoms + ea) * p.e_m_atoms * 2048, 2048, full_bar + stage);
+          if (C::kTailDouble) s_kind[stage] = dbl ? 1 : 0;
+          ptx::mbar_arrive_expect_tx(full_bar + stage, (dbl ? 2 : 1) * e_atoms * 2048);
+          for (int ea = 0; ea < e_atoms; ++ea) {
+            const uint8_t* src = e_base + (long long)(ks * C::kEAtoms + ea) * p.e_m_atoms * 2048;
+            if (dbl) {
+              ptx::bulk_load(st + C::kDblOffE + ea * 2048, src, 2048, full_bar + stage);
+              ptx::bulk_load(st + C::kDblOffE + C::kEBytes + ea * 2048, src + (mt1 - mt) * 2048, 2048, full_bar + stage);
+            } else {
+              ptx::bulk_load(st + C::kOffE + ea * 2048, src, 2048, full_bar + stage);
+            }
+          }
+        } else if (dbl) {
+          ptx::mbar_arrive_expect_tx(full_bar + stage, sf_bytes * 3);
+          const uint8_t* src = sfa_base + ks * (C::kAtoms * 512);
+          ptx::bulk_load(st + C::kDblOffSfa, src, sf_bytes, full_bar + stage);
+          ptx::bulk_load(st + C::kDblOffSfa + C::kSfaBytes, src + (long long)(mt1 - mt) * p.n_kt * 512, sf_bytes, full_bar + stage);
+          ptx::bulk_load(st + C::kDblOffSfb, sfb_base + (long long)(ks * C::kAtoms) * 512, sf_bytes, full_bar + stage);
         } else {
           ptx::mbar_arrive_expect_tx(full_bar + stage, sf_bytes * (1 + sfb_row_atoms));
           ptx::bulk_load(st + C::kOffSfa, sfa_base + ks * (C::kAtoms * 512), sf_bytes, full_bar + stage);
@@ -353,12 +424,12 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     // tiles once and then only waits, issues and commits.
     constexpr int kIssuers = C::kAccStages == 2 ? 2 : 1;
     const int issuer = warp - 2;
-    const int n_items = my_work_items<TILE_N>(s_counts, p.E, n_mu, unit, n_units, lane);
+    const int n_items = my_work_items<TILE_N>(s_counts, p.E, n_mu, dbl_tails, unit, n_units, lane);
     if (lane == 0 && issuer < kIssuers && rank == 0) {
       constexpr uint32_t idesc_full = ptx::mma_sp_nvf4_idesc(TILE_N, kTileM * kCtas);
       constexpr uint32_t idesc_tail = ptx::mma_sp_nvf4_idesc(C::kTailN, kTileM * kCtas);
       Tiles tiles;
-      tiles.init(s_counts, p.E, n_mu, unit, n_units);
+      tiles.init(s_counts, p.E, n_mu, dbl_tails, unit, n_units);
       int stage = 0, acc = kIssuers == 2 ? issuer : 0;
       uint32_t phase = 0, acc_phase = 0, soff = 0;
       bool ok = true;
@@ -394,6 +465,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         // faults on an odd scale column); wider tiles start at column 0 and need no tile coordinates
         uint32_t sfb_off = 0;
         uint32_t idesc = idesc_full, bbox16 = C::kBBoxBytes >> 4;
+        bool dbl = false;
         if (TILE_N < 128 || p.b_tail != 0) {
           // (two issuers: each walks every tile and uses every other one)
           bool any = true;
@@ -403,6 +475,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           if (narrow_tail<TILE_N>(p, s_counts[tiles.e], tiles.nt * TILE_N)) {
             idesc = idesc_tail;
             bbox16 = C::kTailBBoxBytes >> 4;
+            dbl = C::kTailDouble && tiles.dbl;
           }
         }
         const long long ta0 = PNV_PROF_T();
@@ -414,36 +487,64 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         PNV_PROF_ACC(pf_acc, ta0);                              // waiting for a free accumulator
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * TILE_N;
+        // The K loop of one item, compiled twice (ordinary items; double tail items) and chosen per item: whatever
+        // the issuing thread executes between two MMAs is time the tensor pipe waits for, so the loop of an ordinary
+        // item carries nothing of the other kind.
+        auto item_stages = [&](auto dbl_kind, auto full_kind) {
+          constexpr bool kDbl = decltype(dbl_kind)::value;
+          constexpr bool kFull = decltype(full_kind)::value;      // K is a whole number of stages: no short last stage
 #pragma unroll 1
-        for (int ks = 0; ks < p.k_stages; ++ks) {
-          const int k_atoms = ks + 1 == p.k_stages ? last_atoms : C::kAtoms;
-          const long long ts0 = PNV_PROF_T();
-          if (!ptx::mbar_wait(sf_full + stage, phase)) {
-            atomicExch(&g_status, kMmaScaleTimeout);
-            ok = false;
-            break;
-          }
-          PNV_PROF_ACC(pf_slot, ts0);                           // waiting for a filled slot (own tiles)
-          ptx::tc_fence_after();
-          const long long tm0 = PNV_PROF_T();
-          // descriptors of this stage: the precomputed ones of stage 0 plus the stage's offset in
-          // 16-byte units (the address field is the low 14 bits, so a 32-bit add cannot carry out)
-          const uint32_t la = lo_a0 + soff, lb = lo_b0 + soff;
-          const uint32_t slot = slots0 + stage * C::kSlotCols;
-          const uint32_t sfb_cols = slot + C::kSlotSfb + sfb_off;
+          for (int ks = 0; ks < p.k_stages; ++ks) {
+            const int k_atoms = kFull ? C::kAtoms : ks + 1 == p.k_stages ? last_atoms : C::kAtoms;
+            const long long ts0 = PNV_PROF_T();
+            if (!ptx::mbar_wait(sf_full + stage, phase)) {
+              atomicExch(&g_status, kMmaScaleTimeout);
+              ok = false;
+              break;
+            }
+            PNV_PROF_ACC(pf_slot, ts0);                           // waiting for a filled slot (own tiles)
+            ptx::tc_fence_after();
+            const long long tm0 = PNV_PROF_T();
+            // descriptors of this stage: the precomputed ones of stage 0 plus the stage's offset in
+            // 16-byte units (the address field is the low 14 bits, so a 32-bit add cannot carry out)
+            const uint32_t la = lo_a0 + soff, lb = lo_b0 + soff;
+            const uint32_t slot = slots0 + stage * C::kSlotCols;
+            if constexpr (kDbl) {
+              // a narrow tail tile against two M units: the units' weights sit kABytes apart, their accumulators
+              // kTailN columns apart, and both read the one activation box and its scales
+              const uint32_t lbd = lb + ((C::kDblOffB - C::kOffB) >> 4);
 #pragma unroll
-          for (int ka = 0; ka < C::kAtoms; ++ka)
-            if (ka < k_atoms)
-              ptx::tc_mma_sp_nvf4<kCtas>(d_tmem, pack_desc(la + ka * 2, hi_a),
-                                         pack_desc(lb + (ka >> 1) * bbox16 + (ka & 1) * 4, hi_b), idesc,
-                                         (ks | ka) != 0 ? 1u : 0u, slot + ka * 4, sfb_cols + ka * C::kSfbColsPerAtom,
-                                         slot + C::kSlotE + ka * 2);
-          // shared-memory stage and tensor-memory slot reusable (in both CTAs of a pair) once these MMAs retire
-          ptx::tc_commit_n<kCtas>(empty_bar + stage);
-          PNV_PROF_ACC(pf_issue, tm0);                          // issuing MMAs + commit
-          soff += C::kStageBytes >> 4;
-          if (++stage == p.stages) { stage = 0; soff = 0; phase ^= 1; }
-        }
+              for (int ka = 0; ka < C::kAtoms; ++ka) {
+                if (ka < k_atoms) {
+                  const uint64_t db = pack_desc(lbd + (ka >> 1) * (C::kTailBBoxBytes >> 4) + (ka & 1) * 4, hi_b);
+                  const uint32_t sfb_d = slot + C::kDblSlotSfb + ka * 4;
+                  ptx::tc_mma_sp_nvf4<kCtas>(d_tmem, pack_desc(la + ka * 2, hi_a), db, idesc_tail, (ks | ka) != 0 ? 1u : 0u,
+                                             slot + ka * 4, sfb_d, slot + C::kDblSlotE + ka * 2);
+                  ptx::tc_mma_sp_nvf4<kCtas>(d_tmem + C::kTailN, pack_desc(la + (C::kDblOffA1 >> 4) + ka * 2, hi_a), db,
+                                             idesc_tail, (ks | ka) != 0 ? 1u : 0u, slot + C::kDblSlotSfa1 + ka * 4, sfb_d,
+                                             slot + C::kDblSlotE1 + ka * 2);
+                }
+              }
+            } else {
+              const uint32_t sfb_cols = slot + C::kSlotSfb + sfb_off;
+#pragma unroll
+              for (int ka = 0; ka < C::kAtoms; ++ka)
+                if (kFull || ka < k_atoms)
+                  ptx::tc_mma_sp_nvf4<kCtas>(d_tmem, pack_desc(la + ka * 2, hi_a),
+                                             pack_desc(lb + (ka >> 1) * bbox16 + (ka & 1) * 4, hi_b), idesc,
+                                             ka != 0 ? 1u : ks != 0 ? 1u : 0u, slot + ka * 4,
+                                             sfb_cols + ka * C::kSfbColsPerAtom, slot + C::kSlotE + ka * 2);
+            }
+            // shared-memory stage and tensor-memory slot reusable (in both CTAs of a pair) once these MMAs retire
+            ptx::tc_commit_n<kCtas>(empty_bar + stage);
+            PNV_PROF_ACC(pf_issue, tm0);                          // issuing MMAs + commit
+            soff += C::kStageBytes >> 4;
+            if (++stage == p.stages) { stage = 0; soff = 0; phase ^= 1; }
+          }
+        };
+        if (C::kTailDouble && dbl) item_stages(std::true_type{}, std::false_type{});
+        else if (last_atoms == C::kAtoms) item_stages(std::false_type{}, std::true_type{});
+        else item_stages(std::false_type{}, std::false_type{});
         if (!ok) break;
         ptx::tc_commit_n<kCtas>(acc_full + acc);
         if (kIssuers == 2) {
@@ -464,11 +565,12 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   } else if (warp == 4 || warp == 5) {
     // =============================== copiers ===============================
     // Both copiers take every pipeline stage and split its atoms: copier 0 the weight scales and the metadata,
-    // copier 1 the activation scales.  Each commits on the stage's sf_full barrier (two arrivals).  The copiers
-    // do not walk the tiles: a narrow tail tile loads one activation-scale row atom instead of two, and the copy of
-    // the other (whatever an older stage left there) lands in columns its 64-token MMAs never read.
+    // copier 1 the activation scales.  Each commits on the stage's sf_full barrier (two arrivals).  Without
+    // double tail items the copiers do not walk the tiles: a narrow tail tile loads one activation-scale row atom
+    // instead of two, and the copy of the other (whatever an older stage left there) lands in columns its
+    // 64-token MMAs never read.
     const int copier = warp - 4;
-    const int n_items = my_work_items<TILE_N>(s_counts, p.E, n_mu, unit, n_units, lane);
+    const int n_items = my_work_items<TILE_N>(s_counts, p.E, n_mu, dbl_tails, unit, n_units, lane);
     const long long n_stages = (long long)n_items * p.k_stages;
     if (lane == 0 && (rank == 0 || (kPair && copier == 0))) {
       // of a pair's second CTA only warp 4 works here: it tells the first CTA when each stage's copies have landed
@@ -480,9 +582,12 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       const uint32_t hi = (uint32_t)(d_e0 >> 32);           // the three descriptors differ in the address only
       const uint32_t slots0 = tmem_base + C::kColSlots;
       const int last_atoms = p.n_kt - (p.k_stages - 1) * C::kAtoms;
+      const bool whole_stages = last_atoms == C::kAtoms;
       int stage = 0, ks = 0;
       uint32_t phase = 0;
       long long pf_cwait = 0, pf_cissue = 0;
+      bool dbl = false;       // a double tail item's stages are laid out differently: the producer says which they are
+      const uint32_t lo_st0 = (uint32_t)ptx::smem_desc(ptx::smem_u32(stage_base), 128, 0, 0);
 
 #pragma unroll 1
       for (long long g = 0; g < n_stages; ++g) {
@@ -495,29 +600,61 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         if (relay) {
           ptx::mbar_arrive_cluster(peer_full + stage, 0);
         } else {
+          if (C::kTailDouble && dbl_tails && ks == 0) dbl = s_kind[stage] != 0;
           ptx::tc_fence_after();
           const long long tc1 = PNV_PROF_T();
-          const int k_atoms = ks + 1 == p.k_stages ? last_atoms : C::kAtoms;
-          const uint32_t soff = (uint32_t)stage * (C::kStageBytes >> 4);
-          const uint32_t slot = slots0 + stage * C::kSlotCols;
-          if (copier == 0) {
-#pragma unroll
-            for (int ka = 0; ka < C::kAtoms; ++ka)
-              if (ka < k_atoms) ptx::tc_cp_32x128b_warpx4<kCtas>(slot + ka * 4, pack_desc(lo_sfa0 + soff + ka * 32, hi));
-#pragma unroll
-            for (int ea = 0; ea < C::kEAtoms; ++ea)
-              if (2 * ea < k_atoms) ptx::tc_cp_128x128b<kCtas>(slot + C::kSlotE + ea * 4, pack_desc(lo_e0 + soff + ea * 128, hi));
-          } else {
-#pragma unroll
-            for (int ka = 0; ka < C::kAtoms; ++ka) {
-              if (ka < k_atoms) {
-#pragma unroll
-                for (int ra = 0; ra < C::kSfbRowAtoms; ++ra)
-                  ptx::tc_cp_32x128b_warpx4<kCtas>(slot + C::kSlotSfb + ka * C::kSfbColsPerAtom + ra * 4,
-                                                   pack_desc(lo_sfb0 + soff + ra * (C::kSfaBytes >> 4) + ka * 32, hi));
+          // (compiled twice: K a whole number of stages, so that no copy needs a guard; or a short last stage)
+          auto copy_stage = [&](auto full_kind) {
+            constexpr bool kFull = decltype(full_kind)::value;
+            const int k_atoms = kFull ? C::kAtoms : ks + 1 == p.k_stages ? last_atoms : C::kAtoms;
+            const uint32_t soff = (uint32_t)stage * (C::kStageBytes >> 4);
+            const uint32_t slot = slots0 + stage * C::kSlotCols;
+            if (C::kTailDouble && dbl) {
+              // double tail item: copier 0 both units' weight scales, copier 1 the activation scales and both
+              // units' metadata
+              const uint32_t lo = lo_st0 + soff;
+              if (copier == 0) {
+  #pragma unroll
+                for (int u = 0; u < 2; ++u)
+  #pragma unroll
+                  for (int ka = 0; ka < C::kAtoms; ++ka)
+                    if (kFull || ka < k_atoms)
+                      ptx::tc_cp_32x128b_warpx4<kCtas>(slot + u * C::kDblSlotSfa1 + ka * 4,
+                                                       pack_desc(lo + ((C::kDblOffSfa + u * C::kSfaBytes) >> 4) + ka * 32, hi));
+              } else {
+  #pragma unroll
+                for (int ka = 0; ka < C::kAtoms; ++ka)
+                  if (kFull || ka < k_atoms)
+                    ptx::tc_cp_32x128b_warpx4<kCtas>(slot + C::kDblSlotSfb + ka * 4, pack_desc(lo + (C::kDblOffSfb >> 4) + ka * 32, hi));
+  #pragma unroll
+                for (int u = 0; u < 2; ++u)
+  #pragma unroll
+                  for (int ea = 0; ea < C::kEAtoms; ++ea)
+                    if (kFull || 2 * ea < k_atoms)
+                      ptx::tc_cp_128x128b<kCtas>(slot + C::kDblSlotE + u * (C::kDblSlotE1 - C::kDblSlotE) + ea * 4,
+                                                 pack_desc(lo + ((C::kDblOffE + u * C::kEBytes) >> 4) + ea * 128, hi));
+              }
+            } else if (copier == 0) {
+  #pragma unroll
+              for (int ka = 0; ka < C::kAtoms; ++ka)
+                if (kFull || ka < k_atoms) ptx::tc_cp_32x128b_warpx4<kCtas>(slot + ka * 4, pack_desc(lo_sfa0 + soff + ka * 32, hi));
+  #pragma unroll
+              for (int ea = 0; ea < C::kEAtoms; ++ea)
+                if (kFull || 2 * ea < k_atoms) ptx::tc_cp_128x128b<kCtas>(slot + C::kSlotE + ea * 4, pack_desc(lo_e0 + soff + ea * 128, hi));
+            } else {
+  #pragma unroll
+              for (int ka = 0; ka < C::kAtoms; ++ka) {
+                if (kFull || ka < k_atoms) {
+  #pragma unroll
+                  for (int ra = 0; ra < C::kSfbRowAtoms; ++ra)
+                    ptx::tc_cp_32x128b_warpx4<kCtas>(slot + C::kSlotSfb + ka * C::kSfbColsPerAtom + ra * 4,
+                                                     pack_desc(lo_sfb0 + soff + ra * (C::kSfaBytes >> 4) + ka * 32, hi));
+                }
               }
             }
-          }
+          };
+          if (whole_stages) copy_stage(std::true_type{});
+          else copy_stage(std::false_type{});
           ptx::tc_commit_local<kCtas>(sf_full + stage);     // arrives once the copies above have completed
           PNV_PROF_ACC(pf_cissue, tc1);                           // issuing copies
         }
@@ -581,12 +718,18 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     };
     long long pf_ewait = 0, pf_ework = 0, pf_f0 = 0, pf_f1 = 0, pf_f2 = 0, pf_f3 = 0;
     Tiles tiles;
-    tiles.init(s_counts, p.E, n_mu, unit, n_units);
+    tiles.init(s_counts, p.E, n_mu, dbl_tails, unit, n_units);
     while (tiles.next()) {
-      const int e = tiles.e, mu = tiles.mu, nt = tiles.nt;
+      // A double tail item holds two M units' 64-column accumulators side by side: epilogue groups 0-1 take the
+      // first unit's two chunks, groups 2-3 the second unit's.
+      const bool dbl = C::kTailDouble && tiles.dbl;
+      const int e = tiles.e, mu = tiles.mu + (dbl ? group >> 1 : 0), nt = tiles.nt;
+      const int chunk0 = dbl ? group & 1 : group;          // this group's first chunk of token columns
       const int cnt = s_counts[e];
       const int mt = kPair ? 2 * mu + (int)rank : mu;
-      const bool mt_valid = mt < p.n_mt;       // the second CTA of the last pair of an odd tile count stores nothing
+      // the second CTA of the last pair of an odd tile count stores nothing, nor does anyone for a double item's
+      // second unit past the last one
+      const bool mt_valid = mt < p.n_mt;
       const float alpha = p.alphas[e];
       const int n0 = nt * TILE_N;
       const long long te0 = PNV_PROF_T();
@@ -597,7 +740,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       PNV_PROF_ACC(pf_ewait, te0);                              // waiting for an accumulator
       const long long te1 = PNV_PROF_T();
       ptx::tc_fence_after();
-      const uint32_t t_row = tmem_base + ((uint32_t)(sub * 32) << 16) + acc * TILE_N;
+      const uint32_t t_row = tmem_base + ((uint32_t)(sub * 32) << 16) + acc * TILE_N + (dbl ? (group >> 1) * C::kTailN : 0);
       bool released = false;
       if (!kFused) {
         // Plain epilogue.  A warp holds 32 features x kChunk tokens of the accumulator: it scales and rounds them to
@@ -616,7 +759,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         // traffic to L2 was of the order of the output itself).
 #pragma unroll
         for (int j = 0; j < kOwn; ++j) {
-          const int c0 = (group + 4 * j) * kChunk;
+          const int c0 = (chunk0 + 4 * j) * kChunk;
           const int rows = cnt - (n0 + c0);               // live token rows from c0 on; the same for all lanes
           uint32_t pk[kChunk / 2];
           if (rows > 0) {
@@ -863,7 +1006,7 @@ group_mm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           // registers, partner halves in the two exchange areas) and the accumulator goes back to the issuer
           // before any of the arithmetic.  Two pair barriers per tile: the partner has finished reading the
           // previous tile's areas; this tile's are filled.
-          const int cA = group * kChunk, cB = cA + 4 * kChunk;
+          const int cA = chunk0 * kChunk, cB = cA + 4 * kChunk;
           const bool liveA = n0 + cA < cnt, liveB = n0 + cB < cnt;
           if (mt_valid && liveA) {
             const long long tf0 = PNV_PROF_T();

@@ -106,6 +106,19 @@ def test_pair_kernels_over_many_ragged_experts(pnk, config_id, K):
     run_case(pnk, E=28, M=768 - 24, K=K, max_n=600, counts=counts.tolist(), config_id=config_id, seed=K, wscale=0.05)
 
 
+@pytest.mark.parametrize("M", [256, 640 - 8, 1536])
+@pytest.mark.parametrize("K", [256, 1280, 3328])
+def test_narrow_tail_tiles_against_two_m_units(pnk, M, K):
+    # the 256 x 256 pair kernel multiplies an expert's last token tile, when it holds at most 64 rows, against two
+    # M units per work item (when no expert can hold more than four token tiles): counts just past a tile boundary
+    # (1, 64 rows over), at it, and past the narrow limit (65 over), over one, three (odd: the last item has one unit)
+    # and six M units, K loops of one stage, fewer stages than the ring and more; the longest K runs 512-K stages
+    # with a short last one
+    counts = [257, 320, 321, 256, 64, 1, 512 + 64, 300, 0, 512 + 65]
+    for cid in (1, 3) if M == 256 else (1,):   # the pair kernel (and once the single-CTA 256-token kernel beside it)
+        run_case(pnk, E=len(counts), M=M, K=K, max_n=640, counts=counts, config_id=cid, seed=M + K, wscale=0.05)
+
+
 def test_gscale_and_alpha_undo_each_other(pnk):
     E, M, K, max_n = 4, 256, 512, 48
     x_amax = 4.5

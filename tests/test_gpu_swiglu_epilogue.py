@@ -40,6 +40,9 @@ CASES = [
     (2048, 1024, 2, 16, [9, 16]),           # decode-like
     (192, 768, 2, 130, [130, 64]),
     (384, 1536, 9, 520, [520, 0, 300, 1, 257, 128, 519, 33, 256]),   # many ragged experts, several token tiles each
+    (128, 1280, 6, 330, [257, 320, 330, 64, 321, 289]),   # narrow tail tiles (two M units per item) over one M unit
+    (512, 256, 4, 580, [576, 300, 577, 290]),             # ... over four M units, a one-stage K loop
+    (128, 3072, 3, 330, [257, 320, 64]),                  # ... with 512-K stages
 ]
 
 
