@@ -45,7 +45,7 @@ NOMINAL_SPARSE_FP4_TFLOPS = 18000.0
 # under profiles/ (c2, c3: the same workload; c4: a capture of 32 of the 256 experts with the same rows per expert,
 # times 8 - the traffic is the weights and rows of the experts, so it grows with their number); None where no
 # capture exists
-NCU_TRAFFIC_BYTES = {"c2": 331.3e6, "c3": 336.5e6, "c4": 8 * 371.6e6}
+NCU_TRAFFIC_BYTES = {"c2": 331.3e6, "c3": 336.5e6, "c4": 8 * 376.2e6}
 
 WORKLOADS = {
     # Mixtral-8x7B expert FFN, decode: per-expert counts uniform in [1, 16]
