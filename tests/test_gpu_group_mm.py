@@ -146,6 +146,7 @@ ROW_MAP_CASES = [
     # E, M, K, max_n, counts, config ids
     (3, 384, 768, 200, [200, 0, 77], (0, 1, 3, 5, 8)),       # wide kernels, single CTA and pairs, odd tile count
     (2, 250, 512, 300, [300, 150], (1, 2)),                  # 256-token tiles (two chunks per group); M tail
+    (4, 768, 512, 330, [300, 257, 320, 64], (1,)),           # narrow tail tiles against two M units (three units: odd)
     (4, 512, 2048, 16, [16, 0, 3, 9], (7,)),                 # narrow kernel, K split across CTAs
     (2, 202, 1024, 32, [32, 20], (7,)),                      # narrow kernel, scalar store path (M % 8 != 0)
 ]
