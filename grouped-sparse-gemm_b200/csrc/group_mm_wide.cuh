@@ -18,6 +18,8 @@
 // expert a second tile of a dozen rows).  When it holds at most 64 live rows - and the launch has the tensor map for
 // it (K a multiple of 256, tiles of 128 tokens or more) - the tile runs 64 tokens wide: a quarter or half of the
 // activation bytes, one scale row-atom, MMAs a quarter or half as long.  Every role derives the width from counts[].
+// The pair kernel with 256-token tiles has a variant (kDblTails) that multiplies such a tile against two M units per
+// work item (WideCfg::kTailDouble); the host picks it when experts hold few token tiles.
 //
 // 22 warps per CTA:
 //   warp 0   tile producer: TMA copies of the compressed weights and of the activations
